@@ -1,0 +1,165 @@
+/*
+ * C ABI of libint64gemm.so — the B200 (sm_100a) implementation of the int64
+ * fixed-point hot path of ZK-DeepSeek's integer DeepSeek-V3 forward pass.
+ *
+ * Two groups of entry points:
+ *
+ *  1. The 21 symbols the reference library exports (inference/int64_gemm.cu),
+ *     with identical names and argument lists, so that the reference's
+ *     inference/kernel.py can load this library unchanged.  They return void,
+ *     launch on the legacy default stream and take C `int` extents like the
+ *     originals; a call whose extents would overflow 32-bit element indexing is
+ *     refused (nothing is written, the status is kept for zkds_last_status()
+ *     and one line goes to stderr) instead of corrupting memory.
+ *
+ *  2. zkds_* entry points: same arithmetic, 64-bit extents, an explicit stream,
+ *     an int status return, and the parameters the reference hard-codes.
+ *
+ * All pointers are device pointers unless a comment says HOST.  Tensors are
+ * dense and row-major in the shapes given.  No entry point synchronises the
+ * device except where a comment says so.
+ */
+#ifndef ZKDS_INT64_H
+#define ZKDS_INT64_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status ------------------------------------------------------------------ */
+#define ZKDS_OK 0
+#define ZKDS_ERR_ARG 1
+#define ZKDS_ERR_RANGE 2
+#define ZKDS_ERR_CUDA 3
+#define ZKDS_ERR_WORKSPACE 4
+#define ZKDS_ERR_DEVICE 5
+#define ZKDS_ERR_UNSUPPORTED 6
+
+int zkds_last_status(void);         /* status of the most recent call on this thread */
+int zkds_last_cuda_error(void);     /* cudaError_t behind the last ZKDS_ERR_CUDA */
+const char* zkds_status_string(int status);
+const char* zkds_version(void);
+void zkds_shutdown(void);           /* frees the library's scratch arenas (synchronises) */
+
+/* ---- flags of the contraction entry points ----------------------------------- */
+#define ZKDS_ALGO_AUTO 0        /* limb tensor-core kernel when it applies, else exact */
+#define ZKDS_ALGO_EXACT 1       /* CUDA-core kernel with 128-bit accumulators */
+#define ZKDS_ALGO_LIMB 2        /* tensor-core kernel or ZKDS_ERR_UNSUPPORTED */
+#define ZKDS_ALGO_MASK 3
+#define ZKDS_REMAINDER_LEGACY 4 /* R = sum & ((int)(1 << s) - 1) as the reference's device
+                                   code evaluates it: exact for s <= 31, the low 64 bits of
+                                   the sum for s >= 32.  Default: R = sum mod 2^s. */
+
+/* =============================================================================
+ * Group 1 — the reference's symbols (same names, same argument lists)
+ * ========================================================================== */
+
+/* inference/int64_gemm.cu:36-47.  C = (sum_k (A/a_rescale)*(B/b_rescale)) >> c_rescale with
+ * a 128-bit sum, R = remainder (legacy flavour).  A (B,M,K) int64, B (N,K) int32. */
+void int64_32_bmm_broadcast_launcher(const int64_t* A, const int32_t* B, int64_t* C, int64_t* R,
+                                     const int64_t a_rescale, const int64_t b_rescale,
+                                     const int64_t c_rescale, int Bdim, int M, int K, int N);
+/* inference/int64_gemm.cu:79-90.  Same with B (N,K) int64. */
+void int64_64_bmm_broadcast_launcher(const int64_t* A, const int64_t* B, int64_t* C, int64_t* R,
+                                     const int64_t a_rescale, const int64_t b_rescale,
+                                     const int64_t c_rescale, int Bdim, int M, int K, int N);
+/* inference/int64_gemm.cu:126-132, 173-179, 215-221: float bit pattern -> fixed point
+ * (exported by the reference, called by nothing). */
+void bf16_to_int32_2d(const uint16_t* input, int32_t* output, int rows, int cols, int rescale);
+void wkv_b_bf16_to_int32(const uint16_t* input, int32_t* output, int rows, int cols);
+void float32_to_int64_2d(const uint32_t* input, int64_t* output, int rows, int cols, int rescale);
+/* inference/int64_gemm.cu:274-286.  RoPE complex multiply, products >> 42; headDim is the
+ * number of PAIRS.  A, C (batch,seq,head,pairs,2); B (seq,pairs,2) broadcast. */
+void complex_int64_mul(const int64_t* A, const int64_t* B, int64_t* C, int batchSize, int seqLen,
+                       int headCount, int headDim);
+/* inference/int64_gemm.cu:365-385.  C = floor(A*W / rms[row]); rms is a device array. */
+void rms_norm_32(const int64_t* A, const int32_t* W, const int64_t* rms, int64_t* C, int seqLen,
+                 int Dim);
+void rms_norm_64(const int64_t* A, const int64_t* W, const int64_t* rms, int64_t* C, int seqLen,
+                 int Dim);
+/* inference/int64_gemm.cu:416-425, 458-467, 499-509, 539-549: the absorbed-MLA einsums.
+ * The first three add rescale/2 before the shift, the fourth does not. */
+void einsum_bshd_hdc_bshc(const int64_t* q_nope, const int32_t* wkv_b_1, int64_t* out,
+                          int64_t rescale, int B, int S, int H, int D, int C);
+void einsum_bshc_btc_bsht(const int64_t* A, const int64_t* B, int64_t* C, int64_t rescale, int Bsz,
+                          int S, int H, int T, int Cdim);
+void einsum_bsht_btc_bshc(const int64_t* A, const int64_t* B, int64_t* C, int64_t rescale, int Bsz,
+                          int S, int H, int T, int Cdim);
+void einsum_bshc_hdc_bshd(const int64_t* A, const int32_t* B, int64_t* C, int64_t rescale, int Bsz,
+                          int S, int H, int D, int Cdim);
+/* inference/int64_gemm.cu:661-670, 748-757.  Rows are the last dimension T.  R is
+ * overwritten with the unnormalised weights, as in the reference. */
+void softmax_q21(int64_t* R, int64_t* C, int64_t* EXP2_FRAC_LUT, int Bsz, int S, int H, int T);
+void softmax_q19(int64_t* R, int64_t* C, int64_t* EXP2_FRAC_LUT, int Bsz, int S, int H, int T);
+/* inference/int64_gemm.cu:672-680, 759-767.  Fill a HOST table of 256 entries. */
+void softmax_init_q21(int64_t* EXP2_FRAC_LUT);
+void softmax_init_q19(int64_t* EXP2_FRAC_LUT);
+/* inference/int64_gemm.cu:821-830, 884-893, 949-958, 1019-1028 (no device printf). */
+void silu_q25(int64_t* R, int64_t* C, int64_t* EXP2_FRAC_LUT_25, int Bsz, int S, int Dim);
+void sigmoid_q25(int64_t* R, int64_t* C, int64_t* EXP2_FRAC_LUT_25, int Bsz, int S, int Dim);
+void silu_q23(int64_t* R, int64_t* C, int64_t* EXP2_FRAC_LUT_23, int Bsz, int S, int Dim);
+void sigmoid_q23(int64_t* R, int64_t* C, int64_t* EXP2_FRAC_LUT_23, int Bsz, int S, int Dim);
+/* inference/int64_gemm.cu:832-839, 960-967.  Fill a HOST table of 256 entries. */
+void silu_init_q25(int64_t* EXP2_FRAC_LUT);
+void silu_init_q23(int64_t* EXP2_FRAC_LUT);
+
+/* =============================================================================
+ * Group 2 — status-returning entry points
+ * ========================================================================== */
+
+/* Replaces int64_{32,64}_bmm_broadcast_launcher (int64_gemm.cu:36-47, 79-90).
+ * b_bits: 32 or 64.  R may be null.  a_limbs/b_limbs: number of signed 8-bit limbs that
+ * cover |A/a_rescale| and |B/b_rescale| (0 = measure on the device, which costs one
+ * reduction pass and a host synchronisation). */
+int zkds_gemm(const int64_t* A, const void* B, int b_bits, int64_t* C, int64_t* R,
+              int64_t a_rescale, int64_t b_rescale, int64_t c_rescale, int64_t Bdim, int64_t M,
+              int64_t K, int64_t N, int a_limbs, int b_limbs, int flags, void* stream);
+
+/* Replace the four einsum entry points (int64_gemm.cu:416-549). */
+int zkds_einsum_bshd_hdc_bshc(const int64_t* q, const int32_t* W, int64_t* out, int64_t rescale,
+                              int64_t B, int64_t S, int64_t H, int64_t D, int64_t C, int a_limbs,
+                              int b_limbs, int flags, void* stream);
+int zkds_einsum_bshc_btc_bsht(const int64_t* A, const int64_t* KV, int64_t* out, int64_t rescale,
+                              int64_t B, int64_t S, int64_t H, int64_t T, int64_t C, int a_limbs,
+                              int b_limbs, int flags, void* stream);
+int zkds_einsum_bsht_btc_bshc(const int64_t* P, const int64_t* KV, int64_t* out, int64_t rescale,
+                              int64_t B, int64_t S, int64_t H, int64_t T, int64_t C, int a_limbs,
+                              int b_limbs, int flags, void* stream);
+int zkds_einsum_bshc_hdc_bshd(const int64_t* A, const int32_t* W, int64_t* out, int64_t rescale,
+                              int64_t B, int64_t S, int64_t H, int64_t D, int64_t C, int a_limbs,
+                              int b_limbs, int flags, void* stream);
+
+/* Replaces complex_int64_mul (int64_gemm.cu:274-286) with the product shift as a
+ * parameter (the reference hard-codes 42). */
+int zkds_rope(const int64_t* A, const int64_t* table, int64_t* C, int64_t batch, int64_t seq,
+              int64_t heads, int64_t pairs, int shift, void* stream);
+
+/* Replaces RMS_Norm_int64's host loop plus rms_norm_32/64 (kernel.py:477-550,
+ * int64_gemm.cu:365-385) with one fused pass: rms[m] = isqrt((eps + sum a^2) / dim),
+ * C = floor(A*W / rms).  w_bits: 32 or 64.  rms_out (device, M entries) may be null.
+ * A row whose rms is 0 (undefined in the reference) yields zeros. */
+int zkds_rms_norm(const int64_t* A, const void* W, int w_bits, int64_t* C, int64_t* rms_out,
+                  int64_t M, int64_t N, int64_t eps, int64_t dim, void* stream);
+/* rms_norm_32/64 with 64-bit extents: normalise with the caller's per-row rms. */
+int zkds_rms_norm_apply(const int64_t* A, const void* W, int w_bits, const int64_t* rms,
+                        int64_t* C, int64_t M, int64_t N, void* stream);
+
+/* Replaces softmax_q19 / softmax_q21 (int64_gemm.cu:661-670, 748-757).  frac: 19 or 21.
+ * weights_out (may be null, may equal X) receives the unnormalised weights. */
+int zkds_softmax(const int64_t* X, int64_t* weights_out, int64_t* C, const int64_t* lut,
+                 int64_t rows, int64_t T, int frac, void* stream);
+
+/* Replaces silu_q23/q25 and sigmoid_q23/q25 (int64_gemm.cu:821-1028).  frac: 23 or 25. */
+int zkds_act(const int64_t* X, int64_t* C, const int64_t* lut, int64_t n, int frac, int silu,
+             void* stream);
+
+/* Replaces the four *_init_* functions.  HOST table of 256 entries.
+ * kind: 0 softmax Q19, 1 softmax Q21, 2 silu Q23, 3 silu Q25. */
+int zkds_lut(int64_t* host_lut, int kind);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ZKDS_INT64_H */

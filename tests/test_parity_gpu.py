@@ -1,0 +1,376 @@
+"""GPU parity: the sm_100a library, called through its C ABI (the drop-in kernel
+module and the reference's own symbol names), against the CPU oracle and against the
+reference's CUDA kernels.  Bit-exact: 0 mismatched int64 words everywhere."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import rand_i64
+
+pytestmark = pytest.mark.gpu
+
+
+def g(a, dev):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+
+def same(got, want, what=""):
+    got = got.cpu().numpy() if isinstance(got, torch.Tensor) else got
+    assert got.shape == want.shape, (what, got.shape, want.shape)
+    bad = int((got != want).sum())
+    assert bad == 0, "%s: %d of %d words differ" % (what, bad, got.size)
+
+
+# ---- GEMM ---------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("algo", ["exact", "auto"])
+@pytest.mark.parametrize("wdtype", [np.int64, np.int32])
+def test_gemm_config1(kmod, orc, dev, algo, wdtype):
+    """BASELINE config: X int64 [32,7168] in +-2^20, W [576,7168] in +-2^15, shift 16, seed 0."""
+    rng = np.random.default_rng(0)
+    X = rng.integers(-2**20, 2**20, (1, 32, 7168), dtype=np.int64)
+    W = rng.integers(-2**15, 2**15, (576, 7168), dtype=np.int64).astype(wdtype)
+    kmod.ALGO = kmod.ALGO_EXACT if algo == "exact" else kmod.ALGO_AUTO
+    try:
+        C, R = kmod.int64_bmm_broadcast(g(X, dev), g(W, dev), 1, 1, 16)
+    finally:
+        kmod.ALGO = kmod.ALGO_AUTO
+    Co, Ro = orc.gemm(X, W, 1, 1, 16, orc.R_LEGACY)
+    same(C, Co, "C")
+    same(R, Ro, "R")
+    # wrapping int64 equals the 128-bit sum here (|sum| < 2^63): the reference's torch CPU path
+    same(C[0], orc.gemm_wrap64(X[0], W.astype(np.int64), 16), "wrap64")
+
+
+@pytest.mark.parametrize("algo", ["exact", "auto"])
+@pytest.mark.parametrize("shape", [(1, 1, 1, 1), (2, 5, 37, 7), (1, 130, 200, 70), (3, 64, 128, 64),
+                                   (1, 257, 1000, 129), (1, 128, 4096, 256)])
+@pytest.mark.parametrize("s,a_r,b_r,abits,bbits,b32", [
+    (16, 1, 1, 20, 15, True), (30, 1, 1, 36, 31, True), (29, 1, 256, 30, 43, False),
+    (33, 3, -7, 62, 62, False), (0, 1, 1, 8, 8, True), (64, 1, 1, 62, 31, True),
+    (100, 1, 1, 62, 62, False)])
+def test_gemm_shapes_ranges_shifts(kmod, orc, dev, algo, shape, s, a_r, b_r, abits, bbits, b32):
+    Bd, M, K, N = shape
+    rng = np.random.default_rng(M * 131 + K + s)
+    A = rand_i64(rng, (Bd, M, K), abits)
+    B = rand_i64(rng, (N, K), bbits)
+    if b32:
+        B = B.astype(np.int32)
+    kmod.ALGO = kmod.ALGO_EXACT if algo == "exact" else kmod.ALGO_AUTO
+    try:
+        for legacy in (True, False):
+            kmod.LEGACY_REMAINDER = legacy
+            C, R = kmod.int64_bmm_broadcast(g(A, dev), g(B, dev), a_r, b_r, s)
+            Co, Ro = orc.gemm(A, B, a_r, b_r, s, orc.R_LEGACY if legacy else orc.R_MATH)
+            same(C, Co, "C")
+            same(R, Ro, "R legacy=%s" % legacy)
+    finally:
+        kmod.ALGO = kmod.ALGO_AUTO
+        kmod.LEGACY_REMAINDER = True
+
+
+def test_gemm_extreme_values(kmod, orc, dev):
+    """INT64_MIN / INT32_MIN operands and sums that straddle 2^63 and 2^127."""
+    A = np.array([[[np.iinfo(np.int64).min, np.iinfo(np.int64).max, -1, 0, 1, 2**62, -2**62, 7]]],
+                 np.int64).repeat(3, 1)
+    B = np.array([[np.iinfo(np.int32).min] * 8, [np.iinfo(np.int32).max] * 8,
+                  [1, -1, 1, -1, 1, -1, 1, -1]], np.int32)
+    for s in (0, 1, 31, 63):
+        C, R = kmod.int64_bmm_broadcast(g(A, dev), g(B, dev), 1, 1, s)
+        Co, Ro = orc.gemm(A, B, 1, 1, s, orc.R_LEGACY)
+        same(C, Co)
+        same(R, Ro)
+
+
+def test_gemm_empty(kmod, dev):
+    A = torch.zeros((1, 0, 16), dtype=torch.int64, device=dev)
+    B = torch.zeros((4, 16), dtype=torch.int32, device=dev)
+    C, R = kmod.int64_bmm_broadcast(A, B, 1, 1, 3)
+    assert C.shape == (1, 0, 4)
+    A = torch.ones((1, 2, 0), dtype=torch.int64, device=dev)
+    B = torch.zeros((4, 0), dtype=torch.int32, device=dev)
+    C, R = kmod.int64_bmm_broadcast(A, B, 1, 1, 3)
+    assert not C.any() and not R.any()
+
+
+def test_gemm_rejects_bad_arguments(kmod, dev):
+    A = torch.zeros((1, 2, 4), dtype=torch.int64, device=dev)
+    B = torch.zeros((4, 4), dtype=torch.int32, device=dev)
+    with pytest.raises(kmod.ZkdsError):
+        kmod.int64_bmm_broadcast(A, B, 0, 1, 3)      # zero divisor
+    with pytest.raises(kmod.ZkdsError):
+        kmod.int64_bmm_broadcast(A, B, 1, 1, 200)    # shift out of range
+    with pytest.raises(TypeError):
+        kmod.int64_bmm_broadcast(A, B.to(torch.int16), 1, 1, 3)
+
+
+# ---- the four MLA einsums ------------------------------------------------------------------
+
+@pytest.mark.parametrize("algo", ["exact", "auto"])
+@pytest.mark.parametrize("dims", [(1, 3, 2, 8, 16, 5), (2, 7, 3, 128, 512, 33),
+                                  (1, 64, 16, 128, 512, 200)])
+def test_einsums(kmod, orc, dev, algo, dims):
+    Bn, S, H, D, C, T = dims
+    rng = np.random.default_rng(S + H)
+    q = rand_i64(rng, (Bn, S, H, D), 30)
+    W1 = rand_i64(rng, (H, D, C), 31).astype(np.int32)
+    A = rand_i64(rng, (Bn, S, H, C), 34)
+    KV = rand_i64(rng, (Bn, T, C), 30)
+    P = rng.integers(0, 2**19 + 1, (Bn, S, H, T), dtype=np.int64)
+    W2 = rand_i64(rng, (H, D, C), 31).astype(np.int32)
+    kmod.ALGO = kmod.ALGO_EXACT if algo == "exact" else kmod.ALGO_AUTO
+    try:
+        same(kmod.einsum_bshd_hdc_bshc(g(q, dev), g(W1, dev), 33),
+             orc.einsum_bshd_hdc_bshc(q, W1, 33), "bshd,hdc->bshc")
+        same(kmod.einsum_bshc_btc_bsht(g(A, dev), g(KV, dev), 23),
+             orc.einsum_bshc_btc_bsht(A, KV, 23), "bshc,btc->bsht")
+        same(kmod.einsum_bsht_btc_bshc(g(P, dev), g(KV, dev), 23),
+             orc.einsum_bsht_btc_bshc(P, KV, 23), "bsht,btc->bshc")
+        same(kmod.einsum_bshc_hdc_bshd(g(A, dev), g(W2, dev), 30),
+             orc.einsum_bshc_hdc_bshd(A, W2, 30), "bshc,hdc->bshd")
+    finally:
+        kmod.ALGO = kmod.ALGO_AUTO
+
+
+# ---- RoPE -------------------------------------------------------------------------------------
+
+def rope_table(S, pairs, frac, base=10000.0):
+    freqs = 1.0 / (base ** (np.arange(0, 2 * pairs, 2, dtype=np.float64) / (2 * pairs)))
+    ang = np.outer(np.arange(S), freqs)
+    return np.stack([np.rint(np.cos(ang) * 2.0**frac), np.rint(np.sin(ang) * 2.0**frac)],
+                    -1).astype(np.int64)
+
+
+@pytest.mark.parametrize("shape", [(1, 256, 128, 32), (2, 5, 1, 32), (1, 3, 7, 3), (1, 1, 1, 1)])
+@pytest.mark.parametrize("shift", [42, 16])
+def test_rope(kmod, orc, dev, shape, shift):
+    Bn, S, H, P = shape
+    rng = np.random.default_rng(S)
+    A = np.rint(rng.standard_normal((Bn, S, H, P, 2)) * 2**16).astype(np.int64)
+    A.flat[:7] = [2**62, -2**62, 2**63 - 1, -2**63, 0, 1, -1][:A.size][:min(7, A.size)]
+    T = rope_table(S, P, shift)
+    C = kmod.complex_int64_mul_broadcast(g(A, dev), g(T.reshape(1, S, 1, P, 2), dev), shift)
+    same(C, orc.rope(A, T, shift))
+
+
+# ---- RMSNorm ------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("M,N,bits,wdt", [(64, 7168, 17, np.int32), (33, 1536, 37, np.int32),
+                                          (5, 512, 50, np.int64), (3, 7, 3, np.int32),
+                                          (2, 30001, 31, np.int64)])
+def test_rms_norm(kmod, orc, dev, M, N, bits, wdt):
+    rng = np.random.default_rng(N)
+    A = np.rint(rng.standard_normal((M, N)) * 2.0**bits).astype(np.int64)
+    A[0, :] = 0                                    # all-zero row: rms 0, defined as zeros
+    if M > 1:
+        A[1, ::2] = -A[1, ::2]
+    W = (2**16 + np.rint(rng.standard_normal(N) * 2**8)).astype(wdt)
+    W[: min(4, N)] = [-3, 0, 2**30, -2**30][: min(4, N)]
+    C, rms = kmod.RMS_Norm_int64(g(A, dev), g(W, dev), 1, N)
+    Co, rmso = orc.rms_norm(A, W, 1, N)
+    assert rms.device.type == "cpu" and rms.numel() >= 500
+    same(rms[:M], rmso, "rms")
+    same(C, Co, "C")
+    # caller-provided rms (the reference's rms_norm_32/64 entry points)
+    given = np.maximum(rmso, 1) + 3
+    same(kmod.rms_norm_apply(g(A, dev), g(W, dev), g(given, dev)), orc.rms_norm_given(A, W, given))
+
+
+# ---- softmax ------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("frac", [19, 21])
+@pytest.mark.parametrize("shape", [(1, 32, 8, 2048), (1, 3, 2, 37), (1, 2, 1, 1), (1, 1, 2, 30000)])
+def test_softmax(kmod, orc, dev, frac, shape):
+    rng = np.random.default_rng(shape[-1] + frac)
+    X = np.rint(rng.standard_normal(shape) * 4 * 2.0**frac).astype(np.int64)
+    T = shape[-1]
+    if T > 8:
+        S = shape[1]
+        mask = np.triu(np.full((S, T), -(64 << 36), np.int64), T - S + 1)   # causal, model.py:1555
+        X += mask[None, :, None, :]
+        X[0, 0, 0, :] = 123                                                     # constant row
+    (kmod.softmax_init_q19 if frac == 19 else kmod.softmax_init_q21)()
+    fn = kmod.softmax_q19 if frac == 19 else kmod.softmax_q21
+    Xd = g(X, dev)
+    C = torch.empty_like(Xd)
+    fn(Xd, C)
+    Co, Wo = orc.softmax(X, frac, want_weights=True)
+    same(C, Co, "probabilities")
+    same(Xd, Wo, "input buffer holds the weights afterwards")
+    kmod.SOFTMAX_WRITES_WEIGHTS = False
+    try:
+        Xd = g(X, dev)
+        C = torch.empty_like(Xd)
+        fn(Xd, C)
+        same(C, Co)
+        same(Xd, X, "input untouched")
+    finally:
+        kmod.SOFTMAX_WRITES_WEIGHTS = True
+
+
+# ---- SiLU / sigmoid -------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("frac", [23, 25])
+def test_activations(kmod, orc, dev, frac):
+    LIM = 64 << frac
+    rng = np.random.default_rng(frac)
+    X = np.concatenate([
+        np.array([0, 1, -1, LIM - 1, LIM, LIM + 1, -LIM + 1, -LIM, -LIM - 1, 2**62, -2**62,
+                  np.iinfo(np.int64).min, np.iinfo(np.int64).max]),
+        rng.integers(-LIM, LIM, 100000),
+        rng.integers(-LIM, -20 * 2**frac, 100000),
+        np.rint(rng.standard_normal(300001) * 2.0**frac).astype(np.int64),
+        np.rint(rng.standard_normal(100000) * 2.0**16).astype(np.int64),
+    ]).astype(np.int64)
+    (kmod.silu_init_q23 if frac == 23 else kmod.silu_init_q25)()
+    silu = kmod.silu_q23 if frac == 23 else kmod.silu_q25
+    sigm = kmod.sigmoid_q23 if frac == 23 else kmod.sigmoid_q25
+    for view in (X.reshape(1, 1, -1), X[:-1].reshape(1, 2, -1), X[1:]):
+        Xd = g(view, dev)
+        C = torch.empty_like(Xd)
+        silu(Xd, C)
+        same(C, orc.act(view, "silu", frac), "silu")
+        sigm(Xd, C)
+        same(C, orc.act(view, "sigmoid", frac), "sigmoid")
+
+
+# ---- the reference's own symbol names, and the reference's own kernels ------------------------------
+
+def test_reference_symbols_against_reference_kernels(libpath, reflib, orc, dev):
+    """Calls the 21-symbol ABI of both libraries with the same raw pointers, the way the
+    reference's kernel.py does, inside the reference's limits."""
+    ours = type(reflib)(libpath).lib
+    ref = reflib.lib
+    rng = np.random.default_rng(11)
+
+    def z(shape):
+        return torch.zeros(shape, dtype=torch.int64, device=dev)
+
+    def both(name, args_fn, outs):
+        res = []
+        for L in (ours, ref):
+            bufs = [z(o) for o in outs]
+            getattr(L, name)(*args_fn(bufs))
+            torch.cuda.synchronize()
+            res.append([b.cpu().numpy() for b in bufs])
+        for a, b in zip(*res):
+            assert np.array_equal(a, b), name
+        return res[0]
+
+    A = g(rand_i64(rng, (2, 40, 300), 36), dev)
+    B32 = g(rand_i64(rng, (50, 300), 31).astype(np.int32), dev)
+    B64 = g(rand_i64(rng, (50, 300), 43), dev)
+    for s in (16, 30, 31, 32, 33, 37):
+        both("int64_32_bmm_broadcast_launcher",
+             lambda o: (A.data_ptr(), B32.data_ptr(), o[0].data_ptr(), o[1].data_ptr(), 1, 1, s, 2, 40,
+                        300, 50), [(2, 40, 50)] * 2)
+    both("int64_64_bmm_broadcast_launcher",
+         lambda o: (A.data_ptr(), B64.data_ptr(), o[0].data_ptr(), o[1].data_ptr(), 1, 256, 29, 2, 40,
+                    300, 50), [(2, 40, 50)] * 2)
+
+    q = g(rand_i64(rng, (1, 9, 4, 128), 30), dev)
+    W1 = g(rand_i64(rng, (4, 128, 512), 31).astype(np.int32), dev)
+    Ae = g(rand_i64(rng, (1, 9, 4, 512), 34), dev)
+    KV = g(rand_i64(rng, (1, 100, 512), 30), dev)
+    P = g(rng.integers(0, 2**19, (1, 9, 4, 100), dtype=np.int64), dev)
+    both("einsum_bshd_hdc_bshc", lambda o: (q.data_ptr(), W1.data_ptr(), o[0].data_ptr(), 33, 1, 9, 4,
+                                            128, 512), [(1, 9, 4, 512)])
+    both("einsum_bshc_btc_bsht", lambda o: (Ae.data_ptr(), KV.data_ptr(), o[0].data_ptr(), 23, 1, 9, 4,
+                                            100, 512), [(1, 9, 4, 100)])
+    both("einsum_bsht_btc_bshc", lambda o: (P.data_ptr(), KV.data_ptr(), o[0].data_ptr(), 23, 1, 9, 4,
+                                            100, 512), [(1, 9, 4, 512)])
+    both("einsum_bshc_hdc_bshd", lambda o: (Ae.data_ptr(), W1.data_ptr(), o[0].data_ptr(), 30, 1, 9, 4,
+                                            128, 512), [(1, 9, 4, 128)])
+
+    Ar = g(rand_i64(rng, (1, 50, 16, 32, 2), 30), dev)
+    Tr = g(rope_table(50, 32, 42), dev)
+    both("complex_int64_mul", lambda o: (Ar.data_ptr(), Tr.data_ptr(), o[0].data_ptr(), 1, 50, 16, 32),
+         [(1, 50, 16, 32, 2)])
+
+    An = rand_i64(rng, (20, 1536), 37)
+    Wn = (2**19 + rand_i64(rng, (1536,), 10)).astype(np.int32)
+    rms = g(orc.rms_rows(An, 1, 1536), dev)
+    And, Wnd = g(An, dev), g(Wn, dev)
+    both("rms_norm_32", lambda o: (And.data_ptr(), Wnd.data_ptr(), rms.data_ptr(), o[0].data_ptr(), 20,
+                                   1536), [(20, 1536)])
+    Wn64 = g(Wn.astype(np.int64) << 12, dev)
+    both("rms_norm_64", lambda o: (And.data_ptr(), Wn64.data_ptr(), rms.data_ptr(), o[0].data_ptr(), 20,
+                                   1536), [(20, 1536)])
+
+    for frac in (19, 21):
+        lut = torch.zeros(256, dtype=torch.int64)
+        getattr(ours, "softmax_init_q%d" % frac)(lut.data_ptr())
+        lut = lut.to(dev)
+        X = np.rint(rng.standard_normal((1, 6, 8, 333)) * 4 * 2.0**frac).astype(np.int64)
+        outs = []
+        for L in (ours, ref):
+            Xd, C = g(X, dev), z(X.shape)
+            getattr(L, "softmax_q%d" % frac)(Xd.data_ptr(), C.data_ptr(), lut.data_ptr(), 1, 6, 8, 333)
+            torch.cuda.synchronize()
+            outs.append((C.cpu().numpy(), Xd.cpu().numpy()))
+        assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
+
+    for frac in (23, 25):
+        lut = torch.zeros(256, dtype=torch.int64)
+        getattr(ours, "silu_init_q%d" % frac)(lut.data_ptr())
+        lut = lut.to(dev)
+        LIM = 64 << frac
+        X = g(np.concatenate([rng.integers(-LIM + 1, LIM, 5000),
+                              rng.integers(-LIM + 1, -20 * 2**frac, 5000)]).reshape(1, 2, 5000), dev)
+        for name in ("silu_q%d" % frac, "sigmoid_q%d" % frac):
+            both(name, lambda o: (X.data_ptr(), o[0].data_ptr(), lut.data_ptr(), 1, 2, 5000),
+                 [(1, 2, 5000)])
+
+
+def test_golden_vectors_from_the_reference_replay_on_the_gpu(kmod, orc, dev):
+    """The committed reference-kernel outputs also hold for the CUDA path (via the oracle's
+    replay helper, with the GPU library standing in for the oracle)."""
+    import os
+    import sys
+    from conftest import ROOT
+    path = os.path.join(ROOT, "tests", "golden", "ref_gpu_vectors.npz")
+    if not os.path.exists(path):
+        pytest.skip("ref_gpu_vectors.npz not generated yet")
+    sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+    import make_gpu_golden as mk
+
+    class GpuAsOracle:
+        R_LEGACY, R_MATH = 1, 0
+
+        def gemm(self, A, B, a_r, b_r, s, rmode):
+            kmod.LEGACY_REMAINDER = bool(rmode)
+            C, R = kmod.int64_bmm_broadcast(g(A, dev), g(B, dev), a_r, b_r, s)
+            kmod.LEGACY_REMAINDER = True
+            return C.cpu().numpy(), R.cpu().numpy()
+
+        def rope(self, A, T, shift):
+            S, P = T.shape[0], T.shape[1]
+            return kmod.complex_int64_mul_broadcast(g(A, dev), g(T.reshape(1, S, 1, P, 2), dev),
+                                                    shift).cpu().numpy()
+
+        def rms_norm_given(self, A, W, rms):
+            return kmod.rms_norm_apply(g(A, dev), g(W, dev), g(rms, dev)).cpu().numpy()
+
+        def softmax(self, X, frac, want_weights=False):
+            (kmod.softmax_init_q19 if frac == 19 else kmod.softmax_init_q21)()
+            Xd = g(X, dev)
+            C = torch.empty_like(Xd)
+            (kmod.softmax_q19 if frac == 19 else kmod.softmax_q21)(Xd, C)
+            return C.cpu().numpy(), Xd.cpu().numpy()
+
+        def act(self, X, kind, frac):
+            (kmod.silu_init_q23 if frac == 23 else kmod.silu_init_q25)()
+            Xd = g(X, dev)
+            C = torch.empty_like(Xd)
+            getattr(kmod, "%s_q%d" % (kind, frac))(Xd, C)
+            return C.cpu().numpy()
+
+        def __getattr__(self, name):
+            if name.startswith("einsum_"):
+                return lambda A, B, r: getattr(kmod, name)(g(A, dev), g(B, dev), r).cpu().numpy()
+            raise AttributeError(name)
+
+    bad = mk.check_against(np.load(path), GpuAsOracle())
+    assert not bad, bad

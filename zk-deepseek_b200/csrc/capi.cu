@@ -1,0 +1,481 @@
+// extern "C" surface of libint64gemm.so: argument checks, dispatch between the
+// tensor-core limb kernel and the exact CUDA-core kernel, the library-owned scratch
+// arenas, and the 21 entry points of the reference library with their original
+// names and argument lists (declared and documented in include/zkds_int64.h).
+#include <math.h>
+#include <stdio.h>
+#include <mutex>
+
+#include "../../include/zkds_int64.h"
+#include "common.cuh"
+#include "kernels.h"
+
+namespace zkds {
+
+static thread_local int t_status = ZKDS_OK;
+static thread_local int t_cuda_error = 0;
+
+int set_cuda_error(cudaError_t e)
+{
+    if (e == cudaSuccess) return ZKDS_OK;
+    t_cuda_error = (int)e;
+    return ZKDS_ERR_CUDA;
+}
+
+int check_launch() { return set_cuda_error(cudaGetLastError()); }
+
+static constexpr int kMaxDevices = 64;
+static constexpr int kSlots = 6;
+
+struct Arena {
+    void* ptr[kSlots] = {};
+    size_t cap[kSlots] = {};
+    int sms = 0;
+};
+static Arena g_arena[kMaxDevices];
+static std::mutex g_mu;
+
+int sm_count()
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+    if (g_arena[dev].sms == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+        g_arena[dev].sms = n;
+    }
+    return g_arena[dev].sms;
+}
+
+void* workspace(size_t bytes, int slot)
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    if (slot < 0 || slot >= kSlots) return nullptr;
+    std::lock_guard<std::mutex> lk(g_mu);
+    Arena& a = g_arena[dev];
+    if (a.cap[slot] >= bytes && a.ptr[slot]) return a.ptr[slot];
+    if (a.ptr[slot]) {
+        // earlier launches may still read the old block
+        if (cudaDeviceSynchronize() != cudaSuccess) return nullptr;
+        cudaFree(a.ptr[slot]);
+        a.ptr[slot] = nullptr;
+        a.cap[slot] = 0;
+    }
+    size_t want = bytes + bytes / 4;
+    want = (want + 255) & ~(size_t)255;
+    void* p = nullptr;
+    if (cudaMalloc(&p, want) != cudaSuccess) {
+        cudaGetLastError();
+        want = (bytes + 255) & ~(size_t)255;
+        if (cudaMalloc(&p, want) != cudaSuccess) {
+            set_cuda_error(cudaGetLastError());
+            return nullptr;
+        }
+    }
+    a.ptr[slot] = p;
+    a.cap[slot] = want;
+    return p;
+}
+
+static void free_arenas()
+{
+    std::lock_guard<std::mutex> lk(g_mu);
+    int cur = 0;
+    if (cudaGetDevice(&cur) != cudaSuccess) return;
+    for (int d = 0; d < kMaxDevices; ++d) {
+        bool any = false;
+        for (int s = 0; s < kSlots; ++s) any |= g_arena[d].ptr[s] != nullptr;
+        if (!any) continue;
+        if (cudaSetDevice(d) != cudaSuccess) continue;
+        cudaDeviceSynchronize();
+        for (int s = 0; s < kSlots; ++s) {
+            if (g_arena[d].ptr[s]) cudaFree(g_arena[d].ptr[s]);
+            g_arena[d].ptr[s] = nullptr;
+            g_arena[d].cap[s] = 0;
+        }
+    }
+    cudaSetDevice(cur);
+}
+
+// smallest number of balanced signed 8-bit limbs (digits in [-128,127]) covering |v| <= maxabs
+static int limbs_for(uint64_t maxabs)
+{
+    unsigned __int128 cover = 0, w = 1;
+    for (int L = 1; L <= 9; ++L) {
+        cover += (unsigned __int128)127 * w;
+        w <<= 8;
+        if ((unsigned __int128)maxabs <= cover) return L;
+    }
+    return 10;
+}
+
+static int run_contraction(const Contraction& p, int a_limbs, int b_limbs, int flags,
+                           cudaStream_t st)
+{
+    const int algo = flags & ZKDS_ALGO_MASK;
+    if (algo == 3) return ZKDS_ERR_ARG;
+    if (p.batches < 0 || p.M < 0 || p.N < 0 || p.K < 0) return ZKDS_ERR_ARG;
+    if (p.batches == 0 || p.M == 0 || p.N == 0) return ZKDS_OK;
+    if (!p.A || !p.B || !p.C) return ZKDS_ERR_ARG;
+    if (p.a_div == 0 || p.b_div == 0) return ZKDS_ERR_ARG;
+    if (p.shift < 0 || p.shift > 127) return ZKDS_ERR_ARG;
+    if (p.b_bits != 32 && p.b_bits != 64) return ZKDS_ERR_ARG;
+    if (algo == ZKDS_ALGO_EXACT) return launch_contraction_exact(p, st);
+
+    if (a_limbs <= 0 || b_limbs <= 0) {
+        uint64_t* d = (uint64_t*)workspace(2 * sizeof(uint64_t), 5);
+        if (!d) return ZKDS_ERR_WORKSPACE;
+        ZKDS_CUDA(cudaMemsetAsync(d, 0, 2 * sizeof(uint64_t), st));
+        int rc = launch_absmax(p.A, 64, p.batches, p.M, p.K, p.a_sz, p.a_sm, 1, p.a_div, d, st);
+        if (rc != ZKDS_OK) return rc;
+        // B may be shared by every batch (b_sz == 0)
+        rc = launch_absmax(p.B, p.b_bits, p.b_sz ? p.batches : 1, p.N, p.K, p.b_sz, p.b_sn, p.b_sk,
+                           p.b_div, d + 1, st);
+        if (rc != ZKDS_OK) return rc;
+        uint64_t h[2];
+        ZKDS_CUDA(cudaMemcpyAsync(h, d, sizeof(h), cudaMemcpyDeviceToHost, st));
+        ZKDS_CUDA(cudaStreamSynchronize(st));
+        if (a_limbs <= 0) a_limbs = limbs_for(h[0]);
+        if (b_limbs <= 0) b_limbs = limbs_for(h[1]);
+    }
+    int rc = launch_contraction_limb(p, a_limbs, b_limbs, st);
+    if (rc == ZKDS_ERR_UNSUPPORTED && algo == ZKDS_ALGO_AUTO) rc = launch_contraction_exact(p, st);
+    return rc;
+}
+
+static Contraction gemm_problem(const int64_t* A, const void* B, int b_bits, int64_t* C, int64_t* R,
+                                int64_t a_r, int64_t b_r, int64_t s, int64_t Bdim, int64_t M,
+                                int64_t K, int64_t N, int legacy_r)
+{
+    Contraction p{};
+    p.A = A; p.B = B; p.b_bits = b_bits; p.C = C; p.R = R;
+    p.batches = Bdim; p.M = M; p.N = N; p.K = K;
+    p.a_sz = M * K; p.a_sm = K;
+    p.b_sz = 0; p.b_sn = K; p.b_sk = 1;
+    p.c_sz = M * N; p.c_sm = N;
+    p.a_div = a_r; p.b_div = b_r;
+    p.addend = 0;
+    p.shift = (s < 0 || s > 127) ? -1 : (int)s;
+    p.r_legacy = legacy_r;
+    return p;
+}
+
+// which: 0 bshd,hdc->bshc  1 bshc,btc->bsht  2 bsht,btc->bshc  3 bshc,hdc->bshd
+static Contraction einsum_problem(int which, const int64_t* A, const void* B, int64_t* out,
+                                  int64_t r, int64_t Bn, int64_t S, int64_t H, int64_t X, int64_t Y)
+{
+    Contraction p{};
+    p.A = A; p.B = B; p.C = out; p.R = nullptr;
+    p.a_div = 1; p.b_div = 1;
+    p.shift = (r < 0 || r > 127) ? -1 : (int)r;
+    p.addend = (which == 3) ? 0 : r / 2;
+    p.r_legacy = 0;
+    switch (which) {
+    case 0: {  // X = D (contracted), Y = C
+        p.b_bits = 32; p.batches = H; p.M = Bn * S; p.K = X; p.N = Y;
+        p.a_sz = X; p.a_sm = H * X;
+        p.b_sz = X * Y; p.b_sn = 1; p.b_sk = Y;
+        p.c_sz = Y; p.c_sm = H * Y;
+        break;
+    }
+    case 1: {  // X = T, Y = C (contracted)
+        p.b_bits = 64; p.batches = Bn; p.M = S * H; p.K = Y; p.N = X;
+        p.a_sz = S * H * Y; p.a_sm = Y;
+        p.b_sz = X * Y; p.b_sn = Y; p.b_sk = 1;
+        p.c_sz = S * H * X; p.c_sm = X;
+        break;
+    }
+    case 2: {  // X = T (contracted), Y = C
+        p.b_bits = 64; p.batches = Bn; p.M = S * H; p.K = X; p.N = Y;
+        p.a_sz = S * H * X; p.a_sm = X;
+        p.b_sz = X * Y; p.b_sn = 1; p.b_sk = Y;
+        p.c_sz = S * H * Y; p.c_sm = Y;
+        break;
+    }
+    default: {  // X = D, Y = C (contracted)
+        p.b_bits = 32; p.batches = H; p.M = Bn * S; p.K = Y; p.N = X;
+        p.a_sz = Y; p.a_sm = H * Y;
+        p.b_sz = X * Y; p.b_sn = Y; p.b_sk = 1;
+        p.c_sz = X; p.c_sm = H * X;
+        break;
+    }
+    }
+    return p;
+}
+
+static int finish(int rc, const char* who)
+{
+    t_status = rc;
+    if (rc != ZKDS_OK)
+        fprintf(stderr, "libint64gemm: %s failed: %s%s%s\n", who, zkds_status_string(rc),
+                rc == ZKDS_ERR_CUDA ? ": " : "",
+                rc == ZKDS_ERR_CUDA ? cudaGetErrorString((cudaError_t)t_cuda_error) : "");
+    return rc;
+}
+
+static int make_lut(int64_t* lut, int kind)
+{
+    if (!lut) return ZKDS_ERR_ARG;
+    // the exponent is formed in float and widened, as the reference's host code does
+    for (int i = 0; i < 256; ++i) {
+        float e = (kind <= 1) ? i * (-1.0f) / 256 : i * 1.0f / 256;
+        double scale = kind == 0 ? 524288.0 : kind == 1 ? 2097152.0 : kind == 2 ? 8388608.0
+                                                                                : 33554432.0;
+        lut[i] = (int64_t)(pow(2.0, (double)e) * scale);
+    }
+    return (kind >= 0 && kind <= 3) ? ZKDS_OK : ZKDS_ERR_ARG;
+}
+
+}  // namespace zkds
+
+using namespace zkds;
+
+#define ST(s) ((cudaStream_t)(s))
+
+extern "C" {
+
+int zkds_last_status(void) { return t_status; }
+int zkds_last_cuda_error(void) { return t_cuda_error; }
+const char* zkds_version(void) { return "zkds-int64 0.1 (sm_100a)"; }
+void zkds_shutdown(void) { free_arenas(); }
+
+const char* zkds_status_string(int s)
+{
+    switch (s) {
+    case ZKDS_OK: return "ok";
+    case ZKDS_ERR_ARG: return "invalid argument";
+    case ZKDS_ERR_RANGE: return "extent out of range";
+    case ZKDS_ERR_CUDA: return "CUDA error";
+    case ZKDS_ERR_WORKSPACE: return "scratch memory unavailable";
+    case ZKDS_ERR_DEVICE: return "device-side wait ran out";
+    case ZKDS_ERR_UNSUPPORTED: return "not supported by the selected algorithm";
+    default: return "unknown status";
+    }
+}
+
+int zkds_gemm(const int64_t* A, const void* B, int b_bits, int64_t* C, int64_t* R, int64_t a_rescale,
+              int64_t b_rescale, int64_t c_rescale, int64_t Bdim, int64_t M, int64_t K, int64_t N,
+              int a_limbs, int b_limbs, int flags, void* stream)
+{
+    Contraction p = gemm_problem(A, B, b_bits, C, R, a_rescale, b_rescale, c_rescale, Bdim, M, K, N,
+                                 (flags & ZKDS_REMAINDER_LEGACY) ? 1 : 0);
+    return finish(run_contraction(p, a_limbs, b_limbs, flags, ST(stream)), "zkds_gemm");
+}
+
+int zkds_einsum_bshd_hdc_bshc(const int64_t* q, const int32_t* W, int64_t* out, int64_t rescale,
+                              int64_t B, int64_t S, int64_t H, int64_t D, int64_t C, int a_limbs,
+                              int b_limbs, int flags, void* stream)
+{
+    Contraction p = einsum_problem(0, q, W, out, rescale, B, S, H, D, C);
+    return finish(run_contraction(p, a_limbs, b_limbs, flags, ST(stream)),
+                  "zkds_einsum_bshd_hdc_bshc");
+}
+
+int zkds_einsum_bshc_btc_bsht(const int64_t* A, const int64_t* KV, int64_t* out, int64_t rescale,
+                              int64_t B, int64_t S, int64_t H, int64_t T, int64_t C, int a_limbs,
+                              int b_limbs, int flags, void* stream)
+{
+    Contraction p = einsum_problem(1, A, KV, out, rescale, B, S, H, T, C);
+    return finish(run_contraction(p, a_limbs, b_limbs, flags, ST(stream)),
+                  "zkds_einsum_bshc_btc_bsht");
+}
+
+int zkds_einsum_bsht_btc_bshc(const int64_t* P, const int64_t* KV, int64_t* out, int64_t rescale,
+                              int64_t B, int64_t S, int64_t H, int64_t T, int64_t C, int a_limbs,
+                              int b_limbs, int flags, void* stream)
+{
+    Contraction p = einsum_problem(2, P, KV, out, rescale, B, S, H, T, C);
+    return finish(run_contraction(p, a_limbs, b_limbs, flags, ST(stream)),
+                  "zkds_einsum_bsht_btc_bshc");
+}
+
+int zkds_einsum_bshc_hdc_bshd(const int64_t* A, const int32_t* W, int64_t* out, int64_t rescale,
+                              int64_t B, int64_t S, int64_t H, int64_t D, int64_t C, int a_limbs,
+                              int b_limbs, int flags, void* stream)
+{
+    Contraction p = einsum_problem(3, A, W, out, rescale, B, S, H, D, C);
+    return finish(run_contraction(p, a_limbs, b_limbs, flags, ST(stream)),
+                  "zkds_einsum_bshc_hdc_bshd");
+}
+
+int zkds_rope(const int64_t* A, const int64_t* table, int64_t* C, int64_t batch, int64_t seq,
+              int64_t heads, int64_t pairs, int shift, void* stream)
+{
+    int rc;
+    if (batch < 0 || seq < 0 || heads < 0 || pairs < 0) rc = ZKDS_ERR_ARG;
+    else if (batch && seq && heads && pairs && (!A || !table || !C)) rc = ZKDS_ERR_ARG;
+    else rc = launch_rope(A, table, C, batch, seq, heads, pairs, shift, ST(stream));
+    return finish(rc, "zkds_rope");
+}
+
+int zkds_rms_norm(const int64_t* A, const void* W, int w_bits, int64_t* C, int64_t* rms_out,
+                  int64_t M, int64_t N, int64_t eps, int64_t dim, void* stream)
+{
+    int rc;
+    if (M < 0 || N < 0 || dim <= 0) rc = ZKDS_ERR_ARG;
+    else if (M && N && (!A || !W || !C)) rc = ZKDS_ERR_ARG;
+    else rc = launch_rmsnorm(A, W, w_bits, nullptr, rms_out, C, M, N, eps, dim, 1, ST(stream));
+    return finish(rc, "zkds_rms_norm");
+}
+
+int zkds_rms_norm_apply(const int64_t* A, const void* W, int w_bits, const int64_t* rms, int64_t* C,
+                        int64_t M, int64_t N, void* stream)
+{
+    int rc;
+    if (M < 0 || N < 0) rc = ZKDS_ERR_ARG;
+    else if (M && N && (!A || !W || !C || !rms)) rc = ZKDS_ERR_ARG;
+    else rc = launch_rmsnorm(A, W, w_bits, rms, nullptr, C, M, N, 0, 1, 0, ST(stream));
+    return finish(rc, "zkds_rms_norm_apply");
+}
+
+int zkds_softmax(const int64_t* X, int64_t* weights_out, int64_t* C, const int64_t* lut,
+                 int64_t rows, int64_t T, int frac, void* stream)
+{
+    int rc;
+    if (rows < 0 || T < 0) rc = ZKDS_ERR_ARG;
+    else if (rows && T && (!X || !C || !lut)) rc = ZKDS_ERR_ARG;
+    else rc = launch_softmax(X, weights_out, C, lut, rows, T, frac, ST(stream));
+    return finish(rc, "zkds_softmax");
+}
+
+int zkds_act(const int64_t* X, int64_t* C, const int64_t* lut, int64_t n, int frac, int silu,
+             void* stream)
+{
+    int rc;
+    if (n < 0) rc = ZKDS_ERR_ARG;
+    else if (n && (!X || !C || !lut)) rc = ZKDS_ERR_ARG;
+    else rc = launch_act(X, C, lut, n, frac, silu, ST(stream));
+    return finish(rc, "zkds_act");
+}
+
+int zkds_lut(int64_t* host_lut, int kind) { return finish(make_lut(host_lut, kind), "zkds_lut"); }
+
+// ---- the reference's 21 symbols ---------------------------------------------------
+
+static bool nonneg(int a, int b, int c, int d) { return a >= 0 && b >= 0 && c >= 0 && d >= 0; }
+
+void int64_32_bmm_broadcast_launcher(const int64_t* A, const int32_t* B, int64_t* C, int64_t* R,
+                                     const int64_t a_rescale, const int64_t b_rescale,
+                                     const int64_t c_rescale, int Bdim, int M, int K, int N)
+{
+    if (!nonneg(Bdim, M, K, N)) { finish(ZKDS_ERR_ARG, "int64_32_bmm_broadcast_launcher"); return; }
+    Contraction p = gemm_problem(A, B, 32, C, R, a_rescale, b_rescale, c_rescale, Bdim, M, K, N, 1);
+    finish(run_contraction(p, 0, 0, ZKDS_ALGO_AUTO, 0), "int64_32_bmm_broadcast_launcher");
+}
+
+void int64_64_bmm_broadcast_launcher(const int64_t* A, const int64_t* B, int64_t* C, int64_t* R,
+                                     const int64_t a_rescale, const int64_t b_rescale,
+                                     const int64_t c_rescale, int Bdim, int M, int K, int N)
+{
+    if (!nonneg(Bdim, M, K, N)) { finish(ZKDS_ERR_ARG, "int64_64_bmm_broadcast_launcher"); return; }
+    Contraction p = gemm_problem(A, B, 64, C, R, a_rescale, b_rescale, c_rescale, Bdim, M, K, N, 1);
+    finish(run_contraction(p, 0, 0, ZKDS_ALGO_AUTO, 0), "int64_64_bmm_broadcast_launcher");
+}
+
+void bf16_to_int32_2d(const uint16_t* input, int32_t* output, int rows, int cols, int rescale)
+{
+    finish(launch_bf16_to_int32(input, output, rows, cols, rescale, 0, 0), "bf16_to_int32_2d");
+}
+
+void wkv_b_bf16_to_int32(const uint16_t* input, int32_t* output, int rows, int cols)
+{
+    finish(launch_bf16_to_int32(input, output, rows, cols, 0, 1, 0), "wkv_b_bf16_to_int32");
+}
+
+void float32_to_int64_2d(const uint32_t* input, int64_t* output, int rows, int cols, int rescale)
+{
+    finish(launch_f32_to_int64(input, output, rows, cols, rescale, 0), "float32_to_int64_2d");
+}
+
+void complex_int64_mul(const int64_t* A, const int64_t* B, int64_t* C, int batchSize, int seqLen,
+                       int headCount, int headDim)
+{
+    if (!nonneg(batchSize, seqLen, headCount, headDim)) { finish(ZKDS_ERR_ARG, "complex_int64_mul"); return; }
+    finish(launch_rope(A, B, C, batchSize, seqLen, headCount, headDim, 42, 0), "complex_int64_mul");
+}
+
+void rms_norm_32(const int64_t* A, const int32_t* W, const int64_t* rms, int64_t* C, int seqLen,
+                 int Dim)
+{
+    if (seqLen < 0 || Dim < 0) { finish(ZKDS_ERR_ARG, "rms_norm_32"); return; }
+    finish(launch_rmsnorm(A, W, 32, rms, nullptr, C, seqLen, Dim, 0, 1, 0, 0), "rms_norm_32");
+}
+
+void rms_norm_64(const int64_t* A, const int64_t* W, const int64_t* rms, int64_t* C, int seqLen,
+                 int Dim)
+{
+    if (seqLen < 0 || Dim < 0) { finish(ZKDS_ERR_ARG, "rms_norm_64"); return; }
+    finish(launch_rmsnorm(A, W, 64, rms, nullptr, C, seqLen, Dim, 0, 1, 0, 0), "rms_norm_64");
+}
+
+void einsum_bshd_hdc_bshc(const int64_t* q_nope, const int32_t* wkv_b_1, int64_t* out,
+                          int64_t rescale, int B, int S, int H, int D, int C)
+{
+    if (!nonneg(B, S, H, D) || C < 0) { finish(ZKDS_ERR_ARG, "einsum_bshd_hdc_bshc"); return; }
+    Contraction p = einsum_problem(0, q_nope, wkv_b_1, out, rescale, B, S, H, D, C);
+    finish(run_contraction(p, 0, 0, ZKDS_ALGO_AUTO, 0), "einsum_bshd_hdc_bshc");
+}
+
+void einsum_bshc_btc_bsht(const int64_t* A, const int64_t* B, int64_t* C, int64_t rescale, int Bsz,
+                          int S, int H, int T, int Cdim)
+{
+    if (!nonneg(Bsz, S, H, T) || Cdim < 0) { finish(ZKDS_ERR_ARG, "einsum_bshc_btc_bsht"); return; }
+    Contraction p = einsum_problem(1, A, B, C, rescale, Bsz, S, H, T, Cdim);
+    finish(run_contraction(p, 0, 0, ZKDS_ALGO_AUTO, 0), "einsum_bshc_btc_bsht");
+}
+
+void einsum_bsht_btc_bshc(const int64_t* A, const int64_t* B, int64_t* C, int64_t rescale, int Bsz,
+                          int S, int H, int T, int Cdim)
+{
+    if (!nonneg(Bsz, S, H, T) || Cdim < 0) { finish(ZKDS_ERR_ARG, "einsum_bsht_btc_bshc"); return; }
+    Contraction p = einsum_problem(2, A, B, C, rescale, Bsz, S, H, T, Cdim);
+    finish(run_contraction(p, 0, 0, ZKDS_ALGO_AUTO, 0), "einsum_bsht_btc_bshc");
+}
+
+void einsum_bshc_hdc_bshd(const int64_t* A, const int32_t* B, int64_t* C, int64_t rescale, int Bsz,
+                          int S, int H, int D, int Cdim)
+{
+    if (!nonneg(Bsz, S, H, D) || Cdim < 0) { finish(ZKDS_ERR_ARG, "einsum_bshc_hdc_bshd"); return; }
+    Contraction p = einsum_problem(3, A, B, C, rescale, Bsz, S, H, D, Cdim);
+    finish(run_contraction(p, 0, 0, ZKDS_ALGO_AUTO, 0), "einsum_bshc_hdc_bshd");
+}
+
+static void legacy_softmax(int64_t* R, int64_t* C, int64_t* lut, int Bsz, int S, int H, int T,
+                           int frac, const char* who)
+{
+    if (!nonneg(Bsz, S, H, T)) { finish(ZKDS_ERR_ARG, who); return; }
+    int64_t rows = (int64_t)Bsz * S * H;
+    // the reference leaves the unnormalised weights in its input buffer
+    finish(launch_softmax(R, R, C, lut, rows, T, frac, 0), who);
+}
+
+void softmax_q21(int64_t* R, int64_t* C, int64_t* EXP2_FRAC_LUT, int Bsz, int S, int H, int T)
+{
+    legacy_softmax(R, C, EXP2_FRAC_LUT, Bsz, S, H, T, 21, "softmax_q21");
+}
+
+void softmax_q19(int64_t* R, int64_t* C, int64_t* EXP2_FRAC_LUT, int Bsz, int S, int H, int T)
+{
+    legacy_softmax(R, C, EXP2_FRAC_LUT, Bsz, S, H, T, 19, "softmax_q19");
+}
+
+void softmax_init_q21(int64_t* EXP2_FRAC_LUT) { finish(make_lut(EXP2_FRAC_LUT, 1), "softmax_init_q21"); }
+void softmax_init_q19(int64_t* EXP2_FRAC_LUT) { finish(make_lut(EXP2_FRAC_LUT, 0), "softmax_init_q19"); }
+void silu_init_q25(int64_t* EXP2_FRAC_LUT) { finish(make_lut(EXP2_FRAC_LUT, 3), "silu_init_q25"); }
+void silu_init_q23(int64_t* EXP2_FRAC_LUT) { finish(make_lut(EXP2_FRAC_LUT, 2), "silu_init_q23"); }
+
+static void legacy_act(int64_t* R, int64_t* C, int64_t* lut, int Bsz, int S, int Dim, int frac,
+                       int silu, const char* who)
+{
+    if (Bsz < 0 || S < 0 || Dim < 0) { finish(ZKDS_ERR_ARG, who); return; }
+    finish(launch_act(R, C, lut, (int64_t)Bsz * S * Dim, frac, silu, 0), who);
+}
+
+void silu_q25(int64_t* R, int64_t* C, int64_t* L, int Bsz, int S, int Dim) { legacy_act(R, C, L, Bsz, S, Dim, 25, 1, "silu_q25"); }
+void sigmoid_q25(int64_t* R, int64_t* C, int64_t* L, int Bsz, int S, int Dim) { legacy_act(R, C, L, Bsz, S, Dim, 25, 0, "sigmoid_q25"); }
+void silu_q23(int64_t* R, int64_t* C, int64_t* L, int Bsz, int S, int Dim) { legacy_act(R, C, L, Bsz, S, Dim, 23, 1, "silu_q23"); }
+void sigmoid_q23(int64_t* R, int64_t* C, int64_t* L, int Bsz, int S, int Dim) { legacy_act(R, C, L, Bsz, S, Dim, 23, 0, "sigmoid_q23"); }
+
+}  // extern "C"

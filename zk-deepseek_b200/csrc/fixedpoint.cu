@@ -1,0 +1,570 @@
+// Fixed-point streaming kernels: SiLU / sigmoid (Q23, Q25), softmax (Q19, Q21),
+// RoPE complex multiply and RMSNorm.  All are HBM-bound integer work: 128-bit
+// vector loads/stores, warp-shuffle reductions, the row staged in shared memory
+// where a row is read more than once.  Arithmetic follows the reference kernels
+// bit for bit (inference/int64_gemm.cu:223-385, 605-768, 775-1017) with the slow
+// integer divisions replaced by a double-precision estimate plus an exact
+// integer correction.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace zkds {
+
+static constexpr int kThreads = 256;
+
+// ------------------------------------------------------------------------------
+// SiLU / sigmoid
+// ------------------------------------------------------------------------------
+
+// floor-toward-zero NUM / den for NUM = 2^(2*FRAC); den is any int64.
+template <int FRAC>
+__device__ __forceinline__ int64_t div_from_pow2(int64_t den)
+{
+    constexpr int64_t NUM = (int64_t)1 << (2 * FRAC);
+    if (den > 0 && den < ((int64_t)1 << 52)) {
+        int64_t q = (int64_t)((double)NUM / (double)den);
+        int64_t rem = NUM - q * den;
+        if (rem < 0) --q;
+        else if (rem >= den) ++q;
+        return q;
+    }
+    if (den == 0) return 0;  // unreachable for LUT-generated den; keeps the division defined
+    return NUM / den;
+}
+
+template <int FRAC, bool SILU>
+__device__ __forceinline__ int64_t act_one(int64_t r, const int64_t* lut)
+{
+    constexpr int64_t LIM = (int64_t)64 << FRAC;
+    constexpr int64_t LOG2E = (FRAC == 23) ? 12102203ll : 48408813ll;
+    if (r >= LIM) return r;  // the reference returns r here for sigmoid as well
+    if (r <= -LIM) return 0;
+    // |r| < 2^(FRAC+6) and LOG2E < 2^(FRAC+1): the product fits in 64 bits
+    int64_t y = (FRAC == 23) ? ((-r) * LOG2E) >> FRAC : -((r * LOG2E) >> FRAC);
+    int64_t k = y >> FRAC;
+    int64_t f = y & (((int64_t)1 << FRAC) - 1);
+    int64_t t = lut[f >> (FRAC - 8)];
+    int64_t u = 0;
+    if (k > -63) {
+        if (k < 0) u = t >> (int)(-k);
+        else u = (k >= 64) ? 0 : (int64_t)((uint64_t)t << (int)k);
+    }
+    int64_t q = div_from_pow2<FRAC>((int64_t)(((uint64_t)1 << FRAC) + (uint64_t)u));
+    if (!SILU) return q;
+    return (int64_t)((uint64_t)r * (uint64_t)q) >> FRAC;
+}
+
+template <int FRAC, bool SILU, bool VEC>
+__global__ void __launch_bounds__(kThreads)
+act_kernel(const int64_t* X, int64_t* C, const int64_t* __restrict__ lut_g, int64_t n)
+{
+    __shared__ int64_t lut[256];
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) lut[i] = lut_g[i];
+    __syncthreads();
+    constexpr int UNROLL = 4;
+    if (VEC) {
+        const int64_t nv = n >> 1;
+        const longlong2* Xv = reinterpret_cast<const longlong2*>(X);
+        longlong2* Cv = reinterpret_cast<longlong2*>(C);
+        int64_t stride = (int64_t)gridDim.x * kThreads * UNROLL;
+        for (int64_t base = (int64_t)blockIdx.x * kThreads * UNROLL; base < nv; base += stride) {
+            longlong2 v[UNROLL];
+#pragma unroll
+            for (int j = 0; j < UNROLL; ++j) {
+                int64_t i = base + j * kThreads + threadIdx.x;
+                if (i < nv) v[j] = Xv[i];
+            }
+#pragma unroll
+            for (int j = 0; j < UNROLL; ++j) {
+                int64_t i = base + j * kThreads + threadIdx.x;
+                if (i < nv) {
+                    longlong2 o;
+                    o.x = act_one<FRAC, SILU>(v[j].x, lut);
+                    o.y = act_one<FRAC, SILU>(v[j].y, lut);
+                    Cv[i] = o;
+                }
+            }
+        }
+        if ((n & 1) && blockIdx.x == 0 && threadIdx.x == 0)
+            C[n - 1] = act_one<FRAC, SILU>(X[n - 1], lut);
+    } else {
+        int64_t stride = (int64_t)gridDim.x * kThreads;
+        for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride)
+            C[i] = act_one<FRAC, SILU>(X[i], lut);
+    }
+}
+
+static int grid_for(int64_t work_items, int per_block, int sm_count, int waves)
+{
+    int64_t blocks = (work_items + per_block - 1) / per_block;
+    int64_t cap = (int64_t)sm_count * waves;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+
+int launch_act(const int64_t* X, int64_t* C, const int64_t* lut, int64_t n, int frac, int silu,
+               cudaStream_t st)
+{
+    if (n == 0) return ZKDS_OK;
+    bool vec = (((uintptr_t)X | (uintptr_t)C) & 15) == 0;
+    int sms = sm_count();
+    int grid = grid_for(vec ? n / 2 : n, kThreads * (vec ? 4 : 1), sms, 8);
+#define ZKDS_ACT(F, S)                                                           \
+    do {                                                                         \
+        if (vec) act_kernel<F, S, true><<<grid, kThreads, 0, st>>>(X, C, lut, n); \
+        else act_kernel<F, S, false><<<grid, kThreads, 0, st>>>(X, C, lut, n);    \
+    } while (0)
+    if (frac == 23 && silu) ZKDS_ACT(23, true);
+    else if (frac == 23) ZKDS_ACT(23, false);
+    else if (frac == 25 && silu) ZKDS_ACT(25, true);
+    else if (frac == 25) ZKDS_ACT(25, false);
+    else return ZKDS_ERR_ARG;
+#undef ZKDS_ACT
+    return check_launch();
+}
+
+// ------------------------------------------------------------------------------
+// softmax: one CTA per row, the row staged in shared memory
+// ------------------------------------------------------------------------------
+
+__device__ __forceinline__ int64_t block_max_i64(int64_t v, int64_t* red)
+{
+    v = warp_max_i64(v);
+    int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    int nw = blockDim.x >> 5;
+    int64_t r = (lane < nw) ? red[lane] : INT64_MIN;
+    r = warp_max_i64(r);
+    __syncthreads();
+    return r;
+}
+
+__device__ __forceinline__ int64_t block_sum_i64(int64_t v, int64_t* red)
+{
+    v = warp_sum_i64(v);
+    int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    int nw = blockDim.x >> 5;
+    int64_t r = (lane < nw) ? red[lane] : 0;
+    r = warp_sum_i64(r);
+    __syncthreads();
+    return r;
+}
+
+// unnormalised weight of one score, given the row maximum
+template <int FRAC>
+__device__ __forceinline__ int64_t softmax_weight(int64_t x, int64_t mx, const int64_t* lut)
+{
+    if (FRAC == 19) {
+        uint64_t d = (uint64_t)mx - (uint64_t)x;
+        if (d > (uint64_t)(64 << 19)) return 0;
+        int64_t y = (int64_t)((d * 756388ull) >> 19);  // d <= 2^25: no overflow
+        int64_t k = y >> 19, f = y & 0x7FFFF;
+        int64_t t = lut[f >> 11];
+        return (k >= 64) ? 0 : (t >> (int)k);
+    } else {
+        int64_t d = (int64_t)((uint64_t)x - (uint64_t)mx);
+        if (d < -(int64_t)(64 << 21)) return 0;
+        int64_t y = (int64_t)((uint64_t)d * 3025551ull + (uint64_t)(1 << 20)) >> 21;
+        int64_t ny = (int64_t)(0 - (uint64_t)y);
+        int64_t k = ny >> 21, f = ny & 0x1FFFFF;
+        int64_t t = lut[f >> 13];
+        return (k >= 64) ? 0 : (t >> (int)k);
+    }
+}
+
+// exact num / den for 0 <= num < 2^52, 0 < den < 2^52 with a per-row reciprocal
+__device__ __forceinline__ int64_t div_by_row(int64_t num, int64_t den, double inv)
+{
+    // the estimate is within one of the quotient: one exact correction either way
+    int64_t q = (int64_t)((double)num * inv);
+    int64_t rem = num - q * den;
+    if (rem < 0) --q;
+    else if (rem >= den) ++q;
+    return q;
+}
+
+template <int FRAC>
+__device__ __forceinline__ int64_t softmax_norm(int64_t w, int64_t sumW, double inv, bool fast)
+{
+    if (sumW == 0) return 0;
+    int64_t num = (int64_t)((uint64_t)w << FRAC);
+    if (FRAC == 21) num += sumW / 2;
+    if (fast) return div_by_row(num, sumW, inv);
+    return num / sumW;
+}
+
+// STAGE: row held in dynamic shared memory; otherwise C is used as scratch for the
+// weights exactly as the reference uses its input buffer.
+template <int FRAC, bool STAGE, bool VEC>
+__global__ void __launch_bounds__(kThreads)
+softmax_kernel(const int64_t* X, int64_t* Wout, int64_t* C, const int64_t* __restrict__ lut_g,
+               int64_t T)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ int64_t lut[256];
+    __shared__ int64_t red[32];
+    int64_t* row = reinterpret_cast<int64_t*>(smem_raw);
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) lut[i] = lut_g[i];
+    const int64_t off = (int64_t)blockIdx.x * T;
+    const int64_t* x = X + off;
+    int64_t* c = C + off;
+    int64_t* wo = Wout ? Wout + off : nullptr;
+
+    int64_t mx = INT64_MIN;
+    if (VEC) {
+        const longlong2* xv = reinterpret_cast<const longlong2*>(x);
+        longlong2* rv = reinterpret_cast<longlong2*>(row);
+        for (int64_t i = threadIdx.x; i < (T >> 1); i += kThreads) {
+            longlong2 v = xv[i];
+            if (STAGE) rv[i] = v;
+            mx = v.x > mx ? v.x : mx;
+            mx = v.y > mx ? v.y : mx;
+        }
+    } else {
+        for (int64_t i = threadIdx.x; i < T; i += kThreads) {
+            int64_t v = x[i];
+            if (STAGE) row[i] = v;
+            mx = v > mx ? v : mx;
+        }
+    }
+    mx = block_max_i64(mx, red);  // also orders the LUT and row stores
+
+    int64_t sum = 0;
+    if (VEC) {
+        const longlong2* src = STAGE ? reinterpret_cast<const longlong2*>(row)
+                                     : reinterpret_cast<const longlong2*>(x);
+        longlong2* dst = STAGE ? reinterpret_cast<longlong2*>(row) : reinterpret_cast<longlong2*>(c);
+        for (int64_t i = threadIdx.x; i < (T >> 1); i += kThreads) {
+            longlong2 v = src[i];
+            v.x = softmax_weight<FRAC>(v.x, mx, lut);
+            v.y = softmax_weight<FRAC>(v.y, mx, lut);
+            dst[i] = v;
+            sum += v.x + v.y;
+        }
+    } else {
+        const int64_t* src = STAGE ? row : x;
+        int64_t* dst = STAGE ? row : c;
+        for (int64_t i = threadIdx.x; i < T; i += kThreads) {
+            int64_t w = softmax_weight<FRAC>(src[i], mx, lut);
+            dst[i] = w;
+            sum += w;
+        }
+    }
+    const int64_t sumW = block_sum_i64(sum, red);
+    // every weight is < 2^(FRAC+1) so num < 2^(2*FRAC+2); the double path needs sumW < 2^52
+    const bool fast = sumW > 0 && sumW < ((int64_t)1 << 51);
+    const double inv = fast ? 1.0 / (double)sumW : 0.0;
+
+    if (VEC) {
+        const longlong2* src = STAGE ? reinterpret_cast<const longlong2*>(row)
+                                     : reinterpret_cast<const longlong2*>(c);
+        longlong2* cv = reinterpret_cast<longlong2*>(c);
+        longlong2* wv = reinterpret_cast<longlong2*>(wo);
+        for (int64_t i = threadIdx.x; i < (T >> 1); i += kThreads) {
+            longlong2 w = src[i];
+            if (wo) wv[i] = w;
+            longlong2 o;
+            o.x = softmax_norm<FRAC>(w.x, sumW, inv, fast);
+            o.y = softmax_norm<FRAC>(w.y, sumW, inv, fast);
+            cv[i] = o;
+        }
+    } else {
+        const int64_t* src = STAGE ? row : c;
+        for (int64_t i = threadIdx.x; i < T; i += kThreads) {
+            int64_t w = src[i];
+            if (wo) wo[i] = w;
+            c[i] = softmax_norm<FRAC>(w, sumW, inv, fast);
+        }
+    }
+}
+
+template <int FRAC>
+static int launch_softmax_t(const int64_t* X, int64_t* Wout, int64_t* C, const int64_t* lut,
+                            int64_t rows, int64_t T, cudaStream_t st)
+{
+    const size_t row_bytes = (size_t)T * 8;
+    const bool stage = row_bytes <= 200 * 1024;
+    const bool vec = (T % 2 == 0) && ((((uintptr_t)X | (uintptr_t)C | (uintptr_t)Wout) & 15) == 0);
+    size_t smem = stage ? row_bytes : 0;
+#define ZKDS_SM(S, V)                                                                        \
+    do {                                                                                     \
+        auto k = softmax_kernel<FRAC, S, V>;                                                 \
+        if (smem > 48 * 1024)                                                                \
+            ZKDS_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                                           (int)smem));                                      \
+        k<<<(unsigned)rows, kThreads, smem, st>>>(X, Wout, C, lut, T);                       \
+    } while (0)
+    if (stage && vec) ZKDS_SM(true, true);
+    else if (stage) ZKDS_SM(true, false);
+    else if (vec) ZKDS_SM(false, true);
+    else ZKDS_SM(false, false);
+#undef ZKDS_SM
+    return check_launch();
+}
+
+int launch_softmax(const int64_t* X, int64_t* Wout, int64_t* C, const int64_t* lut, int64_t rows,
+                   int64_t T, int frac, cudaStream_t st)
+{
+    if (rows == 0 || T == 0) return ZKDS_OK;
+    if (rows > 0x7fffffffll) return ZKDS_ERR_RANGE;
+    if (frac == 19) return launch_softmax_t<19>(X, Wout, C, lut, rows, T, st);
+    if (frac == 21) return launch_softmax_t<21>(X, Wout, C, lut, rows, T, st);
+    return ZKDS_ERR_ARG;
+}
+
+// ------------------------------------------------------------------------------
+// RoPE: (a0 + i a1) * (b0 + i b1), every product reduced to bits [shift, shift+64)
+// ------------------------------------------------------------------------------
+
+__device__ __forceinline__ int64_t mul_shift(int64_t x, int64_t y, int shift)
+{
+    return sar128_lo(mul64x64(x, y), shift);
+}
+
+// grid.x enumerates (position, chunk); a position is one (batch, seq) row of H*pairs pairs
+__global__ void __launch_bounds__(kThreads)
+rope_kernel(const longlong2* __restrict__ A, const longlong2* __restrict__ Tb,
+            longlong2* __restrict__ C, unsigned chunks, unsigned rowlen, unsigned S,
+            unsigned pairs, int shift)
+{
+    const unsigned pos = blockIdx.x / chunks;
+    const unsigned chunk = blockIdx.x - pos * chunks;
+    const unsigned s = pos % S;
+    const longlong2* a = A + (int64_t)pos * rowlen;
+    longlong2* c = C + (int64_t)pos * rowlen;
+    const longlong2* t = Tb + (int64_t)s * pairs;
+    constexpr int UNROLL = 4;
+    const unsigned base = chunk * (kThreads * UNROLL);
+    longlong2 av[UNROLL], bv[UNROLL];
+#pragma unroll
+    for (int j = 0; j < UNROLL; ++j) {
+        unsigned i = base + j * kThreads + threadIdx.x;
+        if (i < rowlen) {
+            av[j] = a[i];
+            bv[j] = t[i % pairs];
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < UNROLL; ++j) {
+        unsigned i = base + j * kThreads + threadIdx.x;
+        if (i < rowlen) {
+            longlong2 o;
+            o.x = (int64_t)((uint64_t)mul_shift(av[j].x, bv[j].x, shift) -
+                            (uint64_t)mul_shift(av[j].y, bv[j].y, shift));
+            o.y = (int64_t)((uint64_t)mul_shift(av[j].x, bv[j].y, shift) +
+                            (uint64_t)mul_shift(av[j].y, bv[j].x, shift));
+            c[i] = o;
+        }
+    }
+}
+
+int launch_rope(const int64_t* A, const int64_t* Tb, int64_t* C, int64_t batch, int64_t S,
+                int64_t H, int64_t pairs, int shift, cudaStream_t st)
+{
+    if (batch == 0 || S == 0 || H == 0 || pairs == 0) return ZKDS_OK;
+    if (shift < 0 || shift > 127) return ZKDS_ERR_ARG;
+    if ((((uintptr_t)A | (uintptr_t)Tb | (uintptr_t)C) & 15) != 0) return ZKDS_ERR_ARG;
+    int64_t rowlen = H * pairs;
+    int64_t chunks = (rowlen + kThreads * 4 - 1) / (kThreads * 4);
+    int64_t blocks = batch * S * chunks;
+    if (rowlen > 0x7fffffffll || blocks > 0x7fffffffll || S > 0x7fffffffll) return ZKDS_ERR_RANGE;
+    rope_kernel<<<(unsigned)blocks, kThreads, 0, st>>>(
+        reinterpret_cast<const longlong2*>(A), reinterpret_cast<const longlong2*>(Tb),
+        reinterpret_cast<longlong2*>(C), (unsigned)chunks, (unsigned)rowlen, (unsigned)S,
+        (unsigned)pairs, shift);
+    return check_launch();
+}
+
+// ------------------------------------------------------------------------------
+// RMSNorm
+// ------------------------------------------------------------------------------
+
+struct u128w {
+    uint64_t lo, hi;
+};
+
+__device__ __forceinline__ u128w warp_sum_u128(u128w v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        uint64_t lo = __shfl_xor_sync(0xffffffffu, v.lo, o);
+        uint64_t hi = __shfl_xor_sync(0xffffffffu, v.hi, o);
+        uint64_t nlo = v.lo + lo;
+        v.hi = v.hi + hi + (nlo < lo ? 1ull : 0ull);
+        v.lo = nlo;
+    }
+    return v;
+}
+
+// floor(sqrt(v)), v unsigned 128-bit
+__device__ uint64_t isqrt_u128(unsigned __int128 v)
+{
+    if (v == 0) return 0;
+    unsigned __int128 r = 0, bit;
+    uint64_t hi = (uint64_t)(v >> 64);
+    int top = hi ? 127 - __clzll((long long)hi) : 63 - __clzll((long long)(uint64_t)v);
+    bit = (unsigned __int128)1 << (top & ~1);
+    while (bit != 0) {
+        if (v >= r + bit) { v -= r + bit; r = (r >> 1) + bit; }
+        else r >>= 1;
+        bit >>= 2;
+    }
+    return (uint64_t)r;
+}
+
+// the reference's quotient: trunc(P / r), minus one when the remainder is negative
+__device__ __noinline__ int64_t div_slow(i128w P, int64_t r)
+{
+    if (r == 0) return 0;
+    __int128 p = ((__int128)P.hi << 64) | (__int128)(unsigned __int128)P.lo;
+    __int128 qq = p / (__int128)r, rr = p % (__int128)r;
+    if (rr < 0) qq -= 1;
+    return (int64_t)qq;
+}
+
+// floor(a*w / r) for r > 0 through a double estimate corrected with the exact remainder
+__device__ __forceinline__ int64_t norm_one(int64_t a, int64_t w, int64_t r, double inv)
+{
+    i128w P = mul64x64(a, w);
+    if (r > 0) {
+        // convert the magnitude so that the estimate keeps a 2^-52 relative error
+        const bool neg = P.hi < 0;
+        i128w U = neg ? sub128(i128w{0, 0}, P) : P;
+        double pd = (double)(uint64_t)U.hi * 18446744073709551616.0 + (double)U.lo;
+        double qe = neg ? -(pd * inv) : pd * inv;
+        if (fabs(qe) < 562949953421312.0) {  // 2^49: estimate is within 1 of the quotient
+            int64_t q = __double2ll_rd(qe);
+            i128w rem = sub128(P, mul64x64(q, r));
+            if (rem.hi < 0) { --q; rem = add128(rem, make_i128(r)); }
+            else if (rem.hi > 0 || rem.lo >= (uint64_t)r) { ++q; rem = sub128(rem, make_i128(r)); }
+            if (rem.hi == 0 && rem.lo < (uint64_t)r) return q;
+        }
+    }
+    return div_slow(P, r);
+}
+
+// One CTA per row.  FUSED: compute rms = isqrt((eps + sum a^2) / dim) here and write
+// it to rms_out; otherwise read the caller's rms[row].
+template <typename WT, bool FUSED, bool STAGE>
+__global__ void __launch_bounds__(kThreads)
+rmsnorm_kernel(const int64_t* __restrict__ A, const WT* __restrict__ W, const int64_t* rms_in,
+               int64_t* rms_out, int64_t* __restrict__ C, int64_t N, int64_t eps, int64_t dim)
+{
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ u128w red[32];
+    __shared__ int64_t s_rms;
+    int64_t* row = reinterpret_cast<int64_t*>(smem_raw);
+    const int64_t off = (int64_t)blockIdx.x * N;
+    const int64_t* a = A + off;
+    int64_t* c = C + off;
+    const bool vec = ((N & 1) == 0) && ((((uintptr_t)A | (uintptr_t)C) & 15) == 0);
+
+    if (FUSED) {
+        u128w acc = {0, 0};
+        if (vec) {
+            const longlong2* av = reinterpret_cast<const longlong2*>(a);
+            longlong2* rv = reinterpret_cast<longlong2*>(row);
+            for (int64_t i = threadIdx.x; i < (N >> 1); i += kThreads) {
+                longlong2 v = av[i];
+                if (STAGE) rv[i] = v;
+                i128w p = mul64x64(v.x, v.x);
+                uint64_t nlo = acc.lo + p.lo;
+                acc.hi += (uint64_t)p.hi + (nlo < p.lo ? 1ull : 0ull);
+                acc.lo = nlo;
+                p = mul64x64(v.y, v.y);
+                nlo = acc.lo + p.lo;
+                acc.hi += (uint64_t)p.hi + (nlo < p.lo ? 1ull : 0ull);
+                acc.lo = nlo;
+            }
+        } else {
+            for (int64_t i = threadIdx.x; i < N; i += kThreads) {
+                int64_t v = a[i];
+                if (STAGE) row[i] = v;
+                i128w p = mul64x64(v, v);
+                uint64_t nlo = acc.lo + p.lo;
+                acc.hi += (uint64_t)p.hi + (nlo < p.lo ? 1ull : 0ull);
+                acc.lo = nlo;
+            }
+        }
+        acc = warp_sum_u128(acc);
+        int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+        if (lane == 0) red[wid] = acc;
+        __syncthreads();
+        if (wid == 0) {
+            u128w t = (lane < (kThreads >> 5)) ? red[lane] : u128w{0, 0};
+            t = warp_sum_u128(t);
+            if (lane == 0) {
+                unsigned __int128 tot = ((unsigned __int128)t.hi << 64) | t.lo;
+                tot += (unsigned __int128)(__int128)eps;
+                uint64_t r = dim ? isqrt_u128(tot / (unsigned __int128)(uint64_t)dim) : 0;
+                s_rms = (int64_t)r;
+                if (rms_out) rms_out[blockIdx.x] = (int64_t)r;
+            }
+        }
+        __syncthreads();
+    } else {
+        if (threadIdx.x == 0) s_rms = rms_in[blockIdx.x];
+        __syncthreads();
+    }
+    const int64_t r = s_rms;
+    const double inv = r > 0 ? 1.0 / (double)r : 0.0;
+    const int64_t* src = (FUSED && STAGE) ? row : a;
+    if (vec) {
+        const longlong2* sv = reinterpret_cast<const longlong2*>(src);
+        longlong2* cv = reinterpret_cast<longlong2*>(c);
+        for (int64_t i = threadIdx.x; i < (N >> 1); i += kThreads) {
+            longlong2 v = sv[i];
+            longlong2 o;
+            o.x = norm_one(v.x, (int64_t)W[2 * i], r, inv);
+            o.y = norm_one(v.y, (int64_t)W[2 * i + 1], r, inv);
+            cv[i] = o;
+        }
+    } else {
+        for (int64_t i = threadIdx.x; i < N; i += kThreads)
+            c[i] = norm_one(src[i], (int64_t)W[i], r, inv);
+    }
+}
+
+template <typename WT>
+static int launch_rmsnorm_t(const int64_t* A, const WT* W, const int64_t* rms_in, int64_t* rms_out,
+                            int64_t* C, int64_t M, int64_t N, int64_t eps, int64_t dim, bool fused,
+                            cudaStream_t st)
+{
+    size_t row_bytes = (size_t)N * 8;
+    bool stage = fused && row_bytes <= 200 * 1024;
+    size_t smem = stage ? row_bytes : 0;
+#define ZKDS_RMS(F, S)                                                                       \
+    do {                                                                                     \
+        auto k = rmsnorm_kernel<WT, F, S>;                                                   \
+        if (smem > 48 * 1024)                                                                \
+            ZKDS_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                                           (int)smem));                                      \
+        k<<<(unsigned)M, kThreads, smem, st>>>(A, W, rms_in, rms_out, C, N, eps, dim);       \
+    } while (0)
+    if (fused && stage) ZKDS_RMS(true, true);
+    else if (fused) ZKDS_RMS(true, false);
+    else ZKDS_RMS(false, false);
+#undef ZKDS_RMS
+    return check_launch();
+}
+
+int launch_rmsnorm(const int64_t* A, const void* W, int w_bits, const int64_t* rms_in,
+                   int64_t* rms_out, int64_t* C, int64_t M, int64_t N, int64_t eps, int64_t dim,
+                   int fused, cudaStream_t st)
+{
+    if (M == 0 || N == 0) return ZKDS_OK;
+    if (M > 0x7fffffffll) return ZKDS_ERR_RANGE;
+    if (w_bits == 32)
+        return launch_rmsnorm_t<int32_t>(A, (const int32_t*)W, rms_in, rms_out, C, M, N, eps, dim,
+                                         fused != 0, st);
+    if (w_bits == 64)
+        return launch_rmsnorm_t<int64_t>(A, (const int64_t*)W, rms_in, rms_out, C, M, N, eps, dim,
+                                         fused != 0, st);
+    return ZKDS_ERR_ARG;
+}
+
+}  // namespace zkds

@@ -1,0 +1,67 @@
+// Internal launch interface between the C-ABI layer (capi.cu) and the kernel
+// translation units.  Every launcher validates nothing: the C-ABI layer owns the
+// argument checks.  All return a ZKDS_* status.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace zkds {
+
+int sm_count();  // SM count of the current device (cached per device)
+
+// ---- streaming fixed-point kernels (fixedpoint.cu) ---------------------------
+int launch_act(const int64_t* X, int64_t* C, const int64_t* lut, int64_t n, int frac, int silu,
+               cudaStream_t st);
+int launch_softmax(const int64_t* X, int64_t* Wout, int64_t* C, const int64_t* lut, int64_t rows,
+                   int64_t T, int frac, cudaStream_t st);
+int launch_rope(const int64_t* A, const int64_t* Tb, int64_t* C, int64_t batch, int64_t S,
+                int64_t H, int64_t pairs, int shift, cudaStream_t st);
+int launch_rmsnorm(const int64_t* A, const void* W, int w_bits, const int64_t* rms_in,
+                   int64_t* rms_out, int64_t* C, int64_t M, int64_t N, int64_t eps, int64_t dim,
+                   int fused, cudaStream_t st);
+
+// ---- contractions ---------------------------------------------------------------
+// One batched contraction  C[z][m][n] = (addend + sum_k A(z,m,k) * B(z,n,k)) >> shift
+// with the sum held in 128 bits.  A is int64 with unit k-stride; B is int32 or int64
+// with arbitrary n- and k-strides (so the MLA einsums map onto it without copies).
+// a_div / b_div are C truncating divisors applied to each element before the product.
+struct Contraction {
+    const int64_t* A;
+    const void* B;
+    int b_bits;  // 32 or 64
+    int64_t* C;
+    int64_t* R;  // remainder output, may be null
+    int64_t batches, M, N, K;
+    int64_t a_sz, a_sm;
+    int64_t b_sz, b_sn, b_sk;
+    int64_t c_sz, c_sm;
+    int64_t a_div, b_div;
+    int64_t addend;
+    int shift;     // 0..127
+    int r_legacy;  // remainder flavour, see gemm_remainder()
+};
+
+// CUDA-core path: exact for every input, any shape (gemm_exact.cu)
+int launch_contraction_exact(const Contraction& p, cudaStream_t st);
+
+// Tensor-core path (limb_gemm.cu).  La/Lb: signed 8-bit limb counts that cover the
+// operands after division; returns ZKDS_ERR_UNSUPPORTED when the shape or the limb
+// counts fall outside what the kernel handles (caller then uses the exact path).
+int launch_contraction_limb(const Contraction& p, int La, int Lb, cudaStream_t st);
+
+// max |x / div| over a strided int64 / int32 operand, written to *out_dev (uint64)
+int launch_absmax(const void* X, int bits, int64_t batches, int64_t rows, int64_t cols,
+                  int64_t sz, int64_t sr, int64_t sc, int64_t div, uint64_t* out_dev,
+                  cudaStream_t st);
+
+// dead-code converters kept for ABI completeness (converters.cu)
+int launch_bf16_to_int32(const uint16_t* in, int32_t* out, int rows, int cols, int rescale,
+                         int wkv_b_variant, cudaStream_t st);
+int launch_f32_to_int64(const uint32_t* in, int64_t* out, int rows, int cols, int rescale,
+                        cudaStream_t st);
+
+// scratch memory owned by the library, one arena per device, grown on demand and
+// reused by the next call (capi.cu).  Returns null when the allocation fails.
+void* workspace(size_t bytes, int slot);
+
+}  // namespace zkds

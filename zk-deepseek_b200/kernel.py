@@ -1,0 +1,367 @@
+"""Drop-in replacement for the reference's ``inference/kernel.py`` on B200.
+
+Same function names, argument meaning and return values as the reference module
+(``inference/kernel.py:341-687``), so ``inference/model.py`` and
+``inference/generate.py`` import it unchanged::
+
+    from kernel import int64_bmm_broadcast, softmax_q19, RMS_Norm_int64, ...
+
+Every function calls hand-written sm_100a CUDA through the C ABI of
+``libint64gemm.so`` (``include/zkds_int64.h``).  There is no CPU or PyTorch
+fallback: a missing library or a failing launch raises.
+
+Differences from the reference module, all on the host side:
+  * the library is looked up through ``$ZKDS_LIB``, then beside this file, then
+    ``./libint64gemm.so`` (the reference only tries the last, kernel.py:206);
+  * nothing is allocated on the GPU at import time;
+  * launches go to torch's current stream and their status is checked;
+  * ``RMS_Norm_int64`` computes the per-row rms on the GPU (the reference loops
+    over every element on the host, kernel.py:477-494) and returns the same
+    ``(C, rms)`` pair, ``rms`` being a CPU int64 tensor of at least 500 entries
+    whose first M entries are the rows' rms;
+  * the float / Triton helpers of the fp8 path (``act_quant``, ``weight_dequant``,
+    ``fp8_gemm``) are importable but raise: the integer forward pass never
+    reaches them.
+"""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+ALGO_AUTO, ALGO_EXACT, ALGO_LIMB = 0, 1, 2
+REMAINDER_LEGACY = 4
+
+# Remainder flavour of int64_bmm_broadcast.  True reproduces the reference binary:
+# exact for c_rescale <= 31, the low 64 bits of the sum above that
+# (int64_gemm.cu:22 evaluates its mask in 32-bit int).  False gives sum mod 2^s.
+LEGACY_REMAINDER = True
+# Contraction algorithm used by the functions below (ALGO_AUTO picks the tensor-core
+# limb kernel when the shape allows it).
+ALGO = ALGO_AUTO
+
+
+def _find_library():
+    cands = []
+    if os.environ.get("ZKDS_LIB"):
+        cands.append(os.environ["ZKDS_LIB"])
+    cands.append(os.path.join(_HERE, "libint64gemm.so"))
+    cands.append("./libint64gemm.so")
+    for c in cands:
+        if os.path.exists(c):
+            return c
+    raise OSError("libint64gemm.so not found (looked in %s); build it with "
+                  "`python zk-deepseek_b200/build.py`" % ", ".join(cands))
+
+
+lib = ctypes.CDLL(_find_library())
+
+_vp, _ll, _i = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int
+
+
+def _sig(name, argtypes, restype=_i):
+    fn = getattr(lib, name)
+    fn.argtypes = argtypes
+    fn.restype = restype
+    return fn
+
+
+_sig("zkds_last_status", [])
+_sig("zkds_last_cuda_error", [])
+_sig("zkds_status_string", [_i], ctypes.c_char_p)
+_sig("zkds_version", [], ctypes.c_char_p)
+_sig("zkds_shutdown", [], None)
+_sig("zkds_gemm", [_vp, _vp, _i, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _i, _i, _i, _vp])
+for _n in ("zkds_einsum_bshd_hdc_bshc", "zkds_einsum_bshc_btc_bsht", "zkds_einsum_bsht_btc_bshc",
+           "zkds_einsum_bshc_hdc_bshd"):
+    _sig(_n, [_vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _i, _i, _i, _vp])
+_sig("zkds_rope", [_vp, _vp, _vp, _ll, _ll, _ll, _ll, _i, _vp])
+_sig("zkds_rms_norm", [_vp, _vp, _i, _vp, _vp, _ll, _ll, _ll, _ll, _vp])
+_sig("zkds_rms_norm_apply", [_vp, _vp, _i, _vp, _vp, _ll, _ll, _vp])
+_sig("zkds_softmax", [_vp, _vp, _vp, _vp, _ll, _ll, _i, _vp])
+_sig("zkds_act", [_vp, _vp, _vp, _ll, _i, _i, _vp])
+_sig("zkds_lut", [_vp, _i])
+
+
+class ZkdsError(RuntimeError):
+    pass
+
+
+def _check(status, what):
+    if status != 0:
+        msg = lib.zkds_status_string(status).decode()
+        if status == 3:
+            msg += " (cudaError %d)" % lib.zkds_last_cuda_error()
+        raise ZkdsError("%s: %s" % (what, msg))
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dev_i64(t, name):
+    if t.dtype != torch.int64:
+        raise TypeError("%s must be int64, got %s" % (name, t.dtype))
+    if not t.is_cuda:
+        raise ValueError("%s must be a CUDA tensor" % name)
+    if not t.is_contiguous():
+        raise ValueError("%s must be contiguous" % name)
+    return t
+
+
+# ---- float helpers of the fp8 path: not part of the integer forward pass -------------
+
+def act_quant(x, block_size=128):
+    raise NotImplementedError("act_quant belongs to the fp8 path; the integer model never calls it")
+
+
+def weight_dequant(x, s, block_size=128):
+    raise NotImplementedError("weight_dequant belongs to the fp8 path (offline conversion only)")
+
+
+def fp8_gemm(a, a_s, b, b_s):
+    raise NotImplementedError("fp8_gemm belongs to the fp8 path; the integer model never calls it")
+
+
+# ---- contractions --------------------------------------------------------------------
+
+def int64_bmm_broadcast(A, B, a_rescale, b_rescale, c_rescale, a_limbs=0, b_limbs=0):
+    """(Bdim, M, K) int64 x (N, K) int32|int64 -> (C, R), each (Bdim, M, N) int64.
+
+    C = (sum_k (A/a_rescale)*(B/b_rescale)) >> c_rescale with the sum held in 128 bits;
+    R is the remainder (kernel.py:341-371, int64_gemm.cu:6-90).  a_limbs/b_limbs are
+    optional operand-range hints (signed 8-bit limb counts); 0 measures them.
+    """
+    _dev_i64(A, "A")
+    if not B.is_cuda or not B.is_contiguous():
+        raise ValueError("B must be a contiguous CUDA tensor")
+    if B.dtype not in (torch.int64, torch.int32):
+        raise TypeError("Unsupported B type: %s" % B.dtype)
+    Bdim, M, K = A.shape
+    N, K2 = B.shape
+    assert K2 == K
+    C = torch.empty((Bdim, M, N), dtype=torch.int64, device=A.device)
+    R = torch.empty((Bdim, M, N), dtype=torch.int64, device=A.device)
+    flags = ALGO | (REMAINDER_LEGACY if LEGACY_REMAINDER else 0)
+    with torch.cuda.device(A.device):
+        _check(lib.zkds_gemm(A.data_ptr(), B.data_ptr(), 32 if B.dtype == torch.int32 else 64,
+                             C.data_ptr(), R.data_ptr(), int(a_rescale), int(b_rescale),
+                             int(c_rescale), Bdim, M, K, N, a_limbs, b_limbs, flags, _stream()),
+               "int64_bmm_broadcast")
+    return (C, R)
+
+
+def _einsum(fn_name, A, B, out_shape, rescale, dims, a_limbs, b_limbs):
+    _dev_i64(A, "A")
+    if not B.is_cuda or not B.is_contiguous():
+        raise ValueError("B must be a contiguous CUDA tensor")
+    C = torch.empty(out_shape, dtype=torch.int64, device=A.device)
+    with torch.cuda.device(A.device):
+        _check(getattr(lib, fn_name)(A.data_ptr(), B.data_ptr(), C.data_ptr(), int(rescale), *dims,
+                                     a_limbs, b_limbs, ALGO, _stream()), fn_name)
+    return C
+
+
+def einsum_bshd_hdc_bshc(A, B, rescale, a_limbs=0, b_limbs=0):
+    """out[b,s,h,c] = (rescale//2 + sum_d A[b,s,h,d] * B[h,d,c]) >> rescale; B int32."""
+    assert A.shape[2] == B.shape[0] and A.shape[3] == B.shape[1]
+    assert B.dtype == torch.int32
+    Bn, S, H, D = A.shape
+    Cp = B.shape[2]
+    return _einsum("zkds_einsum_bshd_hdc_bshc", A, B, [Bn, S, H, Cp], rescale, (Bn, S, H, D, Cp),
+                   a_limbs, b_limbs)
+
+
+def einsum_bshc_btc_bsht(A, B, rescale, a_limbs=0, b_limbs=0):
+    """out[b,s,h,t] = (rescale//2 + sum_c A[b,s,h,c] * B[b,t,c]) >> rescale; B int64."""
+    Bn, S, H, Cd = A.shape
+    T = B.shape[1]
+    assert Bn == B.shape[0] and Cd == B.shape[2]
+    _dev_i64(B, "B")
+    return _einsum("zkds_einsum_bshc_btc_bsht", A, B, [Bn, S, H, T], rescale, (Bn, S, H, T, Cd),
+                   a_limbs, b_limbs)
+
+
+def einsum_bsht_btc_bshc(A, B, rescale, a_limbs=0, b_limbs=0):
+    """out[b,s,h,c] = (rescale//2 + sum_t A[b,s,h,t] * B[b,t,c]) >> rescale; B int64."""
+    Bn, S, H, T = A.shape
+    Cd = B.shape[2]
+    assert Bn == B.shape[0] and T == B.shape[1]
+    _dev_i64(B, "B")
+    return _einsum("zkds_einsum_bsht_btc_bshc", A, B, [Bn, S, H, Cd], rescale, (Bn, S, H, T, Cd),
+                   a_limbs, b_limbs)
+
+
+def einsum_bshc_hdc_bshd(A, B, rescale, a_limbs=0, b_limbs=0):
+    """out[b,s,h,d] = (sum_c A[b,s,h,c] * B[h,d,c]) >> rescale (no rounding term); B int32."""
+    Bn, S, H, Cd = A.shape
+    D = B.shape[1]
+    assert H == B.shape[0] and Cd == B.shape[2]
+    assert B.dtype == torch.int32
+    return _einsum("zkds_einsum_bshc_hdc_bshd", A, B, [Bn, S, H, D], rescale, (Bn, S, H, D, Cd),
+                   a_limbs, b_limbs)
+
+
+# ---- RoPE ----------------------------------------------------------------------------
+
+def complex_int64_mul_broadcast(A, B, shift=42):
+    """A (batch, seq, heads, pairs, 2) times the table B (1, seq, 1, pairs, 2).
+
+    Every product keeps bits [shift, shift+64) of the 128-bit product
+    (kernel.py:373-395, int64_gemm.cu:223-272; the reference fixes shift = 42).
+    """
+    _dev_i64(A, "A")
+    _dev_i64(B, "B")
+    batch, seq, head, pairs = A.shape[0], A.shape[1], A.shape[2], A.shape[3]
+    assert B.numel() == seq * pairs * 2, "table must hold one entry per (seq, pair)"
+    C = torch.empty(A.shape, dtype=torch.int64, device=A.device)
+    with torch.cuda.device(A.device):
+        _check(lib.zkds_rope(A.data_ptr(), B.data_ptr(), C.data_ptr(), batch, seq, head, pairs,
+                             int(shift), _stream()), "complex_int64_mul_broadcast")
+    return C
+
+
+# ---- RMSNorm -------------------------------------------------------------------------
+
+_RMS_HOST_ENTRIES = 500  # length of the reference's global rms buffer (kernel.py:525)
+
+
+def rms_norm_int64_device(A, W, eps, dim):
+    """Fused RMSNorm, everything on the device: returns (C, rms) with rms int64 [M] on the GPU."""
+    _dev_i64(A, "A")
+    assert A.ndim == 2 and W.is_cuda and W.is_contiguous()
+    assert W.dtype in (torch.int32, torch.int64)
+    M, N = A.shape
+    C = torch.empty((M, N), dtype=torch.int64, device=A.device)
+    rms = torch.empty((M,), dtype=torch.int64, device=A.device)
+    with torch.cuda.device(A.device):
+        _check(lib.zkds_rms_norm(A.data_ptr(), W.data_ptr(), 32 if W.dtype == torch.int32 else 64,
+                                 C.data_ptr(), rms.data_ptr(), M, N, int(eps), int(dim), _stream()),
+               "RMS_Norm_int64")
+    return C, rms
+
+
+def RMS_Norm_int64(A, W, eps, dim):
+    """Reference surface (kernel.py:528-550): returns (C, rms_cpu)."""
+    C, rms_gpu = rms_norm_int64_device(A, W, eps, dim)
+    M = A.shape[0]
+    rms = torch.zeros((max(_RMS_HOST_ENTRIES, M),), dtype=torch.int64, device="cpu")
+    rms[:M] = rms_gpu.cpu()
+    return (C, rms)
+
+
+def rms_norm_apply(A, W, rms):
+    """C = floor(A*W / rms[row]) with a caller-provided device rms (int64_gemm.cu:365-385)."""
+    _dev_i64(A, "A")
+    _dev_i64(rms, "rms")
+    M, N = A.shape
+    C = torch.empty((M, N), dtype=torch.int64, device=A.device)
+    with torch.cuda.device(A.device):
+        _check(lib.zkds_rms_norm_apply(A.data_ptr(), W.data_ptr(),
+                                       32 if W.dtype == torch.int32 else 64, rms.data_ptr(),
+                                       C.data_ptr(), M, N, _stream()), "rms_norm_apply")
+    return C
+
+
+def saveTensor(fileName, t):
+    """Raw little-endian C-order dump, no header (kernel.py:553-565)."""
+    t = t.detach()
+    if t.device.type != "cpu":
+        t = t.cpu()
+    with open(fileName, "wb") as f:
+        f.write(t.contiguous().numpy().tobytes(order="C"))
+
+
+# ---- lookup tables --------------------------------------------------------------------
+
+LOG_TABLE_SIZE = 8
+EXP2_FRAC_LUT_Q21 = None
+EXP2_FRAC_LUT_Q19 = None
+EXP2_FRAC_LUT_Q25 = None
+EXP2_FRAC_LUT_Q23 = None
+
+
+def _host_lut(kind):
+    t = torch.zeros((2 ** LOG_TABLE_SIZE,), dtype=torch.int64, device="cpu")
+    _check(lib.zkds_lut(t.data_ptr(), kind), "zkds_lut")
+    return t
+
+
+def softmax_init_q19():
+    global EXP2_FRAC_LUT_Q19
+    EXP2_FRAC_LUT_Q19 = _host_lut(0).cuda()
+
+
+def softmax_init_q21():
+    global EXP2_FRAC_LUT_Q21
+    EXP2_FRAC_LUT_Q21 = _host_lut(1).cuda()
+
+
+def silu_init_q23():
+    global EXP2_FRAC_LUT_Q23
+    EXP2_FRAC_LUT_Q23 = _host_lut(2).cuda()
+
+
+def silu_init_q25():
+    global EXP2_FRAC_LUT_Q25
+    EXP2_FRAC_LUT_Q25 = _host_lut(3).cuda()
+
+
+def _lut_on(lut, dev, what):
+    if lut is None:
+        raise RuntimeError("call %s() first" % what)
+    return lut if lut.device == dev else lut.to(dev)
+
+
+# ---- softmax ----------------------------------------------------------------------------
+
+# The reference leaves the unnormalised weights in its input buffer R
+# (int64_gemm.cu:708,729).  Keep that side effect by default; model code that never
+# looks at R again can switch it off and save a third of the memory traffic.
+SOFTMAX_WRITES_WEIGHTS = True
+
+
+def _softmax(R, C, lut, frac, what):
+    _dev_i64(R, "R")
+    _dev_i64(C, "C")
+    T = R.shape[-1]
+    rows = R.numel() // T if T else 0
+    w = R.data_ptr() if SOFTMAX_WRITES_WEIGHTS else None
+    with torch.cuda.device(R.device):
+        _check(lib.zkds_softmax(R.data_ptr(), w, C.data_ptr(), lut.data_ptr(), rows, T, frac,
+                                _stream()), what)
+
+
+def softmax_q21(R, C):
+    _softmax(R, C, _lut_on(EXP2_FRAC_LUT_Q21, R.device, "softmax_init_q21"), 21, "softmax_q21")
+
+
+def softmax_q19(R, C):
+    _softmax(R, C, _lut_on(EXP2_FRAC_LUT_Q19, R.device, "softmax_init_q19"), 19, "softmax_q19")
+
+
+# ---- SiLU / sigmoid ---------------------------------------------------------------------
+
+def _act(R, C, lut, frac, silu, what):
+    _dev_i64(R, "R")
+    _dev_i64(C, "C")
+    with torch.cuda.device(R.device):
+        _check(lib.zkds_act(R.data_ptr(), C.data_ptr(), lut.data_ptr(), R.numel(), frac, silu,
+                            _stream()), what)
+
+
+def silu_q25(R, C):
+    _act(R, C, _lut_on(EXP2_FRAC_LUT_Q25, R.device, "silu_init_q25"), 25, 1, "silu_q25")
+
+
+def sigmoid_q25(R, C):
+    _act(R, C, _lut_on(EXP2_FRAC_LUT_Q25, R.device, "silu_init_q25"), 25, 0, "sigmoid_q25")
+
+
+def silu_q23(R, C):
+    _act(R, C, _lut_on(EXP2_FRAC_LUT_Q23, R.device, "silu_init_q23"), 23, 1, "silu_q23")
+
+
+def sigmoid_q23(R, C):
+    _act(R, C, _lut_on(EXP2_FRAC_LUT_Q23, R.device, "silu_init_q23"), 23, 0, "sigmoid_q23")
