@@ -8,9 +8,10 @@
  *     with identical names and argument lists, so that the reference's
  *     inference/kernel.py can load this library unchanged.  They return void,
  *     launch on the legacy default stream and take C `int` extents like the
- *     originals; a call whose extents would overflow 32-bit element indexing is
- *     refused (nothing is written, the status is kept for zkds_last_status()
- *     and one line goes to stderr) instead of corrupting memory.
+ *     originals.  Element indices are 64-bit inside, so tensors of 2^31 elements
+ *     and more (where the reference's `int` indices overflow) are handled.  A
+ *     rejected call writes nothing, keeps its status for zkds_last_status() and
+ *     prints one line to stderr.
  *
  *  2. zkds_* entry points: same arithmetic, 64-bit extents, an explicit stream,
  *     an int status return, and the parameters the reference hard-codes.
@@ -48,9 +49,11 @@ void zkds_shutdown(void);           /* frees the library's scratch arenas (synch
 #define ZKDS_ALGO_EXACT 1       /* CUDA-core kernel with 128-bit accumulators */
 #define ZKDS_ALGO_LIMB 2        /* tensor-core kernel or ZKDS_ERR_UNSUPPORTED */
 #define ZKDS_ALGO_MASK 3
-#define ZKDS_REMAINDER_LEGACY 4 /* R = sum & ((int)(1 << s) - 1) as the reference's device
-                                   code evaluates it: exact for s <= 31, the low 64 bits of
-                                   the sum for s >= 32.  Default: R = sum mod 2^s. */
+#define ZKDS_REMAINDER_LEGACY 4 /* R as the reference binary returns it: its mask
+                                   "(1 << s) - 1" uses a 32-bit 1 (int64_gemm.cu:22), which is
+                                   exact for s <= 31 and yields the low 32 bits of the sum for
+                                   every s >= 32 (observed with its nvcc 12.9 build on a B200).
+                                   Default: R = sum mod 2^s. */
 
 /* =============================================================================
  * Group 1 — the reference's symbols (same names, same argument lists)

@@ -18,9 +18,12 @@
  * behaviour is modelled explicitly:
  *   - a 64-bit shift by >= 64 yields 0 on the GPU (x86 masks the count);
  *   - "(1 << c_rescale) - 1" is evaluated in 32-bit int on the device
- *     (int64_gemm.cu:22,65): the shift count is clamped, so the mask is
- *     2^s-1 for s <= 31 and all-ones for s >= 32.  rmode selects between that
- *     (ORC_R_LEGACY) and the mathematical remainder sum mod 2^s (ORC_R_MATH).
+ *     (int64_gemm.cu:22,65), undefined for c_rescale >= 32.  The reference
+ *     library built with nvcc 12.9 and run on a B200 returns the mask 2^s-1 for
+ *     s <= 31 and 0xFFFFFFFF (the low 32 bits of the sum, zero-extended) for every
+ *     s >= 32 (tests/golden/ref_gpu_vectors.npz, cases gemm32_R_s32..s63).
+ *     rmode selects between that (ORC_R_LEGACY) and the mathematical remainder
+ *     sum mod 2^s (ORC_R_MATH).
  *
  * Every function cites the reference lines it follows.
  */
@@ -55,11 +58,9 @@ static inline int64_t sar128_lo(i128 v, int64_t s)
 static inline int64_t remainder_of(i128 sum, int64_t s, int rmode)
 {
     if (rmode == ORC_R_LEGACY) {
-        /* int64_gemm.cu:22 — (1 << s) - 1 in 32-bit int, count clamped on device */
-        int32_t one_shl = (s >= 0 && s <= 31) ? (int32_t)(1u << s) : 0;
-        int32_t m32 = (int32_t)((uint32_t)one_shl - 1u);
-        i128 mask = (i128)m32; /* sign-extends: all-ones for s >= 32 */
-        return (int64_t)(sum & mask);
+        /* int64_gemm.cu:22 as the reference binary behaves on a B200 */
+        uint64_t mask = (s >= 0 && s <= 31) ? ((((uint64_t)1) << s) - 1) : 0xFFFFFFFFull;
+        return (int64_t)((uint64_t)sum & mask);
     }
     if (s <= 0) return 0;
     if (s >= 64) return (int64_t)sum; /* low 64 bits of sum mod 2^s */

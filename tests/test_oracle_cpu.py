@@ -51,9 +51,7 @@ def py_gemm(A, B, a_r, b_r, s, legacy):
                 tot = sum(_tdiv(int(A[b, m, k]), a_r) * _tdiv(int(B[n, k]), b_r) for k in range(K))
                 C[b, m, n] = _wrap64(tot >> s)
                 if legacy:
-                    mask = ((1 << s) - 1) if s <= 31 else -1
-                    if s == 31:
-                        mask = 0x7FFFFFFF
+                    mask = ((1 << s) - 1) if s <= 31 else 0xFFFFFFFF   # observed on a B200
                     R[b, m, n] = _wrap64(tot & mask)
                 else:
                     R[b, m, n] = _wrap64(tot % (1 << s)) if s > 0 else 0

@@ -118,7 +118,7 @@ static int run_contraction(const Contraction& p, int a_limbs, int b_limbs, int f
     if (algo == 3) return ZKDS_ERR_ARG;
     if (p.batches < 0 || p.M < 0 || p.N < 0 || p.K < 0) return ZKDS_ERR_ARG;
     if (p.batches == 0 || p.M == 0 || p.N == 0) return ZKDS_OK;
-    if (!p.A || !p.B || !p.C) return ZKDS_ERR_ARG;
+    if (!p.C || (p.K > 0 && (!p.A || !p.B))) return ZKDS_ERR_ARG;
     if (p.a_div == 0 || p.b_div == 0) return ZKDS_ERR_ARG;
     if (p.shift < 0 || p.shift > 127) return ZKDS_ERR_ARG;
     if (p.b_bits != 32 && p.b_bits != 64) return ZKDS_ERR_ARG;

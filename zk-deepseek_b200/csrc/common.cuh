@@ -78,15 +78,14 @@ __device__ __forceinline__ int64_t sar128_lo(i128w v, int s)
 
 // remainder written next to a GEMM quotient.
 //   legacy = 0: sum mod 2^s, truncated to 64 bits
-//   legacy = 1: sum & ((int)(1 << s) - 1) as the reference's device code evaluates
-//               it (32-bit shift with clamped count): 2^s-1 for s <= 31, all ones above
+//   legacy = 1: what the reference binary returns for "sum & ((1 << s) - 1)" with a 32-bit
+//               "1" (int64_gemm.cu:22): 2^s-1 as mask for s <= 31, the low 32 bits of the
+//               sum for every s >= 32 (observed on a B200, nvcc 12.9 build)
 __device__ __forceinline__ int64_t gemm_remainder(i128w v, int s, int legacy)
 {
     if (legacy) {
-        if (s >= 32) return (int64_t)v.lo;
-        uint32_t m = (s <= 31 ? (1u << s) : 0u) - 1u;
-        int64_t m64 = (int64_t)(int32_t)m;
-        return (int64_t)(v.lo & (uint64_t)m64);
+        uint64_t m = (s >= 0 && s <= 31) ? ((1ull << s) - 1ull) : 0xFFFFFFFFull;
+        return (int64_t)(v.lo & m);
     }
     if (s <= 0) return 0;
     if (s >= 64) return (int64_t)v.lo;

@@ -34,8 +34,8 @@ ALGO_AUTO, ALGO_EXACT, ALGO_LIMB = 0, 1, 2
 REMAINDER_LEGACY = 4
 
 # Remainder flavour of int64_bmm_broadcast.  True reproduces the reference binary:
-# exact for c_rescale <= 31, the low 64 bits of the sum above that
-# (int64_gemm.cu:22 evaluates its mask in 32-bit int).  False gives sum mod 2^s.
+# exact for c_rescale <= 31, the low 32 bits of the sum above that
+# (int64_gemm.cu:22 builds its mask from a 32-bit 1).  False gives sum mod 2^s.
 LEGACY_REMAINDER = True
 # Contraction algorithm used by the functions below (ALGO_AUTO picks the tensor-core
 # limb kernel when the shape allows it).
