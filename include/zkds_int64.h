@@ -43,6 +43,11 @@ int zkds_last_cuda_error(void);     /* cudaError_t behind the last ZKDS_ERR_CUDA
 const char* zkds_status_string(int status);
 const char* zkds_version(void);
 void zkds_shutdown(void);           /* frees the library's scratch arenas (synchronises) */
+/* Health of the tensor-core kernels that have FINISHED on the current device (no sync):
+ * ZKDS_ERR_DEVICE if one of them gave up a bounded wait, ZKDS_ERR_RANGE if an operand did
+ * not fit the a_limbs/b_limbs the caller promised (the result of that call is wrong), else
+ * ZKDS_OK.  clear != 0 resets the flags. */
+int zkds_device_status(int clear);
 
 /* ---- flags of the contraction entry points ----------------------------------- */
 #define ZKDS_ALGO_AUTO 0        /* limb tensor-core kernel when it applies, else exact */

@@ -350,6 +350,8 @@ int zkds_act(const int64_t* X, int64_t* C, const int64_t* lut, int64_t n, int fr
     return finish(rc, "zkds_act");
 }
 
+int zkds_device_status(int clear) { return limb_device_status(clear); }
+
 int zkds_lut(int64_t* host_lut, int kind) { return finish(make_lut(host_lut, kind), "zkds_lut"); }
 
 // ---- the reference's 21 symbols ---------------------------------------------------

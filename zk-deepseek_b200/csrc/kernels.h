@@ -49,6 +49,12 @@ int launch_contraction_exact(const Contraction& p, cudaStream_t st);
 // counts fall outside what the kernel handles (caller then uses the exact path).
 int launch_contraction_limb(const Contraction& p, int La, int Lb, cudaStream_t st);
 
+// ZKDS_ERR_DEVICE when a tensor-core kernel reported a wait that ran out, ZKDS_ERR_RANGE
+// when an operand did not fit the limb count it was split into, else ZKDS_OK.  The flags
+// live in host-mapped memory: reading them needs no synchronisation, but they describe only
+// kernels that have finished.  clear != 0 resets them.
+int limb_device_status(int clear);
+
 // max |x / div| over a strided int64 / int32 operand, written to *out_dev (uint64)
 int launch_absmax(const void* X, int bits, int64_t batches, int64_t rows, int64_t cols,
                   int64_t sz, int64_t sr, int64_t sc, int64_t div, uint64_t* out_dev,

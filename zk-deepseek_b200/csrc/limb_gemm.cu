@@ -1,11 +1,36 @@
-// Tensor-core contraction on signed 8-bit limbs (placeholder translation unit: the
-// operand range reduction lives here; the tcgen05 kernel follows).
+// Exact int64 contraction on the 5th-generation tensor cores.
+//
+// Every operand element is written in balanced radix 256: v = sum_l d_l * 256^l with
+// signed digits d_l in [-128, 127] ("limbs").  A pre-pass stores each limb of A and B as
+// its own K-major int8 plane.  The product sum is then
+//     sum_k a*b = sum_d 256^d * sum_{i+j=d} sum_k A_i[m,k] * B_j[n,k],
+// i.e. one int8 GEMM per limb pair, accumulated per diagonal d = i + j.  The kernel keeps
+// one int32 accumulator tile per diagonal in tensor memory.  The B limb planes of a tile
+// are stacked along N in shared memory, so a single tcgen05.mma of A_i against the stack
+// covers the diagonals i .. i+Lb-1 at once: the accumulators of consecutive diagonals are
+// adjacent column ranges of tensor memory and the MMA for limb i simply starts NT columns
+// further right.  The epilogue reads the diagonals back, recombines them in 128 bits, adds
+// the rounding addend, shifts, and writes the int64 quotient (and remainder).
+//
+// One CTA computes a 128 x NT output tile: warp 0 issues TMA loads (no multicast),
+// warp 1 owns tensor memory and issues the MMAs, warps 2-5 zero the accumulators, then
+// run the epilogue.  Every wait is bounded; a wait that runs out raises a flag the host
+// reads, and the CTA leaves through the normal exit path (tensor memory released).
+//
+// Exactness bound: a diagonal sums at most min(La, Lb) * K products of magnitude <= 2^14,
+// which must stay below 2^31; the launcher refuses shapes beyond that.
+#include <cuda.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
 namespace zkds {
 
 namespace {
+
+// ------------------------------------------------------------------------------------
+// operand range and limb split
+// ------------------------------------------------------------------------------------
 
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -24,12 +49,476 @@ absmax_kernel(const T* X, int64_t rows, int64_t cols, int64_t sz, int64_t sr, in
         int64_t v = (int64_t)x[r * sr + c * sc];
         if (div != 1) v = v / div;
         uint64_t a = v < 0 ? (uint64_t)0 - (uint64_t)v : (uint64_t)v;
-        // balanced digits reach further down than up: -128 * 256^k needs no extra limb
+        // balanced digits reach one further down than up
         if (v < 0 && a) a -= 1;
         best = a > best ? a : best;
     }
     best = warp_max_u64(best);
     if ((threadIdx.x & 31) == 0 && best) atomicMax((unsigned long long*)out, (unsigned long long)best);
+}
+
+// planes[l][z][r][Kp] (int8) <- X[z*sz + r*sr + k*sk] / div, one 16-byte chunk per thread.
+// A value the L limbs cannot hold raises *overflow.
+template <typename T>
+__global__ void __launch_bounds__(256)
+split_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, int64_t rows, int64_t K,
+             int64_t Kp, int64_t sz, int64_t sr, int64_t sk, int64_t div, int64_t plane_stride,
+             unsigned* overflow)
+{
+    const int64_t chunks = Kp >> 4;
+    const int64_t total = rows * chunks;
+    const int64_t z = blockIdx.y;
+    const T* x = X + z * sz;
+    const bool k_fast = (sk == 1);
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total;
+         t += (int64_t)gridDim.x * blockDim.x) {
+        int64_t r, ch;
+        if (k_fast) { r = t / chunks; ch = t - r * chunks; }
+        else { ch = t / rows; r = t - ch * rows; }
+        const int64_t k0 = ch << 4;
+        uint32_t w[9][4];
+#pragma unroll
+        for (int l = 0; l < 9; ++l)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) w[l][q] = 0;
+        bool ovf = false;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            int64_t k = k0 + j;
+            int64_t v = 0;
+            if (k < K) {
+                v = (int64_t)x[r * sr + k * sk];
+                if (div != 1) v = v / div;
+            }
+#pragma unroll
+            for (int l = 0; l < 9; ++l) {
+                if (l < L) {
+                    w[l][j >> 2] |= (uint32_t)(v & 0xFF) << ((j & 3) * 8);
+                    v = (v >> 8) + ((v >> 7) & 1);
+                }
+            }
+            ovf |= (v != 0);
+        }
+        int8_t* dst = planes + (z * rows + r) * Kp + k0;
+#pragma unroll
+        for (int l = 0; l < 9; ++l)
+            if (l < L)
+                *reinterpret_cast<uint4*>(dst + l * plane_stride) =
+                    make_uint4(w[l][0], w[l][1], w[l][2], w[l][3]);
+        if (ovf) *overflow = 1u;
+    }
+}
+
+// ------------------------------------------------------------------------------------
+// PTX wrappers
+// ------------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p)
+{
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+// Bounded wait.  Returns false when the limit ran out or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag)
+{
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        if (mbar_try(bar, parity)) return true;
+        if ((it & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"((uint64_t)map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),
+                 "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+                 : "memory");
+}
+
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                        uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n"
+        "}\n"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, int32_t (&v)[8])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_st8_zero(uint32_t taddr)
+{
+    const uint32_t z = 0;
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr), "r"(z)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile, 128-byte rows, 128-byte swizzle: 8-row groups are 1024 bytes apart
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;               // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;     // stride byte offset
+    d |= (uint64_t)1 << 46;               // descriptor version
+    d |= (uint64_t)2 << 61;               // SWIZZLE_128B
+    return d;
+}
+
+// ------------------------------------------------------------------------------------
+// the kernel
+// ------------------------------------------------------------------------------------
+
+constexpr int kTileM = 128;
+constexpr int kBlockK = 128;   // bytes (= int8 elements) of K per pipeline stage
+constexpr int kThreads = 192;
+
+struct LimbParams {
+    int La, Lb, NT, stages;
+    int kblocks;
+    uint32_t tmem_cols;       // power of two >= (La + Lb - 1) * NT
+    int64_t M, N, batches;
+    int64_t a_rows_per_limb;  // batches * M
+    int64_t b_rows_per_limb;  // nbB * N
+    int b_batched;            // 1: B differs per batch
+    int64_t* C;
+    int64_t* R;
+    int64_t c_sz, c_sm;
+    int64_t addend;
+    int shift, r_legacy;
+    int* error_flag;          // host-mapped
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const LimbParams p)
+{
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bars[2 * 8 + 2];
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t a_bytes = (uint32_t)p.La * kTileM * kBlockK;
+    const uint32_t b_bytes = (uint32_t)p.Lb * p.NT * kBlockK;
+    const uint32_t stage_bytes = a_bytes + b_bytes;
+    const uint32_t bar_full = smem_u32(&bars[0]);
+    const uint32_t bar_empty = smem_u32(&bars[8]);
+    const uint32_t bar_zeroed = smem_u32(&bars[16]);
+    const uint32_t bar_accum = smem_u32(&bars[17]);
+
+    const int64_t m0 = (int64_t)blockIdx.x * kTileM;
+    const int64_t n0 = (int64_t)blockIdx.y * p.NT;
+    const int64_t z = blockIdx.z;
+    const int D = p.La + p.Lb - 1;
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        mbar_init(bar_zeroed, 4);
+        mbar_init(bar_accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(&s_tmem_base), p.tmem_cols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem_base;
+    volatile int* abort_flag = &s_abort;
+
+    if (warp == 0) {
+        // ---- TMA producer -------------------------------------------------------------
+        if (lane == 0) {
+            const int64_t zb = p.b_batched ? z : 0;
+            int armed = 0;
+            for (int kb = 0; kb < p.kblocks; ++kb) {
+                const int s = kb % p.stages;
+                const uint32_t par = ((kb / p.stages) & 1) ^ 1;
+                if (!mbar_wait(bar_empty + 8 * s, par, abort_flag)) break;
+                const uint32_t full = bar_full + 8 * s;
+                mbar_expect_tx(full, stage_bytes);
+                const uint32_t sa = smem_base + s * stage_bytes;
+                const uint32_t sb = sa + a_bytes;
+                for (int i = 0; i < p.La; ++i)
+                    tma_load_2d(sa + i * (kTileM * kBlockK), &tmA, kb * kBlockK,
+                                (int)(i * p.a_rows_per_limb + z * p.M + m0), full);
+                for (int j = 0; j < p.Lb; ++j)
+                    tma_load_2d(sb + j * (p.NT * kBlockK), &tmB, kb * kBlockK,
+                                (int)(j * p.b_rows_per_limb + zb * p.N + n0), full);
+                armed = kb + 1;
+            }
+            if (*abort_flag) {
+                // leave no copy in flight: wait (bounded) for every stage that was armed and
+                // that no consumer waited for
+                for (int kb = (armed > p.stages ? armed - p.stages : 0); kb < armed; ++kb)
+                    for (uint32_t it = 0; it < kSpinLimit; ++it)
+                        if (mbar_try(bar_full + 8 * (kb % p.stages), (kb / p.stages) & 1)) break;
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer ---------------------------------------------------------------
+        if (lane == 0) {
+            const uint32_t idesc = (2u << 4)                               // int32 accumulators
+                                   | (1u << 7) | (1u << 10)                 // signed 8-bit A and B
+                                   | ((uint32_t)((p.Lb * p.NT) >> 3) << 17)  // N
+                                   | ((uint32_t)(kTileM >> 4) << 24);        // M
+            bool ok = mbar_wait(bar_zeroed, 0, abort_flag);
+            tc_fence_after();
+            for (int kb = 0; ok && kb < p.kblocks; ++kb) {
+                const int s = kb % p.stages;
+                ok = mbar_wait(bar_full + 8 * s, (kb / p.stages) & 1, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t sa = smem_base + s * stage_bytes;
+                const uint64_t bdesc0 = smem_desc_sw128(sa + a_bytes);
+#pragma unroll
+                for (int ks = 0; ks < kBlockK / 32; ++ks) {
+                    for (int i = 0; i < p.La; ++i) {
+                        const uint64_t adesc = smem_desc_sw128(sa + i * (kTileM * kBlockK)) + (uint64_t)(ks * 2);
+                        umma_i8(tmem + (uint32_t)(i * p.NT), adesc, bdesc0 + (uint64_t)(ks * 2), idesc, 1u);
+                    }
+                }
+                umma_commit(bar_empty + 8 * s);
+            }
+            umma_commit(bar_accum);
+        }
+    } else {
+        // ---- accumulator zeroing, then epilogue -------------------------------------------
+        const int q = warp & 3;  // tensor-memory lane quarter this warp may touch
+        const uint32_t tq = tmem + ((uint32_t)(q * 32) << 16);
+        for (int c = 0; c < D * p.NT; c += 8) tmem_st8_zero(tq + (uint32_t)c);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_zeroed);
+
+        const bool ok = mbar_wait(bar_accum, 0, abort_flag);
+        tc_fence_after();
+        const int64_t m = m0 + q * 32 + lane;
+        int64_t* crow = p.C + z * p.c_sz + m * p.c_sm;
+        int64_t* rrow = p.R ? p.R + z * p.c_sz + m * p.c_sm : nullptr;
+        const bool row_ok = ok && m < p.M;
+        const bool vec_ok = ((((uintptr_t)p.C | (uintptr_t)p.R) & 15) == 0) && ((p.c_sm & 1) == 0) &&
+                            ((p.c_sz & 1) == 0);
+        const int groups = (D + 3) >> 2;
+        for (int nc = 0; ok && nc < p.NT; nc += 8) {
+            i128w sum[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) sum[c] = make_i128(p.addend);
+            for (int g = 0; g < groups; ++g) {
+                int32_t a[4][8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (4 * g + j < D) tmem_ld8(tq + (uint32_t)((4 * g + j) * p.NT + nc), a[j]);
+                    else {
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) a[j][c] = 0;
+                    }
+                }
+                tmem_ld_wait();
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    // four diagonals fit one int64: |a| < 2^31, weights up to 2^24
+                    int64_t v = (int64_t)a[0][c] + ((int64_t)a[1][c] << 8) + ((int64_t)a[2][c] << 16) +
+                                ((int64_t)a[3][c] << 24);
+                    i128w t;  // v * 2^(32 g)
+                    if (g == 0) { t.lo = (uint64_t)v; t.hi = v >> 63; }
+                    else if (g == 1) { t.lo = (uint64_t)v << 32; t.hi = v >> 32; }
+                    else if (g == 2) { t.lo = 0; t.hi = v; }
+                    else { t.lo = 0; t.hi = (int64_t)((uint64_t)v << 32); }
+                    sum[c] = add128(sum[c], t);
+                }
+            }
+            if (row_ok) {
+                int64_t cv[8], rv[8];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    cv[c] = sar128_lo(sum[c], p.shift);
+                    rv[c] = gemm_remainder(sum[c], p.shift, p.r_legacy);
+                }
+                const int64_t n = n0 + nc;
+                if (vec_ok && n + 8 <= p.N) {
+#pragma unroll
+                    for (int c = 0; c < 8; c += 2) {
+                        *reinterpret_cast<longlong2*>(crow + n + c) = make_longlong2(cv[c], cv[c + 1]);
+                        if (rrow) *reinterpret_cast<longlong2*>(rrow + n + c) = make_longlong2(rv[c], rv[c + 1]);
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        if (n + c < p.N) {
+                            crow[n + c] = cv[c];
+                            if (rrow) rrow[n + c] = rv[c];
+                        }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) tmem_dealloc(tmem, p.tmem_cols);
+    if (threadIdx.x == 0 && s_abort) *p.error_flag = 1;
+}
+
+// ------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// planes seen as a 2-D uint8 tensor [rows_total][Kp], box = box_rows x 128 bytes, 128B swizzle
+bool make_plane_map(CUtensorMap* map, void* base, int64_t rows_total, int64_t Kp, int box_rows)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    cuuint64_t gdim[2] = {(cuuint64_t)Kp, (cuuint64_t)rows_total};
+    cuuint64_t gstride[1] = {(cuuint64_t)Kp};
+    cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, gdim, gstride, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct DeviceFlags {
+    int* host = nullptr;      // mapped, host view
+    int* dev = nullptr;       // device view of the same word
+    unsigned* overflow = nullptr;  // second mapped word
+    unsigned* overflow_dev = nullptr;
+};
+DeviceFlags g_flags[64];
+
+DeviceFlags* flags_for_device()
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    DeviceFlags& f = g_flags[dev];
+    if (!f.host) {
+        int* h = nullptr;
+        if (cudaHostAlloc((void**)&h, 64, cudaHostAllocMapped) != cudaSuccess) return nullptr;
+        h[0] = 0;
+        h[1] = 0;
+        int* d = nullptr;
+        if (cudaHostGetDevicePointer((void**)&d, h, 0) != cudaSuccess) return nullptr;
+        f.host = h;
+        f.dev = d;
+        f.overflow = (unsigned*)(h + 1);
+        f.overflow_dev = (unsigned*)(d + 1);
+    }
+    return &f;
+}
+
+template <typename T>
+int launch_split_t(const T* X, int8_t* planes, int L, int64_t nb, int64_t rows, int64_t K, int64_t Kp,
+                   int64_t sz, int64_t sr, int64_t sk, int64_t div, unsigned* overflow, cudaStream_t st)
+{
+    int64_t total = rows * (Kp >> 4);
+    int64_t bx = (total + 255) / 256;
+    int64_t cap = (int64_t)sm_count() * 16;
+    if (bx > cap) bx = cap;
+    if (nb > 65535) return ZKDS_ERR_RANGE;
+    dim3 grid((unsigned)bx, (unsigned)nb);
+    split_kernel<T><<<grid, 256, 0, st>>>(X, planes, L, rows, K, Kp, sz, sr, sk, div, nb * rows * Kp, overflow);
+    return check_launch();
 }
 
 }  // namespace
@@ -52,6 +541,96 @@ int launch_absmax(const void* X, int bits, int64_t batches, int64_t rows, int64_
     return check_launch();
 }
 
-int launch_contraction_limb(const Contraction&, int, int, cudaStream_t) { return ZKDS_ERR_UNSUPPORTED; }
+int limb_device_status(int clear)
+{
+    DeviceFlags* f = flags_for_device();
+    if (!f) return ZKDS_OK;
+    int rc = ZKDS_OK;
+    if (f->host[0]) rc = ZKDS_ERR_DEVICE;
+    else if (*f->overflow) rc = ZKDS_ERR_RANGE;
+    if (clear) { f->host[0] = 0; *f->overflow = 0; }
+    return rc;
+}
+
+int launch_contraction_limb(const Contraction& p, int La, int Lb, cudaStream_t st)
+{
+    if (La < 1 || Lb < 1 || La > 9 || Lb > 9) return ZKDS_ERR_UNSUPPORTED;
+    if (p.K <= 0) return ZKDS_ERR_UNSUPPORTED;
+    const int D = La + Lb - 1;
+    const int pairs = La < Lb ? La : Lb;
+    if ((int64_t)pairs * p.K >= 131072) return ZKDS_ERR_UNSUPPORTED;  // int32 diagonal bound
+    // tile width: the B stack must fit one MMA (<= 256 columns), the diagonals tensor memory
+    // (<= 512 columns), and two pipeline stages shared memory
+    const size_t smem_max = 227 * 1024 - 4096;  // static barriers + alignment slack stay below the opt-in limit
+    int NT = 0, stages = 0;
+    for (int cand : {128, 64, 32, 16}) {
+        if (Lb * cand > 256 || D * cand > 512) continue;
+        size_t stage = (size_t)La * kTileM * kBlockK + (size_t)Lb * cand * kBlockK;
+        int s = (int)(smem_max / stage);
+        if (s < 2) continue;
+        NT = cand;
+        stages = s > 8 ? 8 : s;
+        break;
+    }
+    if (!NT) return ZKDS_ERR_UNSUPPORTED;
+    // shrink the tile for narrow outputs (fewer wasted columns)
+    while (NT > 16 && p.N <= NT / 2) NT /= 2;
+    {
+        size_t stage = (size_t)La * kTileM * kBlockK + (size_t)Lb * NT * kBlockK;
+        int s = (int)(smem_max / stage);
+        stages = s > 8 ? 8 : s;
+    }
+    const int64_t Kp = (p.K + 15) & ~(int64_t)15;
+    const int64_t nbB = p.b_sz ? p.batches : 1;
+    const int64_t a_rows = p.batches * p.M, b_rows = nbB * p.N;
+    if (a_rows * La > 0x7fffff00ll || b_rows * Lb > 0x7fffff00ll || Kp > 0x7fffff00ll) return ZKDS_ERR_UNSUPPORTED;
+    const int64_t mt = (p.M + kTileM - 1) / kTileM, nt = (p.N + NT - 1) / NT;
+    if (mt > 0x7fffffffll || nt > 65535 || p.batches > 65535) return ZKDS_ERR_UNSUPPORTED;
+
+    DeviceFlags* fl = flags_for_device();
+    if (!fl) return ZKDS_ERR_WORKSPACE;
+    int8_t* pa = (int8_t*)workspace((size_t)La * a_rows * Kp + 1024, 0);
+    int8_t* pb = (int8_t*)workspace((size_t)Lb * b_rows * Kp + 1024, 1);
+    if (!pa || !pb) return ZKDS_ERR_WORKSPACE;
+
+    int rc = launch_split_t<int64_t>(p.A, pa, La, p.batches, p.M, p.K, Kp, p.a_sz, p.a_sm, 1, p.a_div,
+                                     fl->overflow_dev, st);
+    if (rc != ZKDS_OK) return rc;
+    if (p.b_bits == 32)
+        rc = launch_split_t<int32_t>((const int32_t*)p.B, pb, Lb, nbB, p.N, p.K, Kp, p.b_sz, p.b_sn, p.b_sk,
+                                     p.b_div, fl->overflow_dev, st);
+    else
+        rc = launch_split_t<int64_t>((const int64_t*)p.B, pb, Lb, nbB, p.N, p.K, Kp, p.b_sz, p.b_sn, p.b_sk,
+                                     p.b_div, fl->overflow_dev, st);
+    if (rc != ZKDS_OK) return rc;
+
+    CUtensorMap tmA, tmB;
+    if (!make_plane_map(&tmA, pa, (int64_t)La * a_rows, Kp, kTileM)) return ZKDS_ERR_UNSUPPORTED;
+    if (!make_plane_map(&tmB, pb, (int64_t)Lb * b_rows, Kp, NT)) return ZKDS_ERR_UNSUPPORTED;
+
+    LimbParams lp{};
+    lp.La = La; lp.Lb = Lb; lp.NT = NT; lp.stages = stages;
+    lp.kblocks = (int)((Kp + kBlockK - 1) / kBlockK);
+    uint32_t cols = 32;
+    while (cols < (uint32_t)(D * NT)) cols <<= 1;
+    lp.tmem_cols = cols;
+    lp.M = p.M; lp.N = p.N; lp.batches = p.batches;
+    lp.a_rows_per_limb = a_rows; lp.b_rows_per_limb = b_rows;
+    lp.b_batched = p.b_sz ? 1 : 0;
+    lp.C = p.C; lp.R = p.R; lp.c_sz = p.c_sz; lp.c_sm = p.c_sm;
+    lp.addend = p.addend; lp.shift = p.shift; lp.r_legacy = p.r_legacy;
+    lp.error_flag = fl->dev;
+
+    size_t stage = (size_t)La * kTileM * kBlockK + (size_t)Lb * NT * kBlockK;
+    size_t smem = stage * stages + 1024;
+    // more than half the shared memory per CTA keeps one CTA per SM, so its tensor-memory
+    // allocation can never wait for a co-resident CTA
+    if (smem < 120 * 1024) smem = 120 * 1024;
+    ZKDS_CUDA(cudaFuncSetAttribute(limb_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)(227 * 1024 - 3072)));
+    dim3 grid((unsigned)mt, (unsigned)nt, (unsigned)p.batches);
+    limb_gemm_kernel<<<grid, kThreads, smem, st>>>(tmA, tmB, lp);
+    return check_launch();
+}
 
 }  // namespace zkds
