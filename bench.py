@@ -1,0 +1,338 @@
+"""Benchmark of the int64 fixed-point hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+Prints ONE JSON line (rank 0).  A "step" is one pass of the hot path over one batch of
+seeded synthetic input.  `value` is measured with the inputs resident in HBM; `e2e` is
+the same metric through the drop-in kernel module with host buffers (pinned host ->
+device copy of the step's input and device -> host copy of its result inside the timed
+region).  `roofline` describes the dominant kernel, timed live with CUDA events on its
+own stream; `cpu_baseline` is the CPU oracle (an OpenMP int128 restatement of the
+reference's CUDA kernels, which have no CPU implementation of their own) timed on the
+host cores on a bounded sample of the same workload.
+
+--impl reference runs that CPU restatement alone, on all host threads, and prints the
+same line shape with "impl": "reference".
+"""
+import argparse
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+PKG = "zk-deepseek_b200"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+                for n, v in zip(names, r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except (ValueError, IndexError):
+                continue
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------------------------
+# workloads
+# --------------------------------------------------------------------------------------------
+
+class GemmWorkload:
+    """One bit-exact int64 GEMM of a large dense projection (the `wo` shape of the MLA block,
+    inference/model.py:722): X int64 [4096, 16384] uniform in +-2^20, W int32 [7168, 16384]
+    uniform in +-2^15, Y = (X W^T) >> 16 with a 128-bit sum.  Each rank runs its own batch of
+    4096 tokens (weak scaling, no collective on the path)."""
+    name = "gemm_wo_4096x16384x7168"
+    metric = "int64_gemm_gops"
+    unit = "Gop/s"
+    M, K, N, SHIFT = 4096, 16384, 7168, 16
+    A_BITS, W_BITS = 20, 15
+
+    def __init__(self, torch, k, dev, rank):
+        import numpy as np
+        self.torch, self.k, self.dev, self.np = torch, k, dev, np
+        g = torch.Generator().manual_seed(1000 + rank)
+        self.X_host = torch.randint(-2**self.A_BITS, 2**self.A_BITS, (1, self.M, self.K),
+                                    generator=g, dtype=torch.int64).pin_memory()
+        gw = torch.Generator().manual_seed(7)
+        self.W_host = torch.randint(-2**self.W_BITS, 2**self.W_BITS, (self.N, self.K), generator=gw,
+                                    dtype=torch.int32)
+        self.X = self.X_host.to(dev)
+        self.W = self.W_host.to(dev)
+        self.planes = k.WeightPlanes(self.W)          # static weights: split once
+        self.a_limbs = 3                               # |x| < 2^20 fits three signed 8-bit limbs
+        self.C_host = torch.empty((1, self.M, self.N), dtype=torch.int64).pin_memory()
+        self.X_dev2 = torch.empty_like(self.X)
+        self.ops = 2.0 * self.M * self.N * self.K
+        self.launches_per_step = 2                     # limb split of X + tensor-core kernel
+        self.units = self.ops
+
+    def config(self):
+        return {"workload": self.name, "M": self.M, "K": self.K, "N": self.N, "shift": self.SHIFT,
+                "x_range": "+-2^20", "w_range": "+-2^15 int32", "a_limbs": self.a_limbs,
+                "w_limbs": self.planes.limbs, "weights": "limb planes prepared once",
+                "l2": "inputs larger than L2 (X 537 MB, W planes %d MB)"
+                      % (self.planes.limbs * self.N * self.K >> 20)}
+
+    def step(self):
+        return self.k.linear_prepared(self.X, self.planes, self.SHIFT, a_limbs=self.a_limbs)
+
+    def step_e2e(self):
+        self.X_dev2.copy_(self.X_host, non_blocking=True)
+        C = self.k.linear_prepared(self.X_dev2, self.planes, self.SHIFT, a_limbs=self.a_limbs)
+        self.C_host.copy_(C, non_blocking=True)
+        return C
+
+    def e2e_bytes(self):
+        return self.X_host.numel() * 8, self.C_host.numel() * 8
+
+    def value(self, seconds_per_step, world):
+        return self.ops * world / seconds_per_step / 1e9
+
+    def roofline(self, kernel_ms, peaks):
+        int8_peak = 2.0 * peaks["bf16_tflops"]         # int8 tcgen05 rate is twice the bf16 rate
+        pairs = self.a_limbs * self.planes.limbs
+        achieved = pairs * self.ops / (kernel_ms * 1e-3) / 1e12
+        return {"bound": "tensor", "kernel": "limb_gemm_kernel", "achieved": round(achieved, 1),
+                "peak": round(int8_peak, 1), "unit": "TFLOP/s", "frac": round(achieved / int8_peak, 4),
+                "traffic": None, "kernel_ms": round(kernel_ms, 4), "limb_pairs": pairs,
+                "note": "int8 tensor ops = limb pairs x 2MNK; peak = 2 x cuBLAS bf16 burst (%s)"
+                        % peaks["source"]}
+
+    def check(self, orc):
+        """bit-exact against the CPU oracle on a row sample"""
+        C = self.step()[0, :8].cpu().numpy()
+        want, _ = orc.gemm(self.X_host[:, :8].numpy(), self.W_host.numpy(), 1, 1, self.SHIFT)
+        return int((C != want[0]).sum())
+
+    @staticmethod
+    def cpu_sample(orc, np, seconds, rank=0):
+        """the same GEMM on a bounded row sample; returns (Gop/s, description)"""
+        K, N = GemmWorkload.K, GemmWorkload.N
+        rng = np.random.default_rng(7)
+        W = rng.integers(-2**15, 2**15, (N, K), dtype=np.int64).astype(np.int32)
+        X = rng.integers(-2**20, 2**20, (1, 4, K), dtype=np.int64)
+        t0 = time.time()
+        orc.gemm(X, W, 1, 1, 16)
+        per_row = (time.time() - t0) / 4
+        rows = int(max(4, min(4096, seconds / max(per_row, 1e-6))))
+        X = rng.integers(-2**20, 2**20, (1, rows, K), dtype=np.int64)
+        t0 = time.time()
+        orc.gemm(X, W, 1, 1, 16)
+        dt = time.time() - t0
+        return 2.0 * rows * N * K / dt / 1e9, "%d of 4096 rows of X against the full W" % rows, dt
+
+
+class GemmProfWorkload(GemmWorkload):
+    """Smaller GEMM of the same kernel for profiler captures (inputs still exceed L2)."""
+    name = "gemm_4096x8192x4096"
+    M, K, N = 4096, 8192, 4096
+
+    @staticmethod
+    def cpu_sample(orc, np, seconds, rank=0):
+        return GemmWorkload.cpu_sample(orc, np, seconds, rank)
+
+
+WORKLOADS = {"gemm": GemmWorkload, "gemm_prof": GemmProfWorkload}
+DEFAULT_WORKLOAD = "gemm"
+
+
+# --------------------------------------------------------------------------------------------
+
+def run_reference(args, rank, world):
+    """The reference has no CPU implementation of this path (its kernels are CUDA only); the
+    CPU arm is the OpenMP int128 oracle on every host thread, on a bounded sample per step."""
+    if rank != 0:
+        return
+    import numpy as np
+    from oracle import oracle as orc
+    orc.build()
+    wl = WORKLOADS[args.workload]
+    vals = []
+    budget = 60.0 / max(1, args.steps + args.warmup)
+    desc = ""
+    for i in range(args.warmup + args.steps):
+        v, desc, dt = wl.cpu_sample(orc, np, min(budget, 10.0))
+        if i >= args.warmup:
+            vals.append((v, dt))
+    value = statistics.mean(v for v, _ in vals)
+    line = {"impl": "reference", "metric": wl.metric, "value": round(value, 3), "unit": wl.unit,
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(1e3 * statistics.mean(d for _, d in vals), 3),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int64",
+            "data": "synthetic", "config": {"workload": wl.name},
+            "cpu_baseline": {"value": round(value, 3), "unit": wl.unit, "cores": orc.num_threads(),
+                             "kind": "port", "sample": desc},
+            "e2e": {"value": round(value, 3), "unit": wl.unit, "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    k = importlib.import_module(PKG + ".kernel")
+    peaks = measured_peaks()
+    wl = WORKLOADS[args.workload](torch, k, dev, rank)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing ------------------------------------------------------------
+    for _ in range(args.warmup):
+        wl.step()
+    k.device_status()
+    k.kernel_timing(True)
+    kernel_ms = []
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        wl.step()
+    ev1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    elapsed = ev0.elapsed_time(ev1) * 1e-3
+    # per-launch duration of the dominant kernel, CUDA events recorded around it on its stream
+    for _ in range(min(args.steps, 10)):
+        wl.step()
+        kernel_ms.append(k.last_kernel_ms())
+    k.kernel_timing(False)
+    k.device_status()
+    t = torch.tensor([elapsed], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    sec_per_step = float(t.item()) / args.steps
+
+    # ---- end to end through the drop-in module with host buffers -------------------------------
+    for _ in range(3):
+        wl.step_e2e()
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        wl.step_e2e()
+    ev1.record()
+    barrier()
+    t = torch.tensor([ev0.elapsed_time(ev1) * 1e-3], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_sec = float(t.item()) / args.steps
+    h2d, d2h = wl.e2e_bytes()
+
+    if rank == 0:
+        from oracle import oracle as orc
+        orc.build()
+        mismatches = wl.check(orc)
+        cpu_v, cpu_desc, _ = (wl.cpu_sample(orc, np, args.cpu_seconds)
+                                if world == 1 and args.cpu_seconds > 0 else (None, None, 0))
+        line = {"metric": wl.metric, "value": round(wl.value(sec_per_step, world), 2), "unit": wl.unit,
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": round(sec_per_step * 1e3, 4), "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
+                "config": wl.config(),
+                "e2e": {"value": round(wl.value(e2e_sec, world), 2), "unit": wl.unit,
+                        "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                        "ms_per_step": round(e2e_sec * 1e3, 4)},
+                "gpu_launches": wl.launches_per_step * args.steps,
+                "roofline": wl.roofline(statistics.mean(kernel_ms), peaks),
+                "clocks": clocks, "mismatched_words_vs_oracle": mismatches}
+        if cpu_v is not None:
+            line["cpu_baseline"] = {"value": round(cpu_v, 3), "unit": wl.unit,
+                                    "cores": orc.num_threads(), "kind": "port", "sample": cpu_desc}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -163,6 +163,30 @@ int zkds_softmax(const int64_t* X, int64_t* weights_out, int64_t* C, const int64
 int zkds_act(const int64_t* X, int64_t* C, const int64_t* lut, int64_t n, int frac, int silu,
              void* stream);
 
+/* ---- static operands prepared once (no counterpart in the reference, which re-reads its
+ * int32/int64 weights in every call, int64_gemm.cu:25,68) ------------------------------------
+ * zkds_planes_create splits W[z*s_batch + n*s_row + k*s_k] / div (z < nb, n < rows, k < K;
+ * bits 32 or 64) into signed 8-bit limb planes kept on the device until zkds_planes_destroy.
+ * limbs = 0 measures the range (one reduction and a host synchronisation).  Allocates with
+ * cudaMalloc. */
+int zkds_planes_create(const void* W, int bits, int64_t nb, int64_t rows, int64_t K, int64_t s_batch,
+                       int64_t s_row, int64_t s_k, int64_t div, int limbs, void** out, void* stream);
+int zkds_planes_limbs(const void* planes);
+int zkds_planes_destroy(void* planes);
+/* C[z][m][n] = (addend + sum_k (A[z*a_s_batch + m*a_s_row + k] / a_rescale) * W(z or 0, n, k)) >> shift
+ * on the tensor-core kernel, W given as prepared planes (N and K come from them; b_batched:
+ * W differs per batch z).  R may be null. */
+int zkds_contraction_prepared(const int64_t* A, int64_t a_s_batch, int64_t a_s_row, const void* planes,
+                              int b_batched, int64_t* C, int64_t* R, int64_t c_s_batch, int64_t c_s_row,
+                              int64_t batches, int64_t M, int64_t a_rescale, int64_t addend, int64_t shift,
+                              int a_limbs, int flags, void* stream);
+
+/* CUDA-event timing of the tensor-core kernel alone: zkds_timing(1) makes every later
+ * contraction record an event pair around that kernel on its stream; zkds_last_kernel_ms
+ * waits for the most recent pair and returns its duration (< 0 if there is none). */
+void zkds_timing(int enable);
+float zkds_last_kernel_ms(void);
+
 /* Replaces the four *_init_* functions.  HOST table of 256 entries.
  * kind: 0 softmax Q19, 1 softmax Q21, 2 silu Q23, 3 silu Q25. */
 int zkds_lut(int64_t* host_lut, int kind);

@@ -99,30 +99,25 @@ static void free_arenas()
     cudaSetDevice(cur);
 }
 
-// smallest number of balanced signed 8-bit limbs (digits in [-128,127]) covering |v| <= maxabs
-static int limbs_for(uint64_t maxabs)
-{
-    unsigned __int128 cover = 0, w = 1;
-    for (int L = 1; L <= 9; ++L) {
-        cover += (unsigned __int128)127 * w;
-        w <<= 8;
-        if ((unsigned __int128)maxabs <= cover) return L;
-    }
-    return 10;
-}
+struct PlanesHandle {
+    Planes pl;
+    int device;
+    int b_bits;
+};
 
 static int run_contraction(const Contraction& p, int a_limbs, int b_limbs, int flags,
-                           cudaStream_t st)
+                           cudaStream_t st, const Planes* pre_b = nullptr)
 {
     const int algo = flags & ZKDS_ALGO_MASK;
     if (algo == 3) return ZKDS_ERR_ARG;
     if (p.batches < 0 || p.M < 0 || p.N < 0 || p.K < 0) return ZKDS_ERR_ARG;
     if (p.batches == 0 || p.M == 0 || p.N == 0) return ZKDS_OK;
-    if (!p.C || (p.K > 0 && (!p.A || !p.B))) return ZKDS_ERR_ARG;
+    if (!p.C || (p.K > 0 && (!p.A || (!p.B && !pre_b)))) return ZKDS_ERR_ARG;
     if (p.a_div == 0 || p.b_div == 0) return ZKDS_ERR_ARG;
     if (p.shift < 0 || p.shift > 127) return ZKDS_ERR_ARG;
     if (p.b_bits != 32 && p.b_bits != 64) return ZKDS_ERR_ARG;
-    if (algo == ZKDS_ALGO_EXACT) return launch_contraction_exact(p, st);
+    if (algo == ZKDS_ALGO_EXACT) return pre_b ? ZKDS_ERR_ARG : launch_contraction_exact(p, st);
+    if (pre_b) b_limbs = pre_b->L;
 
     if (a_limbs <= 0 || b_limbs <= 0) {
         uint64_t* d = (uint64_t*)workspace(2 * sizeof(uint64_t), 5);
@@ -131,17 +126,19 @@ static int run_contraction(const Contraction& p, int a_limbs, int b_limbs, int f
         int rc = launch_absmax(p.A, 64, p.batches, p.M, p.K, p.a_sz, p.a_sm, 1, p.a_div, d, st);
         if (rc != ZKDS_OK) return rc;
         // B may be shared by every batch (b_sz == 0)
-        rc = launch_absmax(p.B, p.b_bits, p.b_sz ? p.batches : 1, p.N, p.K, p.b_sz, p.b_sn, p.b_sk,
-                           p.b_div, d + 1, st);
-        if (rc != ZKDS_OK) return rc;
+        if (b_limbs <= 0) {
+            rc = launch_absmax(p.B, p.b_bits, p.b_sz ? p.batches : 1, p.N, p.K, p.b_sz, p.b_sn, p.b_sk,
+                               p.b_div, d + 1, st);
+            if (rc != ZKDS_OK) return rc;
+        }
         uint64_t h[2];
         ZKDS_CUDA(cudaMemcpyAsync(h, d, sizeof(h), cudaMemcpyDeviceToHost, st));
         ZKDS_CUDA(cudaStreamSynchronize(st));
-        if (a_limbs <= 0) a_limbs = limbs_for(h[0]);
-        if (b_limbs <= 0) b_limbs = limbs_for(h[1]);
+        if (a_limbs <= 0) a_limbs = limbs_needed(h[0]);
+        if (b_limbs <= 0) b_limbs = limbs_needed(h[1]);
     }
-    int rc = launch_contraction_limb(p, a_limbs, b_limbs, st);
-    if (rc == ZKDS_ERR_UNSUPPORTED && algo == ZKDS_ALGO_AUTO) rc = launch_contraction_exact(p, st);
+    int rc = launch_contraction_limb(p, a_limbs, b_limbs, pre_b, st);
+    if (rc == ZKDS_ERR_UNSUPPORTED && algo == ZKDS_ALGO_AUTO && !pre_b) rc = launch_contraction_exact(p, st);
     return rc;
 }
 
@@ -351,6 +348,82 @@ int zkds_act(const int64_t* X, int64_t* C, const int64_t* lut, int64_t n, int fr
 }
 
 int zkds_device_status(int clear) { return limb_device_status(clear); }
+void zkds_timing(int enable) { limb_timing_enable(enable); }
+float zkds_last_kernel_ms(void) { return limb_last_kernel_ms(); }
+
+int zkds_planes_create(const void* W, int bits, int64_t nb, int64_t rows, int64_t K, int64_t s_batch,
+                       int64_t s_row, int64_t s_k, int64_t div, int limbs, void** out, void* stream)
+{
+    if (!out) return finish(ZKDS_ERR_ARG, "zkds_planes_create");
+    *out = nullptr;
+    if (!W || (bits != 32 && bits != 64) || nb <= 0 || rows <= 0 || K <= 0 || div == 0 || limbs < 0 ||
+        limbs > 9)
+        return finish(ZKDS_ERR_ARG, "zkds_planes_create");
+    cudaStream_t st = ST(stream);
+    int rc = ZKDS_OK;
+    if (limbs == 0) {
+        uint64_t* d = (uint64_t*)workspace(2 * sizeof(uint64_t), 5);
+        if (!d) return finish(ZKDS_ERR_WORKSPACE, "zkds_planes_create");
+        uint64_t h = 0;
+        rc = set_cuda_error(cudaMemsetAsync(d, 0, sizeof(uint64_t), st));
+        if (rc == ZKDS_OK) rc = launch_absmax(W, bits, nb, rows, K, s_batch, s_row, s_k, div, d, st);
+        if (rc == ZKDS_OK) rc = set_cuda_error(cudaMemcpyAsync(&h, d, sizeof(h), cudaMemcpyDeviceToHost, st));
+        if (rc == ZKDS_OK) rc = set_cuda_error(cudaStreamSynchronize(st));
+        if (rc != ZKDS_OK) return finish(rc, "zkds_planes_create");
+        limbs = limbs_needed(h);
+        if (limbs > 9) return finish(ZKDS_ERR_UNSUPPORTED, "zkds_planes_create");
+    }
+    const int64_t Kp = (K + 15) & ~(int64_t)15;
+    PlanesHandle* hd = new PlanesHandle();
+    hd->pl.L = limbs; hd->pl.nb = nb; hd->pl.rows = rows; hd->pl.K = K;
+    hd->b_bits = bits;
+    cudaGetDevice(&hd->device);
+    void* mem = nullptr;
+    rc = set_cuda_error(cudaMalloc(&mem, (size_t)limbs * nb * rows * Kp + 1024));
+    if (rc == ZKDS_OK) {
+        hd->pl.data = (int8_t*)mem;
+        rc = planes_split(W, bits, nb, rows, K, s_batch, s_row, s_k, div, limbs, hd->pl.data, st);
+    }
+    if (rc != ZKDS_OK) {
+        if (mem) cudaFree(mem);
+        delete hd;
+        return finish(rc, "zkds_planes_create");
+    }
+    *out = hd;
+    return finish(ZKDS_OK, "zkds_planes_create");
+}
+
+int zkds_planes_limbs(const void* planes) { return planes ? ((const PlanesHandle*)planes)->pl.L : 0; }
+
+int zkds_planes_destroy(void* planes)
+{
+    if (!planes) return ZKDS_OK;
+    PlanesHandle* hd = (PlanesHandle*)planes;
+    int rc = set_cuda_error(cudaFree(hd->pl.data));
+    delete hd;
+    return finish(rc, "zkds_planes_destroy");
+}
+
+int zkds_contraction_prepared(const int64_t* A, int64_t a_s_batch, int64_t a_s_row, const void* planes,
+                              int b_batched, int64_t* C, int64_t* R, int64_t c_s_batch, int64_t c_s_row,
+                              int64_t batches, int64_t M, int64_t a_rescale, int64_t addend, int64_t shift,
+                              int a_limbs, int flags, void* stream)
+{
+    if (!planes) return finish(ZKDS_ERR_ARG, "zkds_contraction_prepared");
+    const PlanesHandle* hd = (const PlanesHandle*)planes;
+    Contraction p{};
+    p.A = A; p.B = nullptr; p.b_bits = hd->b_bits; p.C = C; p.R = R;
+    p.batches = batches; p.M = M; p.N = hd->pl.rows; p.K = hd->pl.K;
+    p.a_sz = a_s_batch; p.a_sm = a_s_row;
+    p.b_sz = b_batched ? 1 : 0; p.b_sn = 0; p.b_sk = 0;
+    p.c_sz = c_s_batch; p.c_sm = c_s_row;
+    p.a_div = a_rescale; p.b_div = 1;
+    p.addend = addend;
+    p.shift = (shift < 0 || shift > 127) ? -1 : (int)shift;
+    p.r_legacy = (flags & ZKDS_REMAINDER_LEGACY) ? 1 : 0;
+    int f = (flags & ~ZKDS_ALGO_MASK) | ZKDS_ALGO_LIMB;
+    return finish(run_contraction(p, a_limbs, 0, f, ST(stream), &hd->pl), "zkds_contraction_prepared");
+}
 
 int zkds_lut(int64_t* host_lut, int kind) { return finish(make_lut(host_lut, kind), "zkds_lut"); }
 

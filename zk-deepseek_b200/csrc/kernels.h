@@ -47,7 +47,23 @@ int launch_contraction_exact(const Contraction& p, cudaStream_t st);
 // Tensor-core path (limb_gemm.cu).  La/Lb: signed 8-bit limb counts that cover the
 // operands after division; returns ZKDS_ERR_UNSUPPORTED when the shape or the limb
 // counts fall outside what the kernel handles (caller then uses the exact path).
-int launch_contraction_limb(const Contraction& p, int La, int Lb, cudaStream_t st);
+// pre_b: limb planes of B prepared ahead of time (static weights), or null to split B now.
+struct Planes {
+    int8_t* data;     // [L][nb][rows][Kp] int8, Kp = K rounded up to 16
+    int L;
+    int64_t nb, rows, K;
+};
+int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* pre_b, cudaStream_t st);
+
+// planes[l][z][r][Kp] <- limb l of X[z*sz + r*sr + k*sk] / div
+int planes_split(const void* X, int bits, int64_t nb, int64_t rows, int64_t K, int64_t sz, int64_t sr,
+                 int64_t sk, int64_t div, int L, int8_t* dst, cudaStream_t st);
+// smallest count of balanced signed 8-bit limbs (digits in [-128,127]) covering |v| <= maxabs
+int limbs_needed(uint64_t maxabs);
+
+// CUDA-event timing of the tensor-core kernel alone (events recorded on the launching stream)
+void limb_timing_enable(int on);
+float limb_last_kernel_ms();
 
 // ZKDS_ERR_DEVICE when a tensor-core kernel reported a wait that ran out, ZKDS_ERR_RANGE
 // when an operand did not fit the limb count it was split into, else ZKDS_OK.  The flags

@@ -552,8 +552,66 @@ int limb_device_status(int clear)
     return rc;
 }
 
-int launch_contraction_limb(const Contraction& p, int La, int Lb, cudaStream_t st)
+// ---- kernel timing hooks -------------------------------------------------------------
+static bool g_timing = false;
+static cudaEvent_t g_ev[64][2];
+static bool g_ev_made[64];
+static bool g_ev_valid[64];
+
+void limb_timing_enable(int on) { g_timing = on != 0; }
+
+float limb_last_kernel_ms()
 {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || !g_ev_valid[dev]) return -1.f;
+    float ms = -1.f;
+    if (cudaEventSynchronize(g_ev[dev][1]) != cudaSuccess) return -1.f;
+    if (cudaEventElapsedTime(&ms, g_ev[dev][0], g_ev[dev][1]) != cudaSuccess) return -1.f;
+    return ms;
+}
+
+static cudaEvent_t* timing_events()
+{
+    int dev = 0;
+    if (!g_timing || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!g_ev_made[dev]) {
+        if (cudaEventCreate(&g_ev[dev][0]) != cudaSuccess || cudaEventCreate(&g_ev[dev][1]) != cudaSuccess)
+            return nullptr;
+        g_ev_made[dev] = true;
+    }
+    g_ev_valid[dev] = true;
+    return g_ev[dev];
+}
+
+int limbs_needed(uint64_t maxabs)
+{
+    unsigned __int128 cover = 0, w = 1;
+    for (int L = 1; L <= 9; ++L) {
+        cover += (unsigned __int128)127 * w;
+        w <<= 8;
+        if ((unsigned __int128)maxabs <= cover) return L;
+    }
+    return 10;
+}
+
+int planes_split(const void* X, int bits, int64_t nb, int64_t rows, int64_t K, int64_t sz, int64_t sr,
+                 int64_t sk, int64_t div, int L, int8_t* dst, cudaStream_t st)
+{
+    DeviceFlags* fl = flags_for_device();
+    if (!fl) return ZKDS_ERR_WORKSPACE;
+    const int64_t Kp = (K + 15) & ~(int64_t)15;
+    if (bits == 32)
+        return launch_split_t<int32_t>((const int32_t*)X, dst, L, nb, rows, K, Kp, sz, sr, sk, div,
+                                       fl->overflow_dev, st);
+    if (bits == 64)
+        return launch_split_t<int64_t>((const int64_t*)X, dst, L, nb, rows, K, Kp, sz, sr, sk, div,
+                                       fl->overflow_dev, st);
+    return ZKDS_ERR_ARG;
+}
+
+int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* pre_b, cudaStream_t st)
+{
+    if (pre_b) Lb = pre_b->L;
     if (La < 1 || Lb < 1 || La > 9 || Lb > 9) return ZKDS_ERR_UNSUPPORTED;
     if (p.K <= 0) return ZKDS_ERR_UNSUPPORTED;
     const int D = La + Lb - 1;
@@ -562,47 +620,42 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, cudaStream_t s
     // tile width: the B stack must fit one MMA (<= 256 columns), the diagonals tensor memory
     // (<= 512 columns), and two pipeline stages shared memory
     const size_t smem_max = 227 * 1024 - 4096;  // static barriers + alignment slack stay below the opt-in limit
-    int NT = 0, stages = 0;
+    int NT = 0;
     for (int cand : {128, 64, 32, 16}) {
         if (Lb * cand > 256 || D * cand > 512) continue;
         size_t stage = (size_t)La * kTileM * kBlockK + (size_t)Lb * cand * kBlockK;
-        int s = (int)(smem_max / stage);
-        if (s < 2) continue;
+        if (smem_max / stage < 2) continue;
         NT = cand;
-        stages = s > 8 ? 8 : s;
         break;
     }
     if (!NT) return ZKDS_ERR_UNSUPPORTED;
     // shrink the tile for narrow outputs (fewer wasted columns)
     while (NT > 16 && p.N <= NT / 2) NT /= 2;
-    {
-        size_t stage = (size_t)La * kTileM * kBlockK + (size_t)Lb * NT * kBlockK;
-        int s = (int)(smem_max / stage);
-        stages = s > 8 ? 8 : s;
-    }
+    const size_t stage = (size_t)La * kTileM * kBlockK + (size_t)Lb * NT * kBlockK;
+    int stages = (int)(smem_max / stage);
+    if (stages > 8) stages = 8;
     const int64_t Kp = (p.K + 15) & ~(int64_t)15;
     const int64_t nbB = p.b_sz ? p.batches : 1;
     const int64_t a_rows = p.batches * p.M, b_rows = nbB * p.N;
     if (a_rows * La > 0x7fffff00ll || b_rows * Lb > 0x7fffff00ll || Kp > 0x7fffff00ll) return ZKDS_ERR_UNSUPPORTED;
     const int64_t mt = (p.M + kTileM - 1) / kTileM, nt = (p.N + NT - 1) / NT;
     if (mt > 0x7fffffffll || nt > 65535 || p.batches > 65535) return ZKDS_ERR_UNSUPPORTED;
+    if (pre_b && (pre_b->nb != nbB || pre_b->rows != p.N || pre_b->K != p.K)) return ZKDS_ERR_ARG;
 
     DeviceFlags* fl = flags_for_device();
     if (!fl) return ZKDS_ERR_WORKSPACE;
     int8_t* pa = (int8_t*)workspace((size_t)La * a_rows * Kp + 1024, 0);
-    int8_t* pb = (int8_t*)workspace((size_t)Lb * b_rows * Kp + 1024, 1);
-    if (!pa || !pb) return ZKDS_ERR_WORKSPACE;
-
-    int rc = launch_split_t<int64_t>(p.A, pa, La, p.batches, p.M, p.K, Kp, p.a_sz, p.a_sm, 1, p.a_div,
-                                     fl->overflow_dev, st);
+    if (!pa) return ZKDS_ERR_WORKSPACE;
+    int rc = planes_split(p.A, 64, p.batches, p.M, p.K, p.a_sz, p.a_sm, 1, p.a_div, La, pa, st);
     if (rc != ZKDS_OK) return rc;
-    if (p.b_bits == 32)
-        rc = launch_split_t<int32_t>((const int32_t*)p.B, pb, Lb, nbB, p.N, p.K, Kp, p.b_sz, p.b_sn, p.b_sk,
-                                     p.b_div, fl->overflow_dev, st);
-    else
-        rc = launch_split_t<int64_t>((const int64_t*)p.B, pb, Lb, nbB, p.N, p.K, Kp, p.b_sz, p.b_sn, p.b_sk,
-                                     p.b_div, fl->overflow_dev, st);
-    if (rc != ZKDS_OK) return rc;
+    int8_t* pb;
+    if (pre_b) pb = pre_b->data;
+    else {
+        pb = (int8_t*)workspace((size_t)Lb * b_rows * Kp + 1024, 1);
+        if (!pb) return ZKDS_ERR_WORKSPACE;
+        rc = planes_split(p.B, p.b_bits, nbB, p.N, p.K, p.b_sz, p.b_sn, p.b_sk, p.b_div, Lb, pb, st);
+        if (rc != ZKDS_OK) return rc;
+    }
 
     CUtensorMap tmA, tmB;
     if (!make_plane_map(&tmA, pa, (int64_t)La * a_rows, Kp, kTileM)) return ZKDS_ERR_UNSUPPORTED;
@@ -621,7 +674,6 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, cudaStream_t s
     lp.addend = p.addend; lp.shift = p.shift; lp.r_legacy = p.r_legacy;
     lp.error_flag = fl->dev;
 
-    size_t stage = (size_t)La * kTileM * kBlockK + (size_t)Lb * NT * kBlockK;
     size_t smem = stage * stages + 1024;
     // more than half the shared memory per CTA keeps one CTA per SM, so its tensor-memory
     // allocation can never wait for a co-resident CTA
@@ -629,8 +681,12 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, cudaStream_t s
     ZKDS_CUDA(cudaFuncSetAttribute(limb_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)(227 * 1024 - 3072)));
     dim3 grid((unsigned)mt, (unsigned)nt, (unsigned)p.batches);
+    cudaEvent_t* ev = timing_events();
+    if (ev) ZKDS_CUDA(cudaEventRecord(ev[0], st));
     limb_gemm_kernel<<<grid, kThreads, smem, st>>>(tmA, tmB, lp);
-    return check_launch();
+    rc = check_launch();
+    if (ev) ZKDS_CUDA(cudaEventRecord(ev[1], st));
+    return rc;
 }
 
 }  // namespace zkds

@@ -82,6 +82,14 @@ _sig("zkds_rms_norm_apply", [_vp, _vp, _i, _vp, _vp, _ll, _ll, _vp])
 _sig("zkds_softmax", [_vp, _vp, _vp, _vp, _ll, _ll, _i, _vp])
 _sig("zkds_act", [_vp, _vp, _vp, _ll, _i, _i, _vp])
 _sig("zkds_lut", [_vp, _i])
+_sig("zkds_device_status", [_i])
+_sig("zkds_timing", [_i], None)
+_sig("zkds_last_kernel_ms", [], ctypes.c_float)
+_sig("zkds_planes_create", [_vp, _i, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _i, ctypes.POINTER(_vp), _vp])
+_sig("zkds_planes_limbs", [_vp])
+_sig("zkds_planes_destroy", [_vp])
+_sig("zkds_contraction_prepared", [_vp, _ll, _ll, _vp, _i, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _ll,
+                                   _i, _i, _vp])
 
 
 class ZkdsError(RuntimeError):
@@ -201,6 +209,93 @@ def einsum_bshc_hdc_bshd(A, B, rescale, a_limbs=0, b_limbs=0):
     assert B.dtype == torch.int32
     return _einsum("zkds_einsum_bshc_hdc_bshd", A, B, [Bn, S, H, D], rescale, (Bn, S, H, D, Cd),
                    a_limbs, b_limbs)
+
+
+# ---- static weights prepared once ---------------------------------------------------------
+
+def device_status(clear=True):
+    """Raises if a finished tensor-core kernel gave up a bounded wait, or if an operand did not
+    fit the limb count a caller promised through a_limbs (that call's result is wrong)."""
+    _check(lib.zkds_device_status(1 if clear else 0), "device status")
+
+
+def kernel_timing(enable):
+    lib.zkds_timing(1 if enable else 0)
+
+
+def last_kernel_ms():
+    return float(lib.zkds_last_kernel_ms())
+
+
+class WeightPlanes:
+    """Signed 8-bit limb planes of a static weight, split once and kept on the device.
+
+    ``W`` is (N, K) for a plain linear layer or (H, N, K) / (H, K, N) for the per-head MLA
+    weights; ``k_last`` says whether K is the last (contiguous) dimension.
+    """
+
+    def __init__(self, W, k_last=True, div=1, limbs=0):
+        assert W.is_cuda and W.is_contiguous() and W.dtype in (torch.int32, torch.int64)
+        if W.ndim == 2:
+            nb, (rows, K) = 1, W.shape
+            s_batch, s_row, s_k = 0, K, 1
+            assert k_last
+        else:
+            nb = W.shape[0]
+            if k_last:
+                rows, K = W.shape[1], W.shape[2]
+                s_row, s_k = K, 1
+            else:
+                K, rows = W.shape[1], W.shape[2]
+                s_row, s_k = 1, rows
+            s_batch = rows * K
+        self.nb, self.N, self.K = nb, rows, K
+        self.device = W.device
+        h = _vp()
+        with torch.cuda.device(W.device):
+            _check(lib.zkds_planes_create(W.data_ptr(), 32 if W.dtype == torch.int32 else 64, nb, rows,
+                                          K, s_batch, s_row, s_k, int(div), limbs, ctypes.byref(h),
+                                          _stream()), "zkds_planes_create")
+        self.handle = h
+        self.limbs = lib.zkds_planes_limbs(h)
+
+    def __del__(self):
+        h, self.handle = getattr(self, "handle", None), None
+        if h:
+            lib.zkds_planes_destroy(h)
+
+
+def linear_prepared(A, planes, c_rescale, a_rescale=1, a_limbs=0, want_remainder=False):
+    """int64_bmm_broadcast against prepared weights: A (Bdim, M, K) -> C (Bdim, M, N) [, R]."""
+    _dev_i64(A, "A")
+    Bdim, M, K = A.shape
+    assert K == planes.K and planes.nb == 1
+    C = torch.empty((Bdim, M, planes.N), dtype=torch.int64, device=A.device)
+    R = torch.empty_like(C) if want_remainder else None
+    flags = REMAINDER_LEGACY if LEGACY_REMAINDER else 0
+    with torch.cuda.device(A.device):
+        _check(lib.zkds_contraction_prepared(A.data_ptr(), M * K, K, planes.handle, 0, C.data_ptr(),
+                                             R.data_ptr() if want_remainder else None, M * planes.N,
+                                             planes.N, Bdim, M, int(a_rescale), 0, int(c_rescale),
+                                             a_limbs, flags, _stream()), "linear_prepared")
+    return (C, R) if want_remainder else C
+
+
+def einsum_heads_prepared(A, planes, rescale, rounding, a_limbs=0):
+    """out[b,s,h,n] = (addend + sum_k A[b,s,h,k] * W[h,n,k]) >> rescale with per-head prepared
+    weights; addend = rescale // 2 when ``rounding`` (einsum_bshd_hdc_bshc) else 0
+    (einsum_bshc_hdc_bshd)."""
+    _dev_i64(A, "A")
+    Bn, S, H, K = A.shape
+    assert H == planes.nb and K == planes.K
+    N = planes.N
+    C = torch.empty((Bn, S, H, N), dtype=torch.int64, device=A.device)
+    with torch.cuda.device(A.device):
+        _check(lib.zkds_contraction_prepared(A.data_ptr(), K, H * K, planes.handle, 1, C.data_ptr(), None,
+                                             N, H * N, H, Bn * S, 1, int(rescale) // 2 if rounding else 0,
+                                             int(rescale), a_limbs, 0, _stream()),
+               "einsum_heads_prepared")
+    return C
 
 
 # ---- RoPE ----------------------------------------------------------------------------
