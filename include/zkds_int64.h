@@ -125,6 +125,34 @@ int zkds_gemm(const int64_t* A, const void* B, int b_bits, int64_t* C, int64_t* 
               int64_t a_rescale, int64_t b_rescale, int64_t c_rescale, int64_t Bdim, int64_t M,
               int64_t K, int64_t N, int a_limbs, int b_limbs, int flags, void* stream);
 
+/* zkds_gemm for callers that must not allocate (this entry point has no counterpart in the
+ * reference).  Same arithmetic and arguments as zkds_gemm, always on the tensor-core limb
+ * kernel, but it calls no cudaMalloc, cudaFree, cudaHostAlloc or any other allocating
+ * routine: the limb planes and status words it needs live in a fixed 64 MiB device array that
+ * is part of the library image, so every GPU that loads the library holds those 64 MiB until
+ * the process exits.  Meant for hosts whose own pool already owns the whole GPU (an
+ * allocation here would fail or fragment it) or that cannot afford the device-wide
+ * synchronisation an allocation implies.
+ *   - Capacity: a_limbs*Bdim*M*K16 + b_limbs*N*K16 bytes (K16 = K rounded up to 16, each term
+ *     rounded up to 1 KiB) must not exceed zkds_gemm_noalloc_capacity(); larger shapes are
+ *     rejected with ZKDS_ERR_RANGE and a message on stderr.  zkds_gemm_noalloc_bytes computes
+ *     the need of a shape.  Shapes the limb kernel cannot take give ZKDS_ERR_UNSUPPORTED
+ *     (there is no fallback).
+ *   - The first call on a device looks up the device address of that array
+ *     (cudaGetSymbolAddress with the device current); make that first call outside any
+ *     stream capture.
+ *   - Every call uses the same array, which keeps the previous call's bytes; the status words
+ *     are cleared at the start of each call.  Two calls whose GPU work overlaps (different
+ *     streams or threads) race on it: serialise them.
+ *   - The call waits for its own kernels before returning (it reads the status words back),
+ *     so the returned status already covers operand-range overflow and device-side waits. */
+int zkds_gemm_noalloc(const int64_t* A, const void* B, int b_bits, int64_t* C, int64_t* R,
+                      int64_t a_rescale, int64_t b_rescale, int64_t c_rescale, int64_t Bdim, int64_t M,
+                      int64_t K, int64_t N, int a_limbs, int b_limbs, int flags, void* stream);
+unsigned long long zkds_gemm_noalloc_capacity(void);
+unsigned long long zkds_gemm_noalloc_bytes(int64_t Bdim, int64_t M, int64_t K, int64_t N, int a_limbs,
+                                           int b_limbs);
+
 /* Replace the four einsum entry points (int64_gemm.cu:416-549). */
 int zkds_einsum_bshd_hdc_bshc(const int64_t* q, const int32_t* W, int64_t* out, int64_t rescale,
                               int64_t B, int64_t S, int64_t H, int64_t D, int64_t C, int a_limbs,

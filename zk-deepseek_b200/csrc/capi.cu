@@ -261,6 +261,38 @@ int zkds_gemm(const int64_t* A, const void* B, int b_bits, int64_t* C, int64_t* 
     return finish(run_contraction(p, a_limbs, b_limbs, flags, ST(stream)), "zkds_gemm");
 }
 
+int zkds_gemm_noalloc(const int64_t* A, const void* B, int b_bits, int64_t* C, int64_t* R,
+                      int64_t a_rescale, int64_t b_rescale, int64_t c_rescale, int64_t Bdim, int64_t M,
+                      int64_t K, int64_t N, int a_limbs, int b_limbs, int flags, void* stream)
+{
+    Contraction p = gemm_problem(A, B, b_bits, C, R, a_rescale, b_rescale, c_rescale, Bdim, M, K, N,
+                                 (flags & ZKDS_REMAINDER_LEGACY) ? 1 : 0);
+    int rc;
+    if (Bdim < 0 || M < 0 || K < 0 || N < 0 || a_limbs < 0 || b_limbs < 0) rc = ZKDS_ERR_ARG;
+    else if (Bdim == 0 || M == 0 || N == 0) rc = ZKDS_OK;
+    else if (!A || !B || !C || a_rescale == 0 || b_rescale == 0 || p.shift < 0 ||
+             (b_bits != 32 && b_bits != 64))
+        rc = ZKDS_ERR_ARG;
+    else if (a_limbs > 0 && b_limbs > 0 &&
+             gemm_noalloc_bytes(Bdim, M, K, N, a_limbs, b_limbs) > gemm_noalloc_capacity()) {
+        fprintf(stderr,
+                "libint64gemm: zkds_gemm_noalloc: this shape needs %zu bytes of limb planes, the fixed "
+                "scratch array holds %zu\n",
+                gemm_noalloc_bytes(Bdim, M, K, N, a_limbs, b_limbs), gemm_noalloc_capacity());
+        rc = ZKDS_ERR_RANGE;
+    } else
+        rc = launch_gemm_noalloc(p, a_limbs, b_limbs, ST(stream));
+    return finish(rc, "zkds_gemm_noalloc");
+}
+
+unsigned long long zkds_gemm_noalloc_capacity(void) { return (unsigned long long)gemm_noalloc_capacity(); }
+
+unsigned long long zkds_gemm_noalloc_bytes(int64_t Bdim, int64_t M, int64_t K, int64_t N, int a_limbs,
+                                           int b_limbs)
+{
+    return (unsigned long long)gemm_noalloc_bytes(Bdim, M, K, N, a_limbs, b_limbs);
+}
+
 int zkds_einsum_bshd_hdc_bshc(const int64_t* q, const int32_t* W, int64_t* out, int64_t rescale,
                               int64_t B, int64_t S, int64_t H, int64_t D, int64_t C, int a_limbs,
                               int b_limbs, int flags, void* stream)

@@ -61,6 +61,12 @@ int planes_split(const void* X, int bits, int64_t nb, int64_t rows, int64_t K, i
 // smallest count of balanced signed 8-bit limbs (digits in [-128,127]) covering |v| <= maxabs
 int limbs_needed(uint64_t maxabs);
 
+// GEMM on the tensor-core kernel with every byte of scratch in a fixed device array of the
+// module (no allocation of any kind); p.b_sz must be 0 (B shared by the batches)
+int launch_gemm_noalloc(const Contraction& p, int La, int Lb, cudaStream_t st);
+size_t gemm_noalloc_capacity();
+size_t gemm_noalloc_bytes(int64_t Bdim, int64_t M, int64_t K, int64_t N, int a_limbs, int b_limbs);
+
 // CUDA-event timing of the tensor-core kernel alone (events recorded on the launching stream)
 void limb_timing_enable(int on);
 float limb_last_kernel_ms();

@@ -689,4 +689,137 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     return rc;
 }
 
+// ------------------------------------------------------------------------------------
+// GEMM for callers that must not allocate
+// ------------------------------------------------------------------------------------
+// Some hosts of this library cannot tolerate a memory allocation inside a call: a serving
+// loop that has handed every byte of the GPU to its own pool (so a cudaMalloc here would
+// fail or fragment it), or a latency-critical section where the implicit device
+// synchronisation of cudaMalloc / cudaFree is not acceptable.  For them the limb planes and
+// the status words live in the fixed array below, which is part of the loaded module: every
+// GPU that loads the library holds kNoAllocBytes of it until the process exits.
+//
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not an address a
+// kernel could use; the device address is fetched once per device with
+// cudaGetSymbolAddress while that device is current, and that pointer is what the kernels
+// receive.
+constexpr size_t kNoAllocBytes = (size_t)64 << 20;   // 64 MiB
+constexpr size_t kNoAllocHeader = 256;               // status words live in front of the planes
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+static unsigned char* g_noalloc_ptr[64];
+
+size_t gemm_noalloc_capacity() { return kNoAllocBytes - kNoAllocHeader; }
+
+size_t gemm_noalloc_bytes(int64_t Bdim, int64_t M, int64_t K, int64_t N, int a_limbs, int b_limbs)
+{
+    const int64_t Kp = (K + 15) & ~(int64_t)15;
+    size_t a = ((size_t)a_limbs * Bdim * M * Kp + 1023) & ~(size_t)1023;
+    size_t b = ((size_t)b_limbs * N * Kp + 1023) & ~(size_t)1023;
+    return a + b;
+}
+
+int launch_gemm_noalloc(const Contraction& p, int La, int Lb, cudaStream_t st)
+{
+    int dev = 0;
+    ZKDS_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return ZKDS_ERR_ARG;
+    if (!g_noalloc_ptr[dev]) {
+        // first call on this device: resolve the device address of the static array
+        void* sym = nullptr;
+        ZKDS_CUDA(cudaGetSymbolAddress(&sym, g_noalloc_scratch));
+        if (!sym) return ZKDS_ERR_WORKSPACE;
+        g_noalloc_ptr[dev] = (unsigned char*)sym;
+    }
+    unsigned char* base = g_noalloc_ptr[dev];
+    // header: [0] device error word, [1] limb overflow word, [2..5] two 64-bit range words
+    int* d_err = (int*)base;
+    unsigned* d_ovf = (unsigned*)(base + 4);
+    uint64_t* d_range = (uint64_t*)(base + 8);
+    // the array keeps what the previous call left: the status words must start at zero
+    ZKDS_CUDA(cudaMemsetAsync(base, 0, kNoAllocHeader, st));
+
+    if (p.K <= 0) return ZKDS_ERR_UNSUPPORTED;
+    if (La <= 0 || Lb <= 0) {
+        int rc = launch_absmax(p.A, 64, p.batches, p.M, p.K, p.a_sz, p.a_sm, 1, p.a_div, d_range, st);
+        if (rc != ZKDS_OK) return rc;
+        rc = launch_absmax(p.B, p.b_bits, 1, p.N, p.K, 0, p.b_sn, p.b_sk, p.b_div, d_range + 1, st);
+        if (rc != ZKDS_OK) return rc;
+        uint64_t h[2] = {0, 0};
+        ZKDS_CUDA(cudaMemcpyAsync(h, d_range, sizeof(h), cudaMemcpyDeviceToHost, st));
+        ZKDS_CUDA(cudaStreamSynchronize(st));
+        if (La <= 0) La = limbs_needed(h[0]);
+        if (Lb <= 0) Lb = limbs_needed(h[1]);
+    }
+    if (La > 9 || Lb > 9) return ZKDS_ERR_UNSUPPORTED;
+    const int D = La + Lb - 1;
+    const int pairs = La < Lb ? La : Lb;
+    if ((int64_t)pairs * p.K >= 131072) return ZKDS_ERR_UNSUPPORTED;
+    const size_t smem_max = 227 * 1024 - 4096;
+    int NT = 0;
+    for (int cand : {128, 64, 32, 16}) {
+        if (Lb * cand > 256 || D * cand > 512) continue;
+        size_t stage = (size_t)La * kTileM * kBlockK + (size_t)Lb * cand * kBlockK;
+        if (smem_max / stage < 2) continue;
+        NT = cand;
+        break;
+    }
+    if (!NT) return ZKDS_ERR_UNSUPPORTED;
+    while (NT > 16 && p.N <= NT / 2) NT /= 2;
+    const size_t stage = (size_t)La * kTileM * kBlockK + (size_t)Lb * NT * kBlockK;
+    int stages = (int)(smem_max / stage);
+    if (stages > 8) stages = 8;
+    const int64_t Kp = (p.K + 15) & ~(int64_t)15;
+    const int64_t a_rows = p.batches * p.M, b_rows = p.N;
+    const int64_t mt = (p.M + kTileM - 1) / kTileM, nt = (p.N + NT - 1) / NT;
+    if (mt > 0x7fffffffll || nt > 65535 || p.batches > 65535) return ZKDS_ERR_UNSUPPORTED;
+    if (gemm_noalloc_bytes(p.batches, p.M, p.K, p.N, La, Lb) > gemm_noalloc_capacity())
+        return ZKDS_ERR_RANGE;
+
+    int8_t* pa = (int8_t*)(base + kNoAllocHeader);
+    int8_t* pb = pa + (((size_t)La * a_rows * Kp + 1023) & ~(size_t)1023);
+    int rc = launch_split_t<int64_t>(p.A, pa, La, p.batches, p.M, p.K, Kp, p.a_sz, p.a_sm, 1, p.a_div,
+                                     d_ovf, st);
+    if (rc != ZKDS_OK) return rc;
+    if (p.b_bits == 32)
+        rc = launch_split_t<int32_t>((const int32_t*)p.B, pb, Lb, 1, p.N, p.K, Kp, 0, p.b_sn, p.b_sk,
+                                     p.b_div, d_ovf, st);
+    else
+        rc = launch_split_t<int64_t>((const int64_t*)p.B, pb, Lb, 1, p.N, p.K, Kp, 0, p.b_sn, p.b_sk,
+                                     p.b_div, d_ovf, st);
+    if (rc != ZKDS_OK) return rc;
+
+    CUtensorMap tmA, tmB;
+    if (!make_plane_map(&tmA, pa, (int64_t)La * a_rows, Kp, kTileM)) return ZKDS_ERR_UNSUPPORTED;
+    if (!make_plane_map(&tmB, pb, (int64_t)Lb * b_rows, Kp, NT)) return ZKDS_ERR_UNSUPPORTED;
+
+    LimbParams lp{};
+    lp.La = La; lp.Lb = Lb; lp.NT = NT; lp.stages = stages;
+    lp.kblocks = (int)((Kp + kBlockK - 1) / kBlockK);
+    uint32_t cols = 32;
+    while (cols < (uint32_t)(D * NT)) cols <<= 1;
+    lp.tmem_cols = cols;
+    lp.M = p.M; lp.N = p.N; lp.batches = p.batches;
+    lp.a_rows_per_limb = a_rows; lp.b_rows_per_limb = b_rows;
+    lp.b_batched = 0;
+    lp.C = p.C; lp.R = p.R; lp.c_sz = p.c_sz; lp.c_sm = p.c_sm;
+    lp.addend = p.addend; lp.shift = p.shift; lp.r_legacy = p.r_legacy;
+    lp.error_flag = d_err;
+
+    size_t smem = stage * stages + 1024;
+    if (smem < 120 * 1024) smem = 120 * 1024;
+    ZKDS_CUDA(cudaFuncSetAttribute(limb_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)(227 * 1024 - 3072)));
+    dim3 grid((unsigned)mt, (unsigned)nt, (unsigned)p.batches);
+    limb_gemm_kernel<<<grid, kThreads, smem, st>>>(tmA, tmB, lp);
+    rc = check_launch();
+    if (rc != ZKDS_OK) return rc;
+    // the status words are device memory: read them back (this waits for the kernels)
+    int hs[2] = {0, 0};
+    ZKDS_CUDA(cudaMemcpyAsync(hs, base, sizeof(hs), cudaMemcpyDeviceToHost, st));
+    ZKDS_CUDA(cudaStreamSynchronize(st));
+    if (hs[0]) return ZKDS_ERR_DEVICE;
+    if (hs[1]) return ZKDS_ERR_RANGE;
+    return ZKDS_OK;
+}
+
 }  // namespace zkds
