@@ -181,6 +181,158 @@ class GemmWorkload:
         return 2.0 * rows * N * K / dt / 1e9, "%d of 4096 rows of X against the full W" % rows, dt
 
 
+class ChainWorkload:
+    """Fixed-point nonlinearity chain on one MLA block's activations (T = 2048 tokens):
+    RMSNorm over x int64 [T, 7168] ~ N(0, 2^16) with int32 weight near 2^16; RoPE on q_pe
+    [1, T, 128, 64] with a 2^42-scaled cos/sin table (base 10000); Q19 softmax over scores
+    [1, T, 128, T] ~ N(0, 4*2^16) with the causal mask -(64<<36) added; Q23 SiLU over
+    [1, T, 18432] ~ N(0, 2^16).  Four kernel launches per step, each an HBM stream."""
+    name = "fixedpoint_chain_T2048"
+    metric = "fixedpoint_chain_tokens_per_s"
+    unit = "tokens/s"
+    T, DIM, H, ROPE, INTER = 2048, 7168, 128, 64, 18432
+
+    def __init__(self, torch, k, dev, rank, T=None):
+        import numpy as np
+        if T:
+            self.T = T
+        self.torch, self.k, self.dev, self.np = torch, k, dev, np
+        T = self.T
+        g = torch.Generator(device=dev).manual_seed(2000 + rank)
+
+        def normal(shape, scale):
+            return torch.round(torch.randn(shape, generator=g, device=dev, dtype=torch.float32)
+                               * scale).to(torch.int64)
+
+        self.x = normal((T, self.DIM), 2.0**16)
+        self.w = (2**16 + normal((self.DIM,), 2.0**8)).to(torch.int32)
+        self.q_pe = normal((1, T, self.H, self.ROPE // 2, 2), 2.0**16)
+        freqs = 1.0 / (10000.0 ** (np.arange(0, self.ROPE, 2, dtype=np.float64) / self.ROPE))
+        ang = np.outer(np.arange(T), freqs)
+        tab = np.stack([np.rint(np.cos(ang) * 2.0**42), np.rint(np.sin(ang) * 2.0**42)], -1)
+        self.table = torch.from_numpy(tab.astype(np.int64)).to(dev).view(1, T, 1, self.ROPE // 2, 2)
+        self.scores = normal((1, T, self.H, T), 4 * 2.0**16)
+        self.scores += torch.full((T, T), -(64 << 36), dtype=torch.int64, device=dev).triu_(1)[:, None, :]
+        self.act = normal((1, T, self.INTER), 2.0**16)
+        self.probs = torch.empty_like(self.scores)
+        self.act_out = torch.empty_like(self.act)
+        k.softmax_init_q19()
+        k.silu_init_q23()
+        k.SOFTMAX_WRITES_WEIGHTS = False      # keep the scores intact from step to step
+        self.bytes = {"rmsnorm": 16 * self.x.numel() + 4 * self.DIM,
+                      "rope": 16 * self.q_pe.numel() + 8 * self.table.numel(),
+                      "softmax": 16 * self.scores.numel(), "silu": 16 * self.act.numel()}
+        self.launches_per_step = 4
+        self.host = None
+
+    def config(self):
+        return {"workload": self.name, "tokens": self.T, "rmsnorm": [self.T, self.DIM],
+                "rope": [1, self.T, self.H, self.ROPE], "softmax": [1, self.T, self.H, self.T],
+                "silu": [1, self.T, self.INTER], "rope_shift": 42, "softmax_frac": 19, "silu_frac": 23,
+                "l2": "every tensor is larger than L2 (117 MB to 4.3 GB)"}
+
+    def step(self):
+        k = self.k
+        n, _ = k.rms_norm_int64_device(self.x, self.w, 1, self.DIM)
+        r = k.complex_int64_mul_broadcast(self.q_pe, self.table)
+        k.softmax_q19(self.scores, self.probs)
+        k.silu_q23(self.act, self.act_out)
+        return n, r
+
+    def time_parts(self, reps=5):
+        """CUDA-event duration of each kernel on the launching stream (average of reps)"""
+        torch, k = self.torch, self.k
+        out = {}
+        calls = {"rmsnorm": lambda: k.rms_norm_int64_device(self.x, self.w, 1, self.DIM),
+                 "rope": lambda: k.complex_int64_mul_broadcast(self.q_pe, self.table),
+                 "softmax": lambda: k.softmax_q19(self.scores, self.probs),
+                 "silu": lambda: k.silu_q23(self.act, self.act_out)}
+        for name, fn in calls.items():
+            fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            out[name] = e0.elapsed_time(e1) / reps
+        return out
+
+    def step_e2e(self):
+        torch = self.torch
+        if self.host is None:
+            self.host = {n: getattr(self, n).cpu().pin_memory() for n in ("x", "q_pe", "scores", "act")}
+            self.dev_in = {n: torch.empty_like(getattr(self, n)) for n in self.host}
+            self.host_out = {n: torch.empty_like(t).pin_memory() for n, t in self.host.items()}
+        for n, h in self.host.items():
+            self.dev_in[n].copy_(h, non_blocking=True)
+        k = self.k
+        nrm, _ = k.rms_norm_int64_device(self.dev_in["x"], self.w, 1, self.DIM)
+        rot = k.complex_int64_mul_broadcast(self.dev_in["q_pe"], self.table)
+        k.softmax_q19(self.dev_in["scores"], self.probs)
+        k.silu_q23(self.dev_in["act"], self.act_out)
+        self.host_out["x"].copy_(nrm, non_blocking=True)
+        self.host_out["q_pe"].copy_(rot, non_blocking=True)
+        self.host_out["scores"].copy_(self.probs, non_blocking=True)
+        self.host_out["act"].copy_(self.act_out, non_blocking=True)
+
+    def e2e_bytes(self):
+        n = 8 * (self.x.numel() + self.q_pe.numel() + self.scores.numel() + self.act.numel())
+        return n, n
+
+    def value(self, seconds_per_step, world):
+        return self.T * world / seconds_per_step
+
+    def roofline(self, kernel_ms, peaks):
+        parts = self.time_parts()
+        gbs = {n: self.bytes[n] / (ms * 1e-3) / 1e9 for n, ms in parts.items()}
+        dom = "softmax"
+        return {"bound": "hbm", "kernel": "softmax_kernel<19>", "achieved": round(gbs[dom], 1),
+                "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(gbs[dom] / peaks["hbm_gbs"], 4),
+                "traffic": None, "kernel_ms": round(parts[dom], 4),
+                "parts": {n: {"ms": round(parts[n], 4), "GB/s": round(gbs[n], 1),
+                              "frac": round(gbs[n] / peaks["hbm_gbs"], 4),
+                              "algorithmic_bytes": self.bytes[n]} for n in parts},
+                "note": "algorithmic bytes = 8 B read + 8 B written per element (+ weights/table); "
+                        "peak = STREAM-style copy (%s)" % peaks["source"]}
+
+    def check(self, orc):
+        """bit-exact against the CPU oracle on slices of every tensor"""
+        k, bad = self.k, 0
+        nrm, rot = self.step()
+        want, _ = orc.rms_norm(self.x[:16].cpu().numpy(), self.w.cpu().numpy(), 1, self.DIM)
+        bad += int((nrm[:16].cpu().numpy() != want).sum())
+        want = orc.rope(self.q_pe[:, :8].cpu().numpy(), self.table.view(self.T, -1, 2)[:8].cpu().numpy(), 42)
+        bad += int((rot[:, :8].cpu().numpy() != want).sum())
+        sl = slice(self.T - 2, self.T)
+        bad += int((self.probs[:, sl].cpu().numpy() != orc.softmax(self.scores[:, sl].cpu().numpy(), 19)).sum())
+        bad += int((self.act_out[:, :4].cpu().numpy() != orc.act(self.act[:, :4].cpu().numpy(), "silu", 23)).sum())
+        return bad
+
+    @staticmethod
+    def cpu_sample(orc, np, seconds, rank=0):
+        """the chain on a bounded token sample (softmax rows stay 2048 long)"""
+        T, rows = ChainWorkload.T, 8
+        rng = np.random.default_rng(3)
+        while True:
+            x = np.rint(rng.standard_normal((rows, 7168)) * 2**16).astype(np.int64)
+            w = (2**16 + np.rint(rng.standard_normal(7168) * 2**8)).astype(np.int32)
+            q = np.rint(rng.standard_normal((1, rows, 128, 32, 2)) * 2**16).astype(np.int64)
+            tab = np.rint(rng.uniform(-1, 1, (rows, 32, 2)) * 2**42).astype(np.int64)
+            sc = np.rint(rng.standard_normal((1, rows, 128, T)) * 4 * 2**16).astype(np.int64)
+            a = np.rint(rng.standard_normal((1, rows, 18432)) * 2**16).astype(np.int64)
+            t0 = time.time()
+            orc.rms_norm(x, w, 1, 7168)
+            orc.rope(q, tab, 42)
+            orc.softmax(sc, 19)
+            orc.act(a, "silu", 23)
+            dt = time.time() - t0
+            if dt > seconds / 4 or rows >= 256:
+                return rows / dt, "%d of %d tokens through all four kernels" % (rows, T), dt
+            rows = min(256, int(rows * max(2.0, 0.8 * seconds / max(dt, 1e-3))))
+
+
 class GemmProfWorkload(GemmWorkload):
     """Smaller GEMM of the same kernel for profiler captures (inputs still exceed L2)."""
     name = "gemm_4096x8192x4096"
@@ -191,7 +343,18 @@ class GemmProfWorkload(GemmWorkload):
         return GemmWorkload.cpu_sample(orc, np, seconds, rank)
 
 
-WORKLOADS = {"gemm": GemmWorkload, "gemm_prof": GemmProfWorkload}
+class ChainProfWorkload(ChainWorkload):
+    """The chain at T = 1024 for profiler captures (softmax tensor 1 GB, still far beyond L2)."""
+    name = "fixedpoint_chain_T1024"
+    T = 1024
+
+    @staticmethod
+    def cpu_sample(orc, np, seconds, rank=0):
+        return ChainWorkload.cpu_sample(orc, np, seconds, rank)
+
+
+WORKLOADS = {"gemm": GemmWorkload, "gemm_prof": GemmProfWorkload, "chain": ChainWorkload,
+             "chain_prof": ChainProfWorkload}
 DEFAULT_WORKLOAD = "gemm"
 
 
@@ -286,7 +449,7 @@ def main():
     # per-launch duration of the dominant kernel, CUDA events recorded around it on its stream
     for _ in range(min(args.steps, 10)):
         wl.step()
-        kernel_ms.append(k.last_kernel_ms())
+        kernel_ms.append(max(k.last_kernel_ms(), 0.0))
     k.kernel_timing(False)
     k.device_status()
     t = torch.tensor([elapsed], dtype=torch.float64, device=dev)
