@@ -60,6 +60,11 @@ int zkds_device_status(int clear);
                                    every s >= 32 (observed with its nvcc 12.9 build on a B200).
                                    Default: R = sum mod 2^s. */
 
+#define ZKDS_LIMBS_DYNAMIC 8    /* a_limbs > 0 is an upper bound on the limbs of A: the count
+                                   actually needed is derived on the device from the range seen
+                                   while A is split (no host synchronisation).  Data beyond the
+                                   bound raises the flag zkds_device_status reports. */
+
 /* =============================================================================
  * Group 1 — the reference's symbols (same names, same argument lists)
  * ========================================================================== */
@@ -167,6 +172,28 @@ int zkds_einsum_bshc_hdc_bshd(const int64_t* A, const int32_t* W, int64_t* out, 
                               int64_t B, int64_t S, int64_t H, int64_t D, int64_t C, int a_limbs,
                               int b_limbs, int flags, void* stream);
 
+/* einsum_bshc_btc_bsht (int64_gemm.cu:458-467) with the element-wise tail of the attention
+ * scores fused into its epilogue (model.py:897-905): v = quotient; v += addin[b,s,h,t] if addin;
+ * v = floor(v * ep_mul / ep_div) if ep_div (wrapping int64 multiply, floor division as torch's //);
+ * v += mask_value where causal and t > start_pos + s.  MLA uses it as
+ * scores = (score1 + score2) * 94 // 695 + mask with score1 passed as addin. */
+int zkds_einsum_bshc_btc_bsht_ex(const int64_t* A, const int64_t* KV, int64_t* out, int64_t rescale,
+                                 int64_t B, int64_t S, int64_t H, int64_t T, int64_t C,
+                                 const int64_t* addin, int64_t ep_mul, int64_t ep_div, int causal,
+                                 int64_t start_pos, int64_t mask_value, int a_limbs, int b_limbs,
+                                 int flags, void* stream);
+
+/* Grouped linear layer for the routed experts (replaces the per-expert Python loop of
+ * MoE.forward, model.py:1355-1379): A is a flat [n_tiles*128, K] int64 matrix whose i-th
+ * 128-row tile holds tokens of expert tile_group[i] (device array; negative = unused tile),
+ * planes hold every expert's weight (nb = experts).  C [n_tiles*128, N] = (addend + A W_g^T) >> shift.
+ * group_shift (device, may be null): per-expert shifts, [2g] for output columns < n_split and
+ * [2g+1] from n_split on (n_split a multiple of 8) — each expert's w1, w3, w2 carry their own
+ * shift (model.py:231-232) and w1|w3 may be stacked into one weight. */
+int zkds_grouped_prepared(const int64_t* A, const void* planes, const int* tile_group, int64_t n_tiles,
+                          int64_t* C, int64_t a_rescale, int64_t addend, int64_t shift,
+                          const int* group_shift, int64_t n_split, int a_limbs, int flags, void* stream);
+
 /* Replaces complex_int64_mul (int64_gemm.cu:274-286) with the product shift as a
  * parameter (the reference hard-codes 42). */
 int zkds_rope(const int64_t* A, const int64_t* table, int64_t* C, int64_t batch, int64_t seq,
@@ -214,6 +241,22 @@ int zkds_contraction_prepared(const int64_t* A, int64_t a_s_batch, int64_t a_s_r
  * waits for the most recent pair and returns its duration (< 0 if there is none). */
 void zkds_timing(int enable);
 float zkds_last_kernel_ms(void);
+
+/* Tail of the gated MLP (model.py:1034-1048, 1266-1280): h = (silu_q23(r1) * r2) >> 23 with a
+ * wrapping int64 product.  r1, r2: rows x n with row stride ld (both halves of a fused w1|w3
+ * GEMM output can be passed in place); h dense rows x n; s1_out (may be null) receives
+ * silu_q23(r1) for the zk dump.  n and ld even, pointers 16-byte aligned. */
+int zkds_glu_q23(const int64_t* r1, const int64_t* r2, int64_t ld, int64_t* h, int64_t* s1_out,
+                 const int64_t* lut, int64_t rows, int64_t n, void* stream);
+/* Expert dispatch (replaces x[idx] per expert, model.py:1372-1374): dst[r] = src[index[r]], zeros
+ * where index[r] < 0.  cols even. */
+int zkds_gather_rows(const int64_t* src, const int* index, int64_t* dst, int64_t rows, int64_t cols,
+                     void* stream);
+/* Expert combine (replaces y[idx] += y2 * w // 2^23 and the final y + z, model.py:1379-1383):
+ * y[t] = base[t] + sum_slot floor(out[pos[t][slot]] * w[t][slot] / 2^23); pos < 0 skips the slot;
+ * base may be null. */
+int zkds_moe_combine(const int64_t* out, const int* pos, const int64_t* w, const int64_t* base,
+                     int64_t* y, int64_t tokens, int slots, int64_t cols, void* stream);
 
 /* Replaces the four *_init_* functions.  HOST table of 256 entries.
  * kind: 0 softmax Q19, 1 softmax Q21, 2 silu Q23, 3 silu Q25. */

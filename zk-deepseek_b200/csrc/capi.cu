@@ -118,6 +118,8 @@ static int run_contraction(const Contraction& p, int a_limbs, int b_limbs, int f
     if (p.b_bits != 32 && p.b_bits != 64) return ZKDS_ERR_ARG;
     if (algo == ZKDS_ALGO_EXACT) return pre_b ? ZKDS_ERR_ARG : launch_contraction_exact(p, st);
     if (pre_b) b_limbs = pre_b->L;
+    Contraction pd = p;
+    pd.dynamic_a = ((flags & ZKDS_LIMBS_DYNAMIC) && a_limbs > 0) ? 1 : 0;
 
     if (a_limbs <= 0 || b_limbs <= 0) {
         uint64_t* d = (uint64_t*)workspace(2 * sizeof(uint64_t), 5);
@@ -137,7 +139,7 @@ static int run_contraction(const Contraction& p, int a_limbs, int b_limbs, int f
         if (a_limbs <= 0) a_limbs = limbs_needed(h[0]);
         if (b_limbs <= 0) b_limbs = limbs_needed(h[1]);
     }
-    int rc = launch_contraction_limb(p, a_limbs, b_limbs, pre_b, st);
+    int rc = launch_contraction_limb(pd, a_limbs, b_limbs, pre_b, st);
     if (rc == ZKDS_ERR_UNSUPPORTED && algo == ZKDS_ALGO_AUTO && !pre_b) rc = launch_contraction_exact(p, st);
     return rc;
 }
@@ -329,6 +331,41 @@ int zkds_einsum_bshc_hdc_bshd(const int64_t* A, const int32_t* W, int64_t* out, 
                   "zkds_einsum_bshc_hdc_bshd");
 }
 
+int zkds_einsum_bshc_btc_bsht_ex(const int64_t* A, const int64_t* KV, int64_t* out, int64_t rescale,
+                                 int64_t B, int64_t S, int64_t H, int64_t T, int64_t C,
+                                 const int64_t* addin, int64_t ep_mul, int64_t ep_div, int causal,
+                                 int64_t start_pos, int64_t mask_value, int a_limbs, int b_limbs,
+                                 int flags, void* stream)
+{
+    Contraction p = einsum_problem(1, A, KV, out, rescale, B, S, H, T, C);
+    p.addin = addin; p.ep_mul = ep_mul; p.ep_div = ep_div;
+    p.causal_H = causal ? H : 0; p.causal_start = start_pos; p.mask_value = mask_value;
+    return finish(run_contraction(p, a_limbs, b_limbs, flags, ST(stream)),
+                  "zkds_einsum_bshc_btc_bsht_ex");
+}
+
+int zkds_grouped_prepared(const int64_t* A, const void* planes, const int* tile_group, int64_t n_tiles,
+                          int64_t* C, int64_t a_rescale, int64_t addend, int64_t shift,
+                          const int* group_shift, int64_t n_split, int a_limbs, int flags, void* stream)
+{
+    if (!planes || !tile_group || n_tiles < 0 || (group_shift && (n_split & 7)))
+        return finish(ZKDS_ERR_ARG, "zkds_grouped_prepared");
+    const PlanesHandle* hd = (const PlanesHandle*)planes;
+    Contraction p{};
+    p.A = A; p.B = nullptr; p.b_bits = hd->b_bits; p.C = C; p.R = nullptr;
+    p.batches = 1; p.M = n_tiles * 128; p.N = hd->pl.rows; p.K = hd->pl.K;
+    p.a_sz = 0; p.a_sm = hd->pl.K;
+    p.b_sz = 1; p.b_sn = 0; p.b_sk = 0;
+    p.c_sz = 0; p.c_sm = hd->pl.rows;
+    p.a_div = a_rescale; p.b_div = 1;
+    p.addend = addend;
+    p.shift = (shift < 0 || shift > 127) ? -1 : (int)shift;
+    p.tile_group = tile_group;
+    p.group_shift = group_shift; p.n_split = n_split;
+    int f = (flags & ~ZKDS_ALGO_MASK) | ZKDS_ALGO_LIMB;
+    return finish(run_contraction(p, a_limbs, 0, f, ST(stream), &hd->pl), "zkds_grouped_prepared");
+}
+
 int zkds_rope(const int64_t* A, const int64_t* table, int64_t* C, int64_t batch, int64_t seq,
               int64_t heads, int64_t pairs, int shift, void* stream)
 {
@@ -455,6 +492,33 @@ int zkds_contraction_prepared(const int64_t* A, int64_t a_s_batch, int64_t a_s_r
     p.r_legacy = (flags & ZKDS_REMAINDER_LEGACY) ? 1 : 0;
     int f = (flags & ~ZKDS_ALGO_MASK) | ZKDS_ALGO_LIMB;
     return finish(run_contraction(p, a_limbs, 0, f, ST(stream), &hd->pl), "zkds_contraction_prepared");
+}
+
+int zkds_glu_q23(const int64_t* r1, const int64_t* r2, int64_t ld, int64_t* h, int64_t* s1_out,
+                 const int64_t* lut, int64_t rows, int64_t n, void* stream)
+{
+    int rc = (rows < 0 || n < 0 || (rows && n && (!r1 || !r2 || !h || !lut)))
+                 ? ZKDS_ERR_ARG
+                 : launch_glu(r1, r2, ld, h, s1_out, lut, rows, n, ST(stream));
+    return finish(rc, "zkds_glu_q23");
+}
+
+int zkds_gather_rows(const int64_t* src, const int* index, int64_t* dst, int64_t rows, int64_t cols,
+                     void* stream)
+{
+    int rc = (rows < 0 || cols < 0 || (rows && cols && (!src || !index || !dst)))
+                 ? ZKDS_ERR_ARG
+                 : launch_gather_rows(src, index, dst, rows, cols, ST(stream));
+    return finish(rc, "zkds_gather_rows");
+}
+
+int zkds_moe_combine(const int64_t* out, const int* pos, const int64_t* w, const int64_t* base,
+                     int64_t* y, int64_t tokens, int slots, int64_t cols, void* stream)
+{
+    int rc = (tokens < 0 || cols < 0 || slots < 0 || (tokens && cols && (!out || !pos || !w || !y)))
+                 ? ZKDS_ERR_ARG
+                 : launch_moe_combine(out, pos, w, base, y, tokens, slots, cols, ST(stream));
+    return finish(rc, "zkds_moe_combine");
 }
 
 int zkds_lut(int64_t* host_lut, int kind) { return finish(make_lut(host_lut, kind), "zkds_lut"); }

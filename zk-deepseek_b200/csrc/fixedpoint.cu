@@ -567,4 +567,110 @@ int launch_rmsnorm(const int64_t* A, const void* W, int w_bits, const int64_t* r
     return ZKDS_ERR_ARG;
 }
 
+// ------------------------------------------------------------------------------
+// gated MLP tail, expert dispatch and combine
+// ------------------------------------------------------------------------------
+
+// h = (silu_q23(r1) * r2) >> 23 (wrapping product, arithmetic shift: model.py:1048, 1280);
+// r1/r2 are rows of length n with row stride ld (so both halves of one fused w1|w3 GEMM output
+// can be read in place); s1_out (optional, dense) receives silu(r1) for the zk dump.
+__global__ void __launch_bounds__(kThreads)
+glu_kernel(const int64_t* __restrict__ r1, const int64_t* __restrict__ r2, int64_t ld,
+           int64_t* __restrict__ h, int64_t* __restrict__ s1_out, const int64_t* __restrict__ lut_g,
+           int64_t rows, int64_t n)
+{
+    __shared__ int64_t lut[256];
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) lut[i] = lut_g[i];
+    __syncthreads();
+    const int64_t nv = n >> 1;  // n is even (checked by the launcher)
+    const int64_t total = rows * nv;
+    for (int64_t t = (int64_t)blockIdx.x * kThreads + threadIdx.x; t < total;
+         t += (int64_t)gridDim.x * kThreads) {
+        const int64_t row = t / nv, c = (t - row * nv) << 1;
+        const longlong2 a = *reinterpret_cast<const longlong2*>(r1 + row * ld + c);
+        const longlong2 b = *reinterpret_cast<const longlong2*>(r2 + row * ld + c);
+        longlong2 sv, o;
+        sv.x = act_one<23, true>(a.x, lut);
+        sv.y = act_one<23, true>(a.y, lut);
+        o.x = (int64_t)((uint64_t)sv.x * (uint64_t)b.x) >> 23;
+        o.y = (int64_t)((uint64_t)sv.y * (uint64_t)b.y) >> 23;
+        *reinterpret_cast<longlong2*>(h + row * n + c) = o;
+        if (s1_out) *reinterpret_cast<longlong2*>(s1_out + row * n + c) = sv;
+    }
+}
+
+int launch_glu(const int64_t* r1, const int64_t* r2, int64_t ld, int64_t* h, int64_t* s1_out,
+               const int64_t* lut, int64_t rows, int64_t n, cudaStream_t st)
+{
+    if (rows == 0 || n == 0) return ZKDS_OK;
+    if ((n & 1) || (ld & 1) ||
+        ((((uintptr_t)r1 | (uintptr_t)r2 | (uintptr_t)h | (uintptr_t)s1_out) & 15) != 0))
+        return ZKDS_ERR_ARG;
+    int grid = grid_for(rows * (n / 2), kThreads, sm_count(), 16);
+    glu_kernel<<<grid, kThreads, 0, st>>>(r1, r2, ld, h, s1_out, lut, rows, n);
+    return check_launch();
+}
+
+// dst[r][:] = src[index[r]][:] for index[r] >= 0, zeros otherwise (token rows -> expert order)
+__global__ void __launch_bounds__(kThreads)
+gather_rows_kernel(const longlong2* __restrict__ src, const int* __restrict__ index,
+                   longlong2* __restrict__ dst, int64_t cols2)
+{
+    const int64_t r = blockIdx.x;
+    const int i = index[r];
+    longlong2* d = dst + r * cols2;
+    if (i < 0) {
+        for (int64_t c = threadIdx.x; c < cols2; c += kThreads) d[c] = make_longlong2(0, 0);
+    } else {
+        const longlong2* sp = src + (int64_t)i * cols2;
+        for (int64_t c = threadIdx.x; c < cols2; c += kThreads) d[c] = sp[c];
+    }
+}
+
+int launch_gather_rows(const int64_t* src, const int* index, int64_t* dst, int64_t rows, int64_t cols,
+                       cudaStream_t st)
+{
+    if (rows == 0 || cols == 0) return ZKDS_OK;
+    if ((cols & 1) || rows > 0x7fffffffll || ((((uintptr_t)src | (uintptr_t)dst) & 15) != 0))
+        return ZKDS_ERR_ARG;
+    gather_rows_kernel<<<(unsigned)rows, kThreads, 0, st>>>(
+        reinterpret_cast<const longlong2*>(src), index, reinterpret_cast<longlong2*>(dst), cols / 2);
+    return check_launch();
+}
+
+// y[t][:] = base[t][:] + sum_slot floor(out[pos[t][slot]][:] * w[t][slot] / 2^23)   (model.py:1379-1383:
+// wrapping int64 product, floor division by 2^23, order-free integer sum); pos < 0 skips a slot
+__global__ void __launch_bounds__(kThreads)
+moe_combine_kernel(const longlong2* __restrict__ out, const int* __restrict__ pos,
+                   const int64_t* __restrict__ w, const longlong2* __restrict__ base,
+                   longlong2* __restrict__ y, int slots, int64_t cols2)
+{
+    const int64_t t = blockIdx.x;
+    for (int64_t c = threadIdx.x; c < cols2; c += kThreads) {
+        longlong2 acc = base ? base[t * cols2 + c] : make_longlong2(0, 0);
+        for (int s = 0; s < slots; ++s) {
+            const int r = pos[t * slots + s];
+            if (r < 0) continue;
+            const int64_t ws = w[t * slots + s];
+            const longlong2 v = out[(int64_t)r * cols2 + c];
+            acc.x = (int64_t)((uint64_t)acc.x + (uint64_t)((int64_t)((uint64_t)v.x * (uint64_t)ws) >> 23));
+            acc.y = (int64_t)((uint64_t)acc.y + (uint64_t)((int64_t)((uint64_t)v.y * (uint64_t)ws) >> 23));
+        }
+        y[t * cols2 + c] = acc;
+    }
+}
+
+int launch_moe_combine(const int64_t* out, const int* pos, const int64_t* w, const int64_t* base,
+                       int64_t* y, int64_t tokens, int slots, int64_t cols, cudaStream_t st)
+{
+    if (tokens == 0 || cols == 0) return ZKDS_OK;
+    if ((cols & 1) || tokens > 0x7fffffffll ||
+        ((((uintptr_t)out | (uintptr_t)base | (uintptr_t)y) & 15) != 0))
+        return ZKDS_ERR_ARG;
+    moe_combine_kernel<<<(unsigned)tokens, kThreads, 0, st>>>(
+        reinterpret_cast<const longlong2*>(out), pos, w, reinterpret_cast<const longlong2*>(base),
+        reinterpret_cast<longlong2*>(y), slots, cols / 2);
+    return check_launch();
+}
+
 }  // namespace zkds

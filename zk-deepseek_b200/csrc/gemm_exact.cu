@@ -87,7 +87,16 @@ __global__ void __launch_bounds__(THREADS) exact_kernel(Contraction p)
         for (int j = 0; j < 4; ++j) {
             int64_t n = n0 + tx * 4 + j;
             if (n >= p.N) continue;
-            C[m * p.c_sm + n] = sar128_lo(acc[i][j], p.shift);
+            int64_t v = sar128_lo(acc[i][j], p.shift);
+            if (p.addin) v = (int64_t)((uint64_t)v + (uint64_t)p.addin[z * p.c_sz + m * p.c_sm + n]);
+            if (p.ep_div) {
+                int64_t t = (int64_t)((uint64_t)v * (uint64_t)p.ep_mul);
+                int64_t qd = t / p.ep_div, rd = t % p.ep_div;
+                v = (rd != 0 && ((rd < 0) != (p.ep_div < 0))) ? qd - 1 : qd;
+            }
+            if (p.causal_H && n > p.causal_start + m / p.causal_H)
+                v = (int64_t)((uint64_t)v + (uint64_t)p.mask_value);
+            C[m * p.c_sm + n] = v;
             if (R) R[m * p.c_sm + n] = gemm_remainder(acc[i][j], p.shift, p.r_legacy);
         }
     }
@@ -98,6 +107,7 @@ __global__ void __launch_bounds__(THREADS) exact_kernel(Contraction p)
 int launch_contraction_exact(const Contraction& p, cudaStream_t st)
 {
     if (p.batches == 0 || p.M == 0 || p.N == 0) return ZKDS_OK;
+    if (p.tile_group) return ZKDS_ERR_UNSUPPORTED;
     int64_t gx = (p.M + TM - 1) / TM, gy = (p.N + TN - 1) / TN;
     if (gx > 0x7fffffffll || gy > 65535) return ZKDS_ERR_RANGE;
     if (p.batches > 65535) {

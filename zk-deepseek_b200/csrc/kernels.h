@@ -20,6 +20,13 @@ int launch_rmsnorm(const int64_t* A, const void* W, int w_bits, const int64_t* r
                    int64_t* rms_out, int64_t* C, int64_t M, int64_t N, int64_t eps, int64_t dim,
                    int fused, cudaStream_t st);
 
+int launch_glu(const int64_t* r1, const int64_t* r2, int64_t ld, int64_t* h, int64_t* s1_out,
+               const int64_t* lut, int64_t rows, int64_t n, cudaStream_t st);
+int launch_gather_rows(const int64_t* src, const int* index, int64_t* dst, int64_t rows, int64_t cols,
+                       cudaStream_t st);
+int launch_moe_combine(const int64_t* out, const int* pos, const int64_t* w, const int64_t* base,
+                       int64_t* y, int64_t tokens, int slots, int64_t cols, cudaStream_t st);
+
 // ---- contractions ---------------------------------------------------------------
 // One batched contraction  C[z][m][n] = (addend + sum_k A(z,m,k) * B(z,n,k)) >> shift
 // with the sum held in 128 bits.  A is int64 with unit k-stride; B is int32 or int64
@@ -39,6 +46,23 @@ struct Contraction {
     int64_t addend;
     int shift;     // 0..127
     int r_legacy;  // remainder flavour, see gemm_remainder()
+    // ---- optional extensions (all zero = plain contraction) ----
+    // epilogue: v = quotient; v += addin[z][m][n] (same layout as C); v = floor(v * ep_mul / ep_div)
+    // when ep_div != 0 (wrapping multiply); rows are (s, h) pairs with causal_H heads per s:
+    // v += mask_value where n > causal_start + m / causal_H
+    const int64_t* addin;
+    int64_t ep_mul, ep_div;
+    int64_t causal_H, causal_start, mask_value;
+    // a_limbs passed to the limb kernel is an upper bound; the count needed is derived on the
+    // device from the range measured while splitting A (no host synchronisation)
+    int dynamic_a;
+    // grouped mode (limb kernel only): batches == 1, A is a flat [M, K] matrix, tile_group[i]
+    // gives the B batch of the i-th 128-row tile (negative: tile skipped)
+    const int* tile_group;
+    // grouped mode: shift per group, [2g] for columns < n_split, [2g+1] from n_split on (values in
+    // 0..127, n_split a multiple of 8); null = the uniform shift
+    const int* group_shift;
+    int64_t n_split;
 };
 
 // CUDA-core path: exact for every input, any shape (gemm_exact.cu)

@@ -63,8 +63,9 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 split_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, int64_t rows, int64_t K,
              int64_t Kp, int64_t sz, int64_t sr, int64_t sk, int64_t div, int64_t plane_stride,
-             unsigned* overflow)
+             unsigned* overflow, unsigned long long* absmax_out)
 {
+    uint64_t seen = 0;
     const int64_t chunks = Kp >> 4;
     const int64_t total = rows * chunks;
     const int64_t z = blockIdx.y;
@@ -90,6 +91,11 @@ split_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, int64_
                 v = (int64_t)x[r * sr + k * sk];
                 if (div != 1) v = v / div;
             }
+            {
+                // |v| for v >= 0, |v| - 1 for v < 0: balanced digits reach one further down
+                uint64_t a = (uint64_t)(v ^ (v >> 63));
+                seen = a > seen ? a : seen;
+            }
 #pragma unroll
             for (int l = 0; l < 9; ++l) {
                 if (l < L) {
@@ -106,6 +112,10 @@ split_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, int64_
                 *reinterpret_cast<uint4*>(dst + l * plane_stride) =
                     make_uint4(w[l][0], w[l][1], w[l][2], w[l][3]);
         if (ovf) *overflow = 1u;
+    }
+    if (absmax_out) {
+        seen = warp_max_u64(seen);
+        if ((threadIdx.x & 31) == 0 && seen) atomicMax(absmax_out, (unsigned long long)seen);
     }
 }
 
@@ -263,7 +273,39 @@ struct LimbParams {
     int64_t addend;
     int shift, r_legacy;
     int* error_flag;          // host-mapped
+    // La is an upper bound when a_absmax is set: the kernel derives the limb count actually
+    // needed from the range the split pass measured and skips the all-zero upper limbs
+    const unsigned long long* a_absmax;
+    unsigned* overflow_flag;
+    // grouped mode: A is one flat [M, K] matrix whose 128-row tiles each belong to one group
+    // (expert); tile_group[tile] selects the B batch, a negative entry skips the tile
+    const int* tile_group;
+    // grouped mode: per-group shift, group_shift[2g] for columns < n_split and [2g+1] from
+    // n_split on (n_split a multiple of 8); null = the uniform shift above
+    const int* group_shift;
+    int64_t n_split;
+    // epilogue extension: v = quotient; v += addin[m][n]; v = floor(v * ep_mul / ep_div);
+    // rows are (s, h) pairs with causal_H heads: v += mask_value where n > causal_start + s
+    const int64_t* addin;
+    int64_t ep_mul, ep_div;
+    int64_t causal_H, causal_start, mask_value;
 };
+
+__device__ __forceinline__ int limbs_needed_dev(unsigned long long maxabs)
+{
+    unsigned long long cover = 0;
+    for (int L = 1; L <= 8; ++L) {
+        cover = cover * 256ull + 127ull;
+        if (maxabs <= cover) return L;
+    }
+    return 9;
+}
+
+__device__ __forceinline__ int64_t floor_div_i64(int64_t a, int64_t b)
+{
+    int64_t q = a / b, r = a % b;
+    return (r != 0 && ((r < 0) != (b < 0))) ? q - 1 : q;
+}
 
 __global__ void __launch_bounds__(kThreads, 1)
 limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -275,6 +317,18 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     __shared__ int s_abort;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int group = 0;
+    if (p.tile_group) {
+        group = p.tile_group[blockIdx.x];
+        if (group < 0) return;  // uniform for the CTA, before any barrier or allocation
+    }
+    int La = p.La;
+    if (p.a_absmax) {
+        const int need = limbs_needed_dev(*p.a_absmax);
+        if (need > La) {
+            if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) *p.overflow_flag = 1u;
+        } else La = need;
+    }
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t a_bytes = (uint32_t)p.La * kTileM * kBlockK;
     const uint32_t b_bytes = (uint32_t)p.Lb * p.NT * kBlockK;
@@ -287,7 +341,7 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int64_t m0 = (int64_t)blockIdx.x * kTileM;
     const int64_t n0 = (int64_t)blockIdx.y * p.NT;
     const int64_t z = blockIdx.z;
-    const int D = p.La + p.Lb - 1;
+    const int D = La + p.Lb - 1;
 
     if (threadIdx.x == 0) {
         s_abort = 0;
@@ -310,17 +364,18 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (warp == 0) {
         // ---- TMA producer -------------------------------------------------------------
         if (lane == 0) {
-            const int64_t zb = p.b_batched ? z : 0;
+            const int64_t zb = p.tile_group ? group : (p.b_batched ? z : 0);
+            const uint32_t tx_bytes = (uint32_t)La * kTileM * kBlockK + b_bytes;
             int armed = 0;
             for (int kb = 0; kb < p.kblocks; ++kb) {
                 const int s = kb % p.stages;
                 const uint32_t par = ((kb / p.stages) & 1) ^ 1;
                 if (!mbar_wait(bar_empty + 8 * s, par, abort_flag)) break;
                 const uint32_t full = bar_full + 8 * s;
-                mbar_expect_tx(full, stage_bytes);
+                mbar_expect_tx(full, tx_bytes);
                 const uint32_t sa = smem_base + s * stage_bytes;
                 const uint32_t sb = sa + a_bytes;
-                for (int i = 0; i < p.La; ++i)
+                for (int i = 0; i < La; ++i)
                     tma_load_2d(sa + i * (kTileM * kBlockK), &tmA, kb * kBlockK,
                                 (int)(i * p.a_rows_per_limb + z * p.M + m0), full);
                 for (int j = 0; j < p.Lb; ++j)
@@ -354,7 +409,7 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 const uint64_t bdesc0 = smem_desc_sw128(sa + a_bytes);
 #pragma unroll
                 for (int ks = 0; ks < kBlockK / 32; ++ks) {
-                    for (int i = 0; i < p.La; ++i) {
+                    for (int i = 0; i < La; ++i) {
                         const uint64_t adesc = smem_desc_sw128(sa + i * (kTileM * kBlockK)) + (uint64_t)(ks * 2);
                         umma_i8(tmem + (uint32_t)(i * p.NT), adesc, bdesc0 + (uint64_t)(ks * 2), idesc, 1u);
                     }
@@ -412,12 +467,27 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
             if (row_ok) {
                 int64_t cv[8], rv[8];
+                const int64_t n = n0 + nc;
+                const int shift = p.group_shift ? p.group_shift[2 * group + (n >= p.n_split ? 1 : 0)] : p.shift;
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
-                    cv[c] = sar128_lo(sum[c], p.shift);
-                    rv[c] = gemm_remainder(sum[c], p.shift, p.r_legacy);
+                    cv[c] = sar128_lo(sum[c], shift);
+                    rv[c] = gemm_remainder(sum[c], shift, p.r_legacy);
                 }
-                const int64_t n = n0 + nc;
+                if (p.addin || p.ep_div || p.causal_H) {
+                    const int64_t* arow = p.addin ? p.addin + z * p.c_sz + m * p.c_sm : nullptr;
+                    const int64_t srow = p.causal_H ? m / p.causal_H : 0;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        if (n + c >= p.N) continue;
+                        int64_t v = cv[c];
+                        if (arow) v = (int64_t)((uint64_t)v + (uint64_t)arow[n + c]);
+                        if (p.ep_div) v = floor_div_i64((int64_t)((uint64_t)v * (uint64_t)p.ep_mul), p.ep_div);
+                        if (p.causal_H && n + c > p.causal_start + srow)
+                            v = (int64_t)((uint64_t)v + (uint64_t)p.mask_value);
+                        cv[c] = v;
+                    }
+                }
                 if (vec_ok && n + 8 <= p.N) {
 #pragma unroll
                     for (int c = 0; c < 8; c += 2) {
@@ -509,7 +579,8 @@ DeviceFlags* flags_for_device()
 
 template <typename T>
 int launch_split_t(const T* X, int8_t* planes, int L, int64_t nb, int64_t rows, int64_t K, int64_t Kp,
-                   int64_t sz, int64_t sr, int64_t sk, int64_t div, unsigned* overflow, cudaStream_t st)
+                   int64_t sz, int64_t sr, int64_t sk, int64_t div, unsigned* overflow, cudaStream_t st,
+                   unsigned long long* absmax_out = nullptr)
 {
     int64_t total = rows * (Kp >> 4);
     int64_t bx = (total + 255) / 256;
@@ -517,7 +588,8 @@ int launch_split_t(const T* X, int8_t* planes, int L, int64_t nb, int64_t rows, 
     if (bx > cap) bx = cap;
     if (nb > 65535) return ZKDS_ERR_RANGE;
     dim3 grid((unsigned)bx, (unsigned)nb);
-    split_kernel<T><<<grid, 256, 0, st>>>(X, planes, L, rows, K, Kp, sz, sr, sk, div, nb * rows * Kp, overflow);
+    split_kernel<T><<<grid, 256, 0, st>>>(X, planes, L, rows, K, Kp, sz, sr, sk, div, nb * rows * Kp, overflow,
+                                          absmax_out);
     return check_launch();
 }
 
@@ -635,7 +707,8 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     int stages = (int)(smem_max / stage);
     if (stages > 8) stages = 8;
     const int64_t Kp = (p.K + 15) & ~(int64_t)15;
-    const int64_t nbB = p.b_sz ? p.batches : 1;
+    const int64_t nbB = p.tile_group ? (pre_b ? pre_b->nb : 0) : (p.b_sz ? p.batches : 1);
+    if (p.tile_group && (!pre_b || p.batches != 1)) return ZKDS_ERR_ARG;
     const int64_t a_rows = p.batches * p.M, b_rows = nbB * p.N;
     if (a_rows * La > 0x7fffff00ll || b_rows * Lb > 0x7fffff00ll || Kp > 0x7fffff00ll) return ZKDS_ERR_UNSUPPORTED;
     const int64_t mt = (p.M + kTileM - 1) / kTileM, nt = (p.N + NT - 1) / NT;
@@ -646,7 +719,16 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     if (!fl) return ZKDS_ERR_WORKSPACE;
     int8_t* pa = (int8_t*)workspace((size_t)La * a_rows * Kp + 1024, 0);
     if (!pa) return ZKDS_ERR_WORKSPACE;
-    int rc = planes_split(p.A, 64, p.batches, p.M, p.K, p.a_sz, p.a_sm, 1, p.a_div, La, pa, st);
+    unsigned long long* d_absmax = nullptr;
+    if (p.dynamic_a) {
+        unsigned long long* words = (unsigned long long*)workspace(8 * sizeof(uint64_t), 5);
+        if (!words) return ZKDS_ERR_WORKSPACE;
+        d_absmax = words + 2;
+        ZKDS_CUDA(cudaMemsetAsync(d_absmax, 0, sizeof(uint64_t), st));
+    }
+    const int64_t Kp16 = Kp;
+    int rc = launch_split_t<int64_t>(p.A, pa, La, p.batches, p.M, p.K, Kp16, p.a_sz, p.a_sm, 1, p.a_div,
+                                     fl->overflow_dev, st, d_absmax);
     if (rc != ZKDS_OK) return rc;
     int8_t* pb;
     if (pre_b) pb = pre_b->data;
@@ -673,6 +755,12 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     lp.C = p.C; lp.R = p.R; lp.c_sz = p.c_sz; lp.c_sm = p.c_sm;
     lp.addend = p.addend; lp.shift = p.shift; lp.r_legacy = p.r_legacy;
     lp.error_flag = fl->dev;
+    lp.a_absmax = d_absmax;
+    lp.overflow_flag = fl->overflow_dev;
+    lp.tile_group = p.tile_group;
+    lp.group_shift = p.group_shift; lp.n_split = p.n_split;
+    lp.addin = p.addin; lp.ep_mul = p.ep_mul; lp.ep_div = p.ep_div;
+    lp.causal_H = p.causal_H; lp.causal_start = p.causal_start; lp.mask_value = p.mask_value;
 
     size_t smem = stage * stages + 1024;
     // more than half the shared memory per CTA keeps one CTA per SM, so its tensor-memory

@@ -32,6 +32,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 
 ALGO_AUTO, ALGO_EXACT, ALGO_LIMB = 0, 1, 2
 REMAINDER_LEGACY = 4
+LIMBS_DYNAMIC = 8
 
 # Remainder flavour of int64_bmm_broadcast.  True reproduces the reference binary:
 # exact for c_rescale <= 31, the low 32 bits of the sum above that
@@ -88,6 +89,12 @@ _sig("zkds_last_kernel_ms", [], ctypes.c_float)
 _sig("zkds_planes_create", [_vp, _i, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _i, ctypes.POINTER(_vp), _vp])
 _sig("zkds_planes_limbs", [_vp])
 _sig("zkds_planes_destroy", [_vp])
+_sig("zkds_einsum_bshc_btc_bsht_ex", [_vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _vp, _ll, _ll, _i, _ll,
+                                      _ll, _i, _i, _i, _vp])
+_sig("zkds_grouped_prepared", [_vp, _vp, _vp, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _i, _i, _vp])
+_sig("zkds_glu_q23", [_vp, _vp, _ll, _vp, _vp, _vp, _ll, _ll, _vp])
+_sig("zkds_gather_rows", [_vp, _vp, _vp, _ll, _ll, _vp])
+_sig("zkds_moe_combine", [_vp, _vp, _vp, _vp, _vp, _ll, _i, _ll, _vp])
 _sig("zkds_contraction_prepared", [_vp, _ll, _ll, _vp, _i, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _ll,
                                    _i, _i, _vp])
 
@@ -227,6 +234,23 @@ def last_kernel_ms():
     return float(lib.zkds_last_kernel_ms())
 
 
+def limb_kernel_takes(K, a_limbs, b_limbs):
+    """True when the tensor-core limb kernel handles a contraction of depth K with these limb
+    counts (mirrors the launcher: int32 diagonal bound, tile and pipeline fit)."""
+    if K <= 0 or not (1 <= a_limbs <= 9 and 1 <= b_limbs <= 9):
+        return False
+    if min(a_limbs, b_limbs) * K >= 131072:
+        return False
+    diagonals = a_limbs + b_limbs - 1
+    smem_max = 227 * 1024 - 4096
+    for nt in (128, 64, 32, 16):
+        if b_limbs * nt > 256 or diagonals * nt > 512:
+            continue
+        if smem_max // (a_limbs * 16384 + b_limbs * nt * 128) >= 2:
+            return True
+    return False
+
+
 class WeightPlanes:
     """Signed 8-bit limb planes of a static weight, split once and kept on the device.
 
@@ -265,14 +289,22 @@ class WeightPlanes:
             lib.zkds_planes_destroy(h)
 
 
-def linear_prepared(A, planes, c_rescale, a_rescale=1, a_limbs=0, want_remainder=False):
-    """int64_bmm_broadcast against prepared weights: A (Bdim, M, K) -> C (Bdim, M, N) [, R]."""
+def _a_flags(a_limbs, dynamic):
+    return LIMBS_DYNAMIC if (dynamic and a_limbs > 0) else 0
+
+
+def linear_prepared(A, planes, c_rescale, a_rescale=1, a_limbs=0, want_remainder=False, dynamic=False):
+    """int64_bmm_broadcast against prepared weights: A (Bdim, M, K) -> C (Bdim, M, N) [, R].
+
+    a_limbs: 0 measures the range of A (host synchronisation); > 0 promises that A fits that
+    many signed 8-bit limbs; with dynamic=True it is only an upper bound and the count used is
+    derived on the device."""
     _dev_i64(A, "A")
     Bdim, M, K = A.shape
     assert K == planes.K and planes.nb == 1
     C = torch.empty((Bdim, M, planes.N), dtype=torch.int64, device=A.device)
     R = torch.empty_like(C) if want_remainder else None
-    flags = REMAINDER_LEGACY if LEGACY_REMAINDER else 0
+    flags = (REMAINDER_LEGACY if LEGACY_REMAINDER else 0) | _a_flags(a_limbs, dynamic)
     with torch.cuda.device(A.device):
         _check(lib.zkds_contraction_prepared(A.data_ptr(), M * K, K, planes.handle, 0, C.data_ptr(),
                                              R.data_ptr() if want_remainder else None, M * planes.N,
@@ -281,7 +313,7 @@ def linear_prepared(A, planes, c_rescale, a_rescale=1, a_limbs=0, want_remainder
     return (C, R) if want_remainder else C
 
 
-def einsum_heads_prepared(A, planes, rescale, rounding, a_limbs=0):
+def einsum_heads_prepared(A, planes, rescale, rounding, a_limbs=0, dynamic=False):
     """out[b,s,h,n] = (addend + sum_k A[b,s,h,k] * W[h,n,k]) >> rescale with per-head prepared
     weights; addend = rescale // 2 when ``rounding`` (einsum_bshd_hdc_bshc) else 0
     (einsum_bshc_hdc_bshd)."""
@@ -293,9 +325,98 @@ def einsum_heads_prepared(A, planes, rescale, rounding, a_limbs=0):
     with torch.cuda.device(A.device):
         _check(lib.zkds_contraction_prepared(A.data_ptr(), K, H * K, planes.handle, 1, C.data_ptr(), None,
                                              N, H * N, H, Bn * S, 1, int(rescale) // 2 if rounding else 0,
-                                             int(rescale), a_limbs, 0, _stream()),
+                                             int(rescale), a_limbs, _a_flags(a_limbs, dynamic), _stream()),
                "einsum_heads_prepared")
     return C
+
+
+def grouped_prepared(A, planes, tile_group, c_rescale, a_limbs=0, dynamic=False, group_shift=None,
+                     n_split=0):
+    """Routed-expert linear layer: A flat (n_tiles*128, K), tile_group int32 (n_tiles,) on the
+    device (expert of each 128-row tile, negative = unused) -> C (n_tiles*128, N).
+    group_shift: optional int32 (experts, 2) device tensor of per-expert shifts for the output
+    columns below / from n_split; otherwise the uniform c_rescale."""
+    if group_shift is not None:
+        assert group_shift.dtype == torch.int32 and group_shift.is_cuda and group_shift.is_contiguous()
+    _dev_i64(A, "A")
+    assert tile_group.dtype == torch.int32 and tile_group.is_cuda and tile_group.is_contiguous()
+    n_tiles = tile_group.numel()
+    assert A.shape == (n_tiles * 128, planes.K)
+    C = torch.empty((n_tiles * 128, planes.N), dtype=torch.int64, device=A.device)
+    with torch.cuda.device(A.device):
+        _check(lib.zkds_grouped_prepared(A.data_ptr(), planes.handle, tile_group.data_ptr(), n_tiles,
+                                         C.data_ptr(), 1, 0, int(c_rescale),
+                                         group_shift.data_ptr() if group_shift is not None else None,
+                                         int(n_split), a_limbs, _a_flags(a_limbs, dynamic), _stream()),
+               "grouped_prepared")
+    return C
+
+
+def attention_scores_fused(A, KV, rescale, addin=None, mul=0, div=0, causal=False, start_pos=0,
+                           mask_value=-(64 << 36), a_limbs=0, b_limbs=0, dynamic=False):
+    """einsum_bshc_btc_bsht with the element-wise tail of the MLA scores in its epilogue:
+    out = floor(((sum >> rescale, rounded as the einsum does) + addin) * mul / div) + causal mask
+    (model.py:884-905).  mul = div = 0 skips the rescale, addin=None the addition."""
+    _dev_i64(A, "A")
+    _dev_i64(KV, "KV")
+    Bn, S, H, Cd = A.shape
+    T = KV.shape[1]
+    assert Bn == KV.shape[0] and Cd == KV.shape[2]
+    if addin is not None:
+        _dev_i64(addin, "addin")
+        assert tuple(addin.shape) == (Bn, S, H, T)
+    C = torch.empty((Bn, S, H, T), dtype=torch.int64, device=A.device)
+    with torch.cuda.device(A.device):
+        _check(lib.zkds_einsum_bshc_btc_bsht_ex(A.data_ptr(), KV.data_ptr(), C.data_ptr(), int(rescale), Bn,
+                                                S, H, T, Cd, addin.data_ptr() if addin is not None else None,
+                                                int(mul), int(div), 1 if causal else 0, int(start_pos),
+                                                int(mask_value), a_limbs, b_limbs,
+                                                ALGO | _a_flags(a_limbs, dynamic), _stream()),
+               "attention_scores_fused")
+    return C
+
+
+def glu_q23(r1, r2, ld=None, want_silu=False):
+    """h = (silu_q23(r1) * r2) >> 23 (model.py:1034-1048).  r1, r2: (..., n) views sharing the row
+    stride ld (default n).  Returns h, or (h, silu(r1)) when want_silu."""
+    n = r1.shape[-1]
+    rows = r1.numel() // n if ld is None else r1.shape[0]
+    ld = n if ld is None else ld
+    lut = _lut_on(EXP2_FRAC_LUT_Q23, r1.device, "silu_init_q23")
+    h = torch.empty((rows, n), dtype=torch.int64, device=r1.device)
+    s1 = torch.empty_like(h) if want_silu else None
+    with torch.cuda.device(r1.device):
+        _check(lib.zkds_glu_q23(r1.data_ptr(), r2.data_ptr(), ld, h.data_ptr(),
+                                s1.data_ptr() if want_silu else None, lut.data_ptr(), rows, n, _stream()),
+               "glu_q23")
+    return (h, s1) if want_silu else h
+
+
+def gather_rows(src, index):
+    """dst[r] = src[index[r]] (zeros where index[r] < 0); index int32 on the device."""
+    _dev_i64(src, "src")
+    assert index.dtype == torch.int32 and index.is_cuda
+    rows, cols = index.numel(), src.shape[-1]
+    dst = torch.empty((rows, cols), dtype=torch.int64, device=src.device)
+    with torch.cuda.device(src.device):
+        _check(lib.zkds_gather_rows(src.data_ptr(), index.data_ptr(), dst.data_ptr(), rows, cols, _stream()),
+               "gather_rows")
+    return dst
+
+
+def moe_combine(out, pos, w, base=None):
+    """y[t] = base[t] + sum_slot floor(out[pos[t, slot]] * w[t, slot] / 2^23) (model.py:1379-1383)."""
+    _dev_i64(out, "out")
+    _dev_i64(w, "w")
+    assert pos.dtype == torch.int32 and pos.is_cuda and pos.is_contiguous()
+    tokens, slots = pos.shape
+    cols = out.shape[-1]
+    y = torch.empty((tokens, cols), dtype=torch.int64, device=out.device)
+    with torch.cuda.device(out.device):
+        _check(lib.zkds_moe_combine(out.data_ptr(), pos.data_ptr(), w.data_ptr(),
+                                    base.data_ptr() if base is not None else None, y.data_ptr(), tokens,
+                                    slots, cols, _stream()), "moe_combine")
+    return y
 
 
 # ---- RoPE ----------------------------------------------------------------------------
