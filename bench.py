@@ -17,6 +17,7 @@ same line shape with "impl": "reference".
 import argparse
 import importlib
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -147,7 +148,15 @@ class GemmWorkload:
     def value(self, seconds_per_step, world):
         return self.ops * world / seconds_per_step / 1e9
 
-    def roofline(self, kernel_ms, peaks):
+    def roofline(self, peaks):
+        k = self.k
+        k.kernel_timing(True)
+        times = []
+        for _ in range(8):
+            self.step()
+            times.append(k.last_kernel_ms())
+        k.kernel_timing(False)
+        kernel_ms = statistics.mean(times)
         int8_peak = 2.0 * peaks["bf16_tflops"]         # int8 tcgen05 rate is twice the bf16 rate
         pairs = self.a_limbs * self.planes.limbs
         achieved = pairs * self.ops / (kernel_ms * 1e-3) / 1e12
@@ -284,7 +293,7 @@ class ChainWorkload:
     def value(self, seconds_per_step, world):
         return self.T * world / seconds_per_step
 
-    def roofline(self, kernel_ms, peaks):
+    def roofline(self, peaks):
         parts = self.time_parts()
         gbs = {n: self.bytes[n] / (ms * 1e-3) / 1e9 for n, ms in parts.items()}
         dom = "softmax"
@@ -333,6 +342,190 @@ class ChainWorkload:
             rows = min(256, int(rows * max(2.0, 0.8 * seconds / max(dt, 1e-3))))
 
 
+def _normal_i(torch, gen, shape, scale, dev, dtype):
+    """round(N(0,1) * scale) generated on the device in chunks (seeded generator)"""
+    out = torch.empty(shape, dtype=dtype, device=dev)
+    flat = out.view(-1)
+    step = 1 << 26
+    for i in range(0, flat.numel(), step):
+        n = min(step, flat.numel() - i)
+        flat[i:i + n] = torch.round(torch.randn(n, generator=gen, device=dev) * scale).to(dtype)
+    return out
+
+
+class MlaWorkload:
+    """One DeepSeek-V3 MLA attention layer in int64 fixed point, prefill of 4096 tokens
+    (dim 7168, q_lora 1536, kv_lora 512, 128 heads, nope 128, rope 64, v 128; MLA.forward of
+    inference/model.py:747-957).  Hidden states ~ N(0, 2^16), int32 weights ~ N(0, 2^16/sqrt(fan_in)),
+    norm weights near 2^16, every runtime shift 16 (the layer's fixed-point scale); the shifts the
+    reference hard-codes stay (scores 23 / 21, RoPE 42, softmax Q19).  `scales="reference"` uses the
+    reference's magnitudes instead (activations 2^21, weights 2^30/sqrt(fan_in), shifts 29-31).
+    With N GPUs the heads are split N ways (wq_b, wkv_b, attention per head local) and wo is
+    column-split after an all-gather: strong scaling of the same 4096 tokens."""
+    name = "mla_layer_prefill_4096"
+    metric = "int64_mla_layer_tokens_per_s"
+    unit = "tokens/s"
+    scaling = "strong"
+    T = 4096
+
+    def __init__(self, torch, k, dev, rank, T=None, scales="baseline"):
+        import numpy as np
+        self.torch, self.k, self.dev, self.np, self.rank = torch, k, dev, np, rank
+        if T:
+            self.T = T
+        M = importlib.import_module(PKG + ".model")
+        self.M = M
+        import torch.distributed as dist
+        M.world_size = dist.get_world_size() if dist.is_initialized() else 1
+        M.rank = dist.get_rank() if dist.is_initialized() else 0
+        self.world = M.world_size
+        a = M.ModelArgs(max_seq_len=self.T, vocab_size=129280, dim=7168, inter_dim=18432, moe_inter_dim=2048,
+                        n_layers=61, n_dense_layers=3, n_heads=128, n_routed_experts=256, n_shared_experts=1,
+                        n_activated_experts=8, n_expert_groups=8, n_limited_groups=4, score_func="sigmoid",
+                        route_scale=2.5, q_lora_rank=1536, kv_lora_rank=512, qk_nope_head_dim=128,
+                        qk_rope_head_dim=64, v_head_dim=128)
+        self.args = a
+        self.scales = scales
+        if scales == "baseline":
+            xs, wb, nb, shift, self.act_limbs, self.score_limbs = 16, 16, 16, 16, 3, (3, 3)
+        else:
+            xs, wb, nb, shift, self.act_limbs, self.score_limbs = 21, 30, 19, 30, 4, (5, 5)
+        self.shift = shift
+        with torch.device(dev):
+            attn = M.MLA(0, a)
+        g = torch.Generator(device=dev).manual_seed(5)          # same weights on every rank
+        H, Hl = a.n_heads, a.n_heads // self.world
+        r = M.rank
+
+        def weight(out_f, in_f, rows=None):
+            w = _normal_i(torch, g, (out_f, in_f), 2.0**wb / math.sqrt(in_f), dev, torch.int32)
+            return w if rows is None else w[rows[0]:rows[1]].contiguous()
+
+        def norm_weight(n):
+            return (2**nb + _normal_i(torch, g, (n,), 2.0**(nb - 8), dev, torch.int64)).to(torch.int32)
+
+        heads = lambda d: (r * Hl * d, (r + 1) * Hl * d)
+        attn.wq_a.weight = weight(a.q_lora_rank, a.dim)
+        attn.q_norm.weight = norm_weight(a.q_lora_rank)
+        attn.wq_b1.weight = weight(H * a.qk_nope_head_dim, a.q_lora_rank, heads(a.qk_nope_head_dim))
+        attn.wq_b2.weight = weight(H * a.qk_rope_head_dim, a.q_lora_rank, heads(a.qk_rope_head_dim))
+        attn.wkv_a1.weight = weight(a.kv_lora_rank, a.dim)
+        attn.wkv_a2.weight = weight(a.qk_rope_head_dim, a.dim)
+        attn.kv_norm.weight = norm_weight(a.kv_lora_rank)
+        attn.wkv_b_1.weight = weight(H * a.qk_nope_head_dim, a.kv_lora_rank, heads(a.qk_nope_head_dim))
+        attn.wkv_b_2.weight = weight(H * a.v_head_dim, a.kv_lora_rank, heads(a.v_head_dim))
+        wo_cols = a.dim // self.world
+        attn.wo.weight = weight(a.dim, H * a.v_head_dim, (r * wo_cols, (r + 1) * wo_cols))
+        for lin in (attn.wq_a, attn.wq_b1, attn.wq_b2, attn.wkv_a1, attn.wkv_a2):
+            lin.res_rescale = shift if scales == "baseline" else lin.res_rescale
+        for lin in (attn.wkv_b_1, attn.wkv_b_2, attn.wo):
+            lin.scale = torch.tensor(shift, dtype=torch.int32, device=dev)
+        attn.score_limbs = self.score_limbs
+        self.attn = attn
+        gx = torch.Generator(device=dev).manual_seed(55)
+        self.x = _normal_i(torch, gx, (1, self.T, a.dim), 2.0**xs, dev, torch.int64)
+        self.freqs = M.precompute_freqs_cis(a).to(dev)
+        self.mask = torch.full((self.T, self.T), -(64 << 36), dtype=torch.int64, device=dev).triu_(1)
+        self.mask._zkds_causal = True
+        M.ACT_LIMBS = self.act_limbs
+        k.softmax_init_q19()
+        k.SOFTMAX_WRITES_WEIGHTS = False
+        self.x_host = None
+        T, D, C, R = self.T, a.dim, a.kv_lora_rank, a.qk_rope_head_dim
+        nope, v, q = a.qk_nope_head_dim, a.v_head_dim, a.q_lora_rank
+        self.ops = 2.0 * T * (D * q + q * H * (nope + R) + D * (C + R) + H * nope * C + H * T * (C + R)
+                              + H * T * C + H * C * v + H * v * D)
+        self.launches_per_step = 0
+
+    def config(self):
+        a = self.args
+        return {"workload": self.name, "tokens": self.T, "dim": a.dim, "heads": a.n_heads,
+                "q_lora": a.q_lora_rank, "kv_lora": a.kv_lora_rank, "scales": self.scales,
+                "shift": self.shift, "act_limbs_bound": self.act_limbs, "score_limbs_bound": self.score_limbs,
+                "heads_per_gpu": a.n_heads // self.world, "useful_ops_per_step": self.ops,
+                "l2": "activations and score tensors (up to 17 GB) far exceed L2"}
+
+    def step(self):
+        return self.attn(self.x, 0, self.freqs, self.mask)
+
+    def step_e2e(self):
+        torch = self.torch
+        if self.x_host is None:
+            self.x_host = self.x.cpu().pin_memory()
+            self.x_in = torch.empty_like(self.x)
+            self.out_host = torch.empty((1, self.T, self.args.dim), dtype=torch.int64).pin_memory()
+        self.x_in.copy_(self.x_host, non_blocking=True)
+        out = self.attn(self.x_in, 0, self.freqs, self.mask)
+        self.out_host.copy_(out, non_blocking=True)
+
+    def e2e_bytes(self):
+        n = 8 * self.T * self.args.dim
+        return n, n
+
+    def value(self, seconds_per_step, world):
+        return self.T / seconds_per_step          # the same 4096 tokens on every N
+
+    def roofline(self, peaks):
+        k = self.k
+        k.kernel_timing(2)
+        self.step()
+        self.torch.cuda.synchronize()
+        ms, ops, n = k.kernel_timing_totals()
+        k.kernel_timing(False)
+        # per step: n tensor-core launches, a limb split of A for each, a split of the three
+        # un-prepared B operands (kv / pe caches), 2 RMSNorm, 2 RoPE, 1 softmax
+        self.launches_per_step = 2 * n + 3 + 5
+        int8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+        achieved = ops / (ms * 1e-3) / 1e12
+        return {"bound": "tensor", "kernel": "limb_gemm_kernel (%d launches per step)" % n,
+                "achieved": round(achieved, 1), "peak": round(int8_peak, 1), "unit": "TFLOP/s",
+                "frac": round(achieved / int8_peak, 4), "traffic": None, "kernel_ms": round(ms, 3),
+                "int8_ops_per_step": ops,
+                "note": "sum over the step's tensor-core launches of limb pairs x 2MNK / sum of their CUDA-event "
+                        "durations; peak = 2 x sustained cuBLAS bf16 (%s)" % peaks["source"]}
+
+    def check(self, orc):
+        """the layer against the numpy restatement of MLA.forward on the first 48 tokens"""
+        if self.world > 1:
+            return None
+        from oracle import model_oracle as mo
+        np, torch, a = self.np, self.torch, self.args
+        S = 48
+        at = self.attn
+        p = {n: getattr(at, n).weight.cpu().numpy() for n in
+             ("wq_a", "wq_b1", "wq_b2", "wkv_a1", "wkv_a2", "wkv_b_1", "wkv_b_2", "wo", "q_norm", "kv_norm")}
+        p.update(wkv_b_1_scale=self.shift, wkv_b_2_scale=self.shift, wo_scale=self.shift)
+        x = self.x[:, :S].cpu().numpy()
+        kv = np.zeros((1, S, a.kv_lora_rank), np.int64)
+        pe = np.zeros((1, S, a.qk_rope_head_dim), np.int64)
+        sq, skv = (self.shift, self.shift) if self.scales == "baseline" else (30, 29)
+        want = mo.mla_forward(p, x, 0, self.freqs[:S].cpu().numpy(), mo.causal_mask(S), kv, pe, a.n_heads,
+                              s_q=sq, s_kv=skv)
+        mask = torch.full((S, S), -(64 << 36), dtype=torch.int64, device=self.dev).triu_(1)
+        got = self.attn(self.x[:, :S].contiguous(), 0, self.freqs[:S], mask).cpu().numpy()
+        return int((got != want).sum())
+
+    @staticmethod
+    def cpu_sample(orc, np, seconds, rank=0):
+        """the layer's contractions and softmax on a token sample (full K and T extents)"""
+        S, T, H = 4, 4096, 128
+        rng = np.random.default_rng(5)
+        ri = lambda shape, b: np.rint(rng.standard_normal(shape) * 2.0**b).astype(np.int64)
+        x = ri((1, S, 7168), 16)
+        t0 = time.time()
+        for (n, kk) in ((1536, 7168), (24576, 1536), (576, 7168), (7168, 16384)):
+            orc.gemm(ri((1, S, kk), 16), ri((n, kk), 12).astype(np.int32), 1, 1, 16)
+        q = ri((1, S, H, 512), 16)
+        kv = ri((1, T, 512), 16)
+        sc = orc.einsum_bshc_btc_bsht(q, kv, 23) + orc.einsum_bshc_btc_bsht(ri((1, S, H, 64), 16), ri((1, T, 64), 16), 21)
+        pr = orc.softmax(sc * 94 // 695, 19)
+        ctx = orc.einsum_bsht_btc_bshc(pr, kv, 23)
+        orc.einsum_bshc_hdc_bshd(ctx, ri((H, 128, 512), 12).astype(np.int32), 16)
+        orc.einsum_bshd_hdc_bshc(ri((1, S, H, 128), 16), ri((H, 128, 512), 12).astype(np.int32), 16)
+        dt = time.time() - t0
+        return S / dt, "%d of 4096 query tokens against the full 4096-token cache and full weights" % S, dt
+
+
 class GemmProfWorkload(GemmWorkload):
     """Smaller GEMM of the same kernel for profiler captures (inputs still exceed L2)."""
     name = "gemm_4096x8192x4096"
@@ -353,8 +546,32 @@ class ChainProfWorkload(ChainWorkload):
         return ChainWorkload.cpu_sample(orc, np, seconds, rank)
 
 
+class MlaRefScaleWorkload(MlaWorkload):
+    """The MLA layer at the reference's fixed-point magnitudes (activations 2^21, int32 weights
+    2^30/sqrt(fan_in), shifts 29-31): more limbs per operand than the 2^16 configuration."""
+    name = "mla_layer_prefill_4096_reference_scales"
+
+    def __init__(self, torch, k, dev, rank):
+        super().__init__(torch, k, dev, rank, scales="reference")
+
+    @staticmethod
+    def cpu_sample(orc, np, seconds, rank=0):
+        return MlaWorkload.cpu_sample(orc, np, seconds, rank)
+
+
+class MlaSmallWorkload(MlaWorkload):
+    """The MLA layer at 1024 tokens (profiler captures, quick checks)."""
+    name = "mla_layer_prefill_1024"
+    T = 1024
+
+    @staticmethod
+    def cpu_sample(orc, np, seconds, rank=0):
+        return MlaWorkload.cpu_sample(orc, np, seconds, rank)
+
+
 WORKLOADS = {"gemm": GemmWorkload, "gemm_prof": GemmProfWorkload, "chain": ChainWorkload,
-             "chain_prof": ChainProfWorkload}
+             "chain_prof": ChainProfWorkload, "mla": MlaWorkload, "mla_ref": MlaRefScaleWorkload,
+             "mla_small": MlaSmallWorkload}
 DEFAULT_WORKLOAD = "gemm"
 
 
@@ -432,8 +649,6 @@ def main():
     for _ in range(args.warmup):
         wl.step()
     k.device_status()
-    k.kernel_timing(True)
-    kernel_ms = []
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -446,12 +661,9 @@ def main():
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     elapsed = ev0.elapsed_time(ev1) * 1e-3
-    # per-launch duration of the dominant kernel, CUDA events recorded around it on its stream
-    for _ in range(min(args.steps, 10)):
-        wl.step()
-        kernel_ms.append(max(k.last_kernel_ms(), 0.0))
-    k.kernel_timing(False)
     k.device_status()
+    # duration of the dominant kernel, CUDA events recorded around it on its own stream
+    roof = wl.roofline(peaks)
     t = torch.tensor([elapsed], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -478,16 +690,17 @@ def main():
         mismatches = wl.check(orc)
         cpu_v, cpu_desc, _ = (wl.cpu_sample(orc, np, args.cpu_seconds)
                                 if world == 1 and args.cpu_seconds > 0 else (None, None, 0))
+        launches = wl.launches_per_step * args.steps
         line = {"metric": wl.metric, "value": round(wl.value(sec_per_step, world), 2), "unit": wl.unit,
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": round(sec_per_step * 1e3, 4), "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
-                "config": wl.config(),
+                "scaling": getattr(wl, "scaling", "weak"), "vs_baseline": None, "dtype": "int64",
+                "data": "synthetic", "config": wl.config(),
                 "e2e": {"value": round(wl.value(e2e_sec, world), 2), "unit": wl.unit,
                         "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                         "ms_per_step": round(e2e_sec * 1e3, 4)},
-                "gpu_launches": wl.launches_per_step * args.steps,
-                "roofline": wl.roofline(statistics.mean(kernel_ms), peaks),
+                "gpu_launches": launches,
+                "roofline": roof,
                 "clocks": clocks, "mismatched_words_vs_oracle": mismatches}
         if cpu_v is not None:
             line["cpu_baseline"] = {"value": round(cpu_v, 3), "unit": wl.unit,

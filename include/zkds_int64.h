@@ -241,6 +241,10 @@ int zkds_contraction_prepared(const int64_t* A, int64_t a_s_batch, int64_t a_s_r
  * waits for the most recent pair and returns its duration (< 0 if there is none). */
 void zkds_timing(int enable);
 float zkds_last_kernel_ms(void);
+/* zkds_timing(2) resets and starts accumulating, over every tensor-core launch, the kernel's
+ * duration and the int8 work it issued (limb pairs x 2MNK); each launch is then waited for, so
+ * this is a profiling pass.  zkds_timing_totals reads the sums. */
+void zkds_timing_totals(double* ms, double* int8_ops, long long* launches);
 
 /* Tail of the gated MLP (model.py:1034-1048, 1266-1280): h = (silu_q23(r1) * r2) >> 23 with a
  * wrapping int64 product.  r1, r2: rows x n with row stride ld (both halves of a fused w1|w3

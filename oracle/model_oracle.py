@@ -35,26 +35,27 @@ def causal_mask(seqlen):
     return np.triu(np.full((seqlen, seqlen), MASK_VALUE, np.int64), 1) if seqlen > 1 else None
 
 
-def mla_forward(p, x, start_pos, freqs, mask, kv_cache, pe_cache, n_heads, dumps=None):
+def mla_forward(p, x, start_pos, freqs, mask, kv_cache, pe_cache, n_heads, dumps=None, s_q=30, s_kv=29):
     """MLA.forward, absorbed path (model.py:747-957).  p: wq_a, q_norm, wq_b1, wq_b2, wkv_a1,
     wkv_a2, kv_norm, wkv_b_1, wkv_b_2, wo (int32 arrays) and the shifts wkv_b_1_scale,
-    wkv_b_2_scale, wo_scale.  kv_cache / pe_cache [1, max_seq, .] are updated in place."""
+    wkv_b_2_scale, wo_scale.  kv_cache / pe_cache [1, max_seq, .] are updated in place.
+    s_q / s_kv: the shifts of wq_a, wq_b and of wkv_a (30 and 29 in the reference, model.py:702-712)."""
     B, S, _ = x.shape
     end = start_pos + S
     H = n_heads
     d = dumps if dumps is not None else {}
-    q_down, q_rem = linear(x, p["wq_a"], 30)
+    q_down, q_rem = linear(x, p["wq_a"], s_q)
     d.update(wq_a_x=x, wq_a_w=p["wq_a"].view(np.uint32), wq_a_y=q_down, q_norm_r=q_rem)
     q_normed, rms = rms_norm(q_down, p["q_norm"])
     d.update(q_norm_x=q_down, q_norm_weight=p["q_norm"].view(np.uint32), q_norm_rms=rms, q_norm_y=q_normed)
-    q_nope = linear(q_normed, p["wq_b1"], 30)[0].reshape(B, S, H, -1)
-    q_pe = linear(q_normed, p["wq_b2"], 30)[0].reshape(B, S, H, -1)
+    q_nope = linear(q_normed, p["wq_b1"], s_q)[0].reshape(B, S, H, -1)
+    q_pe = linear(q_normed, p["wq_b2"], s_q)[0].reshape(B, S, H, -1)
     d.update(q_pe_x=q_pe, freqs_cis=freqs)
     q_pe = rotary(q_pe, freqs)
     d.update(q_pe_y=p["q_norm"].view(np.uint32))            # model.py:819 writes the norm weight
-    kv, kv_rem = linear(x, p["wkv_a1"], 29)
+    kv, kv_rem = linear(x, p["wkv_a1"], s_kv)
     d.update(wkv_a1_x=x, wkv_a1_w=p["wkv_a1"].view(np.uint32), wkv_a1_y=kv, wkv_a1_r=kv_rem)
-    k_pe = linear(x, p["wkv_a2"], 29)[0]
+    k_pe = linear(x, p["wkv_a2"], s_kv)[0]
     k_pe = rotary(k_pe[:, :, None, :], freqs)
     C = p["wkv_b_1"].shape[1]
     w1 = p["wkv_b_1"].reshape(H, -1, C)

@@ -419,6 +419,10 @@ int zkds_act(const int64_t* X, int64_t* C, const int64_t* lut, int64_t n, int fr
 int zkds_device_status(int clear) { return limb_device_status(clear); }
 void zkds_timing(int enable) { limb_timing_enable(enable); }
 float zkds_last_kernel_ms(void) { return limb_last_kernel_ms(); }
+void zkds_timing_totals(double* ms, double* int8_ops, long long* launches)
+{
+    limb_timing_totals(ms, int8_ops, launches);
+}
 
 int zkds_planes_create(const void* W, int bits, int64_t nb, int64_t rows, int64_t K, int64_t s_batch,
                        int64_t s_row, int64_t s_k, int64_t div, int limbs, void** out, void* stream)

@@ -94,6 +94,9 @@ size_t gemm_noalloc_bytes(int64_t Bdim, int64_t M, int64_t K, int64_t N, int a_l
 // CUDA-event timing of the tensor-core kernel alone (events recorded on the launching stream)
 void limb_timing_enable(int on);
 float limb_last_kernel_ms();
+// on == 2 also accumulates, per launch, the kernel's duration and limb-pairs x 2MNK (waits for
+// every launch: a profiling pass, not a timed one)
+void limb_timing_totals(double* ms, double* int8_ops, long long* launches);
 
 // ZKDS_ERR_DEVICE when a tensor-core kernel reported a wait that ran out, ZKDS_ERR_RANGE
 // when an operand did not fit the limb count it was split into, else ZKDS_OK.  The flags

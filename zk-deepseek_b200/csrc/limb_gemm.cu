@@ -20,6 +20,8 @@
 // Exactness bound: a diagonal sums at most min(La, Lb) * K products of magnitude <= 2^14,
 // which must stay below 2^31; the launcher refuses shapes beyond that.
 #include <cuda.h>
+#include <stdio.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -57,8 +59,10 @@ absmax_kernel(const T* X, int64_t rows, int64_t cols, int64_t sz, int64_t sr, in
     if ((threadIdx.x & 31) == 0 && best) atomicMax((unsigned long long*)out, (unsigned long long)best);
 }
 
-// planes[l][z][r][Kp] (int8) <- X[z*sz + r*sr + k*sk] / div, one 16-byte chunk per thread.
-// A value the L limbs cannot hold raises *overflow.
+// planes[l][z][r][Kp] (int8) <- limb l of X[z*sz + r*sr + k*sk] / div.  One thread converts four
+// consecutive k: with a k-contiguous source a warp reads 1 KB and writes 128 bytes per plane per
+// instruction.  A value the L limbs cannot hold raises *overflow; absmax_out (optional) receives
+// the largest magnitude seen.
 template <typename T>
 __global__ void __launch_bounds__(256)
 split_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, int64_t rows, int64_t K,
@@ -66,53 +70,54 @@ split_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, int64_
              unsigned* overflow, unsigned long long* absmax_out)
 {
     uint64_t seen = 0;
-    const int64_t chunks = Kp >> 4;
-    const int64_t total = rows * chunks;
+    bool ovf = false;
+    const int64_t quads = Kp >> 2;
+    const int64_t total = rows * quads;
     const int64_t z = blockIdx.y;
     const T* x = X + z * sz;
     const bool k_fast = (sk == 1);
+    const bool vec = k_fast && sizeof(T) == 8 && ((((uintptr_t)X) & 15) == 0) && ((sr & 1) == 0) &&
+                     ((sz & 1) == 0);
     for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total;
          t += (int64_t)gridDim.x * blockDim.x) {
-        int64_t r, ch;
-        if (k_fast) { r = t / chunks; ch = t - r * chunks; }
-        else { ch = t / rows; r = t - ch * rows; }
-        const int64_t k0 = ch << 4;
-        uint32_t w[9][4];
+        int64_t r, qd;
+        if (k_fast) { r = t / quads; qd = t - r * quads; }
+        else { qd = t / rows; r = t - qd * rows; }
+        const int64_t k0 = qd << 2;
+        int64_t v[4];
+        if (vec && k0 + 4 <= K) {
+            const longlong2* src = reinterpret_cast<const longlong2*>(x + r * sr + k0);
+            longlong2 a = src[0], b = src[1];
+            v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+        } else {
 #pragma unroll
-        for (int l = 0; l < 9; ++l)
+            for (int j = 0; j < 4; ++j) v[j] = (k0 + j < K) ? (int64_t)x[r * sr + (k0 + j) * sk] : 0;
+        }
+        uint32_t w[9];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) w[l][q] = 0;
-        bool ovf = false;
+        for (int l = 0; l < 9; ++l) w[l] = 0;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            int64_t k = k0 + j;
-            int64_t v = 0;
-            if (k < K) {
-                v = (int64_t)x[r * sr + k * sk];
-                if (div != 1) v = v / div;
-            }
-            {
-                // |v| for v >= 0, |v| - 1 for v < 0: balanced digits reach one further down
-                uint64_t a = (uint64_t)(v ^ (v >> 63));
-                seen = a > seen ? a : seen;
-            }
+        for (int j = 0; j < 4; ++j) {
+            int64_t u = v[j];
+            if (div != 1) u = u / div;
+            // |u| for u >= 0, |u| - 1 for u < 0: balanced digits reach one further down
+            const uint64_t a = (uint64_t)(u ^ (u >> 63));
+            seen = a > seen ? a : seen;
 #pragma unroll
             for (int l = 0; l < 9; ++l) {
                 if (l < L) {
-                    w[l][j >> 2] |= (uint32_t)(v & 0xFF) << ((j & 3) * 8);
-                    v = (v >> 8) + ((v >> 7) & 1);
+                    w[l] |= (uint32_t)(u & 0xFF) << (j * 8);
+                    u = (u >> 8) + ((u >> 7) & 1);
                 }
             }
-            ovf |= (v != 0);
+            ovf |= (u != 0);
         }
         int8_t* dst = planes + (z * rows + r) * Kp + k0;
 #pragma unroll
         for (int l = 0; l < 9; ++l)
-            if (l < L)
-                *reinterpret_cast<uint4*>(dst + l * plane_stride) =
-                    make_uint4(w[l][0], w[l][1], w[l][2], w[l][3]);
-        if (ovf) *overflow = 1u;
+            if (l < L) *reinterpret_cast<uint32_t*>(dst + l * plane_stride) = w[l];
     }
+    if (ovf) *overflow = 1u;
     if (absmax_out) {
         seen = warp_max_u64(seen);
         if ((threadIdx.x & 31) == 0 && seen) atomicMax(absmax_out, (unsigned long long)seen);
@@ -273,6 +278,8 @@ struct LimbParams {
     int64_t addend;
     int shift, r_legacy;
     int* error_flag;          // host-mapped
+    int fits64;               // |addend + sum| < 2^62 proven on the host: one-word epilogue
+    int64_t m_tiles, n_tiles, panel_m;   // tile raster (see the kernel)
     // La is an upper bound when a_absmax is set: the kernel derives the limb count actually
     // needed from the range the split pass measured and skips the all-zero upper limbs
     const unsigned long long* a_absmax;
@@ -307,6 +314,134 @@ __device__ __forceinline__ int64_t floor_div_i64(int64_t a, int64_t b)
     return (r != 0 && ((r < 0) != (b < 0))) ? q - 1 : q;
 }
 
+struct EpilogueCtx {
+    uint32_t tq;
+    int D, NT, group;
+    int64_t m, n0, z;
+    int64_t* crow;
+    int64_t* rrow;
+    bool row_ok, vec_ok;
+};
+
+// element-wise tail of the attention scores: v += *arow (the addin element, if any);
+// v = floor(v * mul / div); causal mask for column n of sequence row srow
+__device__ __forceinline__ int64_t score_tail(const LimbParams& p, int64_t v, const int64_t* arow,
+                                              int64_t n, int64_t srow)
+{
+    if (arow) v = (int64_t)((uint64_t)v + (uint64_t)*arow);
+    if (p.ep_div) {
+        if (p.ep_mul == 94 && p.ep_div == 695) {  // MLA's softmax scale: constant divisor
+            int64_t t = (int64_t)((uint64_t)v * 94ull);
+            int64_t qd = t / 695;
+            v = (t - qd * 695 < 0) ? qd - 1 : qd;
+        } else
+            v = floor_div_i64((int64_t)((uint64_t)v * (uint64_t)p.ep_mul), p.ep_div);
+    }
+    if (p.causal_H && n > p.causal_start + srow) v = (int64_t)((uint64_t)v + (uint64_t)p.mask_value);
+    return v;
+}
+
+// Reads the diagonals of one 128 x NT tile back from tensor memory, recombines them
+// (sum_d acc_d * 2^(8 d)), shifts and stores.  FITS64: the launcher proved |sum| < 2^62, so the
+// recombination runs in one 64-bit word instead of two.
+template <bool FITS64>
+__device__ __forceinline__ void epilogue_tile(const LimbParams& p, const EpilogueCtx& e)
+{
+    const bool tail = p.addin || p.ep_div || p.causal_H;
+    const int64_t* arow = p.addin ? p.addin + e.z * p.c_sz + e.m * p.c_sm : nullptr;
+    const int64_t srow = p.causal_H ? e.m / p.causal_H : 0;
+    for (int nc = 0; nc < e.NT; nc += 8) {
+        i128w sum[8];
+        int64_t s64[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            if (FITS64) s64[c] = p.addend;
+            else sum[c] = make_i128(p.addend);
+        }
+        // up to eight diagonals are fetched before one wait: the loads overlap each other
+        for (int d0 = 0; d0 < e.D; d0 += 8) {
+            int32_t a[8][8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (d0 + j < e.D) tmem_ld8(e.tq + (uint32_t)((d0 + j) * e.NT + nc), a[j]);
+                else {
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) a[j][c] = 0;
+                }
+            }
+            tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                // four diagonals fit one int64: |a| < 2^31, weights up to 2^24
+                const int64_t v0 = (int64_t)a[0][c] + ((int64_t)a[1][c] << 8) + ((int64_t)a[2][c] << 16) +
+                                   ((int64_t)a[3][c] << 24);
+                const int64_t v1 = (int64_t)a[4][c] + ((int64_t)a[5][c] << 8) + ((int64_t)a[6][c] << 16) +
+                                   ((int64_t)a[7][c] << 24);
+                if (FITS64) {
+                    // the sum fits 62 bits, so it has at most 6 diagonals: d0 == 0 here
+                    s64[c] += v0 + (int64_t)((uint64_t)v1 << 32);
+                } else {
+                    i128w t0, t1;  // v0 * 2^(8 d0), v1 * 2^(8 d0 + 32)
+                    if (d0 == 0) {
+                        t0.lo = (uint64_t)v0; t0.hi = v0 >> 63;
+                        t1.lo = (uint64_t)v1 << 32; t1.hi = v1 >> 32;
+                    } else {
+                        t0.lo = 0; t0.hi = v0;
+                        t1.lo = 0; t1.hi = (int64_t)((uint64_t)v1 << 32);
+                    }
+                    sum[c] = add128(add128(sum[c], t0), t1);
+                }
+            }
+        }
+        if (!e.row_ok) continue;
+        int64_t cv[8], rv[8];
+        const int64_t n = e.n0 + nc;
+        const int shift = p.group_shift ? p.group_shift[2 * e.group + (n >= p.n_split ? 1 : 0)] : p.shift;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            if (FITS64) {
+                cv[c] = shift >= 63 ? (s64[c] >> 63) : (s64[c] >> shift);
+                if (e.rrow) rv[c] = gemm_remainder(make_i128(s64[c]), shift, p.r_legacy);
+            } else {
+                cv[c] = sar128_lo(sum[c], shift);
+                if (e.rrow) rv[c] = gemm_remainder(sum[c], shift, p.r_legacy);
+            }
+        }
+        if (tail) {
+            int64_t av[8];
+            if (arow) {
+                if (e.vec_ok && n + 8 <= p.N && ((((uintptr_t)p.addin) & 15) == 0)) {
+#pragma unroll
+                    for (int c = 0; c < 8; c += 2) {
+                        const longlong2 t = *reinterpret_cast<const longlong2*>(arow + n + c);
+                        av[c] = t.x; av[c + 1] = t.y;
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) av[c] = (n + c < p.N) ? arow[n + c] : 0;
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                if (n + c < p.N) cv[c] = score_tail(p, cv[c], arow ? &av[c] : nullptr, n + c, srow);
+        }
+        if (e.vec_ok && n + 8 <= p.N) {
+#pragma unroll
+            for (int c = 0; c < 8; c += 2) {
+                *reinterpret_cast<longlong2*>(e.crow + n + c) = make_longlong2(cv[c], cv[c + 1]);
+                if (e.rrow) *reinterpret_cast<longlong2*>(e.rrow + n + c) = make_longlong2(rv[c], rv[c + 1]);
+            }
+        } else {
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                if (n + c < p.N) {
+                    e.crow[n + c] = cv[c];
+                    if (e.rrow) e.rrow[n + c] = rv[c];
+                }
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const LimbParams p)
@@ -338,8 +473,22 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t bar_zeroed = smem_u32(&bars[16]);
     const uint32_t bar_accum = smem_u32(&bars[17]);
 
-    const int64_t m0 = (int64_t)blockIdx.x * kTileM;
-    const int64_t n0 = (int64_t)blockIdx.y * p.NT;
+    // tiles are walked panel by panel: panel_m row tiles x all column tiles, rows fastest, so the
+    // A tiles of a panel and the B tile in flight stay in L2 while the panel is swept
+    int64_t m_tile, n_tile;
+    if (p.tile_group) { m_tile = blockIdx.x; n_tile = blockIdx.y; }
+    else {
+        const int64_t per_panel = p.panel_m * p.n_tiles;
+        const int64_t panel = blockIdx.x / per_panel;
+        const int64_t within = blockIdx.x - panel * per_panel;
+        const int64_t rows_here = (p.m_tiles - panel * p.panel_m < p.panel_m) ? p.m_tiles - panel * p.panel_m
+                                                                              : p.panel_m;
+        n_tile = within / rows_here;
+        m_tile = panel * p.panel_m + (within - n_tile * rows_here);
+        if (n_tile >= p.n_tiles) return;   // cannot happen; keeps the indices in range
+    }
+    const int64_t m0 = m_tile * kTileM;
+    const int64_t n0 = n_tile * p.NT;
     const int64_t z = blockIdx.z;
     const int D = La + p.Lb - 1;
 
@@ -411,7 +560,8 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 for (int ks = 0; ks < kBlockK / 32; ++ks) {
                     for (int i = 0; i < La; ++i) {
                         const uint64_t adesc = smem_desc_sw128(sa + i * (kTileM * kBlockK)) + (uint64_t)(ks * 2);
-                        umma_i8(tmem + (uint32_t)(i * p.NT), adesc, bdesc0 + (uint64_t)(ks * 2), idesc, 1u);
+                        umma_i8(tmem + (uint32_t)(i * p.NT), adesc, bdesc0 + (uint64_t)(ks * 2), idesc,
+                                (kb | ks | i) ? 1u : 0u);
                     }
                 }
                 umma_commit(bar_empty + 8 * s);
@@ -422,7 +572,9 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // ---- accumulator zeroing, then epilogue -------------------------------------------
         const int q = warp & 3;  // tensor-memory lane quarter this warp may touch
         const uint32_t tq = tmem + ((uint32_t)(q * 32) << 16);
-        for (int c = 0; c < D * p.NT; c += 8) tmem_st8_zero(tq + (uint32_t)c);
+        // the first MMA (limb 0, first K step) overwrites its Lb * NT columns; only the columns the
+        // later limbs extend into must start at zero
+        for (int c = p.Lb * p.NT; c < D * p.NT; c += 8) tmem_st8_zero(tq + (uint32_t)c);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
@@ -436,73 +588,12 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const bool row_ok = ok && m < p.M;
         const bool vec_ok = ((((uintptr_t)p.C | (uintptr_t)p.R) & 15) == 0) && ((p.c_sm & 1) == 0) &&
                             ((p.c_sz & 1) == 0);
-        const int groups = (D + 3) >> 2;
-        for (int nc = 0; ok && nc < p.NT; nc += 8) {
-            i128w sum[8];
-#pragma unroll
-            for (int c = 0; c < 8; ++c) sum[c] = make_i128(p.addend);
-            for (int g = 0; g < groups; ++g) {
-                int32_t a[4][8];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    if (4 * g + j < D) tmem_ld8(tq + (uint32_t)((4 * g + j) * p.NT + nc), a[j]);
-                    else {
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) a[j][c] = 0;
-                    }
-                }
-                tmem_ld_wait();
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    // four diagonals fit one int64: |a| < 2^31, weights up to 2^24
-                    int64_t v = (int64_t)a[0][c] + ((int64_t)a[1][c] << 8) + ((int64_t)a[2][c] << 16) +
-                                ((int64_t)a[3][c] << 24);
-                    i128w t;  // v * 2^(32 g)
-                    if (g == 0) { t.lo = (uint64_t)v; t.hi = v >> 63; }
-                    else if (g == 1) { t.lo = (uint64_t)v << 32; t.hi = v >> 32; }
-                    else if (g == 2) { t.lo = 0; t.hi = v; }
-                    else { t.lo = 0; t.hi = (int64_t)((uint64_t)v << 32); }
-                    sum[c] = add128(sum[c], t);
-                }
-            }
-            if (row_ok) {
-                int64_t cv[8], rv[8];
-                const int64_t n = n0 + nc;
-                const int shift = p.group_shift ? p.group_shift[2 * group + (n >= p.n_split ? 1 : 0)] : p.shift;
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    cv[c] = sar128_lo(sum[c], shift);
-                    rv[c] = gemm_remainder(sum[c], shift, p.r_legacy);
-                }
-                if (p.addin || p.ep_div || p.causal_H) {
-                    const int64_t* arow = p.addin ? p.addin + z * p.c_sz + m * p.c_sm : nullptr;
-                    const int64_t srow = p.causal_H ? m / p.causal_H : 0;
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        if (n + c >= p.N) continue;
-                        int64_t v = cv[c];
-                        if (arow) v = (int64_t)((uint64_t)v + (uint64_t)arow[n + c]);
-                        if (p.ep_div) v = floor_div_i64((int64_t)((uint64_t)v * (uint64_t)p.ep_mul), p.ep_div);
-                        if (p.causal_H && n + c > p.causal_start + srow)
-                            v = (int64_t)((uint64_t)v + (uint64_t)p.mask_value);
-                        cv[c] = v;
-                    }
-                }
-                if (vec_ok && n + 8 <= p.N) {
-#pragma unroll
-                    for (int c = 0; c < 8; c += 2) {
-                        *reinterpret_cast<longlong2*>(crow + n + c) = make_longlong2(cv[c], cv[c + 1]);
-                        if (rrow) *reinterpret_cast<longlong2*>(rrow + n + c) = make_longlong2(rv[c], rv[c + 1]);
-                    }
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 8; ++c)
-                        if (n + c < p.N) {
-                            crow[n + c] = cv[c];
-                            if (rrow) rrow[n + c] = rv[c];
-                        }
-                }
-            }
+        EpilogueCtx ec;
+        ec.tq = tq; ec.D = D; ec.NT = p.NT; ec.m = m; ec.n0 = n0; ec.z = z; ec.group = group;
+        ec.crow = crow; ec.rrow = rrow; ec.row_ok = row_ok; ec.vec_ok = vec_ok;
+        if (ok) {
+            if (p.fits64) epilogue_tile<true>(p, ec);
+            else epilogue_tile<false>(p, ec);
         }
     }
 
@@ -582,9 +673,9 @@ int launch_split_t(const T* X, int8_t* planes, int L, int64_t nb, int64_t rows, 
                    int64_t sz, int64_t sr, int64_t sk, int64_t div, unsigned* overflow, cudaStream_t st,
                    unsigned long long* absmax_out = nullptr)
 {
-    int64_t total = rows * (Kp >> 4);
+    int64_t total = rows * (Kp >> 2);
     int64_t bx = (total + 255) / 256;
-    int64_t cap = (int64_t)sm_count() * 16;
+    int64_t cap = (int64_t)sm_count() * 32;
     if (bx > cap) bx = cap;
     if (nb > 65535) return ZKDS_ERR_RANGE;
     dim3 grid((unsigned)bx, (unsigned)nb);
@@ -626,11 +717,27 @@ int limb_device_status(int clear)
 
 // ---- kernel timing hooks -------------------------------------------------------------
 static bool g_timing = false;
+static bool g_accumulate = false;
 static cudaEvent_t g_ev[64][2];
 static bool g_ev_made[64];
 static bool g_ev_valid[64];
 
-void limb_timing_enable(int on) { g_timing = on != 0; }
+static double g_tot_ms = 0.0, g_tot_ops = 0.0;
+static long long g_tot_launches = 0;
+
+void limb_timing_enable(int on)
+{
+    g_timing = on != 0;
+    if (on == 2) { g_tot_ms = 0.0; g_tot_ops = 0.0; g_tot_launches = 0; }
+    g_accumulate = (on == 2);
+}
+
+void limb_timing_totals(double* ms, double* int8_ops, long long* launches)
+{
+    if (ms) *ms = g_tot_ms;
+    if (int8_ops) *int8_ops = g_tot_ops;
+    if (launches) *launches = g_tot_launches;
+}
 
 float limb_last_kernel_ms()
 {
@@ -653,6 +760,16 @@ static cudaEvent_t* timing_events()
     }
     g_ev_valid[dev] = true;
     return g_ev[dev];
+}
+
+// |addend + sum_k a*b| < 2^62 for every operand the limb counts admit?  |a| <= 2^(8 La - 1) * 1.004
+static int sum_fits64(int La, int Lb, int64_t K, int64_t addend)
+{
+    int kbits = 0;
+    while (((int64_t)1 << kbits) < K) ++kbits;
+    const int bits = (8 * La - 1) + (8 * Lb - 1) + kbits + 1;
+    const int64_t lim = (int64_t)1 << 61;
+    return bits <= 61 && addend < lim && addend > -lim;
 }
 
 int limbs_needed(uint64_t maxabs)
@@ -755,6 +872,7 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     lp.C = p.C; lp.R = p.R; lp.c_sz = p.c_sz; lp.c_sm = p.c_sm;
     lp.addend = p.addend; lp.shift = p.shift; lp.r_legacy = p.r_legacy;
     lp.error_flag = fl->dev;
+    lp.fits64 = sum_fits64(La, Lb, p.K, p.addend);
     lp.a_absmax = d_absmax;
     lp.overflow_flag = fl->overflow_dev;
     lp.tile_group = p.tile_group;
@@ -768,12 +886,39 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     if (smem < 120 * 1024) smem = 120 * 1024;
     ZKDS_CUDA(cudaFuncSetAttribute(limb_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)(227 * 1024 - 3072)));
-    dim3 grid((unsigned)mt, (unsigned)nt, (unsigned)p.batches);
+    // panel height: the A limb tiles of one panel should stay L2 resident (~32 MB)
+    int64_t panel = (32ll << 20) / ((int64_t)La * kTileM * Kp);
+    if (panel < 1) panel = 1;
+    if (panel > mt) panel = mt;
+    lp.m_tiles = mt; lp.n_tiles = nt; lp.panel_m = panel;
+    if (mt * nt > 0x7fffffffll) return ZKDS_ERR_UNSUPPORTED;
+    dim3 grid = p.tile_group ? dim3((unsigned)mt, (unsigned)nt, 1)
+                             : dim3((unsigned)(mt * nt), 1, (unsigned)p.batches);
     cudaEvent_t* ev = timing_events();
     if (ev) ZKDS_CUDA(cudaEventRecord(ev[0], st));
     limb_gemm_kernel<<<grid, kThreads, smem, st>>>(tmA, tmB, lp);
     rc = check_launch();
     if (ev) ZKDS_CUDA(cudaEventRecord(ev[1], st));
+    if (ev && g_accumulate && rc == ZKDS_OK) {
+        // profiling pass: wait for the kernel, add its duration and the int8 work it issued
+        float ms = 0.f;
+        ZKDS_CUDA(cudaEventSynchronize(ev[1]));
+        ZKDS_CUDA(cudaEventElapsedTime(&ms, ev[0], ev[1]));
+        int la_used = La;
+        if (d_absmax) {
+            unsigned long long h = 0;
+            ZKDS_CUDA(cudaMemcpy(&h, d_absmax, sizeof(h), cudaMemcpyDeviceToHost));
+            int need = limbs_needed(h);
+            if (need < la_used) la_used = need;
+        }
+        if (getenv("ZKDS_TRACE"))
+            fprintf(stderr, "limb_gemm batches=%lld M=%lld N=%lld K=%lld La=%d(%d) Lb=%d NT=%d stages=%d fits64=%d tail=%d: %.3f ms\n",
+                    (long long)p.batches, (long long)p.M, (long long)p.N, (long long)p.K, la_used, La, Lb, NT,
+                    stages, lp.fits64, (p.addin || p.ep_div || p.causal_H) ? 1 : 0, ms);
+        g_tot_ms += ms;
+        g_tot_ops += 2.0 * (double)la_used * Lb * (double)p.batches * (double)p.M * (double)p.N * (double)p.K;
+        g_tot_launches += 1;
+    }
     return rc;
 }
 
@@ -892,12 +1037,15 @@ int launch_gemm_noalloc(const Contraction& p, int La, int Lb, cudaStream_t st)
     lp.C = p.C; lp.R = p.R; lp.c_sz = p.c_sz; lp.c_sm = p.c_sm;
     lp.addend = p.addend; lp.shift = p.shift; lp.r_legacy = p.r_legacy;
     lp.error_flag = d_err;
+    lp.fits64 = sum_fits64(La, Lb, p.K, p.addend);
 
     size_t smem = stage * stages + 1024;
     if (smem < 120 * 1024) smem = 120 * 1024;
     ZKDS_CUDA(cudaFuncSetAttribute(limb_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)(227 * 1024 - 3072)));
-    dim3 grid((unsigned)mt, (unsigned)nt, (unsigned)p.batches);
+    lp.m_tiles = mt; lp.n_tiles = nt; lp.panel_m = mt;
+    if (mt * nt > 0x7fffffffll) return ZKDS_ERR_UNSUPPORTED;
+    dim3 grid((unsigned)(mt * nt), 1, (unsigned)p.batches);
     limb_gemm_kernel<<<grid, kThreads, smem, st>>>(tmA, tmB, lp);
     rc = check_launch();
     if (rc != ZKDS_OK) return rc;

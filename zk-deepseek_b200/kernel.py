@@ -86,6 +86,8 @@ _sig("zkds_lut", [_vp, _i])
 _sig("zkds_device_status", [_i])
 _sig("zkds_timing", [_i], None)
 _sig("zkds_last_kernel_ms", [], ctypes.c_float)
+_sig("zkds_timing_totals", [ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double),
+                            ctypes.POINTER(ctypes.c_longlong)], None)
 _sig("zkds_planes_create", [_vp, _i, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _i, ctypes.POINTER(_vp), _vp])
 _sig("zkds_planes_limbs", [_vp])
 _sig("zkds_planes_destroy", [_vp])
@@ -227,7 +229,15 @@ def device_status(clear=True):
 
 
 def kernel_timing(enable):
-    lib.zkds_timing(1 if enable else 0)
+    """True/1: event pair around each tensor-core launch; 2: also accumulate totals (waits per launch)"""
+    lib.zkds_timing(int(enable))
+
+
+def kernel_timing_totals():
+    """(total ms, total int8 ops = limb pairs x 2MNK, launches) since kernel_timing(2)"""
+    ms, ops, n = ctypes.c_double(), ctypes.c_double(), ctypes.c_longlong()
+    lib.zkds_timing_totals(ctypes.byref(ms), ctypes.byref(ops), ctypes.byref(n))
+    return ms.value, ops.value, n.value
 
 
 def last_kernel_ms():
