@@ -526,6 +526,180 @@ class MlaWorkload:
         return S / dt, "%d of 4096 query tokens against the full 4096-token cache and full weights" % S, dt
 
 
+class MoeWorkload:
+    """One DeepSeek-V3 MoE layer in int64 fixed point (MoE.forward, inference/model.py:1325-1383):
+    dim 7168, 256 routed experts + 1 shared expert, moe_inter_dim 2048, sigmoid gate with top-8
+    routing over 8 groups / 4 kept, route scale 2.5.  8192 tokens ~ N(0, 2^16); int32 gate,
+    shared and expert weights ~ N(0, 2^16/sqrt(fan_in)); int32 gate bias >= 0; every shift 16.
+    With N GPUs the experts are split 256/N per GPU and the 8192 tokens N ways; rows travel to the
+    experts' owners and back with NCCL all-to-all (strong scaling)."""
+    name = "moe_layer_8192_tokens"
+    metric = "int64_moe_layer_tokens_per_s"
+    unit = "tokens/s"
+    scaling = "strong"
+    T, E, SHIFT = 8192, 256, 16
+
+    def __init__(self, torch, k, dev, rank, T=None, E=None):
+        import numpy as np
+        import torch.distributed as dist
+        self.torch, self.k, self.dev, self.np, self.rank = torch, k, dev, np, rank
+        if T:
+            self.T = T
+        if E:
+            self.E = E
+        M = importlib.import_module(PKG + ".model")
+        self.M = M
+        M.world_size = dist.get_world_size() if dist.is_initialized() else 1
+        M.rank = dist.get_rank() if dist.is_initialized() else 0
+        self.world = M.world_size
+        a = M.ModelArgs(max_seq_len=64, vocab_size=129280, dim=7168, inter_dim=18432, moe_inter_dim=2048,
+                        n_layers=61, n_dense_layers=3, n_heads=128, n_routed_experts=self.E,
+                        n_shared_experts=1, n_activated_experts=8, n_expert_groups=8, n_limited_groups=4,
+                        score_func="sigmoid", route_scale=2.5, q_lora_rank=1536, kv_lora_rank=512,
+                        qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128)
+        self.args = a
+        D, I = a.dim, a.moe_inter_dim
+        with torch.device(dev):
+            moe = M.MoE(3, a)
+        g = torch.Generator(device=dev).manual_seed(6)
+        sh = self.SHIFT
+
+        def weight(gen, out_f, in_f):
+            return _normal_i(torch, gen, (out_f, in_f), 2.0**16 / math.sqrt(in_f), dev, torch.int32)
+
+        moe.gate.weight = weight(g, self.E, D)
+        moe.gate.scale = torch.tensor(sh, dtype=torch.int32, device=dev)
+        moe.gate.bias = torch.abs(_normal_i(torch, g, (self.E,), 2.0**18, dev, torch.int64)).to(torch.int32)
+        for name, (o, i) in (("w1", (I, D)), ("w3", (I, D)), ("w2", (D, I))):
+            lin = getattr(moe.shared_experts, name)
+            lin.weight = weight(g, o, i)
+            lin.scale = torch.tensor(sh, dtype=torch.int32, device=dev)
+        for j in range(moe.n_local_experts):          # seeded by the global expert id
+            ge = torch.Generator(device=dev).manual_seed(10000 + moe.experts_start_idx + j)
+            moe.experts_w13[j, :I] = weight(ge, I, D)
+            moe.experts_w13[j, I:] = weight(ge, I, D)
+            moe.experts_w2[j] = weight(ge, D, I)
+        moe.experts_shift.fill_(sh)
+        self.moe = moe
+        gx = torch.Generator(device=dev).manual_seed(66)
+        x_all = _normal_i(torch, gx, (self.T, D), 2.0**16, dev, torch.int64)
+        self.T_local = self.T // self.world
+        self.x = x_all[M.rank * self.T_local:(M.rank + 1) * self.T_local].contiguous()[None]
+        del x_all
+        M.ACT_LIMBS = 3
+        k.silu_init_q23()
+        self.x_host = None
+        pairs = self.T * a.n_activated_experts
+        self.ops = 2.0 * 3 * D * I * (pairs + self.T) + 2.0 * self.T * D * self.E
+        self.launches_per_step = 0
+
+    def config(self):
+        a = self.args
+        return {"workload": self.name, "tokens": self.T, "tokens_per_gpu": self.T_local, "dim": a.dim,
+                "routed_experts": self.E, "experts_per_gpu": self.E // self.world, "top_k": 8,
+                "moe_inter_dim": a.moe_inter_dim, "shift": self.SHIFT, "act_limbs_bound": 3,
+                "useful_ops_per_step": self.ops, "weights": "resident limb planes, all experts",
+                "l2": "expert weights (45 GB int32) and token rows far exceed L2"}
+
+    def step(self):
+        return self.moe(0, self.x)
+
+    def step_e2e(self):
+        torch = self.torch
+        if self.x_host is None:
+            self.x_host = self.x.cpu().pin_memory()
+            self.x_in = torch.empty_like(self.x)
+            self.y_host = torch.empty_like(self.x_host).pin_memory()
+        self.x_in.copy_(self.x_host, non_blocking=True)
+        y = self.moe(0, self.x_in)
+        self.y_host.copy_(y, non_blocking=True)
+
+    def e2e_bytes(self):
+        n = 8 * self.T_local * self.args.dim
+        return n, n
+
+    def value(self, seconds_per_step, world):
+        return self.T / seconds_per_step
+
+    def roofline(self, peaks):
+        k = self.k
+        k.kernel_timing(2)
+        self.step()
+        self.torch.cuda.synchronize()
+        recs = k.kernel_timing_records()
+        k.kernel_timing(False)
+        pairs_local = self.T_local * 8 if self.world == 1 else None
+        ms = sum(r["ms"] for r in recs)
+        ops = 0.0
+        for r in recs:
+            rows = r["batches"] * r["M"]
+            if r["grouped"] and pairs_local:
+                rows = pairs_local                      # padded tiles carry no useful work
+            ops += 2.0 * r["la"] * r["lb"] * rows * r["N"] * r["K"]
+        self.launches_per_step = 2 * len(recs) + 3 + 12   # + gather, GLU x2, combine, sigmoid, routing ops
+        int8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+        achieved = ops / (ms * 1e-3) / 1e12
+        return {"bound": "tensor", "kernel": "limb_gemm_kernel (%d launches per step)" % len(recs),
+                "achieved": round(achieved, 1), "peak": round(int8_peak, 1), "unit": "TFLOP/s",
+                "frac": round(achieved / int8_peak, 4), "traffic": None, "kernel_ms": round(ms, 3),
+                "launches": [{kk: (round(v, 3) if kk == "ms" else v) for kk, v in r.items()} for r in recs],
+                "note": "limb pairs x 2 x rows x N x K of every tensor-core launch (grouped launches count the "
+                        "routed rows, not the padding) / sum of CUDA-event durations; peak = 2 x sustained "
+                        "cuBLAS bf16 (%s)" % peaks["source"]}
+
+    def check(self, orc):
+        """four tokens against the numpy restatement of MoE.forward (the GPU's expert choice is
+        passed on so that a score tie cannot make the two differ)"""
+        if self.world > 1:
+            return None
+        from oracle import model_oracle as mo
+        np, a, moe = self.np, self.args, self.moe
+        I = a.moe_inter_dim
+        xs = self.x[:, :4].contiguous()
+        got = moe(0, xs).cpu().numpy()
+        idx = moe.gate(0, xs.view(-1, a.dim))[1].cpu().numpy()
+        sh = self.SHIFT
+        mlp = lambda m: {"w1": m.w1.weight.cpu().numpy(), "w3": m.w3.weight.cpu().numpy(),
+                         "w2": m.w2.weight.cpu().numpy(), "w1_scale": sh, "w3_scale": sh, "w2_scale": sh}
+        experts = [None] * self.E
+        for e in np.unique(idx):
+            experts[e] = {"w1": moe.experts_w13[e, :I].cpu().numpy(), "w3": moe.experts_w13[e, I:].cpu().numpy(),
+                          "w2": moe.experts_w2[e].cpu().numpy(), "w1_scale": sh, "w3_scale": sh, "w2_scale": sh}
+        p = {"gate": {"weight": moe.gate.weight.cpu().numpy(), "scale": sh, "bias": moe.gate.bias.cpu().numpy()},
+             "shared": mlp(moe.shared_experts), "experts": experts}
+        want, _, _ = mo.moe_forward(p, xs.cpu().numpy(), 8, 4, 8, indices=idx)
+        return int((got != want).sum())
+
+    @staticmethod
+    def cpu_sample(orc, np, seconds, rank=0):
+        """per-token work of the layer on a token sample: gate, shared expert and 8 routed experts"""
+        D, I, S = 7168, 2048, 8
+        rng = np.random.default_rng(6)
+        ri = lambda shape, b: np.rint(rng.standard_normal(shape) * 2.0**b).astype(np.int64)
+        w13 = ri((2 * I, D), 9).astype(np.int32)
+        w2 = ri((D, I), 10).astype(np.int32)
+        wg = ri((256, D), 9).astype(np.int32)
+        x = ri((1, S, D), 16)
+        t0 = time.time()
+        orc.act(orc.gemm(x, wg, 1, 1, 16)[0], "sigmoid", 23)
+        for _ in range(9):                       # shared + 8 routed experts per token
+            r = orc.gemm(x, w13, 1, 1, 16)[0]
+            h = (orc.act(np.ascontiguousarray(r[..., :I]), "silu", 23) * r[..., I:]) >> 23
+            orc.gemm(h, w2, 1, 1, 16)
+        dt = time.time() - t0
+        return S / dt, "%d of 8192 tokens through gate, shared expert and 8 routed experts" % S, dt
+
+
+class MoeSmallWorkload(MoeWorkload):
+    """The MoE layer with 2048 tokens and 64 experts (quick checks, profiler captures)."""
+    name = "moe_layer_2048_tokens_64_experts"
+    T, E = 2048, 64
+
+    @staticmethod
+    def cpu_sample(orc, np, seconds, rank=0):
+        return MoeWorkload.cpu_sample(orc, np, seconds, rank)
+
+
 class GemmProfWorkload(GemmWorkload):
     """Smaller GEMM of the same kernel for profiler captures (inputs still exceed L2)."""
     name = "gemm_4096x8192x4096"
@@ -571,7 +745,7 @@ class MlaSmallWorkload(MlaWorkload):
 
 WORKLOADS = {"gemm": GemmWorkload, "gemm_prof": GemmProfWorkload, "chain": ChainWorkload,
              "chain_prof": ChainProfWorkload, "mla": MlaWorkload, "mla_ref": MlaRefScaleWorkload,
-             "mla_small": MlaSmallWorkload}
+             "mla_small": MlaSmallWorkload, "moe": MoeWorkload, "moe_small": MoeSmallWorkload}
 DEFAULT_WORKLOAD = "gemm"
 
 

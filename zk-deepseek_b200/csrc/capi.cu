@@ -419,6 +419,7 @@ int zkds_act(const int64_t* X, int64_t* C, const int64_t* lut, int64_t n, int fr
 int zkds_device_status(int clear) { return limb_device_status(clear); }
 void zkds_timing(int enable) { limb_timing_enable(enable); }
 float zkds_last_kernel_ms(void) { return limb_last_kernel_ms(); }
+int zkds_timing_record(long long i, double* out8) { return limb_timing_record(i, out8); }
 void zkds_timing_totals(double* ms, double* int8_ops, long long* launches)
 {
     limb_timing_totals(ms, int8_ops, launches);

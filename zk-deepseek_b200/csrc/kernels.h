@@ -97,6 +97,8 @@ float limb_last_kernel_ms();
 // on == 2 also accumulates, per launch, the kernel's duration and limb-pairs x 2MNK (waits for
 // every launch: a profiling pass, not a timed one)
 void limb_timing_totals(double* ms, double* int8_ops, long long* launches);
+// i-th launch since accumulation started: {batches, M, N, K, a limbs used, b limbs, ms, grouped}
+int limb_timing_record(long long i, double* out8);
 
 // ZKDS_ERR_DEVICE when a tensor-core kernel reported a wait that ran out, ZKDS_ERR_RANGE
 // when an operand did not fit the limb count it was split into, else ZKDS_OK.  The flags

@@ -724,6 +724,15 @@ static bool g_ev_valid[64];
 
 static double g_tot_ms = 0.0, g_tot_ops = 0.0;
 static long long g_tot_launches = 0;
+struct LaunchRecord { double v[8]; };
+static LaunchRecord g_records[256];
+
+int limb_timing_record(long long i, double* out8)
+{
+    if (i < 0 || i >= g_tot_launches || i >= 256) return 0;
+    for (int j = 0; j < 8; ++j) out8[j] = g_records[i].v[j];
+    return 1;
+}
 
 void limb_timing_enable(int on)
 {
@@ -915,6 +924,11 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
             fprintf(stderr, "limb_gemm batches=%lld M=%lld N=%lld K=%lld La=%d(%d) Lb=%d NT=%d stages=%d fits64=%d tail=%d: %.3f ms\n",
                     (long long)p.batches, (long long)p.M, (long long)p.N, (long long)p.K, la_used, La, Lb, NT,
                     stages, lp.fits64, (p.addin || p.ep_div || p.causal_H) ? 1 : 0, ms);
+        if (g_tot_launches < 256) {
+            LaunchRecord& r = g_records[g_tot_launches];
+            r.v[0] = (double)p.batches; r.v[1] = (double)p.M; r.v[2] = (double)p.N; r.v[3] = (double)p.K;
+            r.v[4] = la_used; r.v[5] = Lb; r.v[6] = ms; r.v[7] = p.tile_group ? 1.0 : 0.0;
+        }
         g_tot_ms += ms;
         g_tot_ops += 2.0 * (double)la_used * Lb * (double)p.batches * (double)p.M * (double)p.N * (double)p.K;
         g_tot_launches += 1;

@@ -84,6 +84,7 @@ _sig("zkds_softmax", [_vp, _vp, _vp, _vp, _ll, _ll, _i, _vp])
 _sig("zkds_act", [_vp, _vp, _vp, _ll, _i, _i, _vp])
 _sig("zkds_lut", [_vp, _i])
 _sig("zkds_device_status", [_i])
+_sig("zkds_timing_record", [ctypes.c_longlong, ctypes.POINTER(ctypes.c_double)])
 _sig("zkds_timing", [_i], None)
 _sig("zkds_last_kernel_ms", [], ctypes.c_float)
 _sig("zkds_timing_totals", [ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double),
@@ -231,6 +232,16 @@ def device_status(clear=True):
 def kernel_timing(enable):
     """True/1: event pair around each tensor-core launch; 2: also accumulate totals (waits per launch)"""
     lib.zkds_timing(int(enable))
+
+
+def kernel_timing_records():
+    """per-launch records since kernel_timing(2): dicts with batches, M, N, K, la, lb, ms, grouped"""
+    out, buf, i = [], (ctypes.c_double * 8)(), 0
+    while lib.zkds_timing_record(ctypes.c_longlong(i), buf):
+        out.append(dict(batches=int(buf[0]), M=int(buf[1]), N=int(buf[2]), K=int(buf[3]), la=int(buf[4]),
+                        lb=int(buf[5]), ms=buf[6], grouped=bool(buf[7])))
+        i += 1
+    return out
 
 
 def kernel_timing_totals():
