@@ -12,7 +12,7 @@
 // further right.  The epilogue reads the diagonals back, recombines them in 128 bits, adds
 // the rounding addend, shifts, and writes the int64 quotient (and remainder).
 //
-// One CTA computes a 128 x NT output tile: warp 0 issues TMA loads (no multicast),
+// One CTA computes a 128 x NT output tile: warp 0 issues plain per-CTA TMA loads,
 // warp 1 owns tensor memory and issues the MMAs, warps 2-5 zero the accumulators, then
 // run the epilogue.  Every wait is bounded; a wait that runs out raises a flag the host
 // reads, and the CTA leaves through the normal exit path (tensor memory released).

@@ -195,9 +195,10 @@ class ColumnParallelLinear_int(Linear_int):
     """Output features split over ranks (each column sees the full K: exact)."""
 
     def __init__(self, layer_id, in_features, out_features, x_rescale, weight_rescale, res_rescale, dtype,
-                 bias=False):
-        assert out_features % world_size == 0
-        self.part_out_features = out_features // world_size
+                 bias=False, parallel=True):
+        parts = world_size if parallel else 1
+        assert out_features % parts == 0
+        self.part_out_features = out_features // parts
         super().__init__(layer_id, in_features, self.part_out_features, x_rescale, weight_rescale,
                          res_rescale, dtype, bias)
 
@@ -206,9 +207,11 @@ class ColumnParallelLinear_int(Linear_int):
 
 
 class ColumnParallelLinear_rescale_int(Linear_int):
-    def __init__(self, layer_id, in_features, out_features, x_rescale, weight_rescale, dtype, bias=False):
-        assert out_features % world_size == 0
-        self.part_out_features = out_features // world_size
+    def __init__(self, layer_id, in_features, out_features, x_rescale, weight_rescale, dtype, bias=False,
+                 parallel=True):
+        parts = world_size if parallel else 1
+        assert out_features % parts == 0
+        self.part_out_features = out_features // parts
         super().__init__(layer_id, in_features, self.part_out_features, x_rescale, weight_rescale, 1, dtype,
                          bias)
         self.register_buffer("scale", torch.tensor(0, dtype=torch.int32))
@@ -223,16 +226,17 @@ class RowParallelLinear_rescale_int(Linear_int):
     columns over ranks; the caller all-gathers (see MLA / MLP_int)."""
 
     def __init__(self, layer_id, in_features, out_features, x_rescale, weight_rescale, res_rescale, dtype,
-                 bias=False):
-        assert out_features % world_size == 0
-        self.part_out_features = out_features // world_size
+                 bias=False, parallel=True):
+        self.parts = world_size if parallel else 1
+        assert out_features % self.parts == 0
+        self.part_out_features = out_features // self.parts
         super().__init__(layer_id, in_features, self.part_out_features, x_rescale, weight_rescale,
                          res_rescale, dtype, bias)
         self.register_buffer("scale", torch.tensor(0, dtype=torch.int32))
 
     def forward(self, x):
         y = self._run(x, self.shift(), False)
-        if world_size > 1:
+        if self.parts > 1:
             y = _all_gather_last(y)
         return y
 
@@ -436,14 +440,15 @@ class MLP_int(nn.Module):
     """w2((silu_q23(w1 x) * w3 x) >> 23) (model.py:994-1049); w1 and w3 run as one stacked GEMM
     when their shifts agree."""
 
-    def __init__(self, layer_id, dim: int, inter_dim: int):
+    def __init__(self, layer_id, dim: int, inter_dim: int, parallel: bool = True):
         super().__init__()
         self.layer_id = layer_id
         self.inter_dim = inter_dim
+        self.parts = world_size if parallel else 1
         i32 = torch.int32
-        self.w1 = ColumnParallelLinear_rescale_int(layer_id, dim, inter_dim, 1, 1, i32)
-        self.w2 = RowParallelLinear_rescale_int(layer_id, inter_dim, dim, 1, 1, 1, i32)
-        self.w3 = ColumnParallelLinear_rescale_int(layer_id, dim, inter_dim, 1, 1, i32)
+        self.w1 = ColumnParallelLinear_rescale_int(layer_id, dim, inter_dim, 1, 1, i32, parallel=parallel)
+        self.w2 = RowParallelLinear_rescale_int(layer_id, inter_dim, dim, 1, 1, 1, i32, parallel=parallel)
+        self.w3 = ColumnParallelLinear_rescale_int(layer_id, dim, inter_dim, 1, 1, i32, parallel=parallel)
         self._w13 = None
 
     def _stacked(self):
@@ -474,7 +479,7 @@ class MLP_int(nn.Module):
         else:
             h = K.glu_q23(r1, r2, ld=ld)
         h = h.view(*x.shape[:-1], n)
-        if world_size > 1:
+        if self.parts > 1:
             h = _all_gather_last(h)
         return self.w2(h)
 
@@ -582,9 +587,14 @@ class MoE(nn.Module):
     grouped GEMMs over token rows sorted by expert.  `set_experts()` fills them from Expert_int
     modules or from the checkpoint's `experts-{layer}/{i}.safetensors` files."""
 
-    def __init__(self, layer_id, args: ModelArgs, ckpt_path=None):
+    def __init__(self, layer_id, args: ModelArgs, ckpt_path=None, token_parallel: bool = False):
         super().__init__()
         self.layer_id, self.ckpt_path = layer_id, ckpt_path
+        # False: every rank sees all tokens (the reference's layout under tensor parallelism),
+        # runs its own experts on them and the partial sums are all-reduced (exact: integer adds).
+        # True: every rank holds its own tokens; rows travel to the experts' owners and back with
+        # all-to-all, gate and shared expert run on the local tokens with whole weights.
+        self.token_parallel = token_parallel
         self.dim, self.moe_inter_dim = args.dim, args.moe_inter_dim
         assert args.n_routed_experts % world_size == 0
         self.n_routed_experts = args.n_routed_experts
@@ -593,7 +603,8 @@ class MoE(nn.Module):
         self.experts_start_idx = rank * self.n_local_experts
         self.experts_end_idx = self.experts_start_idx + self.n_local_experts
         self.gate = Gate(layer_id, args)
-        self.shared_experts = MLP_int(layer_id, args.dim, args.n_shared_experts * args.moe_inter_dim)
+        self.shared_experts = MLP_int(layer_id, args.dim, args.n_shared_experts * args.moe_inter_dim,
+                                      parallel=not token_parallel)
         E, I, D = self.n_local_experts, args.moe_inter_dim, args.dim
         self.register_buffer("experts_w13", torch.empty(E, 2 * I, D, dtype=torch.int32), persistent=False)
         self.register_buffer("experts_w2", torch.empty(E, D, I, dtype=torch.int32), persistent=False)
@@ -691,9 +702,13 @@ class MoE(nn.Module):
         shape = x.size()
         x = x.view(-1, self.dim)
         weights, indices = self.gate(start_pos, x)
-        if world_size > 1:
+        if world_size > 1 and self.token_parallel:
             from . import parallel
             y = parallel.expert_parallel_forward(self, start_pos, x, weights, indices)
+            return (y + z.view(-1, self.dim)).view(shape)
+        if world_size > 1:
+            y = self.experts_forward(start_pos, x, weights, indices)
+            dist.all_reduce(y)                        # model.py:1381-1382
             return (y + z.view(-1, self.dim)).view(shape)
         y = self.experts_forward(start_pos, x, weights, indices, base=z.view(-1, self.dim).contiguous())
         return y.view(shape)
