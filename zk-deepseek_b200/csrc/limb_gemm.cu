@@ -314,6 +314,20 @@ __device__ __forceinline__ int64_t floor_div_i64(int64_t a, int64_t b)
     return (r != 0 && ((r < 0) != (b < 0))) ? q - 1 : q;
 }
 
+// a * b + c with 32-bit signed factors and a 64-bit accumulator in one instruction
+__device__ __forceinline__ int64_t mad_wide(int32_t a, int32_t b, int64_t c)
+{
+    int64_t d;
+    asm("mad.wide.s32 %0, %1, %2, %3;" : "=l"(d) : "r"(a), "r"(b), "l"(c));
+    return d;
+}
+
+// four consecutive diagonals -> a0 + a1 * 2^8 + a2 * 2^16 + a3 * 2^24 (|a| < 2^31: fits 56 bits)
+__device__ __forceinline__ int64_t four_diagonals(int32_t a0, int32_t a1, int32_t a2, int32_t a3)
+{
+    return mad_wide(a3, 1 << 24, mad_wide(a2, 1 << 16, mad_wide(a1, 1 << 8, (int64_t)a0)));
+}
+
 struct EpilogueCtx {
     uint32_t tq;
     int D, NT, group;
@@ -358,11 +372,10 @@ __device__ __forceinline__ void epilogue_tile(const LimbParams& p, const Epilogu
             if (FITS64) s64[c] = p.addend;
             else sum[c] = make_i128(p.addend);
         }
-        // up to eight diagonals are fetched before one wait: the loads overlap each other
-        for (int d0 = 0; d0 < e.D; d0 += 8) {
-            int32_t a[8][8];
+        for (int d0 = 0, g = 0; d0 < e.D; d0 += 4, ++g) {
+            int32_t a[4][8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < 4; ++j) {
                 if (d0 + j < e.D) tmem_ld8(e.tq + (uint32_t)((d0 + j) * e.NT + nc), a[j]);
                 else {
 #pragma unroll
@@ -372,24 +385,17 @@ __device__ __forceinline__ void epilogue_tile(const LimbParams& p, const Epilogu
             tmem_ld_wait();
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
-                // four diagonals fit one int64: |a| < 2^31, weights up to 2^24
-                const int64_t v0 = (int64_t)a[0][c] + ((int64_t)a[1][c] << 8) + ((int64_t)a[2][c] << 16) +
-                                   ((int64_t)a[3][c] << 24);
-                const int64_t v1 = (int64_t)a[4][c] + ((int64_t)a[5][c] << 8) + ((int64_t)a[6][c] << 16) +
-                                   ((int64_t)a[7][c] << 24);
+                const int64_t v = four_diagonals(a[0][c], a[1][c], a[2][c], a[3][c]);
                 if (FITS64) {
-                    // the sum fits 62 bits, so it has at most 6 diagonals: d0 == 0 here
-                    s64[c] += v0 + (int64_t)((uint64_t)v1 << 32);
+                    // the sum fits 62 bits, so it has at most 6 diagonals: g <= 1 here
+                    s64[c] += g ? (int64_t)((uint64_t)v << 32) : v;
                 } else {
-                    i128w t0, t1;  // v0 * 2^(8 d0), v1 * 2^(8 d0 + 32)
-                    if (d0 == 0) {
-                        t0.lo = (uint64_t)v0; t0.hi = v0 >> 63;
-                        t1.lo = (uint64_t)v1 << 32; t1.hi = v1 >> 32;
-                    } else {
-                        t0.lo = 0; t0.hi = v0;
-                        t1.lo = 0; t1.hi = (int64_t)((uint64_t)v1 << 32);
-                    }
-                    sum[c] = add128(add128(sum[c], t0), t1);
+                    i128w t;  // v * 2^(32 g)
+                    if (g == 0) { t.lo = (uint64_t)v; t.hi = v >> 63; }
+                    else if (g == 1) { t.lo = (uint64_t)v << 32; t.hi = v >> 32; }
+                    else if (g == 2) { t.lo = 0; t.hi = v; }
+                    else { t.lo = 0; t.hi = (int64_t)((uint64_t)v << 32); }
+                    sum[c] = add128(sum[c], t);
                 }
             }
         }
@@ -594,6 +600,308 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (ok) {
             if (p.fits64) epilogue_tile<true>(p, ec);
             else epilogue_tile<false>(p, ec);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) tmem_dealloc(tmem, p.tmem_cols);
+    if (threadIdx.x == 0 && s_abort) *p.error_flag = 1;
+}
+
+// ------------------------------------------------------------------------------------
+// persistent variant for shallow K
+// ------------------------------------------------------------------------------------
+// When K is small (attention scores, per-head projections) a tile's MMAs take a few thousand
+// cycles and the prologue and epilogue of a one-tile CTA dominate.  Here one CTA per SM walks
+// many tiles: the accumulators are double-buffered in tensor memory so the MMAs of tile t+1
+// run while eight epilogue warps drain tile t, the TMA pipeline keeps streaming across tile
+// boundaries, and the results leave through a shared-memory staging tile as whole rows
+// (coalesced 16-byte stores) instead of one 64-byte fragment per thread.
+constexpr int kPThreads = 320;   // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue
+constexpr int kEpiWarps = 8;
+
+struct TileCoord {
+    int64_t z, m0, n0;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const LimbParams& p, int64_t tile)
+{
+    const int64_t per_batch = p.m_tiles * p.n_tiles;
+    TileCoord c;
+    c.z = tile / per_batch;
+    const int64_t id = tile - c.z * per_batch;
+    const int64_t per_panel = p.panel_m * p.n_tiles;
+    const int64_t panel = id / per_panel;
+    const int64_t within = id - panel * per_panel;
+    const int64_t rows_here = (p.m_tiles - panel * p.panel_m < p.panel_m) ? p.m_tiles - panel * p.panel_m
+                                                                          : p.panel_m;
+    const int64_t n_tile = within / rows_here;
+    c.m0 = (panel * p.panel_m + (within - n_tile * rows_here)) * kTileM;
+    c.n0 = n_tile * p.NT;
+    return c;
+}
+
+// one epilogue warp: rows 32 q .. 32 q + 31 of the tile, columns [c0, c0 + CW) of it
+template <bool FITS64>
+__device__ __forceinline__ void epilogue_part(const LimbParams& p, uint32_t tq, int D, const TileCoord& tc,
+                                              int q, int lane, int c0, int CW, uint8_t* stage, int RS)
+{
+    const int64_t m = tc.m0 + q * 32 + lane;
+    const bool tail = p.addin || p.ep_div || p.causal_H;
+    const int64_t srow = p.causal_H ? m / p.causal_H : 0;
+    const int64_t nbase = tc.n0 + c0;
+    const bool vec_ok = ((((uintptr_t)p.C | (uintptr_t)p.addin) & 15) == 0) && ((p.c_sm & 1) == 0) &&
+                        ((p.c_sz & 1) == 0);
+    // lanes_per_row lanes move one staged row (16 bytes each); several rows per instruction
+    int lanes_per_row = 1;
+    while (lanes_per_row * 2 < CW) lanes_per_row <<= 1;
+    const int rows_per_it = 32 / lanes_per_row;
+    const int rl = lane / lanes_per_row, cl = (lane % lanes_per_row) * 2;
+
+    if (p.addin) {
+        // bring this warp's part of the addin tile in as whole rows; the 16-byte copies are
+        // asynchronous (all in flight together), one wait at the end
+        for (int r0 = 0; r0 < 32; r0 += rows_per_it) {
+            const int r = r0 + rl;
+            const int64_t mr = tc.m0 + q * 32 + r;
+            if (cl < CW && mr < p.M) {
+                const int64_t* src = p.addin + tc.z * p.c_sz + mr * p.c_sm + nbase + cl;
+                uint8_t* dst = stage + r * RS + cl * 8;
+                if (vec_ok && nbase + cl + 2 <= p.N) {
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src)
+                                 : "memory");
+                } else {
+                    int64_t v0 = 0, v1 = 0;
+                    if (nbase + cl < p.N) v0 = src[0];
+                    if (nbase + cl + 1 < p.N) v1 = src[1];
+                    *reinterpret_cast<longlong2*>(dst) = make_longlong2(v0, v1);
+                }
+            }
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        __syncwarp();
+    }
+
+    for (int nc = 0; nc < CW; nc += 8) {
+        i128w sum[8];
+        int64_t s64[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            if (FITS64) s64[c] = p.addend;
+            else sum[c] = make_i128(p.addend);
+        }
+        for (int d0 = 0, g = 0; d0 < D; d0 += 4, ++g) {
+            int32_t a[4][8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (d0 + j < D) tmem_ld8(tq + (uint32_t)((d0 + j) * p.NT + c0 + nc), a[j]);
+                else {
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) a[j][c] = 0;
+                }
+            }
+            tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const int64_t v = four_diagonals(a[0][c], a[1][c], a[2][c], a[3][c]);
+                if (FITS64) {
+                    s64[c] += g ? (int64_t)((uint64_t)v << 32) : v;
+                } else {
+                    i128w t;  // v * 2^(32 g)
+                    if (g == 0) { t.lo = (uint64_t)v; t.hi = v >> 63; }
+                    else if (g == 1) { t.lo = (uint64_t)v << 32; t.hi = v >> 32; }
+                    else if (g == 2) { t.lo = 0; t.hi = v; }
+                    else { t.lo = 0; t.hi = (int64_t)((uint64_t)v << 32); }
+                    sum[c] = add128(sum[c], t);
+                }
+            }
+        }
+        int64_t cv[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            if (FITS64) cv[c] = p.shift >= 63 ? (s64[c] >> 63) : (s64[c] >> p.shift);
+            else cv[c] = sar128_lo(sum[c], p.shift);
+        }
+        int64_t* srow_ptr = reinterpret_cast<int64_t*>(stage + lane * RS + nc * 8);
+        if (tail) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                cv[c] = score_tail(p, cv[c], p.addin ? srow_ptr + c : nullptr, nbase + nc + c, srow);
+        }
+#pragma unroll
+        for (int c = 0; c < 8; c += 2)
+            *reinterpret_cast<longlong2*>(srow_ptr + c) = make_longlong2(cv[c], cv[c + 1]);
+    }
+    __syncwarp();
+    // write the staged rows out, whole rows at a time
+    for (int r0 = 0; r0 < 32; r0 += rows_per_it) {
+        const int r = r0 + rl;
+        const int64_t mr = tc.m0 + q * 32 + r;
+        if (cl < CW && mr < p.M) {
+            const longlong2 v = *reinterpret_cast<const longlong2*>(stage + r * RS + cl * 8);
+            int64_t* dst = p.C + tc.z * p.c_sz + mr * p.c_sm + nbase + cl;
+            if (vec_ok && nbase + cl + 2 <= p.N) *reinterpret_cast<longlong2*>(dst) = v;
+            else {
+                if (nbase + cl < p.N) dst[0] = v.x;
+                if (nbase + cl + 1 < p.N) dst[1] = v.y;
+            }
+        }
+    }
+    __syncwarp();
+}
+
+__global__ void __launch_bounds__(kPThreads, 1)
+limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                            const LimbParams p)
+{
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bars[2 * 8 + 4];
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int La = p.La;
+    if (p.a_absmax) {
+        const int need = limbs_needed_dev(*p.a_absmax);
+        if (need > La) {
+            if (threadIdx.x == 0 && blockIdx.x == 0) *p.overflow_flag = 1u;
+        } else La = need;
+    }
+    const int D = La + p.Lb - 1;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t a_bytes = (uint32_t)p.La * kTileM * kBlockK;
+    const uint32_t b_bytes = (uint32_t)p.Lb * p.NT * kBlockK;
+    const uint32_t stage_bytes = a_bytes + b_bytes;
+    const uint32_t bar_full = smem_u32(&bars[0]);
+    const uint32_t bar_empty = smem_u32(&bars[8]);
+    const uint32_t bar_tfull = smem_u32(&bars[16]);    // [2]: accumulators of a tile complete
+    const uint32_t bar_tempty = smem_u32(&bars[18]);   // [2]: buffer drained and re-zeroed
+    const int buf_cols = (p.La + p.Lb - 1) * p.NT;     // spacing of the two accumulator buffers
+    const int64_t n_tiles_total = p.batches * p.m_tiles * p.n_tiles;
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_tfull + 8 * b, 1);
+            mbar_init(bar_tempty + 8 * b, kEpiWarps);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(&s_tmem_base), p.tmem_cols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem_base;
+    volatile int* abort_flag = &s_abort;
+
+    if (warp == 0) {
+        // ---- TMA producer: one continuous pipeline over all of this CTA's tiles ---------------
+        if (lane == 0) {
+            const uint32_t tx_bytes = (uint32_t)La * kTileM * kBlockK + b_bytes;
+            int64_t it = 0, armed = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; ok && tile < n_tiles_total; tile += gridDim.x) {
+                const TileCoord tc = decode_tile(p, tile);
+                const int64_t zb = p.b_batched ? tc.z : 0;
+                for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+                    const int s = (int)(it % p.stages);
+                    const uint32_t par = (uint32_t)((it / p.stages) & 1) ^ 1u;
+                    if (!mbar_wait(bar_empty + 8 * s, par, abort_flag)) { ok = false; break; }
+                    const uint32_t full = bar_full + 8 * s;
+                    mbar_expect_tx(full, tx_bytes);
+                    const uint32_t sa = smem_base + s * stage_bytes;
+                    const uint32_t sb = sa + a_bytes;
+                    for (int i = 0; i < La; ++i)
+                        tma_load_2d(sa + i * (kTileM * kBlockK), &tmA, kb * kBlockK,
+                                    (int)(i * p.a_rows_per_limb + tc.z * p.M + tc.m0), full);
+                    for (int j = 0; j < p.Lb; ++j)
+                        tma_load_2d(sb + j * (p.NT * kBlockK), &tmB, kb * kBlockK,
+                                    (int)(j * p.b_rows_per_limb + zb * p.N + tc.n0), full);
+                    armed = it + 1;
+                }
+            }
+            if (*abort_flag) {
+                // leave no copy in flight: wait (bounded) for the stages armed last
+                for (int64_t j = (armed > p.stages ? armed - p.stages : 0); j < armed; ++j)
+                    for (uint32_t w = 0; w < kSpinLimit; ++w)
+                        if (mbar_try(bar_full + 8 * (int)(j % p.stages), (uint32_t)((j / p.stages) & 1))) break;
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer ---------------------------------------------------------------------
+        if (lane == 0) {
+            const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) |
+                                   ((uint32_t)((p.Lb * p.NT) >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+            int64_t it = 0, t = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; ok && tile < n_tiles_total; tile += gridDim.x, ++t) {
+                const int b = (int)(t & 1);
+                ok = mbar_wait(bar_tempty + 8 * b, (uint32_t)((t >> 1) & 1), abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t acc = tmem + (uint32_t)(b * buf_cols);
+                for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+                    const int s = (int)(it % p.stages);
+                    ok = mbar_wait(bar_full + 8 * s, (uint32_t)((it / p.stages) & 1), abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + s * stage_bytes;
+                    const uint64_t bdesc0 = smem_desc_sw128(sa + a_bytes);
+#pragma unroll
+                    for (int ks = 0; ks < kBlockK / 32; ++ks) {
+                        for (int i = 0; i < La; ++i) {
+                            const uint64_t adesc = smem_desc_sw128(sa + i * (kTileM * kBlockK)) + (uint64_t)(ks * 2);
+                            umma_i8(acc + (uint32_t)(i * p.NT), adesc, bdesc0 + (uint64_t)(ks * 2), idesc,
+                                    (kb | ks | i) ? 1u : 0u);
+                        }
+                    }
+                    umma_commit(bar_empty + 8 * s);
+                }
+                if (ok) umma_commit(bar_tfull + 8 * b);
+            }
+        }
+    } else {
+        // ---- epilogue warps: zero the buffers, then drain tile after tile -------------------------
+        const int ew = warp - 2;
+        const int q = warp & 3;                 // tensor-memory lane quarter of this warp
+        const int half = ew >> 2;               // which half of the tile's columns
+        const int CW = p.NT / 2, c0 = half * CW;
+        const int RS = CW * 8 + 16;             // staged row stride (padded against bank conflicts)
+        uint8_t* stage = smem_raw + ((smem_base - smem_u32(smem_raw)) + (uint32_t)p.stages * stage_bytes) +
+                         (size_t)ew * 32 * RS;
+        const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
+        // columns no first-step MMA initialises: [Lb * NT, D * NT) of each buffer, this warp's half
+        for (int b = 0; b < 2; ++b) {
+            for (int d = p.Lb; d < D; ++d)
+                for (int c = 0; c < CW; c += 8)
+                    tmem_st8_zero(lane_base + (uint32_t)(b * buf_cols + d * p.NT + c0 + c));
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
+        }
+        int64_t t = 0;
+        for (int64_t tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++t) {
+            const int b = (int)(t & 1);
+            if (!mbar_wait(bar_tfull + 8 * b, (uint32_t)((t >> 1) & 1), abort_flag)) break;
+            tc_fence_after();
+            const TileCoord tc = decode_tile(p, tile);
+            const uint32_t tq = lane_base + (uint32_t)(b * buf_cols);
+            if (p.fits64) epilogue_part<true>(p, tq, D, tc, q, lane, c0, CW, stage, RS);
+            else epilogue_part<false>(p, tq, D, tc, q, lane, c0, CW, stage, RS);
+            for (int d = p.Lb; d < D; ++d)
+                for (int c = 0; c < CW; c += 8) tmem_st8_zero(tq + (uint32_t)(d * p.NT + c0 + c));
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
         }
     }
 
@@ -841,6 +1149,43 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     if (mt > 0x7fffffffll || nt > 65535 || p.batches > 65535) return ZKDS_ERR_UNSUPPORTED;
     if (pre_b && (pre_b->nb != nbB || pre_b->rows != p.N || pre_b->K != p.K)) return ZKDS_ERR_ARG;
 
+    // shallow K, plain output: the persistent double-buffered kernel (see above)
+    bool persistent = false;
+    int pNT = 0, pstages = 0;
+    size_t psmem = 0;
+    if (!p.tile_group && !p.R && !p.group_shift && (Kp + kBlockK - 1) / kBlockK <= 16 &&
+        !getenv("ZKDS_NO_PERSISTENT")) {
+        for (int cand : {64, 48, 32, 16}) {
+            if (Lb * cand > 256 || 2 * D * cand > 512) continue;
+            size_t st_b = (size_t)La * kTileM * kBlockK + (size_t)Lb * cand * kBlockK;
+            size_t staging = (size_t)kEpiWarps * 32 * ((cand / 2) * 8 + 16);
+            if (smem_max < staging + 1024) continue;
+            int ns = (int)((smem_max - staging - 1024) / st_b);
+            if (ns < 2) continue;
+            pNT = cand;
+            pstages = ns > 8 ? 8 : ns;
+            psmem = st_b * pstages + staging + 1024;
+            persistent = true;
+            break;
+        }
+        // narrow outputs: the smallest valid width (16, 32, 48, 64) that still covers N
+        if (persistent) {
+            int want = pNT;
+            for (int cand : {48, 32, 16})
+                if (cand < pNT && p.N <= cand) want = cand;
+            if (want != pNT) {
+                pNT = want;
+                size_t st_b = (size_t)La * kTileM * kBlockK + (size_t)Lb * pNT * kBlockK;
+                size_t staging = (size_t)kEpiWarps * 32 * ((pNT / 2) * 8 + 16);
+                int ns = (int)((smem_max - staging - 1024) / st_b);
+                pstages = ns > 8 ? 8 : ns;
+                psmem = st_b * pstages + staging + 1024;
+            }
+        }
+    }
+    if (persistent) NT = pNT;
+    const int64_t nt_eff = (p.N + NT - 1) / NT;
+
     DeviceFlags* fl = flags_for_device();
     if (!fl) return ZKDS_ERR_WORKSPACE;
     int8_t* pa = (int8_t*)workspace((size_t)La * a_rows * Kp + 1024, 0);
@@ -873,8 +1218,9 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     lp.La = La; lp.Lb = Lb; lp.NT = NT; lp.stages = stages;
     lp.kblocks = (int)((Kp + kBlockK - 1) / kBlockK);
     uint32_t cols = 32;
-    while (cols < (uint32_t)(D * NT)) cols <<= 1;
+    while (cols < (uint32_t)((persistent ? 2 : 1) * D * NT)) cols <<= 1;
     lp.tmem_cols = cols;
+    if (persistent) lp.stages = pstages;
     lp.M = p.M; lp.N = p.N; lp.batches = p.batches;
     lp.a_rows_per_limb = a_rows; lp.b_rows_per_limb = b_rows;
     lp.b_batched = p.b_sz ? 1 : 0;
@@ -899,13 +1245,22 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     int64_t panel = (32ll << 20) / ((int64_t)La * kTileM * Kp);
     if (panel < 1) panel = 1;
     if (panel > mt) panel = mt;
-    lp.m_tiles = mt; lp.n_tiles = nt; lp.panel_m = panel;
-    if (mt * nt > 0x7fffffffll) return ZKDS_ERR_UNSUPPORTED;
-    dim3 grid = p.tile_group ? dim3((unsigned)mt, (unsigned)nt, 1)
-                             : dim3((unsigned)(mt * nt), 1, (unsigned)p.batches);
+    lp.m_tiles = mt; lp.n_tiles = nt_eff; lp.panel_m = panel;
+    if (mt * nt_eff > 0x7fffffffll) return ZKDS_ERR_UNSUPPORTED;
+    dim3 grid = p.tile_group ? dim3((unsigned)mt, (unsigned)nt_eff, 1)
+                             : dim3((unsigned)(mt * nt_eff), 1, (unsigned)p.batches);
     cudaEvent_t* ev = timing_events();
     if (ev) ZKDS_CUDA(cudaEventRecord(ev[0], st));
-    limb_gemm_kernel<<<grid, kThreads, smem, st>>>(tmA, tmB, lp);
+    if (persistent) {
+        ZKDS_CUDA(cudaFuncSetAttribute(limb_gemm_persistent_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024 - 3072)));
+        if (psmem < 120 * 1024) psmem = 120 * 1024;
+        int64_t total_tiles = p.batches * mt * nt_eff;
+        int ctas = sm_count();
+        if (total_tiles < ctas) ctas = (int)total_tiles;
+        limb_gemm_persistent_kernel<<<ctas, kPThreads, psmem, st>>>(tmA, tmB, lp);
+    } else
+        limb_gemm_kernel<<<grid, kThreads, smem, st>>>(tmA, tmB, lp);
     rc = check_launch();
     if (ev) ZKDS_CUDA(cudaEventRecord(ev[1], st));
     if (ev && g_accumulate && rc == ZKDS_OK) {
