@@ -5,6 +5,8 @@
 // bit for bit (inference/int64_gemm.cu:223-385, 605-768, 775-1017) with the slow
 // integer divisions replaced by a double-precision estimate plus an exact
 // integer correction.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -39,6 +41,24 @@ __device__ __forceinline__ int64_t act_one(int64_t r, const int64_t* lut)
     constexpr int64_t LOG2E = (FRAC == 23) ? 12102203ll : 48408813ll;
     if (r >= LIM) return r;  // the reference returns r here for sigmoid as well
     if (r <= -LIM) return 0;
+    if (FRAC == 23) {
+        // |r| < 2^29: everything up to the division runs in 32-bit registers
+        const int32_t r32 = (int32_t)r;
+        const int32_t y = (int32_t)(((int64_t)(-r32) * (int64_t)(int32_t)LOG2E) >> 23);   // |y| < 2^30
+        const int32_t k = y >> 23;
+        const uint32_t t = (uint32_t)lut[(y & 0x7FFFFF) >> 15];                       // < 2^24
+        if (k < 8) {
+            // denominator 2^23 + 2^y fits 32 bits: one double-precision estimate, exact correction
+            const uint32_t u = k < 0 ? (k > -32 ? (t >> (-k)) : 0u) : (t << k);
+            const uint32_t den = 8388608u + u;
+            uint32_t q = (uint32_t)__double2uint_rz(70368744177664.0 / (double)den);
+            const int64_t rem = (int64_t)70368744177664ll - (int64_t)((uint64_t)q * den);
+            if (rem < 0) --q;
+            else if (rem >= (int64_t)den) ++q;
+            if (!SILU) return (int64_t)q;
+            return ((int64_t)r32 * (int64_t)q) >> 23;
+        }
+    }
     // |r| < 2^(FRAC+6) and LOG2E < 2^(FRAC+1): the product fits in 64 bits
     int64_t y = (FRAC == 23) ? ((-r) * LOG2E) >> FRAC : -((r * LOG2E) >> FRAC);
     int64_t k = y >> FRAC;
@@ -282,6 +302,105 @@ softmax_kernel(const int64_t* X, int64_t* Wout, int64_t* C, const int64_t* __res
     }
 }
 
+// Q19 softmax with the row in registers and 32-bit arithmetic wherever the values allow it:
+// after the clip the difference d fits 26 bits, weights fit 20 bits, and the final division
+// (w << 19) / sumW uses one 64-bit reciprocal per row (floor((2^64 - 1) / sumW), an estimate that
+// is at most one below the quotient) plus an exact correction.  E = 16-byte pairs per thread.
+template <int E>
+__global__ void __launch_bounds__(kThreads)
+softmax_q19_reg_kernel(const int64_t* X, int64_t* Wout, int64_t* C, const int64_t* __restrict__ lut_g,
+                       int T)
+{
+    __shared__ uint32_t lut[256];
+    __shared__ int64_t red[32];
+    __shared__ uint64_t s_magic;
+    for (int i = threadIdx.x; i < 256; i += kThreads) lut[i] = (uint32_t)lut_g[i];
+    const int64_t off = (int64_t)blockIdx.x * T;
+    const longlong2* xv = reinterpret_cast<const longlong2*>(X + off);
+    longlong2* cv = reinterpret_cast<longlong2*>(C + off);
+    longlong2* wv = Wout ? reinterpret_cast<longlong2*>(Wout + off) : nullptr;
+    const int half = T >> 1;
+
+    longlong2 v[E];
+    int64_t mx = INT64_MIN;
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+        const int i = threadIdx.x + j * kThreads;
+        if (i < half) {
+            v[j] = xv[i];
+            mx = v[j].x > mx ? v[j].x : mx;
+            mx = v[j].y > mx ? v[j].y : mx;
+        }
+    }
+    mx = block_max_i64(mx, red);
+
+    uint32_t w[2 * E];
+    uint64_t sum = 0;
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+        const int i = threadIdx.x + j * kThreads;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            uint32_t wi = 0;
+            if (i < half) {
+                const uint64_t d = (uint64_t)mx - (uint64_t)(h ? v[j].y : v[j].x);
+                if (d <= (uint64_t)(64 << 19)) {
+                    const uint32_t y = (uint32_t)(((uint64_t)(uint32_t)d * 756388u) >> 19);
+                    const uint32_t k = y >> 19;
+                    const uint32_t t = lut[(y & 0x7FFFFu) >> 11];
+                    wi = k >= 32u ? 0u : (t >> k);
+                }
+            }
+            w[2 * j + h] = wi;
+            sum += wi;
+        }
+    }
+    const uint64_t sumW = (uint64_t)block_sum_i64((int64_t)sum, red);
+    if (threadIdx.x == 0) s_magic = sumW ? 0xFFFFFFFFFFFFFFFFull / sumW : 0;
+    __syncthreads();
+    const uint64_t magic = s_magic;
+    const uint32_t m_lo = (uint32_t)magic, m_hi = (uint32_t)(magic >> 32);
+    const bool small = sumW < (1ull << 32);
+    const uint32_t s32 = (uint32_t)sumW;
+
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+        const int i = threadIdx.x + j * kThreads;
+        if (i >= half) continue;
+        longlong2 o;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t wi = w[2 * j + h];
+            const uint64_t num = (uint64_t)wi << 19;
+            // floor(num * magic / 2^64) = (wi * m_hi + ((wi * m_lo) >> 32)) >> 13
+            uint64_t q = ((uint64_t)wi * m_hi + (((uint64_t)wi * m_lo) >> 32)) >> 13;
+            if (small) {
+                uint64_t rem = num - q * s32;          // q < 2^20, s32 < 2^32
+                if (rem >= sumW) { ++q; rem -= sumW; }
+                if (rem >= sumW) ++q;
+            } else if (sumW) {
+                q = num / sumW;
+            }
+            if (h) o.y = (int64_t)q; else o.x = (int64_t)q;
+        }
+        cv[i] = o;
+        if (wv) wv[i] = make_longlong2((int64_t)w[2 * j], (int64_t)w[2 * j + 1]);
+    }
+}
+
+static int launch_softmax_q19_reg(const int64_t* X, int64_t* Wout, int64_t* C, const int64_t* lut,
+                                  int64_t rows, int64_t T, cudaStream_t st)
+{
+    const int pairs = (int)((T / 2 + kThreads - 1) / kThreads);
+    const unsigned g = (unsigned)rows;
+    if (pairs <= 1) softmax_q19_reg_kernel<1><<<g, kThreads, 0, st>>>(X, Wout, C, lut, (int)T);
+    else if (pairs <= 2) softmax_q19_reg_kernel<2><<<g, kThreads, 0, st>>>(X, Wout, C, lut, (int)T);
+    else if (pairs <= 4) softmax_q19_reg_kernel<4><<<g, kThreads, 0, st>>>(X, Wout, C, lut, (int)T);
+    else if (pairs <= 8) softmax_q19_reg_kernel<8><<<g, kThreads, 0, st>>>(X, Wout, C, lut, (int)T);
+    else softmax_q19_reg_kernel<16><<<g, kThreads, 0, st>>>(X, Wout, C, lut, (int)T);
+    return check_launch();
+}
+
 template <int FRAC>
 static int launch_softmax_t(const int64_t* X, int64_t* Wout, int64_t* C, const int64_t* lut,
                             int64_t rows, int64_t T, cudaStream_t st)
@@ -311,7 +430,12 @@ int launch_softmax(const int64_t* X, int64_t* Wout, int64_t* C, const int64_t* l
 {
     if (rows == 0 || T == 0) return ZKDS_OK;
     if (rows > 0x7fffffffll) return ZKDS_ERR_RANGE;
-    if (frac == 19) return launch_softmax_t<19>(X, Wout, C, lut, rows, T, st);
+    if (frac == 19) {
+        const bool vec = (T % 2 == 0) && ((((uintptr_t)X | (uintptr_t)C | (uintptr_t)Wout) & 15) == 0);
+        if (vec && T >= 64 && T <= 2 * 16 * kThreads && !getenv("ZKDS_SOFTMAX_GENERIC"))
+            return launch_softmax_q19_reg(X, Wout, C, lut, rows, T, st);
+        return launch_softmax_t<19>(X, Wout, C, lut, rows, T, st);
+    }
     if (frac == 21) return launch_softmax_t<21>(X, Wout, C, lut, rows, T, st);
     return ZKDS_ERR_ARG;
 }
@@ -404,6 +528,14 @@ __device__ __forceinline__ u128w warp_sum_u128(u128w v)
 __device__ uint64_t isqrt_u128(unsigned __int128 v)
 {
     if (v == 0) return 0;
+    if ((v >> 62) == 0) {
+        // fits 62 bits: double-precision estimate (within 2 of the root), exact correction
+        const uint64_t x = (uint64_t)v;
+        uint64_t r = (uint64_t)__double2ull_rz(sqrt((double)x));
+        while (r * r > x) --r;
+        while ((r + 1) * (r + 1) <= x) ++r;
+        return r;
+    }
     unsigned __int128 r = 0, bit;
     uint64_t hi = (uint64_t)(v >> 64);
     int top = hi ? 127 - __clzll((long long)hi) : 63 - __clzll((long long)(uint64_t)v);
@@ -429,6 +561,18 @@ __device__ __noinline__ int64_t div_slow(i128w P, int64_t r)
 // floor(a*w / r) for r > 0 through a double estimate corrected with the exact remainder
 __device__ __forceinline__ int64_t norm_one(int64_t a, int64_t w, int64_t r, double inv)
 {
+    if (r > 0 && a == (int64_t)(int32_t)a && w == (int64_t)(int32_t)w) {
+        // both factors fit 32 bits: the product fits 64 bits and everything stays in one word
+        const int64_t p = (int64_t)(int32_t)a * (int64_t)(int32_t)w;
+        const double qe = (double)p * inv;          // |p| < 2^62, |q| < 2^62 / r
+        if (fabs(qe) < 562949953421312.0) {
+            int64_t q = __double2ll_rd(qe);
+            int64_t rem = p - q * r;
+            if (rem < 0) { --q; rem += r; }
+            else if (rem >= r) { ++q; rem -= r; }
+            if (rem >= 0 && rem < r) return q;
+        }
+    }
     i128w P = mul64x64(a, w);
     if (r > 0) {
         // convert the magnitude so that the estimate keeps a 2^-52 relative error
@@ -445,6 +589,22 @@ __device__ __forceinline__ int64_t norm_one(int64_t a, int64_t w, int64_t r, dou
         }
     }
     return div_slow(P, r);
+}
+
+// a^2 added to a two-word accumulator
+__device__ __forceinline__ void add_square(uint64_t& lo, uint64_t& hi, int64_t v)
+{
+    if (v == (int64_t)(int32_t)v) {
+        const uint64_t sq = (uint64_t)((int64_t)(int32_t)v * (int64_t)(int32_t)v);
+        const uint64_t nlo = lo + sq;
+        hi += (nlo < sq ? 1ull : 0ull);
+        lo = nlo;
+    } else {
+        const i128w p = mul64x64(v, v);
+        const uint64_t nlo = lo + p.lo;
+        hi += (uint64_t)p.hi + (nlo < p.lo ? 1ull : 0ull);
+        lo = nlo;
+    }
 }
 
 // One CTA per row.  FUSED: compute rms = isqrt((eps + sum a^2) / dim) here and write
@@ -471,23 +631,14 @@ rmsnorm_kernel(const int64_t* __restrict__ A, const WT* __restrict__ W, const in
             for (int64_t i = threadIdx.x; i < (N >> 1); i += kThreads) {
                 longlong2 v = av[i];
                 if (STAGE) rv[i] = v;
-                i128w p = mul64x64(v.x, v.x);
-                uint64_t nlo = acc.lo + p.lo;
-                acc.hi += (uint64_t)p.hi + (nlo < p.lo ? 1ull : 0ull);
-                acc.lo = nlo;
-                p = mul64x64(v.y, v.y);
-                nlo = acc.lo + p.lo;
-                acc.hi += (uint64_t)p.hi + (nlo < p.lo ? 1ull : 0ull);
-                acc.lo = nlo;
+                add_square(acc.lo, acc.hi, v.x);
+                add_square(acc.lo, acc.hi, v.y);
             }
         } else {
             for (int64_t i = threadIdx.x; i < N; i += kThreads) {
                 int64_t v = a[i];
                 if (STAGE) row[i] = v;
-                i128w p = mul64x64(v, v);
-                uint64_t nlo = acc.lo + p.lo;
-                acc.hi += (uint64_t)p.hi + (nlo < p.lo ? 1ull : 0ull);
-                acc.lo = nlo;
+                add_square(acc.lo, acc.hi, v);
             }
         }
         acc = warp_sum_u128(acc);
@@ -500,7 +651,11 @@ rmsnorm_kernel(const int64_t* __restrict__ A, const WT* __restrict__ W, const in
             if (lane == 0) {
                 unsigned __int128 tot = ((unsigned __int128)t.hi << 64) | t.lo;
                 tot += (unsigned __int128)(__int128)eps;
-                uint64_t r = dim ? isqrt_u128(tot / (unsigned __int128)(uint64_t)dim) : 0;
+                uint64_t r = 0;
+                if (dim) {
+                    if ((tot >> 64) == 0) r = isqrt_u128((unsigned __int128)((uint64_t)tot / (uint64_t)dim));
+                    else r = isqrt_u128(tot / (unsigned __int128)(uint64_t)dim);
+                }
                 s_rms = (int64_t)r;
                 if (rms_out) rms_out[blockIdx.x] = (int64_t)r;
             }
@@ -535,7 +690,7 @@ static int launch_rmsnorm_t(const int64_t* A, const WT* W, const int64_t* rms_in
                             cudaStream_t st)
 {
     size_t row_bytes = (size_t)N * 8;
-    bool stage = fused && row_bytes <= 200 * 1024;
+    bool stage = fused && row_bytes <= 200 * 1024 && !getenv("ZKDS_RMS_NOSTAGE");
     size_t smem = stage ? row_bytes : 0;
 #define ZKDS_RMS(F, S)                                                                       \
     do {                                                                                     \

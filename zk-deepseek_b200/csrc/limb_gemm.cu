@@ -461,7 +461,16 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int group = 0;
     if (p.tile_group) {
         group = p.tile_group[blockIdx.x];
-        if (group < 0) return;  // uniform for the CTA, before any barrier or allocation
+        if (group < 0) {
+            // unused row tile (uniform for the CTA, before any barrier or allocation): its output
+            // rows are defined as zero so that later passes over the whole buffer see clean data
+            const int64_t r0 = (int64_t)blockIdx.x * kTileM, c0 = (int64_t)blockIdx.y * p.NT;
+            for (int i = threadIdx.x; i < kTileM * p.NT; i += kThreads) {
+                const int64_t r = r0 + i / p.NT, c = c0 + i % p.NT;
+                if (r < p.M && c < p.N) p.C[r * p.c_sm + c] = 0;
+            }
+            return;
+        }
     }
     int La = p.La;
     if (p.a_absmax) {
@@ -628,18 +637,21 @@ struct TileCoord {
 
 __device__ __forceinline__ TileCoord decode_tile(const LimbParams& p, int64_t tile)
 {
-    const int64_t per_batch = p.m_tiles * p.n_tiles;
+    // every count here is below 2^31 (checked by the launcher): 32-bit divisions
+    const uint32_t mt = (uint32_t)p.m_tiles, nt = (uint32_t)p.n_tiles, pm = (uint32_t)p.panel_m;
+    const uint32_t per_batch = mt * nt;
+    const uint32_t zz = (uint32_t)tile / per_batch;
+    const uint32_t id = (uint32_t)tile - zz * per_batch;
+    const uint32_t per_panel = pm * nt;
+    const uint32_t panel = id / per_panel;
+    const uint32_t within = id - panel * per_panel;
+    const uint32_t left = mt - panel * pm;
+    const uint32_t rows_here = left < pm ? left : pm;
+    const uint32_t n_tile = within / rows_here;
     TileCoord c;
-    c.z = tile / per_batch;
-    const int64_t id = tile - c.z * per_batch;
-    const int64_t per_panel = p.panel_m * p.n_tiles;
-    const int64_t panel = id / per_panel;
-    const int64_t within = id - panel * per_panel;
-    const int64_t rows_here = (p.m_tiles - panel * p.panel_m < p.panel_m) ? p.m_tiles - panel * p.panel_m
-                                                                          : p.panel_m;
-    const int64_t n_tile = within / rows_here;
-    c.m0 = (panel * p.panel_m + (within - n_tile * rows_here)) * kTileM;
-    c.n0 = n_tile * p.NT;
+    c.z = zz;
+    c.m0 = (int64_t)(panel * pm + (within - n_tile * rows_here)) * kTileM;
+    c.n0 = (int64_t)n_tile * p.NT;
     return c;
 }
 
@@ -659,6 +671,7 @@ __device__ __forceinline__ void epilogue_part(const LimbParams& p, uint32_t tq, 
     while (lanes_per_row * 2 < CW) lanes_per_row <<= 1;
     const int rows_per_it = 32 / lanes_per_row;
     const int rl = lane / lanes_per_row, cl = (lane % lanes_per_row) * 2;
+    const int sh64 = p.shift >= 63 ? 63 : p.shift;
 
     if (p.addin) {
         // bring this warp's part of the addin tile in as whole rows; the 16-byte copies are
@@ -721,7 +734,7 @@ __device__ __forceinline__ void epilogue_part(const LimbParams& p, uint32_t tq, 
         int64_t cv[8];
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-            if (FITS64) cv[c] = p.shift >= 63 ? (s64[c] >> 63) : (s64[c] >> p.shift);
+            if (FITS64) cv[c] = s64[c] >> sh64;
             else cv[c] = sar128_lo(sum[c], p.shift);
         }
         int64_t* srow_ptr = reinterpret_cast<int64_t*>(stage + lane * RS + nc * 8);
@@ -736,16 +749,21 @@ __device__ __forceinline__ void epilogue_part(const LimbParams& p, uint32_t tq, 
     }
     __syncwarp();
     // write the staged rows out, whole rows at a time
-    for (int r0 = 0; r0 < 32; r0 += rows_per_it) {
-        const int r = r0 + rl;
-        const int64_t mr = tc.m0 + q * 32 + r;
-        if (cl < CW && mr < p.M) {
-            const longlong2 v = *reinterpret_cast<const longlong2*>(stage + r * RS + cl * 8);
-            int64_t* dst = p.C + tc.z * p.c_sz + mr * p.c_sm + nbase + cl;
-            if (vec_ok && nbase + cl + 2 <= p.N) *reinterpret_cast<longlong2*>(dst) = v;
-            else {
-                if (nbase + cl < p.N) dst[0] = v.x;
-                if (nbase + cl + 1 < p.N) dst[1] = v.y;
+    {
+        int64_t mr = tc.m0 + q * 32 + rl;
+        int64_t* dst = p.C + tc.z * p.c_sz + mr * p.c_sm + nbase + cl;
+        const uint8_t* src = stage + rl * RS + cl * 8;
+        const int64_t dstep = (int64_t)rows_per_it * p.c_sm;
+        const int sstep = rows_per_it * RS;
+        const bool full2 = vec_ok && nbase + cl + 2 <= p.N;
+        for (int r0 = 0; r0 < 32; r0 += rows_per_it, mr += rows_per_it, dst += dstep, src += sstep) {
+            if (cl < CW && mr < p.M) {
+                const longlong2 v = *reinterpret_cast<const longlong2*>(src);
+                if (full2) *reinterpret_cast<longlong2*>(dst) = v;
+                else {
+                    if (nbase + cl < p.N) dst[0] = v.x;
+                    if (nbase + cl + 1 < p.N) dst[1] = v.y;
+                }
             }
         }
     }
@@ -1256,6 +1274,7 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024 - 3072)));
         if (psmem < 120 * 1024) psmem = 120 * 1024;
         int64_t total_tiles = p.batches * mt * nt_eff;
+        if (total_tiles > 0x7fffffffll) return ZKDS_ERR_UNSUPPORTED;
         int ctas = sm_count();
         if (total_tiles < ctas) ctas = (int)total_tiles;
         limb_gemm_persistent_kernel<<<ctas, kPThreads, psmem, st>>>(tmA, tmB, lp);

@@ -306,7 +306,7 @@ class WeightPlanes:
 
     def __del__(self):
         h, self.handle = getattr(self, "handle", None), None
-        if h:
+        if h and lib is not None:        # `lib` is already gone at interpreter shutdown
             lib.zkds_planes_destroy(h)
 
 
