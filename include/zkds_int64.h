@@ -183,6 +183,19 @@ int zkds_einsum_bshc_btc_bsht_ex(const int64_t* A, const int64_t* KV, int64_t* o
                                  int64_t start_pos, int64_t mask_value, int a_limbs, int b_limbs,
                                  int flags, void* stream);
 
+/* Both score contractions of the absorbed MLA path and their element-wise tail in ONE tensor-core
+ * pass (replaces two einsum_bshc_btc_bsht calls plus the torch ops of model.py:884-905):
+ *   out[b,s,h,t] = floor((((r1/2 + q_abs[b,s,h,:].kv[b,t,:]) >> r1) +
+ *                          ((r2/2 + q_pe[b,s,h,:].pe[b,t,:]) >> r2)) * ep_mul / ep_div)  (+ mask_value
+ *                  where causal and t > start_pos + s).
+ * q_abs [B,S,H,C1], kv [B,T,C1], q_pe [B,S,H,C2], pe [B,T,C2], out [B,S,H,T].  Neither partial score
+ * tensor is materialised.  Returns ZKDS_ERR_UNSUPPORTED (silently) when C1 is not a multiple of 128
+ * or the limb counts do not fit the kernel; callers then fall back to the separate entry points. */
+int zkds_mla_scores(const int64_t* q_abs, const int64_t* kv, const int64_t* q_pe, const int64_t* pe,
+                    int64_t* out, int64_t B, int64_t S, int64_t H, int64_t T, int64_t C1, int64_t C2,
+                    int64_t rescale1, int64_t rescale2, int64_t ep_mul, int64_t ep_div, int causal,
+                    int64_t start_pos, int64_t mask_value, int a_limbs, int b_limbs, int flags, void* stream);
+
 /* Grouped linear layer for the routed experts (replaces the per-expert Python loop of
  * MoE.forward, model.py:1355-1379): A is a flat [n_tiles*128, K] int64 matrix whose i-th
  * 128-row tile holds tokens of expert tile_group[i] (device array; negative = unused tile),

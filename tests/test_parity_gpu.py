@@ -134,6 +134,36 @@ def test_einsums(kmod, orc, dev, algo, dims):
         kmod.ALGO = kmod.ALGO_AUTO
 
 
+@pytest.mark.parametrize("dims,bits", [((1, 40, 4, 40, 128, 64), (20, 20)), ((2, 5, 3, 37, 512, 64), (30, 23)),
+                                       ((1, 200, 16, 333, 512, 64), (34, 30)), ((1, 3, 2, 9, 256, 16), (16, 16))])
+def test_mla_scores_in_one_pass(kmod, orc, dev, dims, bits):
+    """(einsum(q_abs, kv) >> 23 + einsum(q_pe, pe) >> 21) * 94 // 695 + causal mask, fused
+    (model.py:884-905), against the two oracle einsums and numpy's floor division"""
+    Bn, S, H, T, C1, C2 = dims
+    rng = np.random.default_rng(T)
+    qa = rand_i64(rng, (Bn, S, H, C1), bits[0])
+    kv = rand_i64(rng, (Bn, T, C1), bits[1])
+    qp = rand_i64(rng, (Bn, S, H, C2), bits[0])
+    pe = rand_i64(rng, (Bn, T, C2), bits[1])
+    base = (orc.einsum_bshc_btc_bsht(qa, kv, 23) + orc.einsum_bshc_btc_bsht(qp, pe, 21)) * 94 // 695
+    for causal in (False, True):
+        want = base
+        if causal:
+            mask = np.where(np.arange(T)[None, :] > np.arange(S)[:, None], -(64 << 36), 0).astype(np.int64)
+            want = base + mask[None, :, None, :]
+        for (al, bl, dyn) in ((0, 0, False), (5, 5, True), (5, 4, False)):
+            got = kmod.mla_scores_fused(g(qa, dev), g(kv, dev), g(qp, dev), g(pe, dev), causal=causal,
+                                        a_limbs=al, b_limbs=bl, dynamic=dyn)
+            assert got is not None, "the fused kernel should take this shape"
+            same(got, want, "causal=%s limbs=%s" % (causal, (al, bl)))
+    kmod.device_status()
+
+
+def test_mla_scores_fused_declines_other_shapes(kmod, dev):
+    z = lambda *s: torch.zeros(s, dtype=torch.int64, device=dev)
+    assert kmod.mla_scores_fused(z(1, 2, 2, 64), z(1, 4, 64), z(1, 2, 2, 16), z(1, 4, 16)) is None
+
+
 # ---- RoPE -------------------------------------------------------------------------------------
 
 def rope_table(S, pairs, frac, base=10000.0):

@@ -344,6 +344,47 @@ int zkds_einsum_bshc_btc_bsht_ex(const int64_t* A, const int64_t* KV, int64_t* o
                   "zkds_einsum_bshc_btc_bsht_ex");
 }
 
+int zkds_mla_scores(const int64_t* q_abs, const int64_t* kv, const int64_t* q_pe, const int64_t* pe,
+                    int64_t* out, int64_t B, int64_t S, int64_t H, int64_t T, int64_t C1, int64_t C2,
+                    int64_t rescale1, int64_t rescale2, int64_t ep_mul, int64_t ep_div, int causal,
+                    int64_t start_pos, int64_t mask_value, int a_limbs, int b_limbs, int flags, void* stream)
+{
+    if (B < 0 || S < 0 || H < 0 || T < 0 || C1 <= 0 || C2 <= 0 || rescale1 < 0 || rescale1 > 127 ||
+        rescale2 < 0 || rescale2 > 127)
+        return finish(ZKDS_ERR_ARG, "zkds_mla_scores");
+    if (B == 0 || S == 0 || H == 0 || T == 0) return finish(ZKDS_OK, "zkds_mla_scores");
+    if (!q_abs || !kv || !q_pe || !pe || !out) return finish(ZKDS_ERR_ARG, "zkds_mla_scores");
+    cudaStream_t st = ST(stream);
+    if (a_limbs <= 0 || b_limbs <= 0) {
+        uint64_t* d = (uint64_t*)workspace(8 * sizeof(uint64_t), 5);
+        if (!d) return finish(ZKDS_ERR_WORKSPACE, "zkds_mla_scores");
+        int rc = set_cuda_error(cudaMemsetAsync(d, 0, 2 * sizeof(uint64_t), st));
+        if (rc == ZKDS_OK) rc = launch_absmax(q_abs, 64, B, S * H, C1, S * H * C1, C1, 1, 1, d, st);
+        if (rc == ZKDS_OK) rc = launch_absmax(q_pe, 64, B, S * H, C2, S * H * C2, C2, 1, 1, d, st);
+        if (rc == ZKDS_OK) rc = launch_absmax(kv, 64, B, T, C1, T * C1, C1, 1, 1, d + 1, st);
+        if (rc == ZKDS_OK) rc = launch_absmax(pe, 64, B, T, C2, T * C2, C2, 1, 1, d + 1, st);
+        uint64_t h[2] = {0, 0};
+        if (rc == ZKDS_OK) rc = set_cuda_error(cudaMemcpyAsync(h, d, sizeof(h), cudaMemcpyDeviceToHost, st));
+        if (rc == ZKDS_OK) rc = set_cuda_error(cudaStreamSynchronize(st));
+        if (rc != ZKDS_OK) return finish(rc, "zkds_mla_scores");
+        if (a_limbs <= 0) { a_limbs = limbs_needed(h[0]); flags &= ~ZKDS_LIMBS_DYNAMIC; }
+        if (b_limbs <= 0) b_limbs = limbs_needed(h[1]);
+    }
+    FusedScores f{};
+    f.A1 = q_abs; f.A2 = q_pe; f.B1 = kv; f.B2 = pe; f.out = out;
+    f.batches = B; f.M = S * H; f.N = T; f.K1 = C1; f.K2 = C2;
+    f.addend1 = rescale1 / 2; f.addend2 = rescale2 / 2;       // int64_gemm.cu:442
+    f.shift1 = (int)rescale1; f.shift2 = (int)rescale2;
+    f.ep_mul = ep_mul; f.ep_div = ep_div;
+    f.causal_H = causal ? H : 0; f.causal_start = start_pos; f.mask_value = mask_value;
+    f.dynamic_a = (flags & ZKDS_LIMBS_DYNAMIC) ? 1 : 0;
+    // ZKDS_ERR_UNSUPPORTED is an expected answer here (the caller then runs the two contractions
+    // separately), so it is returned without the stderr line
+    int rc = launch_scores_fused(f, a_limbs, b_limbs, st);
+    if (rc == ZKDS_ERR_UNSUPPORTED) { t_status = rc; return rc; }
+    return finish(rc, "zkds_mla_scores");
+}
+
 int zkds_grouped_prepared(const int64_t* A, const void* planes, const int* tile_group, int64_t n_tiles,
                           int64_t* C, int64_t a_rescale, int64_t addend, int64_t shift,
                           const int* group_shift, int64_t n_split, int a_limbs, int flags, void* stream)

@@ -79,6 +79,21 @@ struct Planes {
 };
 int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* pre_b, cudaStream_t st);
 
+// MLA attention scores in one tensor-core pass (limb_gemm.cu): A1/B1 contract over K1 with
+// (addend1, shift1), A2/B2 over K2 with (addend2, shift2); the two quotients are added and the
+// element-wise tail (ep_mul / ep_div, causal mask) applied.  All operands dense int64:
+// A1 [b][M][K1], A2 [b][M][K2], B1 [b][N][K1], B2 [b][N][K2], out [b][M][N].
+struct FusedScores {
+    const int64_t *A1, *A2, *B1, *B2;
+    int64_t* out;
+    int64_t batches, M, N, K1, K2;
+    int64_t addend1, addend2;
+    int shift1, shift2;
+    int64_t ep_mul, ep_div, causal_H, causal_start, mask_value;
+    int dynamic_a;
+};
+int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st);
+
 // planes[l][z][r][Kp] <- limb l of X[z*sz + r*sr + k*sk] / div
 int planes_split(const void* X, int bits, int64_t nb, int64_t rows, int64_t K, int64_t sz, int64_t sr,
                  int64_t sk, int64_t div, int L, int8_t* dst, cudaStream_t st);

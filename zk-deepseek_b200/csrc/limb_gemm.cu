@@ -67,7 +67,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 split_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, int64_t rows, int64_t K,
              int64_t Kp, int64_t sz, int64_t sr, int64_t sk, int64_t div, int64_t plane_stride,
-             unsigned* overflow, unsigned long long* absmax_out)
+             unsigned* overflow, unsigned long long* absmax_out, int64_t dst_pitch)
 {
     uint64_t seen = 0;
     bool ovf = false;
@@ -112,7 +112,7 @@ split_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, int64_
             }
             ovf |= (u != 0);
         }
-        int8_t* dst = planes + (z * rows + r) * Kp + k0;
+        int8_t* dst = planes + (z * rows + r) * dst_pitch + k0;
 #pragma unroll
         for (int l = 0; l < 9; ++l)
             if (l < L) *reinterpret_cast<uint32_t*>(dst + l * plane_stride) = w[l];
@@ -280,6 +280,11 @@ struct LimbParams {
     int* error_flag;          // host-mapped
     int fits64;               // |addend + sum| < 2^62 proven on the host: one-word epilogue
     int64_t m_tiles, n_tiles, panel_m;   // tile raster (see the kernel)
+    // dual accumulation (persistent kernel): K blocks from k_switch on feed a second set of
+    // diagonals with its own addend and shift; the epilogue adds the two shifted sums
+    int k_switch, shift2;
+    int64_t addend2;
+    int nbuf;                 // accumulator buffers in tensor memory: 2 (ping-pong) or 1
     // La is an upper bound when a_absmax is set: the kernel derives the limb count actually
     // needed from the range the split pass measured and skips the all-zero upper limbs
     const unsigned long long* a_absmax;
@@ -658,7 +663,8 @@ __device__ __forceinline__ TileCoord decode_tile(const LimbParams& p, int64_t ti
 // one epilogue warp: rows 32 q .. 32 q + 31 of the tile, columns [c0, c0 + CW) of it
 template <bool FITS64>
 __device__ __forceinline__ void epilogue_part(const LimbParams& p, uint32_t tq, int D, const TileCoord& tc,
-                                              int q, int lane, int c0, int CW, uint8_t* stage, int RS)
+                                              int q, int lane, int c0, int CW, uint8_t* stage, int RS,
+                                              int set_cols)
 {
     const int64_t m = tc.m0 + q * 32 + lane;
     const bool tail = p.addin || p.ep_div || p.causal_H;
@@ -737,6 +743,46 @@ __device__ __forceinline__ void epilogue_part(const LimbParams& p, uint32_t tq, 
             if (FITS64) cv[c] = s64[c] >> sh64;
             else cv[c] = sar128_lo(sum[c], p.shift);
         }
+        if (p.k_switch) {
+            // second set of diagonals: its own addend and shift, then the two quotients add up
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                if (FITS64) s64[c] = p.addend2;
+                else sum[c] = make_i128(p.addend2);
+            }
+            for (int d0 = 0, g = 0; d0 < D; d0 += 4, ++g) {
+                int32_t a[4][8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (d0 + j < D) tmem_ld8(tq + (uint32_t)(set_cols + (d0 + j) * p.NT + c0 + nc), a[j]);
+                    else {
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) a[j][c] = 0;
+                    }
+                }
+                tmem_ld_wait();
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const int64_t v = four_diagonals(a[0][c], a[1][c], a[2][c], a[3][c]);
+                    if (FITS64) {
+                        s64[c] += g ? (int64_t)((uint64_t)v << 32) : v;
+                    } else {
+                        i128w t;
+                        if (g == 0) { t.lo = (uint64_t)v; t.hi = v >> 63; }
+                        else if (g == 1) { t.lo = (uint64_t)v << 32; t.hi = v >> 32; }
+                        else if (g == 2) { t.lo = 0; t.hi = v; }
+                        else { t.lo = 0; t.hi = (int64_t)((uint64_t)v << 32); }
+                        sum[c] = add128(sum[c], t);
+                    }
+                }
+            }
+            const int sh2 = p.shift2 >= 63 ? 63 : p.shift2;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const int64_t v2 = FITS64 ? (s64[c] >> sh2) : sar128_lo(sum[c], p.shift2);
+                cv[c] = (int64_t)((uint64_t)cv[c] + (uint64_t)v2);
+            }
+        }
         int64_t* srow_ptr = reinterpret_cast<int64_t*>(stage + lane * RS + nc * 8);
         if (tail) {
 #pragma unroll
@@ -796,7 +842,9 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
     const uint32_t bar_empty = smem_u32(&bars[8]);
     const uint32_t bar_tfull = smem_u32(&bars[16]);    // [2]: accumulators of a tile complete
     const uint32_t bar_tempty = smem_u32(&bars[18]);   // [2]: buffer drained and re-zeroed
-    const int buf_cols = (p.La + p.Lb - 1) * p.NT;     // spacing of the two accumulator buffers
+    const int set_cols = (p.La + p.Lb - 1) * p.NT;     // one set of diagonals
+    const int nsets = p.k_switch ? 2 : 1;
+    const int buf_cols = nsets * set_cols;             // spacing of the two accumulator buffers
     const int64_t n_tiles_total = p.batches * p.m_tiles * p.n_tiles;
 
     if (threadIdx.x == 0) {
@@ -860,8 +908,8 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             int64_t it = 0, t = 0;
             bool ok = true;
             for (int64_t tile = blockIdx.x; ok && tile < n_tiles_total; tile += gridDim.x, ++t) {
-                const int b = (int)(t & 1);
-                ok = mbar_wait(bar_tempty + 8 * b, (uint32_t)((t >> 1) & 1), abort_flag);
+                const int b = (int)(t % p.nbuf);
+                ok = mbar_wait(bar_tempty + 8 * b, (uint32_t)((t / p.nbuf) & 1), abort_flag);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t acc = tmem + (uint32_t)(b * buf_cols);
@@ -872,12 +920,15 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                     tc_fence_after();
                     const uint32_t sa = smem_base + s * stage_bytes;
                     const uint64_t bdesc0 = smem_desc_sw128(sa + a_bytes);
+                    const bool second = p.k_switch && kb >= p.k_switch;
+                    const uint32_t acc_set = acc + (second ? (uint32_t)set_cols : 0u);
+                    const int kb_first = second ? p.k_switch : 0;     // first K block of this set
 #pragma unroll
                     for (int ks = 0; ks < kBlockK / 32; ++ks) {
                         for (int i = 0; i < La; ++i) {
                             const uint64_t adesc = smem_desc_sw128(sa + i * (kTileM * kBlockK)) + (uint64_t)(ks * 2);
-                            umma_i8(acc + (uint32_t)(i * p.NT), adesc, bdesc0 + (uint64_t)(ks * 2), idesc,
-                                    (kb | ks | i) ? 1u : 0u);
+                            umma_i8(acc_set + (uint32_t)(i * p.NT), adesc, bdesc0 + (uint64_t)(ks * 2), idesc,
+                                    ((kb - kb_first) | ks | i) ? 1u : 0u);
                         }
                     }
                     umma_commit(bar_empty + 8 * s);
@@ -896,10 +947,11 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                          (size_t)ew * 32 * RS;
         const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
         // columns no first-step MMA initialises: [Lb * NT, D * NT) of each buffer, this warp's half
-        for (int b = 0; b < 2; ++b) {
-            for (int d = p.Lb; d < D; ++d)
-                for (int c = 0; c < CW; c += 8)
-                    tmem_st8_zero(lane_base + (uint32_t)(b * buf_cols + d * p.NT + c0 + c));
+        for (int b = 0; b < p.nbuf; ++b) {
+            for (int st = 0; st < nsets; ++st)
+                for (int d = p.Lb; d < D; ++d)
+                    for (int c = 0; c < CW; c += 8)
+                        tmem_st8_zero(lane_base + (uint32_t)(b * buf_cols + st * set_cols + d * p.NT + c0 + c));
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
@@ -907,15 +959,17 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
         }
         int64_t t = 0;
         for (int64_t tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++t) {
-            const int b = (int)(t & 1);
-            if (!mbar_wait(bar_tfull + 8 * b, (uint32_t)((t >> 1) & 1), abort_flag)) break;
+            const int b = (int)(t % p.nbuf);
+            if (!mbar_wait(bar_tfull + 8 * b, (uint32_t)((t / p.nbuf) & 1), abort_flag)) break;
             tc_fence_after();
             const TileCoord tc = decode_tile(p, tile);
             const uint32_t tq = lane_base + (uint32_t)(b * buf_cols);
-            if (p.fits64) epilogue_part<true>(p, tq, D, tc, q, lane, c0, CW, stage, RS);
-            else epilogue_part<false>(p, tq, D, tc, q, lane, c0, CW, stage, RS);
-            for (int d = p.Lb; d < D; ++d)
-                for (int c = 0; c < CW; c += 8) tmem_st8_zero(tq + (uint32_t)(d * p.NT + c0 + c));
+            if (p.fits64) epilogue_part<true>(p, tq, D, tc, q, lane, c0, CW, stage, RS, set_cols);
+            else epilogue_part<false>(p, tq, D, tc, q, lane, c0, CW, stage, RS, set_cols);
+            for (int st = 0; st < nsets; ++st)
+                for (int d = p.Lb; d < D; ++d)
+                    for (int c = 0; c < CW; c += 8)
+                        tmem_st8_zero(tq + (uint32_t)(st * set_cols + d * p.NT + c0 + c));
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
@@ -997,16 +1051,17 @@ DeviceFlags* flags_for_device()
 template <typename T>
 int launch_split_t(const T* X, int8_t* planes, int L, int64_t nb, int64_t rows, int64_t K, int64_t Kp,
                    int64_t sz, int64_t sr, int64_t sk, int64_t div, unsigned* overflow, cudaStream_t st,
-                   unsigned long long* absmax_out = nullptr)
+                   unsigned long long* absmax_out = nullptr, int64_t dst_pitch = 0)
 {
+    if (dst_pitch == 0) dst_pitch = Kp;
     int64_t total = rows * (Kp >> 2);
     int64_t bx = (total + 255) / 256;
     int64_t cap = (int64_t)sm_count() * 32;
     if (bx > cap) bx = cap;
     if (nb > 65535) return ZKDS_ERR_RANGE;
     dim3 grid((unsigned)bx, (unsigned)nb);
-    split_kernel<T><<<grid, 256, 0, st>>>(X, planes, L, rows, K, Kp, sz, sr, sk, div, nb * rows * Kp, overflow,
-                                          absmax_out);
+    split_kernel<T><<<grid, 256, 0, st>>>(X, planes, L, rows, K, Kp, sz, sr, sk, div, nb * rows * dst_pitch,
+                                          overflow, absmax_out, dst_pitch);
     return check_launch();
 }
 
@@ -1239,6 +1294,7 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     while (cols < (uint32_t)((persistent ? 2 : 1) * D * NT)) cols <<= 1;
     lp.tmem_cols = cols;
     if (persistent) lp.stages = pstages;
+    lp.nbuf = 2;
     lp.M = p.M; lp.N = p.N; lp.batches = p.batches;
     lp.a_rows_per_limb = a_rows; lp.b_rows_per_limb = b_rows;
     lp.b_batched = p.b_sz ? 1 : 0;
@@ -1305,6 +1361,144 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
         }
         g_tot_ms += ms;
         g_tot_ops += 2.0 * (double)la_used * Lb * (double)p.batches * (double)p.M * (double)p.N * (double)p.K;
+        g_tot_launches += 1;
+    }
+    return rc;
+}
+
+// ------------------------------------------------------------------------------------
+// MLA attention scores in one pass
+// ------------------------------------------------------------------------------------
+// scores[b,m,n] = tail( ((add1 + A1[b,m,:] . B1[b,n,:]) >> s1) + ((add2 + A2[b,m,:] . B2[b,n,:]) >> s2) )
+// The limb planes of A1|A2 and of B1|B2 are laid side by side along K, so the whole thing is one
+// contraction over K1 + K2 whose K blocks from K1 on accumulate into a second set of diagonals;
+// neither partial score tensor is ever written to memory.
+int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st)
+{
+    if (La < 1 || Lb < 1 || La > 9 || Lb > 9) return ZKDS_ERR_UNSUPPORTED;
+    if (f.K1 <= 0 || f.K2 <= 0 || (f.K1 % kBlockK) != 0) return ZKDS_ERR_UNSUPPORTED;
+    if (getenv("ZKDS_NO_PERSISTENT")) return ZKDS_ERR_UNSUPPORTED;
+    const int D = La + Lb - 1;
+    const int pairs = La < Lb ? La : Lb;
+    const int64_t Kmax = f.K1 > f.K2 ? f.K1 : f.K2;
+    if ((int64_t)pairs * Kmax >= 131072) return ZKDS_ERR_UNSUPPORTED;
+    const size_t smem_max = 227 * 1024 - 4096;
+    // Two sets of diagonals per buffer.  A wide tile matters more than the ping-pong: every
+    // output tile re-reads its A limb tiles, so narrow tiles are bound by L2 traffic.  Take two
+    // buffers only if the tile can still be 32 columns wide, else one buffer with the widest tile.
+    int NT = 0, stages = 0, nbuf = 0;
+    size_t smem = 0;
+    for (int bufs : {2, 1}) {
+        for (int cand : {64, 48, 32, 16}) {
+            if (bufs == 2 && cand < 32) continue;
+            if (Lb * cand > 256 || 2 * bufs * D * cand > 512) continue;
+            size_t st_b = (size_t)La * kTileM * kBlockK + (size_t)Lb * cand * kBlockK;
+            size_t staging = (size_t)kEpiWarps * 32 * ((cand / 2) * 8 + 16);
+            int ns = (int)((smem_max - staging - 1024) / st_b);
+            if (ns < 2) continue;
+            NT = cand;
+            nbuf = bufs;
+            stages = ns > 8 ? 8 : ns;
+            smem = st_b * stages + staging + 1024;
+            break;
+        }
+        if (NT) break;
+    }
+    if (!NT) return ZKDS_ERR_UNSUPPORTED;
+    const int64_t Kp2 = (f.K2 + 15) & ~(int64_t)15;
+    const int64_t pitch = f.K1 + Kp2;
+    const int64_t a_rows = f.batches * f.M, b_rows = f.batches * f.N;
+    if (a_rows * La > 0x7fffff00ll || b_rows * Lb > 0x7fffff00ll) return ZKDS_ERR_UNSUPPORTED;
+    const int64_t mt = (f.M + kTileM - 1) / kTileM, nt = (f.N + NT - 1) / NT;
+    if (f.batches * mt * nt > 0x7fffffffll) return ZKDS_ERR_UNSUPPORTED;
+
+    DeviceFlags* fl = flags_for_device();
+    if (!fl) return ZKDS_ERR_WORKSPACE;
+    int8_t* pa = (int8_t*)workspace((size_t)La * a_rows * pitch + 1024, 0);
+    int8_t* pb = (int8_t*)workspace((size_t)Lb * b_rows * pitch + 1024, 1);
+    if (!pa || !pb) return ZKDS_ERR_WORKSPACE;
+    unsigned long long* d_absmax = nullptr;
+    if (f.dynamic_a) {
+        unsigned long long* words = (unsigned long long*)workspace(8 * sizeof(uint64_t), 5);
+        if (!words) return ZKDS_ERR_WORKSPACE;
+        d_absmax = words + 2;
+        ZKDS_CUDA(cudaMemsetAsync(d_absmax, 0, sizeof(uint64_t), st));
+    }
+    int rc = launch_split_t<int64_t>(f.A1, pa, La, f.batches, f.M, f.K1, f.K1, f.M * f.K1, f.K1, 1, 1,
+                                     fl->overflow_dev, st, d_absmax, pitch);
+    if (rc == ZKDS_OK)
+        rc = launch_split_t<int64_t>(f.A2, pa + f.K1, La, f.batches, f.M, f.K2, Kp2, f.M * f.K2, f.K2, 1, 1,
+                                     fl->overflow_dev, st, d_absmax, pitch);
+    if (rc == ZKDS_OK)
+        rc = launch_split_t<int64_t>(f.B1, pb, Lb, f.batches, f.N, f.K1, f.K1, f.N * f.K1, f.K1, 1, 1,
+                                     fl->overflow_dev, st, nullptr, pitch);
+    if (rc == ZKDS_OK)
+        rc = launch_split_t<int64_t>(f.B2, pb + f.K1, Lb, f.batches, f.N, f.K2, Kp2, f.N * f.K2, f.K2, 1, 1,
+                                     fl->overflow_dev, st, nullptr, pitch);
+    if (rc != ZKDS_OK) return rc;
+
+    CUtensorMap tmA, tmB;
+    if (!make_plane_map(&tmA, pa, (int64_t)La * a_rows, pitch, kTileM)) return ZKDS_ERR_UNSUPPORTED;
+    if (!make_plane_map(&tmB, pb, (int64_t)Lb * b_rows, pitch, NT)) return ZKDS_ERR_UNSUPPORTED;
+
+    LimbParams lp{};
+    lp.La = La; lp.Lb = Lb; lp.NT = NT; lp.stages = stages;
+    lp.k_switch = (int)(f.K1 / kBlockK);
+    lp.kblocks = lp.k_switch + (int)((Kp2 + kBlockK - 1) / kBlockK);
+    uint32_t cols = 32;
+    while (cols < (uint32_t)(2 * nbuf * D * NT)) cols <<= 1;
+    lp.tmem_cols = cols;
+    lp.nbuf = nbuf;
+    lp.M = f.M; lp.N = f.N; lp.batches = f.batches;
+    lp.a_rows_per_limb = a_rows; lp.b_rows_per_limb = b_rows;
+    lp.b_batched = 1;
+    lp.C = f.out; lp.R = nullptr; lp.c_sz = f.M * f.N; lp.c_sm = f.N;
+    lp.addend = f.addend1; lp.shift = f.shift1; lp.addend2 = f.addend2; lp.shift2 = f.shift2;
+    lp.r_legacy = 0;
+    lp.error_flag = fl->dev;
+    lp.fits64 = sum_fits64(La, Lb, Kmax, f.addend1) && sum_fits64(La, Lb, Kmax, f.addend2);
+    lp.a_absmax = d_absmax;
+    lp.overflow_flag = fl->overflow_dev;
+    lp.ep_mul = f.ep_mul; lp.ep_div = f.ep_div;
+    lp.causal_H = f.causal_H; lp.causal_start = f.causal_start; lp.mask_value = f.mask_value;
+    int64_t panel = (32ll << 20) / ((int64_t)La * kTileM * pitch);
+    if (panel < 1) panel = 1;
+    if (panel > mt) panel = mt;
+    lp.m_tiles = mt; lp.n_tiles = nt; lp.panel_m = panel;
+
+    ZKDS_CUDA(cudaFuncSetAttribute(limb_gemm_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)(227 * 1024 - 3072)));
+    if (smem < 120 * 1024) smem = 120 * 1024;
+    const int64_t total_tiles = f.batches * mt * nt;
+    int ctas = sm_count();
+    if (total_tiles < ctas) ctas = (int)total_tiles;
+    cudaEvent_t* ev = timing_events();
+    if (ev) ZKDS_CUDA(cudaEventRecord(ev[0], st));
+    limb_gemm_persistent_kernel<<<ctas, kPThreads, smem, st>>>(tmA, tmB, lp);
+    rc = check_launch();
+    if (ev) ZKDS_CUDA(cudaEventRecord(ev[1], st));
+    if (ev && g_accumulate && rc == ZKDS_OK) {
+        float ms = 0.f;
+        ZKDS_CUDA(cudaEventSynchronize(ev[1]));
+        ZKDS_CUDA(cudaEventElapsedTime(&ms, ev[0], ev[1]));
+        int la_used = La;
+        if (d_absmax) {
+            unsigned long long h = 0;
+            ZKDS_CUDA(cudaMemcpy(&h, d_absmax, sizeof(h), cudaMemcpyDeviceToHost));
+            int need = limbs_needed(h);
+            if (need < la_used) la_used = need;
+        }
+        if (getenv("ZKDS_TRACE"))
+            fprintf(stderr, "scores_fused batches=%lld M=%lld N=%lld K=%lld+%lld La=%d(%d) Lb=%d NT=%d stages=%d fits64=%d: %.3f ms\n",
+                    (long long)f.batches, (long long)f.M, (long long)f.N, (long long)f.K1, (long long)f.K2,
+                    la_used, La, Lb, NT, stages, lp.fits64, ms);
+        if (g_tot_launches < 256) {
+            LaunchRecord& r = g_records[g_tot_launches];
+            r.v[0] = (double)f.batches; r.v[1] = (double)f.M; r.v[2] = (double)f.N; r.v[3] = (double)(f.K1 + f.K2);
+            r.v[4] = la_used; r.v[5] = Lb; r.v[6] = ms; r.v[7] = 0.0;
+        }
+        g_tot_ms += ms;
+        g_tot_ops += 2.0 * (double)la_used * Lb * (double)f.batches * (double)f.M * (double)f.N * (double)(f.K1 + f.K2);
         g_tot_launches += 1;
     }
     return rc;

@@ -94,6 +94,8 @@ _sig("zkds_planes_limbs", [_vp])
 _sig("zkds_planes_destroy", [_vp])
 _sig("zkds_einsum_bshc_btc_bsht_ex", [_vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _vp, _ll, _ll, _i, _ll,
                                       _ll, _i, _i, _i, _vp])
+_sig("zkds_mla_scores", [_vp, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _i, _ll, _ll,
+                         _i, _i, _i, _vp])
 _sig("zkds_grouped_prepared", [_vp, _vp, _vp, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _i, _i, _vp])
 _sig("zkds_glu_q23", [_vp, _vp, _ll, _vp, _vp, _vp, _ll, _ll, _vp])
 _sig("zkds_gather_rows", [_vp, _vp, _vp, _ll, _ll, _vp])
@@ -395,6 +397,28 @@ def attention_scores_fused(A, KV, rescale, addin=None, mul=0, div=0, causal=Fals
                                                 ALGO | _a_flags(a_limbs, dynamic), _stream()),
                "attention_scores_fused")
     return C
+
+
+def mla_scores_fused(q_abs, kv, q_pe, pe, rescale1=23, rescale2=21, mul=94, div=695, causal=False,
+                     start_pos=0, mask_value=-(64 << 36), a_limbs=0, b_limbs=0, dynamic=False):
+    """scores = ((score1 + score2) * mul // div) (+ causal mask) with score1 = einsum(q_abs, kv) at
+    rescale1 and score2 = einsum(q_pe, pe) at rescale2, in one tensor-core pass (model.py:884-905).
+    Returns None when the fused kernel does not take the shape (caller falls back)."""
+    for t, n in ((q_abs, "q_abs"), (kv, "kv"), (q_pe, "q_pe"), (pe, "pe")):
+        _dev_i64(t, n)
+    Bn, S, H, C1 = q_abs.shape
+    T, C2 = kv.shape[1], q_pe.shape[3]
+    assert kv.shape == (Bn, T, C1) and q_pe.shape == (Bn, S, H, C2) and pe.shape == (Bn, T, C2)
+    out = torch.empty((Bn, S, H, T), dtype=torch.int64, device=q_abs.device)
+    with torch.cuda.device(q_abs.device):
+        rc = lib.zkds_mla_scores(q_abs.data_ptr(), kv.data_ptr(), q_pe.data_ptr(), pe.data_ptr(), out.data_ptr(),
+                                 Bn, S, H, T, C1, C2, int(rescale1), int(rescale2), int(mul), int(div),
+                                 1 if causal else 0, int(start_pos), int(mask_value), a_limbs, b_limbs,
+                                 _a_flags(a_limbs, dynamic), _stream())
+    if rc == 6:          # ZKDS_ERR_UNSUPPORTED
+        return None
+    _check(rc, "mla_scores_fused")
+    return out
 
 
 def glu_q23(r1, r2, ld=None, want_silu=False):

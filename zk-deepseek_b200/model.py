@@ -390,12 +390,17 @@ class MLA(nn.Module):
         # scores = (score1 + score2) * 94 // 695 (+ mask): the tail runs in the second epilogue
         al, bl = self.score_limbs
         dyn = al > 0
-        score1 = K.attention_scores_fused(q_abs, kv_all, 23, a_limbs=al, b_limbs=bl, dynamic=dyn)
         causal = mask is not None and start_pos == 0 and _is_causal_mask(mask, seqlen)
-        scores = K.attention_scores_fused(q_pe.contiguous(), pe_all, 21, addin=score1,
-                                          mul=self.softmax_scale1, div=self.softmax_scale2, causal=causal,
-                                          start_pos=0, a_limbs=al, b_limbs=bl, dynamic=dyn)
-        del score1
+        scores = None
+        if K.ALGO != K.ALGO_EXACT:
+            scores = K.mla_scores_fused(q_abs, kv_all, q_pe.contiguous(), pe_all, 23, 21, self.softmax_scale1,
+                                        self.softmax_scale2, causal=causal, a_limbs=al, b_limbs=bl, dynamic=dyn)
+        if scores is None:      # shape outside the fused kernel: two contractions, tail in the second
+            score1 = K.attention_scores_fused(q_abs, kv_all, 23, a_limbs=al, b_limbs=bl, dynamic=dyn)
+            scores = K.attention_scores_fused(q_pe.contiguous(), pe_all, 21, addin=score1,
+                                              mul=self.softmax_scale1, div=self.softmax_scale2, causal=causal,
+                                              start_pos=0, a_limbs=al, b_limbs=bl, dynamic=dyn)
+            del score1
         if mask is not None and not causal:
             scores += mask.unsqueeze(1)
         if snark:
