@@ -333,6 +333,45 @@ __device__ __forceinline__ int64_t four_diagonals(int32_t a0, int32_t a1, int32_
     return mad_wide(a3, 1 << 24, mad_wide(a2, 1 << 16, mad_wide(a1, 1 << 8, (int64_t)a0)));
 }
 
+// One 8-column chunk of a tile whose sum fits 64 bits, diagonal count known at compile time:
+// every diagonal is fetched before the single wait and no absent diagonal costs anything.
+template <int DD>
+__device__ __forceinline__ void gather64_n(uint32_t taddr, int NT, int64_t addend, int64_t (&s)[8])
+{
+    int32_t a[DD][8];
+#pragma unroll
+    for (int d = 0; d < DD; ++d) tmem_ld8(taddr + (uint32_t)(d * NT), a[d]);
+    tmem_ld_wait();
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        int64_t lo = (int64_t)a[0][c];
+        if (DD > 1) lo = mad_wide(a[DD > 1 ? 1 : 0][c], 1 << 8, lo);
+        if (DD > 2) lo = mad_wide(a[DD > 2 ? 2 : 0][c], 1 << 16, lo);
+        if (DD > 3) lo = mad_wide(a[DD > 3 ? 3 : 0][c], 1 << 24, lo);
+        int64_t r = addend + lo;
+        if (DD > 4) {
+            int64_t hi = (int64_t)a[DD > 4 ? 4 : 0][c];
+            if (DD > 5) hi = mad_wide(a[DD > 5 ? 5 : 0][c], 1 << 8, hi);
+            r += (int64_t)((uint64_t)hi << 32);
+        }
+        s[c] = r;
+    }
+}
+
+// false when the diagonal count has no compiled specialisation (caller uses the generic loop)
+__device__ __forceinline__ bool gather64(int D, uint32_t taddr, int NT, int64_t addend, int64_t (&s)[8])
+{
+    switch (D) {
+    case 1: gather64_n<1>(taddr, NT, addend, s); return true;
+    case 2: gather64_n<2>(taddr, NT, addend, s); return true;
+    case 3: gather64_n<3>(taddr, NT, addend, s); return true;
+    case 4: gather64_n<4>(taddr, NT, addend, s); return true;
+    case 5: gather64_n<5>(taddr, NT, addend, s); return true;
+    case 6: gather64_n<6>(taddr, NT, addend, s); return true;
+    default: return false;
+    }
+}
+
 struct EpilogueCtx {
     uint32_t tq;
     int D, NT, group;
@@ -350,9 +389,16 @@ __device__ __forceinline__ int64_t score_tail(const LimbParams& p, int64_t v, co
     if (arow) v = (int64_t)((uint64_t)v + (uint64_t)*arow);
     if (p.ep_div) {
         if (p.ep_mul == 94 && p.ep_div == 695) {  // MLA's softmax scale: constant divisor
-            int64_t t = (int64_t)((uint64_t)v * 94ull);
-            int64_t qd = t / 695;
-            v = (t - qd * 695 < 0) ? qd - 1 : qd;
+            if ((uint64_t)(v + (1 << 24)) < (uint64_t)(1 << 25)) {
+                // |v| < 2^24 (any realistic Q19 score): 32-bit multiply and constant division
+                const int32_t t = (int32_t)v * 94;
+                const int32_t qd = t / 695;
+                v = (int64_t)((t - qd * 695 < 0) ? qd - 1 : qd);
+            } else {
+                int64_t t = (int64_t)((uint64_t)v * 94ull);
+                int64_t qd = t / 695;
+                v = (t - qd * 695 < 0) ? qd - 1 : qd;
+            }
         } else
             v = floor_div_i64((int64_t)((uint64_t)v * (uint64_t)p.ep_mul), p.ep_div);
     }
@@ -711,7 +757,8 @@ __device__ __forceinline__ void epilogue_part(const LimbParams& p, uint32_t tq, 
             if (FITS64) s64[c] = p.addend;
             else sum[c] = make_i128(p.addend);
         }
-        for (int d0 = 0, g = 0; d0 < D; d0 += 4, ++g) {
+        const bool done64 = FITS64 && gather64(D, tq + (uint32_t)(c0 + nc), p.NT, p.addend, s64);
+        for (int d0 = 0, g = 0; !done64 && d0 < D; d0 += 4, ++g) {
             int32_t a[4][8];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -750,7 +797,8 @@ __device__ __forceinline__ void epilogue_part(const LimbParams& p, uint32_t tq, 
                 if (FITS64) s64[c] = p.addend2;
                 else sum[c] = make_i128(p.addend2);
             }
-            for (int d0 = 0, g = 0; d0 < D; d0 += 4, ++g) {
+            const bool done2 = FITS64 && gather64(D, tq + (uint32_t)(set_cols + c0 + nc), p.NT, p.addend2, s64);
+            for (int d0 = 0, g = 0; !done2 && d0 < D; d0 += 4, ++g) {
                 int32_t a[4][8];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
