@@ -753,6 +753,20 @@ class MlaRefScaleWorkload(MlaWorkload):
         return MlaWorkload.cpu_sample(orc, np, seconds, rank)
 
 
+class MlaCausalSkipWorkload(MlaWorkload):
+    """The MLA layer with the masked half of the causal score and probability tensors neither
+    computed, written nor read (same layer output; reported beside the full computation)."""
+    name = "mla_layer_prefill_4096_masked_tiles_skipped"
+
+    def __init__(self, torch, k, dev, rank):
+        super().__init__(torch, k, dev, rank)
+        self.attn.causal_skip = True
+
+    @staticmethod
+    def cpu_sample(orc, np, seconds, rank=0):
+        return MlaWorkload.cpu_sample(orc, np, seconds, rank)
+
+
 class MlaSmallWorkload(MlaWorkload):
     """The MLA layer at 1024 tokens (profiler captures, quick checks)."""
     name = "mla_layer_prefill_1024"
@@ -765,7 +779,8 @@ class MlaSmallWorkload(MlaWorkload):
 
 WORKLOADS = {"gemm": GemmWorkload, "gemm_prof": GemmProfWorkload, "chain": ChainWorkload,
              "chain_prof": ChainProfWorkload, "mla": MlaWorkload, "mla_ref": MlaRefScaleWorkload,
-             "mla_small": MlaSmallWorkload, "moe": MoeWorkload, "moe_small": MoeSmallWorkload}
+             "mla_small": MlaSmallWorkload, "mla_causal": MlaCausalSkipWorkload, "moe": MoeWorkload,
+             "moe_small": MoeSmallWorkload}
 DEFAULT_WORKLOAD = "mla"
 
 
@@ -889,7 +904,7 @@ def main():
     gemm_part = None
     if args.workload in ("mla", "mla_ref", "moe") and rank == 0:
         # the other half of the headline metric: the bit-exact int64 GEMM alone, same kernel
-        del wl.x_host
+        wl.x_host = None
         torch.cuda.empty_cache()
         gw = GemmProfWorkload(torch, k, dev, rank)
         for _ in range(3):

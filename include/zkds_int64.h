@@ -65,6 +65,11 @@ int zkds_device_status(int clear);
                                    while A is split (no host synchronisation).  Data beyond the
                                    bound raises the flag zkds_device_status reports. */
 
+#define ZKDS_CAUSAL_SKIP 16      /* score entry points with causal != 0: output tiles that lie entirely
+                                   in the masked region are neither computed nor written (their
+                                   contents are undefined).  Only for callers that never read masked
+                                   scores: zkds_softmax_causal / zkds_einsum_bsht_btc_bshc_causal. */
+
 /* =============================================================================
  * Group 1 — the reference's symbols (same names, same argument lists)
  * ========================================================================== */
@@ -195,6 +200,20 @@ int zkds_mla_scores(const int64_t* q_abs, const int64_t* kv, const int64_t* q_pe
                     int64_t* out, int64_t B, int64_t S, int64_t H, int64_t T, int64_t C1, int64_t C2,
                     int64_t rescale1, int64_t rescale2, int64_t ep_mul, int64_t ep_div, int causal,
                     int64_t start_pos, int64_t mask_value, int a_limbs, int b_limbs, int flags, void* stream);
+
+/* Causal counterparts for prefill attention whose masked scores were skipped (ZKDS_CAUSAL_SKIP).
+ * Row (b, s, h) owns columns t <= start_pos + s only.  The results equal what softmax_q19 and
+ * einsum_bsht_btc_bshc give on fully written masked scores, because a masked score (-(64<<36) added)
+ * always gets weight 0 (int64_gemm.cu:706-710).
+ *  zkds_softmax_causal: Q19 softmax that reads and writes only the owned columns (T even, <= 8192;
+ *    ZKDS_ERR_UNSUPPORTED otherwise, silently).
+ *  zkds_einsum_bsht_btc_bshc_causal: P . KV that reads only the owned columns of P and skips the K
+ *    blocks beyond them; a_limbs must be given (probabilities fit 3 limbs). */
+int zkds_softmax_causal(const int64_t* X, int64_t* C, const int64_t* lut, int64_t B, int64_t S, int64_t H,
+                        int64_t T, int64_t start_pos, void* stream);
+int zkds_einsum_bsht_btc_bshc_causal(const int64_t* P, const int64_t* KV, int64_t* out, int64_t rescale,
+                                     int64_t B, int64_t S, int64_t H, int64_t T, int64_t C, int64_t start_pos,
+                                     int a_limbs, int b_limbs, int flags, void* stream);
 
 /* Grouped linear layer for the routed experts (replaces the per-expert Python loop of
  * MoE.forward, model.py:1355-1379): A is a flat [n_tiles*128, K] int64 matrix whose i-th

@@ -144,6 +144,27 @@ def test_mla_prefill_then_decode_with_dumps(M, mo, kmod, dev, tmp_path, act_limb
         M.ACT_LIMBS, M.snark, M.zkDataDir = 4, False, "../zkdata"
 
 
+def test_mla_prefill_with_masked_half_skipped(M, mo, kmod, dev):
+    """causal_skip leaves the masked scores / probabilities uncomputed; the layer output is unchanged"""
+    a = small_args(M, kv_lora_rank=128, n_heads=8)
+    rng = np.random.default_rng(11)
+    p = mla_weights(rng, a)
+    attn = M.MLA(0, a).to(dev)
+    load_mla(attn, p, dev)
+    attn.score_limbs = (5, 4)
+    attn.causal_skip = True
+    freqs = freqs_table(M, a)
+    S = 40
+    x = np.rint(rng.standard_normal((1, S, a.dim)) * 2.0**21).astype(np.int64)
+    kv_cache = np.zeros((1, a.max_seq_len, a.kv_lora_rank), np.int64)
+    pe_cache = np.zeros((1, a.max_seq_len, a.qk_rope_head_dim), np.int64)
+    mask_np = mo.causal_mask(S)
+    want = mo.mla_forward(p, x, 0, freqs[:S].numpy(), mask_np, kv_cache, pe_cache, a.n_heads)
+    got = attn(t(x, dev), 0, freqs[:S].to(dev), t(mask_np, dev))
+    same(got, want, "MLA output with the masked half skipped")
+    kmod.device_status()
+
+
 def test_mlp_expert_shapes_and_shifts(M, mo, kmod, dev):
     rng = np.random.default_rng(2)
     for (dim, inter, s1, s3) in ((256, 384, 31, 31), (256, 200, 31, 33)):   # equal shifts: stacked GEMM

@@ -159,6 +159,38 @@ def test_mla_scores_in_one_pass(kmod, orc, dev, dims, bits):
     kmod.device_status()
 
 
+@pytest.mark.parametrize("dims", [(1, 40, 4, 40, 128, 64), (2, 300, 2, 300, 256, 64), (1, 130, 16, 130, 512, 64)])
+def test_causal_skip_pipeline(kmod, orc, dev, dims):
+    """scores with masked tiles skipped -> causal softmax -> causal P.KV gives the same context
+    tensor as the reference's fully materialised path; the unmasked scores and probabilities match"""
+    Bn, S, H, T, C1, C2 = dims
+    rng = np.random.default_rng(S + H)
+    qa = rand_i64(rng, (Bn, S, H, C1), 22)
+    kv = rand_i64(rng, (Bn, T, C1), 23)
+    qp = rand_i64(rng, (Bn, S, H, C2), 21)
+    pe = rand_i64(rng, (Bn, T, C2), 21)
+    mask = np.where(np.arange(T)[None, :] > np.arange(S)[:, None], -(64 << 36), 0).astype(np.int64)
+    scores = (orc.einsum_bshc_btc_bsht(qa, kv, 23) + orc.einsum_bshc_btc_bsht(qp, pe, 21)) * 94 // 695 \
+        + mask[None, :, None, :]
+    probs = orc.softmax(scores, 19)
+    ctx = orc.einsum_bsht_btc_bshc(probs, kv, 23)
+    keep = np.broadcast_to((mask == 0)[None, :, None, :], scores.shape)
+
+    kmod.softmax_init_q19()
+    kvd = g(kv, dev)
+    got_s = kmod.mla_scores_fused(g(qa, dev), kvd, g(qp, dev), g(pe, dev), causal=True, a_limbs=4, b_limbs=4,
+                                  dynamic=True, skip_masked=True)
+    assert got_s is not None
+    assert np.array_equal(got_s.cpu().numpy()[keep], scores[keep])
+    got_p = torch.full_like(got_s, 77)
+    assert kmod.softmax_q19_causal(got_s, got_p, 0)
+    gp = got_p.cpu().numpy()
+    assert np.array_equal(gp[keep], probs[keep])
+    got_c = kmod.einsum_bsht_btc_bshc_causal(got_p, kvd, 23, 0, a_limbs=3, b_limbs=4)
+    same(got_c, ctx, "context")
+    kmod.device_status()
+
+
 def test_mla_scores_fused_declines_other_shapes(kmod, dev):
     z = lambda *s: torch.zeros(s, dtype=torch.int64, device=dev)
     assert kmod.mla_scores_fused(z(1, 2, 2, 64), z(1, 4, 64), z(1, 2, 2, 16), z(1, 4, 16)) is None

@@ -121,6 +121,7 @@ static int run_contraction(const Contraction& p, int a_limbs, int b_limbs, int f
     Contraction pd = p;
     pd.dynamic_a = ((flags & ZKDS_LIMBS_DYNAMIC) && a_limbs > 0) ? 1 : 0;
 
+    if (p.skip_k && a_limbs <= 0) return ZKDS_ERR_ARG;   // the unread part of A may hold anything
     if (a_limbs <= 0 || b_limbs <= 0) {
         uint64_t* d = (uint64_t*)workspace(2 * sizeof(uint64_t), 5);
         if (!d) return ZKDS_ERR_WORKSPACE;
@@ -340,6 +341,7 @@ int zkds_einsum_bshc_btc_bsht_ex(const int64_t* A, const int64_t* KV, int64_t* o
     Contraction p = einsum_problem(1, A, KV, out, rescale, B, S, H, T, C);
     p.addin = addin; p.ep_mul = ep_mul; p.ep_div = ep_div;
     p.causal_H = causal ? H : 0; p.causal_start = start_pos; p.mask_value = mask_value;
+    if (causal && (flags & ZKDS_CAUSAL_SKIP)) { p.skip_tiles = 1; p.skip_H = H; p.skip_start = start_pos; }
     return finish(run_contraction(p, a_limbs, b_limbs, flags, ST(stream)),
                   "zkds_einsum_bshc_btc_bsht_ex");
 }
@@ -378,6 +380,7 @@ int zkds_mla_scores(const int64_t* q_abs, const int64_t* kv, const int64_t* q_pe
     f.ep_mul = ep_mul; f.ep_div = ep_div;
     f.causal_H = causal ? H : 0; f.causal_start = start_pos; f.mask_value = mask_value;
     f.dynamic_a = (flags & ZKDS_LIMBS_DYNAMIC) ? 1 : 0;
+    f.skip_tiles = (flags & ZKDS_CAUSAL_SKIP) ? 1 : 0;
     // ZKDS_ERR_UNSUPPORTED is an expected answer here (the caller then runs the two contractions
     // separately), so it is returned without the stderr line
     int rc = launch_scores_fused(f, a_limbs, b_limbs, st);
@@ -405,6 +408,27 @@ int zkds_grouped_prepared(const int64_t* A, const void* planes, const int* tile_
     p.group_shift = group_shift; p.n_split = n_split;
     int f = (flags & ~ZKDS_ALGO_MASK) | ZKDS_ALGO_LIMB;
     return finish(run_contraction(p, a_limbs, 0, f, ST(stream), &hd->pl), "zkds_grouped_prepared");
+}
+
+int zkds_einsum_bsht_btc_bshc_causal(const int64_t* P, const int64_t* KV, int64_t* out, int64_t rescale,
+                                     int64_t B, int64_t S, int64_t H, int64_t T, int64_t C, int64_t start_pos,
+                                     int a_limbs, int b_limbs, int flags, void* stream)
+{
+    Contraction p = einsum_problem(2, P, KV, out, rescale, B, S, H, T, C);
+    p.skip_k = 1; p.skip_H = H; p.skip_start = start_pos;
+    int f = (flags & ~ZKDS_ALGO_MASK) | ZKDS_ALGO_LIMB;     // only the limb kernel knows the causal layout
+    return finish(run_contraction(p, a_limbs, b_limbs, f, ST(stream)), "zkds_einsum_bsht_btc_bshc_causal");
+}
+
+int zkds_softmax_causal(const int64_t* X, int64_t* C, const int64_t* lut, int64_t B, int64_t S, int64_t H,
+                        int64_t T, int64_t start_pos, void* stream)
+{
+    int rc;
+    if (B < 0 || S < 0 || H < 0 || T < 0) rc = ZKDS_ERR_ARG;
+    else if (B && S && H && T && (!X || !C || !lut)) rc = ZKDS_ERR_ARG;
+    else rc = launch_softmax_causal(X, C, lut, B, S, H, T, start_pos, ST(stream));
+    if (rc == ZKDS_ERR_UNSUPPORTED) { t_status = rc; return rc; }
+    return finish(rc, "zkds_softmax_causal");
 }
 
 int zkds_rope(const int64_t* A, const int64_t* table, int64_t* C, int64_t batch, int64_t seq,

@@ -309,7 +309,7 @@ softmax_kernel(const int64_t* X, int64_t* Wout, int64_t* C, const int64_t* __res
 template <int E>
 __global__ void __launch_bounds__(kThreads)
 softmax_q19_reg_kernel(const int64_t* X, int64_t* Wout, int64_t* C, const int64_t* __restrict__ lut_g,
-                       int T)
+                       int T, int valid_H, int valid_S, int valid_start)
 {
     __shared__ uint32_t lut[256];
     __shared__ int64_t red[32];
@@ -319,7 +319,14 @@ softmax_q19_reg_kernel(const int64_t* X, int64_t* Wout, int64_t* C, const int64_
     const longlong2* xv = reinterpret_cast<const longlong2*>(X + off);
     longlong2* cv = reinterpret_cast<longlong2*>(C + off);
     longlong2* wv = Wout ? reinterpret_cast<longlong2*>(Wout + off) : nullptr;
-    const int half = T >> 1;
+    // valid_H > 0: row (b, s, h) only counts columns <= valid_start + s; the rest is neither read
+    // nor written
+    int valid = T;
+    if (valid_H) {
+        const int sidx = (int)((blockIdx.x / (unsigned)valid_H) % (unsigned)valid_S);
+        valid = valid_start + sidx + 1 < T ? valid_start + sidx + 1 : T;
+    }
+    const int half = (valid + 1) >> 1;
 
     longlong2 v[E];
     int64_t mx = INT64_MIN;
@@ -328,6 +335,7 @@ softmax_q19_reg_kernel(const int64_t* X, int64_t* Wout, int64_t* C, const int64_
         const int i = threadIdx.x + j * kThreads;
         if (i < half) {
             v[j] = xv[i];
+            if (2 * i + 1 >= valid) v[j].y = INT64_MIN;   // odd boundary: the second element is masked
             mx = v[j].x > mx ? v[j].x : mx;
             mx = v[j].y > mx ? v[j].y : mx;
         }
@@ -342,7 +350,7 @@ softmax_q19_reg_kernel(const int64_t* X, int64_t* Wout, int64_t* C, const int64_
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             uint32_t wi = 0;
-            if (i < half) {
+            if (i < half && 2 * i + h < valid) {
                 const uint64_t d = (uint64_t)mx - (uint64_t)(h ? v[j].y : v[j].x);
                 if (d <= (uint64_t)(64 << 19)) {
                     const uint32_t y = (uint32_t)(((uint64_t)(uint32_t)d * 756388u) >> 19);
@@ -389,16 +397,28 @@ softmax_q19_reg_kernel(const int64_t* X, int64_t* Wout, int64_t* C, const int64_
 }
 
 static int launch_softmax_q19_reg(const int64_t* X, int64_t* Wout, int64_t* C, const int64_t* lut,
-                                  int64_t rows, int64_t T, cudaStream_t st)
+                                  int64_t rows, int64_t T, cudaStream_t st, int vH = 0, int vS = 1,
+                                  int vstart = 0)
 {
     const int pairs = (int)((T / 2 + kThreads - 1) / kThreads);
     const unsigned g = (unsigned)rows;
-    if (pairs <= 1) softmax_q19_reg_kernel<1><<<g, kThreads, 0, st>>>(X, Wout, C, lut, (int)T);
-    else if (pairs <= 2) softmax_q19_reg_kernel<2><<<g, kThreads, 0, st>>>(X, Wout, C, lut, (int)T);
-    else if (pairs <= 4) softmax_q19_reg_kernel<4><<<g, kThreads, 0, st>>>(X, Wout, C, lut, (int)T);
-    else if (pairs <= 8) softmax_q19_reg_kernel<8><<<g, kThreads, 0, st>>>(X, Wout, C, lut, (int)T);
-    else softmax_q19_reg_kernel<16><<<g, kThreads, 0, st>>>(X, Wout, C, lut, (int)T);
+    if (pairs <= 1) softmax_q19_reg_kernel<1><<<g, kThreads, 0, st>>>(X, Wout, C, lut, (int)T, vH, vS, vstart);
+    else if (pairs <= 2) softmax_q19_reg_kernel<2><<<g, kThreads, 0, st>>>(X, Wout, C, lut, (int)T, vH, vS, vstart);
+    else if (pairs <= 4) softmax_q19_reg_kernel<4><<<g, kThreads, 0, st>>>(X, Wout, C, lut, (int)T, vH, vS, vstart);
+    else if (pairs <= 8) softmax_q19_reg_kernel<8><<<g, kThreads, 0, st>>>(X, Wout, C, lut, (int)T, vH, vS, vstart);
+    else softmax_q19_reg_kernel<16><<<g, kThreads, 0, st>>>(X, Wout, C, lut, (int)T, vH, vS, vstart);
     return check_launch();
+}
+
+int launch_softmax_causal(const int64_t* X, int64_t* C, const int64_t* lut, int64_t B, int64_t S, int64_t H,
+                          int64_t T, int64_t start, cudaStream_t st)
+{
+    const int64_t rows = B * S * H;
+    if (rows == 0 || T == 0) return ZKDS_OK;
+    if (rows > 0x7fffffffll || T > 2 * 16 * kThreads || (T & 1) || H <= 0 || H > 0x7fffffff || S > 0x7fffffff ||
+        start < 0 || start > 0x7fffffff || ((((uintptr_t)X | (uintptr_t)C) & 15) != 0))
+        return ZKDS_ERR_UNSUPPORTED;
+    return launch_softmax_q19_reg(X, nullptr, C, lut, rows, T, st, (int)H, (int)S, (int)start);
 }
 
 template <int FRAC>

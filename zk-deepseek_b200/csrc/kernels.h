@@ -14,6 +14,10 @@ int launch_act(const int64_t* X, int64_t* C, const int64_t* lut, int64_t n, int 
                cudaStream_t st);
 int launch_softmax(const int64_t* X, int64_t* Wout, int64_t* C, const int64_t* lut, int64_t rows,
                    int64_t T, int frac, cudaStream_t st);
+// Q19 softmax over rows (b, s, h) that only looks at columns <= start + s of each row and writes
+// only those (causal attention with the masked scores left unwritten)
+int launch_softmax_causal(const int64_t* X, int64_t* C, const int64_t* lut, int64_t B, int64_t S, int64_t H,
+                          int64_t T, int64_t start, cudaStream_t st);
 int launch_rope(const int64_t* A, const int64_t* Tb, int64_t* C, int64_t batch, int64_t S,
                 int64_t H, int64_t pairs, int shift, cudaStream_t st);
 int launch_rmsnorm(const int64_t* A, const void* W, int w_bits, const int64_t* rms_in,
@@ -63,6 +67,12 @@ struct Contraction {
     // 0..127, n_split a multiple of 8); null = the uniform shift
     const int* group_shift;
     int64_t n_split;
+    // causal skipping, rows = (s, h) pairs with skip_H heads per sequence position:
+    //  skip_tiles: output tiles entirely beyond column skip_start + s are neither computed nor written;
+    //  skip_k: A holds data only in columns <= skip_start + s (zero beyond, not read), and K blocks
+    //          past that are not accumulated
+    int skip_tiles, skip_k;
+    int64_t skip_H, skip_start;
 };
 
 // CUDA-core path: exact for every input, any shape (gemm_exact.cu)
@@ -91,6 +101,7 @@ struct FusedScores {
     int shift1, shift2;
     int64_t ep_mul, ep_div, causal_H, causal_start, mask_value;
     int dynamic_a;
+    int skip_tiles;   // with causal_H: tiles whose every column is masked are neither computed nor written
 };
 int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st);
 

@@ -67,8 +67,11 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 split_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, int64_t rows, int64_t K,
              int64_t Kp, int64_t sz, int64_t sr, int64_t sk, int64_t div, int64_t plane_stride,
-             unsigned* overflow, unsigned long long* absmax_out, int64_t dst_pitch)
+             unsigned* overflow, unsigned long long* absmax_out, int64_t dst_pitch, int64_t valid_H,
+             int64_t valid_start)
 {
+    // valid_H > 0: row r = (s, h) only holds data in columns <= valid_start + s (causal attention
+    // probabilities); the rest is written as zero without being read
     uint64_t seen = 0;
     bool ovf = false;
     const int64_t quads = Kp >> 2;
@@ -85,13 +88,16 @@ split_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, int64_
         else { qd = t / rows; r = t - qd * rows; }
         const int64_t k0 = qd << 2;
         int64_t v[4];
-        if (vec && k0 + 4 <= K) {
+        const int64_t Kv = valid_H ? (valid_start + r / valid_H + 1 < K ? valid_start + r / valid_H + 1 : K) : K;
+        if (k0 >= Kv) {
+            v[0] = v[1] = v[2] = v[3] = 0;
+        } else if (vec && k0 + 4 <= Kv) {
             const longlong2* src = reinterpret_cast<const longlong2*>(x + r * sr + k0);
             longlong2 a = src[0], b = src[1];
             v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
         } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = (k0 + j < K) ? (int64_t)x[r * sr + (k0 + j) * sk] : 0;
+            for (int j = 0; j < 4; ++j) v[j] = (k0 + j < Kv) ? (int64_t)x[r * sr + (k0 + j) * sk] : 0;
         }
         uint32_t w[9];
 #pragma unroll
@@ -285,6 +291,12 @@ struct LimbParams {
     int k_switch, shift2;
     int64_t addend2;
     int nbuf;                 // accumulator buffers in tensor memory: 2 (ping-pong) or 1
+    // causal skipping (optional): rows are (s, h) pairs with skip_H heads per sequence position s.
+    //  skip_tiles: output tiles whose every column is beyond skip_start + s are not computed
+    //              (the attention scores of masked positions are left unwritten);
+    //  skip_k:     K blocks beyond skip_start + s_max + 1 are not accumulated (P . KV with P = 0 there)
+    int skip_tiles, skip_k;
+    int64_t skip_H, skip_start;
     // La is an upper bound when a_absmax is set: the kernel derives the limb count actually
     // needed from the range the split pass measured and skips the all-zero upper limbs
     const unsigned long long* a_absmax;
@@ -556,6 +568,14 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int64_t m0 = m_tile * kTileM;
     const int64_t n0 = n_tile * p.NT;
     const int64_t z = blockIdx.z;
+    int kb_end = p.kblocks;
+    if (p.skip_k) {
+        // rows of this tile see nothing beyond column skip_start + s_max: later K blocks are all zero
+        int64_t last_row = m0 + kTileM - 1;
+        if (last_row > p.M - 1) last_row = p.M - 1;
+        const int64_t need = (p.skip_start + last_row / p.skip_H + 1 + kBlockK - 1) / kBlockK;
+        if (need < kb_end) kb_end = need < 1 ? 1 : (int)need;
+    }
     const int D = La + p.Lb - 1;
 
     if (threadIdx.x == 0) {
@@ -582,7 +602,7 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const int64_t zb = p.tile_group ? group : (p.b_batched ? z : 0);
             const uint32_t tx_bytes = (uint32_t)La * kTileM * kBlockK + b_bytes;
             int armed = 0;
-            for (int kb = 0; kb < p.kblocks; ++kb) {
+            for (int kb = 0; kb < kb_end; ++kb) {
                 const int s = kb % p.stages;
                 const uint32_t par = ((kb / p.stages) & 1) ^ 1;
                 if (!mbar_wait(bar_empty + 8 * s, par, abort_flag)) break;
@@ -615,7 +635,7 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                    | ((uint32_t)(kTileM >> 4) << 24);        // M
             bool ok = mbar_wait(bar_zeroed, 0, abort_flag);
             tc_fence_after();
-            for (int kb = 0; ok && kb < p.kblocks; ++kb) {
+            for (int kb = 0; ok && kb < kb_end; ++kb) {
                 const int s = kb % p.stages;
                 ok = mbar_wait(bar_full + 8 * s, (kb / p.stages) & 1, abort_flag);
                 if (!ok) break;
@@ -704,6 +724,14 @@ __device__ __forceinline__ TileCoord decode_tile(const LimbParams& p, int64_t ti
     c.m0 = (int64_t)(panel * pm + (within - n_tile * rows_here)) * kTileM;
     c.n0 = (int64_t)n_tile * p.NT;
     return c;
+}
+
+// every column of the tile lies beyond the last unmasked position of every row of the tile
+__device__ __forceinline__ bool tile_masked(const LimbParams& p, const TileCoord& c)
+{
+    int64_t last_row = c.m0 + kTileM - 1;
+    if (last_row > p.M - 1) last_row = p.M - 1;
+    return c.n0 > p.skip_start + last_row / p.skip_H;
 }
 
 // one epilogue warp: rows 32 q .. 32 q + 31 of the tile, columns [c0, c0 + CW) of it
@@ -923,6 +951,7 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             bool ok = true;
             for (int64_t tile = blockIdx.x; ok && tile < n_tiles_total; tile += gridDim.x) {
                 const TileCoord tc = decode_tile(p, tile);
+                if (p.skip_tiles && tile_masked(p, tc)) continue;
                 const int64_t zb = p.b_batched ? tc.z : 0;
                 for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
                     const int s = (int)(it % p.stages);
@@ -955,7 +984,8 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                                    ((uint32_t)((p.Lb * p.NT) >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
             int64_t it = 0, t = 0;
             bool ok = true;
-            for (int64_t tile = blockIdx.x; ok && tile < n_tiles_total; tile += gridDim.x, ++t) {
+            for (int64_t tile = blockIdx.x; ok && tile < n_tiles_total; tile += gridDim.x) {
+                if (p.skip_tiles && tile_masked(p, decode_tile(p, tile))) continue;
                 const int b = (int)(t % p.nbuf);
                 ok = mbar_wait(bar_tempty + 8 * b, (uint32_t)((t / p.nbuf) & 1), abort_flag);
                 if (!ok) break;
@@ -982,6 +1012,7 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                     umma_commit(bar_empty + 8 * s);
                 }
                 if (ok) umma_commit(bar_tfull + 8 * b);
+                ++t;
             }
         }
     } else {
@@ -1006,11 +1037,12 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
         }
         int64_t t = 0;
-        for (int64_t tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x, ++t) {
+        for (int64_t tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x) {
+            const TileCoord tc = decode_tile(p, tile);
+            if (p.skip_tiles && tile_masked(p, tc)) continue;
             const int b = (int)(t % p.nbuf);
             if (!mbar_wait(bar_tfull + 8 * b, (uint32_t)((t / p.nbuf) & 1), abort_flag)) break;
             tc_fence_after();
-            const TileCoord tc = decode_tile(p, tile);
             const uint32_t tq = lane_base + (uint32_t)(b * buf_cols);
             if (p.fits64) epilogue_part<true>(p, tq, D, tc, q, lane, c0, CW, stage, RS, set_cols);
             else epilogue_part<false>(p, tq, D, tc, q, lane, c0, CW, stage, RS, set_cols);
@@ -1022,6 +1054,7 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
+            ++t;
         }
     }
 
@@ -1099,7 +1132,8 @@ DeviceFlags* flags_for_device()
 template <typename T>
 int launch_split_t(const T* X, int8_t* planes, int L, int64_t nb, int64_t rows, int64_t K, int64_t Kp,
                    int64_t sz, int64_t sr, int64_t sk, int64_t div, unsigned* overflow, cudaStream_t st,
-                   unsigned long long* absmax_out = nullptr, int64_t dst_pitch = 0)
+                   unsigned long long* absmax_out = nullptr, int64_t dst_pitch = 0, int64_t valid_H = 0,
+                   int64_t valid_start = 0)
 {
     if (dst_pitch == 0) dst_pitch = Kp;
     int64_t total = rows * (Kp >> 2);
@@ -1109,7 +1143,7 @@ int launch_split_t(const T* X, int8_t* planes, int L, int64_t nb, int64_t rows, 
     if (nb > 65535) return ZKDS_ERR_RANGE;
     dim3 grid((unsigned)bx, (unsigned)nb);
     split_kernel<T><<<grid, 256, 0, st>>>(X, planes, L, rows, K, Kp, sz, sr, sk, div, nb * rows * dst_pitch,
-                                          overflow, absmax_out, dst_pitch);
+                                          overflow, absmax_out, dst_pitch, valid_H, valid_start);
     return check_launch();
 }
 
@@ -1274,7 +1308,7 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     bool persistent = false;
     int pNT = 0, pstages = 0;
     size_t psmem = 0;
-    if (!p.tile_group && !p.R && !p.group_shift && (Kp + kBlockK - 1) / kBlockK <= 16 &&
+    if (!p.tile_group && !p.R && !p.group_shift && !p.skip_k && (Kp + kBlockK - 1) / kBlockK <= 16 &&
         !getenv("ZKDS_NO_PERSISTENT")) {
         for (int cand : {64, 48, 32, 16}) {
             if (Lb * cand > 256 || 2 * D * cand > 512) continue;
@@ -1320,7 +1354,7 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     }
     const int64_t Kp16 = Kp;
     int rc = launch_split_t<int64_t>(p.A, pa, La, p.batches, p.M, p.K, Kp16, p.a_sz, p.a_sm, 1, p.a_div,
-                                     fl->overflow_dev, st, d_absmax);
+                                     fl->overflow_dev, st, d_absmax, 0, p.skip_k ? p.skip_H : 0, p.skip_start);
     if (rc != ZKDS_OK) return rc;
     int8_t* pb;
     if (pre_b) pb = pre_b->data;
@@ -1352,6 +1386,7 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     lp.fits64 = sum_fits64(La, Lb, p.K, p.addend);
     lp.a_absmax = d_absmax;
     lp.overflow_flag = fl->overflow_dev;
+    lp.skip_tiles = p.skip_tiles; lp.skip_k = p.skip_k; lp.skip_H = p.skip_H; lp.skip_start = p.skip_start;
     lp.tile_group = p.tile_group;
     lp.group_shift = p.group_shift; lp.n_split = p.n_split;
     lp.addin = p.addin; lp.ep_mul = p.ep_mul; lp.ep_div = p.ep_div;
@@ -1509,6 +1544,7 @@ int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st)
     lp.overflow_flag = fl->overflow_dev;
     lp.ep_mul = f.ep_mul; lp.ep_div = f.ep_div;
     lp.causal_H = f.causal_H; lp.causal_start = f.causal_start; lp.mask_value = f.mask_value;
+    lp.skip_tiles = (f.skip_tiles && f.causal_H) ? 1 : 0; lp.skip_H = f.causal_H; lp.skip_start = f.causal_start;
     int64_t panel = (32ll << 20) / ((int64_t)La * kTileM * pitch);
     if (panel < 1) panel = 1;
     if (panel > mt) panel = mt;

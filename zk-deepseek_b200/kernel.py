@@ -33,6 +33,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 ALGO_AUTO, ALGO_EXACT, ALGO_LIMB = 0, 1, 2
 REMAINDER_LEGACY = 4
 LIMBS_DYNAMIC = 8
+CAUSAL_SKIP = 16
 
 # Remainder flavour of int64_bmm_broadcast.  True reproduces the reference binary:
 # exact for c_rescale <= 31, the low 32 bits of the sum above that
@@ -96,6 +97,8 @@ _sig("zkds_einsum_bshc_btc_bsht_ex", [_vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _l
                                       _ll, _i, _i, _i, _vp])
 _sig("zkds_mla_scores", [_vp, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _i, _ll, _ll,
                          _i, _i, _i, _vp])
+_sig("zkds_softmax_causal", [_vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _vp])
+_sig("zkds_einsum_bsht_btc_bshc_causal", [_vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _i, _i, _i, _vp])
 _sig("zkds_grouped_prepared", [_vp, _vp, _vp, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _i, _i, _vp])
 _sig("zkds_glu_q23", [_vp, _vp, _ll, _vp, _vp, _vp, _ll, _ll, _vp])
 _sig("zkds_gather_rows", [_vp, _vp, _vp, _ll, _ll, _vp])
@@ -400,7 +403,8 @@ def attention_scores_fused(A, KV, rescale, addin=None, mul=0, div=0, causal=Fals
 
 
 def mla_scores_fused(q_abs, kv, q_pe, pe, rescale1=23, rescale2=21, mul=94, div=695, causal=False,
-                     start_pos=0, mask_value=-(64 << 36), a_limbs=0, b_limbs=0, dynamic=False):
+                     start_pos=0, mask_value=-(64 << 36), a_limbs=0, b_limbs=0, dynamic=False,
+                     skip_masked=False):
     """scores = ((score1 + score2) * mul // div) (+ causal mask) with score1 = einsum(q_abs, kv) at
     rescale1 and score2 = einsum(q_pe, pe) at rescale2, in one tensor-core pass (model.py:884-905).
     Returns None when the fused kernel does not take the shape (caller falls back)."""
@@ -414,11 +418,44 @@ def mla_scores_fused(q_abs, kv, q_pe, pe, rescale1=23, rescale2=21, mul=94, div=
         rc = lib.zkds_mla_scores(q_abs.data_ptr(), kv.data_ptr(), q_pe.data_ptr(), pe.data_ptr(), out.data_ptr(),
                                  Bn, S, H, T, C1, C2, int(rescale1), int(rescale2), int(mul), int(div),
                                  1 if causal else 0, int(start_pos), int(mask_value), a_limbs, b_limbs,
-                                 _a_flags(a_limbs, dynamic), _stream())
+                                 _a_flags(a_limbs, dynamic) | (CAUSAL_SKIP if (skip_masked and causal) else 0),
+                                 _stream())
     if rc == 6:          # ZKDS_ERR_UNSUPPORTED
         return None
     _check(rc, "mla_scores_fused")
     return out
+
+
+def softmax_q19_causal(R, C, start_pos=0):
+    """Q19 softmax of causal scores [B, S, H, T] that reads and writes only columns <= start_pos + s
+    of each row (the masked part of R may be unwritten, the masked part of C stays untouched).
+    Returns False when the kernel does not take the shape."""
+    _dev_i64(R, "R")
+    _dev_i64(C, "C")
+    Bn, S, H, T = R.shape
+    lut = _lut_on(EXP2_FRAC_LUT_Q19, R.device, "softmax_init_q19")
+    with torch.cuda.device(R.device):
+        rc = lib.zkds_softmax_causal(R.data_ptr(), C.data_ptr(), lut.data_ptr(), Bn, S, H, T, int(start_pos),
+                                     _stream())
+    if rc == 6:
+        return False
+    _check(rc, "softmax_q19_causal")
+    return True
+
+
+def einsum_bsht_btc_bshc_causal(A, B, rescale, start_pos=0, a_limbs=3, b_limbs=0):
+    """einsum_bsht_btc_bshc for causal probabilities: only columns t <= start_pos + s of A are read."""
+    _dev_i64(A, "A")
+    _dev_i64(B, "B")
+    Bn, S, H, T = A.shape
+    Cd = B.shape[2]
+    assert Bn == B.shape[0] and T == B.shape[1]
+    C = torch.empty((Bn, S, H, Cd), dtype=torch.int64, device=A.device)
+    with torch.cuda.device(A.device):
+        _check(lib.zkds_einsum_bsht_btc_bshc_causal(A.data_ptr(), B.data_ptr(), C.data_ptr(), int(rescale), Bn, S,
+                                                    H, T, Cd, int(start_pos), a_limbs, b_limbs, 0, _stream()),
+               "einsum_bsht_btc_bshc_causal")
+    return C
 
 
 def glu_q23(r1, r2, ld=None, want_silu=False):

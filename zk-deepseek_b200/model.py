@@ -328,6 +328,11 @@ class MLA(nn.Module):
                                                      dtype=torch.int64), persistent=False)
         self._head_planes = {}
         self.score_limbs = (0, 0)   # (a, b) limb bounds of the score contractions; 0 = measure
+        # Prefill with the causal mask: do not compute, write or read the masked half of the score
+        # and probability tensors.  The layer's output is unchanged (a masked score always gets
+        # weight 0, int64_gemm.cu:706-710); only the masked entries of the two tensors are left
+        # undefined, so it is switched off whenever they are dumped (snark).
+        self.causal_skip = False
 
     def _per_head_planes(self, lin, k_last):
         """limb planes of wkv_b_1 / wkv_b_2 viewed per head: [H, 128, 512]"""
@@ -393,8 +398,21 @@ class MLA(nn.Module):
         causal = mask is not None and start_pos == 0 and _is_causal_mask(mask, seqlen)
         scores = None
         if K.ALGO != K.ALGO_EXACT:
+            skip = causal and self.causal_skip and not snark and dyn and bl > 0
             scores = K.mla_scores_fused(q_abs, kv_all, q_pe.contiguous(), pe_all, 23, 21, self.softmax_scale1,
-                                        self.softmax_scale2, causal=causal, a_limbs=al, b_limbs=bl, dynamic=dyn)
+                                        self.softmax_scale2, causal=causal, a_limbs=al, b_limbs=bl, dynamic=dyn,
+                                        skip_masked=skip)
+            if scores is not None and skip:
+                probs = torch.empty_like(scores)
+                if K.softmax_q19_causal(scores, probs, 0):
+                    del scores
+                    ctx = K.einsum_bsht_btc_bshc_causal(probs, kv_all, 23, 0, a_limbs=3, b_limbs=bl)
+                    del probs
+                    return self._finish(ctx, lim)
+                # softmax shape not taken by the causal kernel: recompute the scores in full
+                scores = K.mla_scores_fused(q_abs, kv_all, q_pe.contiguous(), pe_all, 23, 21, self.softmax_scale1,
+                                            self.softmax_scale2, causal=causal, a_limbs=al, b_limbs=bl,
+                                            dynamic=dyn)
         if scores is None:      # shape outside the fused kernel: two contractions, tail in the second
             score1 = K.attention_scores_fused(q_abs, kv_all, 23, a_limbs=al, b_limbs=bl, dynamic=dyn)
             scores = K.attention_scores_fused(q_pe.contiguous(), pe_all, 21, addin=score1,
@@ -413,6 +431,10 @@ class MLA(nn.Module):
         # probabilities are in [0, 2^19]: three limbs
         ctx = K.einsum_bsht_btc_bshc(probs, kv_all, 23, a_limbs=3 if dyn else 0, b_limbs=bl)
         del probs
+        return self._finish(ctx, lim)
+
+    def _finish(self, ctx, lim):
+        """ctx [b, s, h, c] -> per-head W_uv, concatenate heads, output projection"""
         shift2 = self.wkv_b_2.shift()
         if lim > 0 and K.limb_kernel_takes(self.kv_lora_rank, lim, 5):
             out = K.einsum_heads_prepared(ctx, self._per_head_planes(self.wkv_b_2, True), shift2, False,
