@@ -720,6 +720,223 @@ class MoeSmallWorkload(MoeWorkload):
         return MoeWorkload.cpu_sample(orc, np, seconds, rank)
 
 
+class DecodeWorkload:
+    """Reduced-depth int64 DeepSeek-V3 decode at full width: 3 dense layers (inter_dim 18432) and
+    one MoE layer (256 routed experts + shared, top-8), int64 embedding and head over a vocabulary of
+    129280, every weight random-init at scale 2^16 (int32 layer weights ~ N(0, 2^16/sqrt(fan_in)),
+    int64 head), every shift 16.  64 sequences decode greedily, one token per step, against
+    latent caches of 2048 positions that were filled with seeded random normalised latents
+    (~ N(0, 2^16)) instead of by running a prefill.  One step = one token for each of the 64
+    sequences (embedding, 4 blocks, final norm, head, argmax)."""
+    name = "decode_4_layers_batch64_cache2048"
+    metric = "int64_decode_tokens_per_s"
+    unit = "tokens/s"
+    scaling = "weak"
+    BATCH, CACHE, LAYERS, DENSE = 64, 2048, 4, 3
+
+    def __init__(self, torch, k, dev, rank, experts=256, vocab=129280, inter=18432):
+        import numpy as np
+        self.torch, self.k, self.dev, self.np, self.rank = torch, k, dev, np, rank
+        M = importlib.import_module(PKG + ".model")
+        self.M = M
+        M.world_size, M.rank = 1, 0               # every GPU decodes its own 64 sequences
+        a = M.ModelArgs(max_seq_len=self.CACHE + 512, vocab_size=vocab, dim=7168, inter_dim=inter,
+                        moe_inter_dim=2048, n_layers=self.LAYERS, n_dense_layers=self.DENSE, n_heads=128,
+                        n_routed_experts=experts, n_shared_experts=1, n_activated_experts=8, n_expert_groups=8,
+                        n_limited_groups=4, score_func="sigmoid", route_scale=2.5, q_lora_rank=1536,
+                        kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128)
+        self.args = a
+        sh = 16
+        g = torch.Generator(device=dev).manual_seed(7)
+
+        def weight(out_f, in_f, gen=g):
+            return _normal_i(torch, gen, (out_f, in_f), 2.0**16 / math.sqrt(in_f), dev, torch.int32)
+
+        def norm_weight(n, dtype=torch.int32):
+            return (2**16 + _normal_i(torch, g, (n,), 2.0**8, dev, torch.int64)).to(dtype)
+
+        def scale():
+            return torch.tensor(sh, dtype=torch.int32, device=dev)
+
+        with torch.device(dev):
+            model = M.Transformer(a)
+        model.embed.weight = _normal_i(torch, g, (vocab, a.dim), 2.0**16, dev, torch.int64)
+        model.norm.weight = norm_weight(a.dim, torch.int64)
+        model.head.weight = _normal_i(torch, g, (vocab, a.dim), 2.0**16 / math.sqrt(a.dim), dev, torch.int64)
+        model.head.weight_rescale = 1
+        model.head.res_rescale = sh
+        D, I = a.dim, a.moe_inter_dim
+        for i in range(a.n_layers):
+            with torch.device(dev):
+                blk = M.Block(i, a, cache_batch=self.BATCH)
+            at = blk.attn
+            H = a.n_heads
+            at.wq_a.weight = weight(a.q_lora_rank, D)
+            at.q_norm.weight = norm_weight(a.q_lora_rank)
+            at.wq_b1.weight = weight(H * a.qk_nope_head_dim, a.q_lora_rank)
+            at.wq_b2.weight = weight(H * a.qk_rope_head_dim, a.q_lora_rank)
+            at.wkv_a1.weight = weight(a.kv_lora_rank, D)
+            at.wkv_a2.weight = weight(a.qk_rope_head_dim, D)
+            at.kv_norm.weight = norm_weight(a.kv_lora_rank)
+            at.wkv_b_1.weight = weight(H * a.qk_nope_head_dim, a.kv_lora_rank)
+            at.wkv_b_2.weight = weight(H * a.v_head_dim, a.kv_lora_rank)
+            at.wo.weight = weight(D, H * a.v_head_dim)
+            for lin in (at.wq_a, at.wq_b1, at.wq_b2, at.wkv_a1, at.wkv_a2):
+                lin.res_rescale = sh
+            for lin in (at.wkv_b_1, at.wkv_b_2, at.wo):
+                lin.scale = scale()
+            at.score_limbs = (3, 3)
+            at.kv_cache[:, :self.CACHE] = _normal_i(torch, g, (self.BATCH, self.CACHE, a.kv_lora_rank), 2.0**16, dev,
+                                                    torch.int64)
+            at.pe_cache[:, :self.CACHE] = _normal_i(torch, g, (self.BATCH, self.CACHE, a.qk_rope_head_dim),
+                                                    2.0**16, dev, torch.int64)
+            blk.attn_norm.weight = norm_weight(D)
+            blk.ffn_norm.weight = norm_weight(D)
+            if i < a.n_dense_layers:
+                for name, (o, n_in) in (("w1", (inter, D)), ("w3", (inter, D)), ("w2", (D, inter))):
+                    lin = getattr(blk.ffn, name)
+                    lin.weight = weight(o, n_in)
+                    lin.scale = scale()
+            else:
+                moe = blk.ffn
+                moe.gate.weight = weight(experts, D)
+                moe.gate.scale = scale()
+                moe.gate.bias = torch.abs(_normal_i(torch, g, (experts,), 2.0**18, dev, torch.int64)).to(torch.int32)
+                for name, (o, n_in) in (("w1", (I, D)), ("w3", (I, D)), ("w2", (D, I))):
+                    lin = getattr(moe.shared_experts, name)
+                    lin.weight = weight(o, n_in)
+                    lin.scale = scale()
+                for j in range(experts):
+                    moe.experts_w13[j, :I] = weight(I, D)
+                    moe.experts_w13[j, I:] = weight(I, D)
+                    moe.experts_w2[j] = weight(D, I)
+                moe.experts_shift.fill_(sh)
+            model.layers[i] = blk
+        self.model = model
+        gt = torch.Generator(device=dev).manual_seed(70 + rank)
+        self.tokens = torch.randint(0, vocab, (self.BATCH, 1), generator=gt, device=dev)
+        self.pos = self.CACHE
+        M.ACT_LIMBS = 3
+        self.launches_per_step = 0
+        self.tok_host = None
+        # bytes the step must stream from HBM (limb planes of every weight it touches + caches)
+        self.bytes_fixed = None
+
+    def config(self):
+        a = self.args
+        return {"workload": self.name, "batch": self.BATCH, "cache_positions": self.CACHE, "layers": a.n_layers,
+                "dense_layers": a.n_dense_layers, "dim": a.dim, "vocab": a.vocab_size, "experts": a.n_routed_experts,
+                "shift": 16, "act_limbs_bound": 3, "cache_fill": "seeded random latents, no prefill pass",
+                "l2": "weights streamed per step (tens of GB) far exceed L2"}
+
+    def _decode(self, tokens):
+        m = self.model
+        if self.pos >= self.args.max_seq_len:          # wrap: keep the cache length bounded in long runs
+            self.pos = self.CACHE
+        h, pos, S = m.prep_inference(tokens, self.pos)
+        for i in range(self.args.n_layers):
+            h = m.layer_inference(i, h, pos, S)
+        logits = m.finish_inference(h)                 # [1, B, vocab]
+        self.pos += 1
+        return logits[0].argmax(dim=-1, keepdim=True)  # greedy, first maximum
+
+    def step(self):
+        self.tokens = self._decode(self.tokens)
+        return self.tokens
+
+    def step_e2e(self):
+        torch = self.torch
+        if self.tok_host is None:
+            self.tok_host = self.tokens.cpu().pin_memory()
+            self.tok_in = torch.empty_like(self.tokens)
+        self.tok_in.copy_(self.tok_host, non_blocking=True)
+        nxt = self._decode(self.tok_in)
+        self.tok_host.copy_(nxt, non_blocking=True)
+        torch.cuda.current_stream().synchronize()      # the next step's input is this step's output
+
+    def e2e_bytes(self):
+        return self.BATCH * 8, self.BATCH * 8
+
+    def value(self, seconds_per_step, world):
+        return self.BATCH * world / seconds_per_step
+
+    def roofline(self, peaks):
+        k = self.k
+        k.kernel_timing(2)
+        self.step()
+        self.torch.cuda.synchronize()
+        recs = k.kernel_timing_records()
+        k.kernel_timing(False)
+        ms = sum(r["ms"] for r in recs)
+        # weight bytes each tensor-core launch streams: its B limb planes (N x K x limbs)
+        wbytes = 0.0
+        for r in recs:
+            nb = self.args.n_routed_experts if r["grouped"] else (r["batches"] if r["b_batched"] else 1)
+            wbytes += float(nb) * r["N"] * r["K"] * r["lb"]
+        self.launches_per_step = 2 * len(recs) + 40
+        gbs = wbytes / (ms * 1e-3) / 1e9
+        return {"bound": "hbm", "kernel": "limb_gemm kernels of one decode step (%d launches)" % len(recs),
+                "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": round(gbs / peaks["hbm_gbs"], 4), "traffic": None, "kernel_ms": round(ms, 3),
+                "weight_plane_bytes_per_step": wbytes,
+                "note": "algorithmic bytes = limb planes of the B operand of every tensor-core launch (weights, "
+                        "all 256 experts' planes counted for the grouped launches, latent caches); peak = "
+                        "STREAM-style copy (%s)" % peaks["source"]}
+
+    def check(self, orc):
+        """block 0 (attention over the 2048-position cache + dense MLP) for the first two sequences
+        against the numpy restatement of Block.forward, then the head on the same hidden state"""
+        from oracle import model_oracle as mo
+        np, torch, a, m = self.np, self.torch, self.args, self.model
+        blk = m.layers[0]
+        pos = self.pos if self.pos < a.max_seq_len else self.CACHE
+        h = m.embed(self.tokens)
+        freqs = m.freqs_cis[pos:pos + 1]
+        kv_before = blk.attn.kv_cache[:2, :pos].cpu().numpy()
+        pe_before = blk.attn.pe_cache[:2, :pos].cpu().numpy()
+        got = blk(h, pos, freqs, None)[:2].cpu().numpy()
+        at = blk.attn
+        n = lambda t: t.cpu().numpy()
+        pa = {k2: n(getattr(at, k2).weight) for k2 in ("wq_a", "wq_b1", "wq_b2", "wkv_a1", "wkv_a2", "wkv_b_1", "wkv_b_2",
+                                                       "wo", "q_norm", "kv_norm")}
+        pa.update(wkv_b_1_scale=16, wkv_b_2_scale=16, wo_scale=16)
+        p = {"attn_norm": n(blk.attn_norm.weight), "ffn_norm": n(blk.ffn_norm.weight)}
+        pf = {"w1": n(blk.ffn.w1.weight), "w3": n(blk.ffn.w3.weight), "w2": n(blk.ffn.w2.weight),
+              "w1_scale": 16, "w3_scale": 16, "w2_scale": 16}
+        bad = 0
+        for b in range(2):
+            kv = np.zeros((1, pos + 1, a.kv_lora_rank), np.int64)
+            pe = np.zeros((1, pos + 1, a.qk_rope_head_dim), np.int64)
+            kv[0, :pos], pe[0, :pos] = kv_before[b], pe_before[b]
+            x = n(h[b:b + 1])
+            normed, _ = mo.rms_norm(x, p["attn_norm"])
+            attned = mo.mla_forward(pa, normed, pos, n(freqs), None, kv, pe, a.n_heads, s_q=16, s_kv=16)
+            x1 = x + attned * (2 ** 12)
+            f, _ = mo.rms_norm(x1, p["ffn_norm"])
+            want = x1 + mo.mlp_forward(pf, f) * (2 ** 8)
+            bad += int((got[b:b + 1] != want).sum())
+        hn = n(m.norm(h[:2])[0][:, -1])
+        logits = n(m.head(m.norm(h[:2])[0][:, -1][None, :]))
+        want_l, _ = orc.gemm(hn[None], n(m.head.weight[:4096]), 1, 1, 16)
+        bad += int((logits[:, :, :4096] != want_l).sum())
+        return bad
+
+    @staticmethod
+    def cpu_sample(orc, np, seconds, rank=0):
+        """one token of one sequence through the GEMVs of one dense layer + head (weights at full width)"""
+        rng = np.random.default_rng(7)
+        ri = lambda shape, b: np.rint(rng.standard_normal(shape) * 2.0**b).astype(np.int64)
+        x = ri((1, 1, 7168), 16)
+        shapes = ((1536, 7168), (24576, 1536), (576, 7168), (7168, 16384), (36864, 7168), (7168, 18432))
+        ws = [ri(sh, 9).astype(np.int32) for sh in shapes]
+        t0 = time.time()
+        for w in ws:
+            orc.gemm(ri((1, 1, w.shape[1]), 16), w, 1, 1, 16)
+        dt = time.time() - t0
+        # one dense layer per token; the 4-layer model + head costs about 5.3x that
+        return 1.0 / (dt * 5.3), "GEMVs of one dense layer for one token, scaled to 4 layers + head", dt
+
+
 class GemmProfWorkload(GemmWorkload):
     """Smaller GEMM of the same kernel for profiler captures (inputs still exceed L2)."""
     name = "gemm_4096x8192x4096"
@@ -780,7 +997,7 @@ class MlaSmallWorkload(MlaWorkload):
 WORKLOADS = {"gemm": GemmWorkload, "gemm_prof": GemmProfWorkload, "chain": ChainWorkload,
              "chain_prof": ChainProfWorkload, "mla": MlaWorkload, "mla_ref": MlaRefScaleWorkload,
              "mla_small": MlaSmallWorkload, "mla_causal": MlaCausalSkipWorkload, "moe": MoeWorkload,
-             "moe_small": MoeSmallWorkload}
+             "moe_small": MoeSmallWorkload, "decode": DecodeWorkload}
 DEFAULT_WORKLOAD = "mla"
 
 

@@ -278,7 +278,8 @@ float zkds_last_kernel_ms(void);
  * this is a profiling pass.  zkds_timing_totals reads the sums. */
 void zkds_timing_totals(double* ms, double* int8_ops, long long* launches);
 /* i-th tensor-core launch since zkds_timing(2) (first 256 kept): out8 = {batches, M, N, K, limbs of
- * A used, limbs of B, milliseconds, 1 if grouped}; returns 0 when there is no such record. */
+ * A used, limbs of B, milliseconds, flags: 1 grouped + 2 B differs per batch}; returns 0 when there
+ * is no such record. */
 int zkds_timing_record(long long i, double* out8);
 
 /* Tail of the gated MLP (model.py:1034-1048, 1266-1280): h = (silu_q23(r1) * r2) >> 23 with a

@@ -1440,7 +1440,7 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
         if (g_tot_launches < 256) {
             LaunchRecord& r = g_records[g_tot_launches];
             r.v[0] = (double)p.batches; r.v[1] = (double)p.M; r.v[2] = (double)p.N; r.v[3] = (double)p.K;
-            r.v[4] = la_used; r.v[5] = Lb; r.v[6] = ms; r.v[7] = p.tile_group ? 1.0 : 0.0;
+            r.v[4] = la_used; r.v[5] = Lb; r.v[6] = ms; r.v[7] = (p.tile_group ? 1.0 : 0.0) + (p.b_sz ? 2.0 : 0.0);
         }
         g_tot_ms += ms;
         g_tot_ops += 2.0 * (double)la_used * Lb * (double)p.batches * (double)p.M * (double)p.N * (double)p.K;
@@ -1579,7 +1579,7 @@ int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st)
         if (g_tot_launches < 256) {
             LaunchRecord& r = g_records[g_tot_launches];
             r.v[0] = (double)f.batches; r.v[1] = (double)f.M; r.v[2] = (double)f.N; r.v[3] = (double)(f.K1 + f.K2);
-            r.v[4] = la_used; r.v[5] = Lb; r.v[6] = ms; r.v[7] = 0.0;
+            r.v[4] = la_used; r.v[5] = Lb; r.v[6] = ms; r.v[7] = 2.0;
         }
         g_tot_ms += ms;
         g_tot_ops += 2.0 * (double)la_used * Lb * (double)f.batches * (double)f.M * (double)f.N * (double)(f.K1 + f.K2);

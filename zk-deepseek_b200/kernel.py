@@ -244,7 +244,7 @@ def kernel_timing_records():
     out, buf, i = [], (ctypes.c_double * 8)(), 0
     while lib.zkds_timing_record(ctypes.c_longlong(i), buf):
         out.append(dict(batches=int(buf[0]), M=int(buf[1]), N=int(buf[2]), K=int(buf[3]), la=int(buf[4]),
-                        lb=int(buf[5]), ms=buf[6], grouped=bool(buf[7])))
+                        lb=int(buf[5]), ms=buf[6], grouped=bool(int(buf[7]) & 1), b_batched=bool(int(buf[7]) & 2)))
         i += 1
     return out
 

@@ -170,11 +170,17 @@ class Linear_int(nn.Module):
     def _run(self, x, shift, want_remainder):
         lim = ACT_LIMBS if self.act_limbs is None else self.act_limbs
         pl = self.planes()
+        lead = x.shape[:-1]
+        x3 = x.reshape(1, -1, x.shape[-1])          # every leading dimension is just more rows
         if lim > 0 and K.limb_kernel_takes(x.shape[-1], lim, pl.limbs):
-            return K.linear_prepared(x, pl, shift, a_rescale=self.x_rescale, a_limbs=lim,
-                                     want_remainder=want_remainder, dynamic=True)
-        q, r = K.int64_bmm_broadcast(x, self.weight, self.x_rescale, self.weight_rescale, shift)
-        return (q, r) if want_remainder else q
+            res = K.linear_prepared(x3, pl, shift, a_rescale=self.x_rescale, a_limbs=lim,
+                                    want_remainder=want_remainder, dynamic=True)
+        else:
+            q, r = K.int64_bmm_broadcast(x3.contiguous(), self.weight, self.x_rescale, self.weight_rescale, shift)
+            res = (q, r) if want_remainder else q
+        if want_remainder:
+            return res[0].view(*lead, -1), res[1].view(*lead, -1)
+        return res.view(*lead, -1)
 
     def forward(self, x):
         return self._run(x, self.res_rescale, True)
@@ -257,11 +263,12 @@ class RMSNorm_int(nn.Module):
         self.register_buffer("weight", torch.ones(dim, dtype=dtype))
 
     def forward(self, x):
+        rows = x.reshape(-1, x.shape[-1])            # the reference handles x[0] of a [1, S, dim] input
         if snark:
-            c, rms = K.RMS_Norm_int64(x[0], self.weight, 1, self.dim)
+            c, rms = K.RMS_Norm_int64(rows, self.weight, 1, self.dim)
         else:  # the rms stays on the device: no host copy unless a dump needs it
-            c, rms = K.rms_norm_int64_device(x[0], self.weight, 1, self.dim)
-        return (c[None, :], rms)
+            c, rms = K.rms_norm_int64_device(rows, self.weight, 1, self.dim)
+        return (c.view(x.shape), rms)
 
 
 def precompute_freqs_cis(args: ModelArgs) -> torch.Tensor:
@@ -295,7 +302,7 @@ def apply_rotary_emb(x: torch.Tensor, freqs_cis: torch.Tensor) -> torch.Tensor:
 class MLA(nn.Module):
     """Absorbed multi-head latent attention in int64 (model.py:652-957)."""
 
-    def __init__(self, layer_id, args: ModelArgs):
+    def __init__(self, layer_id, args: ModelArgs, cache_batch: int = 1):
         super().__init__()
         self.layer_id = layer_id
         self.dim, self.n_heads = args.dim, args.n_heads
@@ -322,9 +329,10 @@ class MLA(nn.Module):
                                                         self.n_heads * self.v_head_dim, 1, 1, i32)
         self.wo = RowParallelLinear_rescale_int(layer_id, self.n_heads * self.v_head_dim, self.dim, 1, 1, 1, i32)
         self.softmax_scale1, self.softmax_scale2 = 94, 695
-        self.register_buffer("kv_cache", torch.zeros(1, args.max_seq_len, self.kv_lora_rank, dtype=torch.int64),
-                             persistent=False)
-        self.register_buffer("pe_cache", torch.zeros(1, args.max_seq_len, self.qk_rope_head_dim,
+        # the reference keeps one sequence (model.py:740-744); cache_batch > 1 serves batched decode
+        self.register_buffer("kv_cache", torch.zeros(cache_batch, args.max_seq_len, self.kv_lora_rank,
+                                                     dtype=torch.int64), persistent=False)
+        self.register_buffer("pe_cache", torch.zeros(cache_batch, args.max_seq_len, self.qk_rope_head_dim,
                                                      dtype=torch.int64), persistent=False)
         self._head_planes = {}
         self.score_limbs = (0, 0)   # (a, b) limb bounds of the score contractions; 0 = measure
@@ -677,7 +685,8 @@ class MoE(nn.Module):
         key = torch.where(local, flat, torch.full_like(flat, E))
         order = torch.argsort(key, stable=True)
         skey = key[order]
-        counts = torch.bincount(key, minlength=E + 1)[:E]
+        # every tensor below has a static shape and nothing is read back: no host synchronisation
+        counts = torch.zeros(E + 1, dtype=torch.int64, device=dev).index_add_(0, key, torch.ones_like(key))[:E]
         padded = (counts + 127) // 128 * 128
         pad_end = torch.cumsum(padded, 0)
         pad_start = pad_end - padded
@@ -687,11 +696,12 @@ class MoE(nn.Module):
         ar = torch.arange(T * k, device=dev)
         valid = skey < E
         e_safe = torch.clamp(skey, max=E - 1)
-        rows = torch.where(valid, pad_start[e_safe] + (ar - start[e_safe]), torch.full_like(ar, -1))
-        row_src = torch.full((R,), -1, dtype=torch.int32, device=dev)
-        row_src[rows[valid]] = (order[valid] // k).to(torch.int32)
-        pos = torch.full((T * k,), -1, dtype=torch.int32, device=dev)
-        pos[order] = rows.to(torch.int32)
+        rows = torch.where(valid, pad_start[e_safe] + (ar - start[e_safe]), torch.full_like(ar, R))
+        row_src = torch.full((R + 1,), -1, dtype=torch.int32, device=dev)      # slot R swallows the rest
+        row_src.scatter_(0, rows, (order // k).to(torch.int32))
+        row_src = row_src[:R].contiguous()
+        pos = torch.empty((T * k,), dtype=torch.int32, device=dev)
+        pos[order] = torch.where(valid, rows, torch.full_like(rows, -1)).to(torch.int32)
         tile_start = torch.arange(n_tiles, device=dev) * 128
         g = torch.searchsorted(pad_end, tile_start, right=True)
         tile_group = torch.where(tile_start < pad_end[-1], g, torch.full_like(g, -1)).to(torch.int32)
@@ -745,10 +755,10 @@ class Block(nn.Module):
     """attn_norm -> MLA -> residual (x 2^12) -> ffn_norm -> MLP | MoE -> residual (x 2^8)
     (model.py:1401-1475)."""
 
-    def __init__(self, layer_id: int, args: ModelArgs, ckpt_path=None):
+    def __init__(self, layer_id: int, args: ModelArgs, ckpt_path=None, cache_batch: int = 1):
         super().__init__()
         self.layer_id, self.ckpt_path = layer_id, ckpt_path
-        self.attn = MLA(layer_id, args)
+        self.attn = MLA(layer_id, args, cache_batch)
         self.ffn = (MLP_int(layer_id, args.dim, args.inter_dim) if layer_id < args.n_dense_layers
                     else MoE(layer_id, args, ckpt_path))
         self.attn_norm = RMSNorm_int(args.dim, torch.int32)
@@ -810,8 +820,8 @@ class Transformer(nn.Module):
 
     @torch.inference_mode()
     def finish_inference(self, h):
-        h = self.norm(h)[0][:, -1]
-        logits = self.head(h[None, :])
+        h = self.norm(h)[0][:, -1]          # last position of every sequence: [B, dim]
+        logits = self.head(h[None, :])      # [1, B, vocab] (B = 1 in the reference)
         if world_size > 1:
             logits = _all_gather_last(logits)
         return logits
