@@ -499,7 +499,7 @@ class MLP_int(nn.Module):
         lim = ACT_LIMBS
         n = self.w1.weight.shape[0]
         if lim > 0 and s1 == s3 and K.limb_kernel_takes(x.shape[-1], lim, 5):
-            r13 = K.linear_prepared(x, self._stacked(), s1, a_limbs=lim, dynamic=True)
+            r13 = K.linear_prepared(x.reshape(1, -1, x.shape[-1]), self._stacked(), s1, a_limbs=lim, dynamic=True)
             r13 = r13.view(-1, 2 * n)
             r1, r2, ld = r13[:, :n], r13[:, n:], 2 * n
         else:
