@@ -479,6 +479,8 @@ def gather_rows(src, index):
     _dev_i64(src, "src")
     assert index.dtype == torch.int32 and index.is_cuda
     rows, cols = index.numel(), src.shape[-1]
+    if src.shape[0] == 0:       # nothing to gather from (a rank that received no rows): all padding
+        return torch.zeros((rows, cols), dtype=torch.int64, device=src.device)
     dst = torch.empty((rows, cols), dtype=torch.int64, device=src.device)
     with torch.cuda.device(src.device):
         _check(lib.zkds_gather_rows(src.data_ptr(), index.data_ptr(), dst.data_ptr(), rows, cols, _stream()),
