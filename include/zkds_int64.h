@@ -215,6 +215,19 @@ int zkds_einsum_bsht_btc_bshc_causal(const int64_t* P, const int64_t* KV, int64_
                                      int64_t B, int64_t S, int64_t H, int64_t T, int64_t C, int64_t start_pos,
                                      int a_limbs, int b_limbs, int flags, void* stream);
 
+/* softmax_q19 over the rows of `scores` [B,S,H,T] followed by einsum_bsht_btc_bshc with KV [B,T,C]
+ * (model.py:911-926 with kernel.py:424-448 and :274-305; no single reference entry point): out
+ * [B,S,H,C] = (rescale/2 + sum_t softmax(scores)[b,s,h,t] * KV[b,t,c]) >> rescale.  The softmax kernel
+ * writes the probabilities straight into the int8 limb planes the tensor-core contraction reads, so they
+ * never reach memory as int64 words; `scores` is left untouched.  causal_skip != 0: row (b, s, h) owns
+ * columns t <= start_pos + s only (the rest is not read), as in the two entry points above.
+ * a_limbs <= 0 means 3 (a Q19 probability is at most 2^19).  Returns ZKDS_ERR_UNSUPPORTED (silently)
+ * when T is not a multiple of 4, T > 8176, `scores` is not 16-byte aligned or the limb kernel declines
+ * the shape; callers then use softmax_q19 and the einsum separately. */
+int zkds_softmax_pv(const int64_t* scores, const int64_t* KV, int64_t* out, const int64_t* lut,
+                    int64_t rescale, int64_t B, int64_t S, int64_t H, int64_t T, int64_t C, int causal_skip,
+                    int64_t start_pos, int a_limbs, int b_limbs, int flags, void* stream);
+
 /* Grouped linear layer for the routed experts (replaces the per-expert Python loop of
  * MoE.forward, model.py:1355-1379): A is a flat [n_tiles*128, K] int64 matrix whose i-th
  * 128-row tile holds tokens of expert tile_group[i] (device array; negative = unused tile),

@@ -188,7 +188,39 @@ def test_causal_skip_pipeline(kmod, orc, dev, dims):
     assert np.array_equal(gp[keep], probs[keep])
     got_c = kmod.einsum_bsht_btc_bshc_causal(got_p, kvd, 23, 0, a_limbs=3, b_limbs=4)
     same(got_c, ctx, "context")
+    # softmax and P.KV in one call, reading only the owned columns of the skipped scores
+    if T % 4 == 0:
+        fused = kmod.softmax_pv_fused(got_s, kvd, 23, causal_skip=True, start_pos=0, a_limbs=3, b_limbs=4)
+        assert fused is not None
+        same(fused, ctx, "context, fused softmax")
     kmod.device_status()
+
+
+@pytest.mark.parametrize("dims", [(1, 5, 3, 4, 16), (2, 33, 4, 100, 128), (1, 64, 8, 1024, 512),
+                                  (1, 3, 2, 4100, 64), (1, 2, 2, 8176, 32)])
+def test_softmax_then_pv_in_one_call(kmod, orc, dev, dims):
+    """softmax_q19 -> einsum_bsht_btc_bshc with the probabilities kept as int8 limb planes
+    (model.py:911-926) against the two oracle steps"""
+    Bn, S, H, T, C = dims
+    rng = np.random.default_rng(T + C)
+    scores = np.rint(rng.standard_normal((Bn, S, H, T)) * 2.0**21).astype(np.int64)
+    scores[:, :, :, T // 2:] -= rng.integers(0, 70 << 19, (Bn, S, H, T - T // 2))
+    scores[0, 0, 0, :] = -(64 << 36)              # a fully masked row: uniform weights
+    if S > 1:
+        scores[0, 1, 0, 1:] = -(64 << 36)         # one live column: probability 2^19
+    kv = rand_i64(rng, (Bn, T, C), 24)
+    want = orc.einsum_bsht_btc_bshc(orc.softmax(scores, 19), kv, 23)
+    kmod.softmax_init_q19()
+    sd = g(scores, dev)
+    for al, bl in ((0, 0), (3, 4), (4, 5)):
+        got = kmod.softmax_pv_fused(sd, g(kv, dev), 23, a_limbs=al, b_limbs=bl)
+        assert got is not None
+        same(got, want, "limbs %s" % ((al, bl),))
+    same(sd, scores, "scores untouched")
+    kmod.device_status()
+    # shapes the fused kernel declines
+    z = torch.zeros((1, 1, 1, 6), dtype=torch.int64, device=dev)
+    assert kmod.softmax_pv_fused(z, torch.zeros((1, 6, 8), dtype=torch.int64, device=dev)) is None
 
 
 def test_mla_scores_fused_declines_other_shapes(kmod, dev):
@@ -212,6 +244,9 @@ def test_rope(kmod, orc, dev, shape, shift):
     rng = np.random.default_rng(S)
     A = np.rint(rng.standard_normal((Bn, S, H, P, 2)) * 2**16).astype(np.int64)
     A.flat[:7] = [2**62, -2**62, 2**63 - 1, -2**63, 0, 1, -1][:A.size][:min(7, A.size)]
+    if A.size > 4000:       # magnitudes on both sides of the kernel's one-word multiply bound
+        for k, bits in enumerate((18, 19, 20, 21, 22, 23, 30, 45)):
+            A.flat[100 + 400 * k:500 + 400 * k] = rand_i64(rng, 400, bits)
     T = rope_table(S, P, shift)
     C = kmod.complex_int64_mul_broadcast(g(A, dev), g(T.reshape(1, S, 1, P, 2), dev), shift)
     same(C, orc.rope(A, T, shift))
@@ -296,6 +331,42 @@ def test_activations(kmod, orc, dev, frac):
         same(C, orc.act(view, "silu", frac), "silu")
         sigm(Xd, C)
         same(C, orc.act(view, "sigmoid", frac), "sigmoid")
+
+
+# ---- expert plumbing: gated product, row gather, weighted combine ---------------------------------
+
+def test_glu_gather_combine(kmod, orc, dev):
+    rng = np.random.default_rng(77)
+    rows, n = 37, 258
+    r12 = np.rint(rng.standard_normal((rows, 2 * n)) * 2.0**24).astype(np.int64)
+    r12[0, :4] = [64 << 23, -(64 << 23), (64 << 23) - 1, 0]
+    d = g(r12, dev)
+    kmod.silu_init_q23()
+    h, s1 = kmod.glu_q23(d[:, :n], d[:, n:], ld=2 * n, want_silu=True)
+    want_s = orc.act(np.ascontiguousarray(r12[:, :n]), "silu", 23)
+    same(s1, want_s, "silu part")
+    same(h, (want_s * r12[:, n:]) >> 23, "gated product")
+
+    src = rand_i64(rng, (19, 64), 62)
+    index = rng.integers(-1, 19, 50).astype(np.int32)
+    got = kmod.gather_rows(g(src, dev), torch.from_numpy(index).to(dev))
+    same(got, np.where(index[:, None] >= 0, src[np.maximum(index, 0)], 0), "gather")
+    # a source without rows (an expert-parallel rank that received nothing): all padding
+    got = kmod.gather_rows(torch.empty((0, 64), dtype=torch.int64, device=dev),
+                           torch.full((128,), -1, dtype=torch.int32, device=dev))
+    assert got.shape == (128, 64) and int(got.abs().sum()) == 0
+
+    tokens, slots, cols = 23, 8, 96
+    out = rand_i64(rng, (tokens * slots + 5, cols), 38)
+    pos = rng.permutation(tokens * slots + 5)[:tokens * slots].reshape(tokens, slots).astype(np.int32)
+    w = rng.integers(0, 5 << 22, (tokens, slots)).astype(np.int64)
+    base = rand_i64(rng, (tokens, cols), 40)
+    y = kmod.moe_combine(g(out, dev), torch.from_numpy(pos).to(dev), g(w, dev), g(base, dev))
+    want = base.copy()
+    for t in range(tokens):
+        for sl in range(slots):
+            want[t] += out[pos[t, sl]] * w[t, sl] // (1 << 23)
+    same(y, want, "combine")
 
 
 # ---- the reference's own symbol names, and the reference's own kernels ------------------------------

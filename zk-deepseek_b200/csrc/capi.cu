@@ -420,6 +420,38 @@ int zkds_einsum_bsht_btc_bshc_causal(const int64_t* P, const int64_t* KV, int64_
     return finish(run_contraction(p, a_limbs, b_limbs, f, ST(stream)), "zkds_einsum_bsht_btc_bshc_causal");
 }
 
+int zkds_softmax_pv(const int64_t* scores, const int64_t* KV, int64_t* out, const int64_t* lut,
+                    int64_t rescale, int64_t B, int64_t S, int64_t H, int64_t T, int64_t C, int causal_skip,
+                    int64_t start_pos, int a_limbs, int b_limbs, int flags, void* stream)
+{
+    if (B < 0 || S < 0 || H < 0 || T < 0 || C < 0 || rescale < 0 || rescale > 127 || start_pos < 0)
+        return finish(ZKDS_ERR_ARG, "zkds_softmax_pv");
+    if (B == 0 || S == 0 || H == 0 || C == 0) return finish(ZKDS_OK, "zkds_softmax_pv");
+    if (T == 0 || !scores || !KV || !out || !lut) return finish(ZKDS_ERR_ARG, "zkds_softmax_pv");
+    const int64_t Kp = (T + 15) & ~(int64_t)15;
+    if (!softmax_planes_supported(scores, B * S * H, T, Kp)) { t_status = ZKDS_ERR_UNSUPPORTED; return t_status; }
+    cudaStream_t st = ST(stream);
+    Contraction p = einsum_problem(2, scores, KV, out, rescale, B, S, H, T, C);
+    p.softmax_lut = lut; p.softmax_S = S;
+    if (causal_skip) { p.skip_k = 1; p.skip_H = H; p.skip_start = start_pos; }
+    p.dynamic_a = ((flags & ZKDS_LIMBS_DYNAMIC) && a_limbs > 0) ? 1 : 0;
+    if (a_limbs <= 0) a_limbs = 3;
+    if (b_limbs <= 0) {
+        uint64_t* d = (uint64_t*)workspace(2 * sizeof(uint64_t), 5);
+        if (!d) return finish(ZKDS_ERR_WORKSPACE, "zkds_softmax_pv");
+        int rc = set_cuda_error(cudaMemsetAsync(d, 0, 2 * sizeof(uint64_t), st));
+        if (rc == ZKDS_OK) rc = launch_absmax(KV, 64, B, C, T, T * C, 1, C, 1, d + 1, st);
+        uint64_t h = 0;
+        if (rc == ZKDS_OK) rc = set_cuda_error(cudaMemcpyAsync(&h, d + 1, sizeof(h), cudaMemcpyDeviceToHost, st));
+        if (rc == ZKDS_OK) rc = set_cuda_error(cudaStreamSynchronize(st));
+        if (rc != ZKDS_OK) return finish(rc, "zkds_softmax_pv");
+        b_limbs = limbs_needed(h);
+    }
+    int rc = launch_contraction_limb(p, a_limbs, b_limbs, nullptr, st);
+    if (rc == ZKDS_ERR_UNSUPPORTED) { t_status = rc; return rc; }
+    return finish(rc, "zkds_softmax_pv");
+}
+
 int zkds_softmax_causal(const int64_t* X, int64_t* C, const int64_t* lut, int64_t B, int64_t S, int64_t H,
                         int64_t T, int64_t start_pos, void* stream)
 {

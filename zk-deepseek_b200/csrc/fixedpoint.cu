@@ -410,6 +410,184 @@ static int launch_softmax_q19_reg(const int64_t* X, int64_t* Wout, int64_t* C, c
     return check_launch();
 }
 
+// The same Q19 softmax, but the probabilities leave the kernel as signed 8-bit limb planes (the A
+// operand of the tensor-core contraction that consumes them) instead of int64 words: plane l of row
+// r lives at planes + l * plane_stride + r * Kp.  Balanced radix-256 digits as in the limb split;
+// columns from `valid` (or T) up to Kp are written as zero.  E = groups of four columns per thread.
+template <int E, int LL>      // LL: limb count known at compile time, 0 = use L
+__global__ void __launch_bounds__(kThreads)
+softmax_q19_planes_kernel(const int64_t* X, const int64_t* __restrict__ lut_g, int8_t* __restrict__ planes,
+                          int L, int T, int64_t Kp, int64_t plane_stride, unsigned* overflow,
+                          unsigned long long* absmax_out, int valid_H, int valid_S, int valid_start)
+{
+    __shared__ uint32_t lut[256];
+    __shared__ int64_t red[32];
+    __shared__ uint64_t s_magic;
+    for (int i = threadIdx.x; i < 256; i += kThreads) lut[i] = (uint32_t)lut_g[i];
+    const longlong2* xv = reinterpret_cast<const longlong2*>(X + (int64_t)blockIdx.x * T);
+    int8_t* drow = planes + (int64_t)blockIdx.x * Kp;
+    int valid = T;
+    if (valid_H) {
+        const int sidx = (int)((blockIdx.x / (unsigned)valid_H) % (unsigned)valid_S);
+        valid = valid_start + sidx + 1 < T ? valid_start + sidx + 1 : T;
+    }
+    const int quads_valid = (valid + 3) >> 2;
+    const int quads_all = (int)(Kp >> 2);
+
+    int64_t v[4 * E];
+    int64_t mx = INT64_MIN;
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+        const int q = threadIdx.x + j * kThreads;
+        if (q < quads_valid) {
+            const longlong2 a = xv[2 * q], b = xv[2 * q + 1];
+            v[4 * j] = a.x; v[4 * j + 1] = a.y; v[4 * j + 2] = b.x; v[4 * j + 3] = b.y;
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+                if (4 * q + h >= valid) v[4 * j + h] = INT64_MIN;
+                mx = v[4 * j + h] > mx ? v[4 * j + h] : mx;
+            }
+        }
+    }
+    mx = block_max_i64(mx, red);
+
+    uint32_t w[4 * E];
+    uint32_t sum32 = 0;              // at most 32 weights of at most 2^19 + 1 each
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+        const int q = threadIdx.x + j * kThreads;
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+            uint32_t wi = 0;
+            if (q < quads_valid && 4 * q + h < valid) {
+                const uint64_t d = (uint64_t)mx - (uint64_t)v[4 * j + h];
+                if (d <= (uint64_t)(64 << 19)) {
+                    const uint32_t y = (uint32_t)(((uint64_t)(uint32_t)d * 756388u) >> 19);
+                    const uint32_t k = y >> 19;
+                    const uint32_t t = lut[(y & 0x7FFFFu) >> 11];
+                    wi = k >= 32u ? 0u : (t >> k);
+                }
+            }
+            w[4 * j + h] = wi;
+            sum32 += wi;
+        }
+    }
+    const uint64_t sumW = (uint64_t)block_sum_i64((int64_t)sum32, red);
+    if (threadIdx.x == 0) s_magic = sumW ? 0xFFFFFFFFFFFFFFFFull / sumW : 0;
+    __syncthreads();
+    const uint64_t magic = s_magic;
+    const uint32_t m_lo = (uint32_t)magic, m_hi = (uint32_t)(magic >> 32);
+    const bool small = sumW < (1ull << 32);
+    const uint32_t s32 = (uint32_t)sumW;
+
+    uint32_t seen = 0;
+    bool ovf = false;
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+        const int q = threadIdx.x + j * kThreads;
+        if (q >= quads_all) continue;
+        uint32_t u[4] = {0, 0, 0, 0};
+        if (q < quads_valid) {
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+                const uint32_t wi = w[4 * j + h];
+                const uint64_t num = (uint64_t)wi << 19;
+                uint64_t qt = ((uint64_t)wi * m_hi + (((uint64_t)wi * m_lo) >> 32)) >> 13;
+                if (small) {
+                    uint64_t rem = num - qt * s32;
+                    if (rem >= sumW) { ++qt; rem -= sumW; }
+                    if (rem >= sumW) ++qt;
+                } else if (sumW) {
+                    qt = num / sumW;
+                }
+                u[h] = (uint32_t)qt;                 // 0 .. 2^19
+                seen = u[h] > seen ? u[h] : seen;
+            }
+        }
+        if (LL == 3) {
+            // balanced digits of a value below 2^23 - 2^15: the bytes of u + 0x808080, each with its
+            // top bit flipped (digit + 128 is what the biased sum holds at every position)
+            uint32_t t[4];
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+                t[h] = u[h] + 0x00808080u;
+                ovf |= (t[h] >> 24) != 0;
+            }
+#pragma unroll
+            for (int l = 0; l < 3; ++l) {
+                const uint32_t sel = 0x0040u + 0x0011u * (uint32_t)l;     // byte l of both operands
+                const uint32_t lo = __byte_perm(t[0], t[1], sel), hi = __byte_perm(t[2], t[3], sel);
+                *reinterpret_cast<uint32_t*>(drow + 4 * q + l * plane_stride) =
+                    __byte_perm(lo, hi, 0x5410u) ^ 0x80808080u;
+            }
+        } else {
+            constexpr int LMAX = LL ? LL : 9;
+            uint32_t pl[LMAX];
+#pragma unroll
+            for (int l = 0; l < LMAX; ++l) pl[l] = 0;
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+                int32_t x = (int32_t)u[h];
+#pragma unroll
+                for (int l = 0; l < LMAX; ++l) {
+                    if (LL || l < L) {
+                        pl[l] |= (uint32_t)(x & 0xFF) << (h * 8);
+                        x = (x >> 8) + ((x >> 7) & 1);
+                    }
+                }
+                ovf |= (x != 0);
+            }
+#pragma unroll
+            for (int l = 0; l < LMAX; ++l)
+                if (LL || l < L) *reinterpret_cast<uint32_t*>(drow + 4 * q + l * plane_stride) = pl[l];
+        }
+    }
+    if (ovf) *overflow = 1u;
+    if (absmax_out) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const uint32_t other = __shfl_xor_sync(0xffffffffu, seen, o);
+            seen = other > seen ? other : seen;
+        }
+        if ((threadIdx.x & 31) == 0 && seen) atomicMax(absmax_out, (unsigned long long)seen);
+    }
+}
+
+bool softmax_planes_supported(const int64_t* X, int64_t rows, int64_t T, int64_t Kp)
+{
+    return rows > 0 && rows <= 0x7fffffffll && T >= 4 && (T & 3) == 0 && Kp >= T && (Kp & 3) == 0 &&
+           Kp <= 8 * 4 * kThreads && ((uintptr_t)X & 15) == 0;
+}
+
+int launch_softmax_planes(const int64_t* X, const int64_t* lut, int8_t* planes, int L, int64_t rows, int64_t T,
+                          int64_t Kp, int64_t plane_stride, unsigned* overflow, unsigned long long* absmax_out,
+                          int64_t valid_H, int64_t valid_S, int64_t valid_start, cudaStream_t st)
+{
+    if (!softmax_planes_supported(X, rows, T, Kp) || L < 1 || L > 9 || valid_H > 0x7fffffff ||
+        valid_S > 0x7fffffff || valid_start > 0x7fffffff)
+        return ZKDS_ERR_UNSUPPORTED;
+    const int per = (int)(((Kp >> 2) + kThreads - 1) / kThreads);
+    const unsigned g = (unsigned)rows;
+    const int vS = valid_S > 0 ? (int)valid_S : 1;
+#define ZKDS_SP(E)                                                                                        \
+    do {                                                                                                  \
+        if (L == 3)                                                                                       \
+            softmax_q19_planes_kernel<E, 3><<<g, kThreads, 0, st>>>(X, lut, planes, L, (int)T, Kp,        \
+                                                                    plane_stride, overflow, absmax_out,   \
+                                                                    (int)valid_H, vS, (int)valid_start);  \
+        else                                                                                              \
+            softmax_q19_planes_kernel<E, 0><<<g, kThreads, 0, st>>>(X, lut, planes, L, (int)T, Kp,        \
+                                                                    plane_stride, overflow, absmax_out,   \
+                                                                    (int)valid_H, vS, (int)valid_start);  \
+    } while (0)
+    if (per <= 1) ZKDS_SP(1);
+    else if (per <= 2) ZKDS_SP(2);
+    else if (per <= 4) ZKDS_SP(4);
+    else ZKDS_SP(8);
+#undef ZKDS_SP
+    return check_launch();
+}
+
 int launch_softmax_causal(const int64_t* X, int64_t* C, const int64_t* lut, int64_t B, int64_t S, int64_t H,
                           int64_t T, int64_t start, cudaStream_t st)
 {
@@ -497,10 +675,19 @@ rope_kernel(const longlong2* __restrict__ A, const longlong2* __restrict__ Tb,
         unsigned i = base + j * kThreads + threadIdx.x;
         if (i < rowlen) {
             longlong2 o;
-            o.x = (int64_t)((uint64_t)mul_shift(av[j].x, bv[j].x, shift) -
-                            (uint64_t)mul_shift(av[j].y, bv[j].y, shift));
-            o.y = (int64_t)((uint64_t)mul_shift(av[j].x, bv[j].y, shift) +
-                            (uint64_t)mul_shift(av[j].y, bv[j].x, shift));
+            // magnitudes (|v|, or |v| - 1 for v < 0) of the larger factor on each side
+            const uint64_t ma = (uint64_t)(av[j].x ^ (av[j].x >> 63)) | (uint64_t)(av[j].y ^ (av[j].y >> 63));
+            const uint64_t mb = (uint64_t)(bv[j].x ^ (bv[j].x >> 63)) | (uint64_t)(bv[j].y ^ (bv[j].y >> 63));
+            if (shift < 64 && __clzll((long long)ma) + __clzll((long long)mb) >= 68) {
+                // every product stays below 2^62: one-word multiplies, the arithmetic shift floors
+                o.x = ((av[j].x * bv[j].x) >> shift) - ((av[j].y * bv[j].y) >> shift);
+                o.y = ((av[j].x * bv[j].y) >> shift) + ((av[j].y * bv[j].x) >> shift);
+            } else {
+                o.x = (int64_t)((uint64_t)mul_shift(av[j].x, bv[j].x, shift) -
+                                (uint64_t)mul_shift(av[j].y, bv[j].y, shift));
+                o.y = (int64_t)((uint64_t)mul_shift(av[j].x, bv[j].y, shift) +
+                                (uint64_t)mul_shift(av[j].y, bv[j].x, shift));
+            }
             c[i] = o;
         }
     }
@@ -578,6 +765,25 @@ __device__ __noinline__ int64_t div_slow(i128w P, int64_t r)
     return (int64_t)qq;
 }
 
+__device__ __noinline__ int64_t norm_one_wide(int64_t a, int64_t w, int64_t r, double inv);
+
+// floor(a*w / r): the case of two 32-bit factors inline, everything else out of line
+__device__ __forceinline__ int64_t norm_one_fast(int64_t a, int64_t w, int64_t r, double inv)
+{
+    if (r > 0 && a == (int64_t)(int32_t)a && w == (int64_t)(int32_t)w) {
+        const int64_t p = (int64_t)(int32_t)a * (int64_t)(int32_t)w;
+        const double qe = (double)p * inv;
+        if (fabs(qe) < 562949953421312.0) {
+            int64_t q = __double2ll_rd(qe);
+            int64_t rem = p - q * r;
+            if (rem < 0) { --q; rem += r; }
+            else if (rem >= r) { ++q; rem -= r; }
+            if (rem >= 0 && rem < r) return q;
+        }
+    }
+    return norm_one_wide(a, w, r, inv);
+}
+
 // floor(a*w / r) for r > 0 through a double estimate corrected with the exact remainder
 __device__ __forceinline__ int64_t norm_one(int64_t a, int64_t w, int64_t r, double inv)
 {
@@ -609,6 +815,11 @@ __device__ __forceinline__ int64_t norm_one(int64_t a, int64_t w, int64_t r, dou
         }
     }
     return div_slow(P, r);
+}
+
+__device__ __noinline__ int64_t norm_one_wide(int64_t a, int64_t w, int64_t r, double inv)
+{
+    return norm_one(a, w, r, inv);
 }
 
 // a^2 added to a two-word accumulator
@@ -704,11 +915,89 @@ rmsnorm_kernel(const int64_t* __restrict__ A, const WT* __restrict__ W, const in
     }
 }
 
+// Rows of at most 16 * kRegThreads elements: the row lives in registers (E 16-byte pairs per
+// thread, every load in flight at once), no shared-memory staging, two 512-thread CTAs per SM so one
+// row streams while the other reduces.
+constexpr int kRegThreads = 512;
+
+template <typename WT, int E>
+__global__ void __launch_bounds__(kRegThreads, 2)
+rmsnorm_reg_kernel(const int64_t* __restrict__ A, const WT* __restrict__ W, int64_t* rms_out,
+                   int64_t* __restrict__ C, int half, int64_t eps, int64_t dim)
+{
+    __shared__ u128w red[kRegThreads / 32];
+    __shared__ int64_t s_rms;
+    const int64_t off = (int64_t)blockIdx.x * half;
+    const longlong2* av = reinterpret_cast<const longlong2*>(A) + off;
+    longlong2* cv = reinterpret_cast<longlong2*>(C) + off;
+    longlong2 v[E];
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+        const int i = threadIdx.x + j * kRegThreads;
+        v[j] = i < half ? av[i] : make_longlong2(0, 0);
+    }
+    u128w acc = {0, 0};
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+        add_square(acc.lo, acc.hi, v[j].x);
+        add_square(acc.lo, acc.hi, v[j].y);
+    }
+    acc = warp_sum_u128(acc);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    if (lane == 0) red[wid] = acc;
+    __syncthreads();
+    if (wid == 0) {
+        u128w t = (lane < kRegThreads / 32) ? red[lane] : u128w{0, 0};
+        t = warp_sum_u128(t);
+        if (lane == 0) {
+            unsigned __int128 tot = ((unsigned __int128)t.hi << 64) | t.lo;
+            tot += (unsigned __int128)(__int128)eps;
+            uint64_t r = 0;
+            if (dim) {
+                if ((tot >> 64) == 0) r = isqrt_u128((unsigned __int128)((uint64_t)tot / (uint64_t)dim));
+                else r = isqrt_u128(tot / (unsigned __int128)(uint64_t)dim);
+            }
+            s_rms = (int64_t)r;
+            if (rms_out) rms_out[blockIdx.x] = (int64_t)r;
+        }
+    }
+    __syncthreads();
+    const int64_t r = s_rms;
+    const double inv = r > 0 ? 1.0 / (double)r : 0.0;
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+        const int i = threadIdx.x + j * kRegThreads;
+        if (i < half) {
+            longlong2 o;
+            o.x = norm_one_fast(v[j].x, (int64_t)W[2 * i], r, inv);
+            o.y = norm_one_fast(v[j].y, (int64_t)W[2 * i + 1], r, inv);
+            cv[i] = o;
+        }
+    }
+}
+
+template <typename WT>
+static int launch_rmsnorm_reg(const int64_t* A, const WT* W, int64_t* rms_out, int64_t* C, int64_t M,
+                              int64_t N, int64_t eps, int64_t dim, cudaStream_t st)
+{
+    const int half = (int)(N >> 1);
+    const int per = (half + kRegThreads - 1) / kRegThreads;
+    const unsigned g = (unsigned)M;
+    if (per <= 1) rmsnorm_reg_kernel<WT, 1><<<g, kRegThreads, 0, st>>>(A, W, rms_out, C, half, eps, dim);
+    else if (per <= 2) rmsnorm_reg_kernel<WT, 2><<<g, kRegThreads, 0, st>>>(A, W, rms_out, C, half, eps, dim);
+    else if (per <= 4) rmsnorm_reg_kernel<WT, 4><<<g, kRegThreads, 0, st>>>(A, W, rms_out, C, half, eps, dim);
+    else rmsnorm_reg_kernel<WT, 8><<<g, kRegThreads, 0, st>>>(A, W, rms_out, C, half, eps, dim);
+    return check_launch();
+}
+
 template <typename WT>
 static int launch_rmsnorm_t(const int64_t* A, const WT* W, const int64_t* rms_in, int64_t* rms_out,
                             int64_t* C, int64_t M, int64_t N, int64_t eps, int64_t dim, bool fused,
                             cudaStream_t st)
 {
+    if (fused && (N & 1) == 0 && N <= 16 * kRegThreads && ((((uintptr_t)A | (uintptr_t)C) & 15) == 0) &&
+        !getenv("ZKDS_RMS_STAGED"))
+        return launch_rmsnorm_reg<WT>(A, W, rms_out, C, M, N, eps, dim, st);
     size_t row_bytes = (size_t)N * 8;
     bool stage = fused && row_bytes <= 200 * 1024 && !getenv("ZKDS_RMS_NOSTAGE");
     size_t smem = stage ? row_bytes : 0;

@@ -18,6 +18,12 @@ int launch_softmax(const int64_t* X, int64_t* Wout, int64_t* C, const int64_t* l
 // only those (causal attention with the masked scores left unwritten)
 int launch_softmax_causal(const int64_t* X, int64_t* C, const int64_t* lut, int64_t B, int64_t S, int64_t H,
                           int64_t T, int64_t start, cudaStream_t st);
+// Q19 softmax whose probabilities are written as signed 8-bit limb planes (row pitch Kp, limb l at
+// planes + l * plane_stride); valid_H > 0 restricts row (b, s, h) to columns <= valid_start + s
+bool softmax_planes_supported(const int64_t* X, int64_t rows, int64_t T, int64_t Kp);
+int launch_softmax_planes(const int64_t* X, const int64_t* lut, int8_t* planes, int L, int64_t rows, int64_t T,
+                          int64_t Kp, int64_t plane_stride, unsigned* overflow, unsigned long long* absmax_out,
+                          int64_t valid_H, int64_t valid_S, int64_t valid_start, cudaStream_t st);
 int launch_rope(const int64_t* A, const int64_t* Tb, int64_t* C, int64_t batch, int64_t S,
                 int64_t H, int64_t pairs, int shift, cudaStream_t st);
 int launch_rmsnorm(const int64_t* A, const void* W, int w_bits, const int64_t* rms_in,
@@ -73,6 +79,11 @@ struct Contraction {
     //          past that are not accumulated
     int skip_tiles, skip_k;
     int64_t skip_H, skip_start;
+    // A holds Q19 softmax inputs (rows of K scores, contiguous): the limb planes are produced from
+    // softmax(A) by the softmax kernel itself and the probabilities never reach memory as int64
+    // (limb kernel only; softmax_S = sequence positions per batch when skip_k is set)
+    const int64_t* softmax_lut;
+    int64_t softmax_S;
 };
 
 // CUDA-core path: exact for every input, any shape (gemm_exact.cu)

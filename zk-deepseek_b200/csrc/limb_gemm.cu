@@ -130,6 +130,86 @@ split_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, int64_
     }
 }
 
+// The k-contiguous case of split_kernel without any integer division: a CTA of 256 threads is a
+// (256 / tpr) x tpr grid, tpr = threads per row (a power of two), and walks whole rows; every
+// thread converts four consecutive k per step, two steps in flight.
+template <typename T, int LL>     // LL: limb count known at compile time, 0 = use L
+__global__ void __launch_bounds__(256)
+split_rows_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, int64_t rows, int64_t K,
+                  int64_t Kp, int64_t sz, int64_t sr, int64_t div, int64_t plane_stride,
+                  unsigned* overflow, unsigned long long* absmax_out, int64_t dst_pitch, int64_t valid_H,
+                  int64_t valid_start, int tpr_log2, unsigned nb, unsigned gx, int z_fast)
+{
+    uint64_t seen = 0;
+    bool ovf = false;
+    const int64_t quads = Kp >> 2;
+    // Work items are (batch, row group) pairs, gx row groups per batch, walked grid-stride.  z_fast:
+    // the batches are interleaved inside a source row (batch stride < row stride), so neighbouring
+    // items take neighbouring batches of the same rows and read one contiguous stretch.
+    const int tpr = 1 << tpr_log2;
+    const int lane_q = threadIdx.x & (tpr - 1);
+    const int64_t rpb = 256 >> tpr_log2;
+    const bool vec = sizeof(T) == 8 && ((((uintptr_t)X) & 15) == 0) && ((sr & 1) == 0) && ((sz & 1) == 0);
+    const unsigned items = nb * gx;
+    for (unsigned item = blockIdx.x; item < items; item += gridDim.x) {
+        const unsigned zi = z_fast ? item % nb : item / gx;
+        const unsigned bx = z_fast ? item / nb : item - zi * gx;
+        const int64_t z = zi;
+        const T* x = X + z * sz;
+        const int64_t r = (int64_t)bx * rpb + (threadIdx.x >> tpr_log2);
+        if (r >= rows) continue;
+        int64_t Kv = K;
+        if (valid_H) {
+            const int64_t lim = valid_start + r / valid_H + 1;
+            Kv = lim < K ? lim : K;
+        }
+        const T* xr = x + r * sr;
+        int8_t* drow = planes + (z * rows + r) * dst_pitch;
+#pragma unroll 2
+        for (int64_t qd = lane_q; qd < quads; qd += tpr) {
+            const int64_t k0 = qd << 2;
+            int64_t v[4];
+            if (k0 >= Kv) {
+                v[0] = v[1] = v[2] = v[3] = 0;
+            } else if (vec && k0 + 4 <= Kv) {
+                const longlong2* src = reinterpret_cast<const longlong2*>(xr + k0);
+                longlong2 a = src[0], b = src[1];
+                v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[j] = (k0 + j < Kv) ? (int64_t)xr[k0 + j] : 0;
+            }
+            constexpr int LMAX = LL ? LL : 9;
+            uint32_t w[LMAX];
+#pragma unroll
+            for (int l = 0; l < LMAX; ++l) w[l] = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                int64_t u = v[j];
+                if (div != 1) u = u / div;
+                const uint64_t a = (uint64_t)(u ^ (u >> 63));
+                seen = a > seen ? a : seen;
+#pragma unroll
+                for (int l = 0; l < LMAX; ++l) {
+                    if (LL || l < L) {
+                        w[l] |= (uint32_t)(u & 0xFF) << (j * 8);
+                        u = (u >> 8) + ((u >> 7) & 1);
+                    }
+                }
+                ovf |= (u != 0);
+            }
+#pragma unroll
+            for (int l = 0; l < LMAX; ++l)
+                if (LL || l < L) *reinterpret_cast<uint32_t*>(drow + k0 + l * plane_stride) = w[l];
+        }
+    }
+    if (ovf) *overflow = 1u;
+    if (absmax_out) {
+        seen = warp_max_u64(seen);
+        if ((threadIdx.x & 31) == 0 && seen) atomicMax(absmax_out, (unsigned long long)seen);
+    }
+}
+
 // ------------------------------------------------------------------------------------
 // PTX wrappers
 // ------------------------------------------------------------------------------------
@@ -172,11 +252,28 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
 
 constexpr uint32_t kSpinLimit = 1u << 22;
 
+// try_wait that lets the hardware park the thread for up to ~1 us instead of returning at once:
+// a waiting producer or MMA warp then takes no issue slots from the epilogue warps of its scheduler
+__device__ __forceinline__ bool mbar_try_parked(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(1000u)
+        : "memory");
+    return ok != 0;
+}
+
 // Bounded wait.  Returns false when the limit ran out or another role gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag)
 {
     for (uint32_t it = 0; it < kSpinLimit; ++it) {
-        if (mbar_try(bar, parity)) return true;
+        if (mbar_try_parked(bar, parity)) return true;
         if ((it & 255u) == 255u && *abort_flag) return false;
     }
     *abort_flag = 1;
@@ -223,6 +320,19 @@ __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t adesc, uint64_
         : "memory");
 }
 
+// accumulate flag known at compile time: no predicate set-up in the instruction stream
+__device__ __forceinline__ void umma_i8_acc(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc)
+{
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.eq.u32 p, 1, 1;\n"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n"
+        "}\n"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc)
+        : "memory");
+}
+
 __device__ __forceinline__ void umma_commit(uint32_t bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
@@ -238,6 +348,38 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, int32_t (&v)[8])
         : "memory");
 }
 
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, int32_t (&v)[4])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+                 : "r"(taddr)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_ldn(uint32_t taddr, int32_t (&v)[8]) { tmem_ld8(taddr, v); }
+__device__ __forceinline__ void tmem_ldn(uint32_t taddr, int32_t (&v)[4]) { tmem_ld4(taddr, v); }
+__device__ __forceinline__ void tmem_ldn(uint32_t taddr, int32_t (&v)[16])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ldn(uint32_t taddr, int32_t (&v)[12])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11])
+                 : "r"(taddr + 8u)
+                 : "memory");
+}
+
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ void tmem_st8_zero(uint32_t taddr)
@@ -246,6 +388,19 @@ __device__ __forceinline__ void tmem_st8_zero(uint32_t taddr)
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr), "r"(z)
         : "memory");
+}
+
+__device__ __forceinline__ void tmem_st4_zero(uint32_t taddr)
+{
+    const uint32_t z = 0;
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %1, %1, %1};" ::"r"(taddr), "r"(z) : "memory");
+}
+
+template <int CH>
+__device__ __forceinline__ void tmem_stn_zero(uint32_t taddr)
+{
+    if (CH == 8) tmem_st8_zero(taddr);
+    else tmem_st4_zero(taddr);
 }
 
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -262,6 +417,48 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr)
     return d;
 }
 
+// The MMAs of one K block (up to four K steps of 32 bytes, LA limb tiles of A against the stacked B
+// tile), straight-line: the descriptors differ from the block's first one only in the 14-bit
+// address field (units of 16 bytes), so each MMA costs one 32-bit add.  `first_accumulates` is 0 only
+// for the K block that opens a set of accumulators (its very first MMA then overwrites).
+template <int LA>
+__device__ __forceinline__ void issue_k_block(uint32_t acc, uint32_t nt_cols, uint32_t sa, uint32_t sb,
+                                              uint32_t idesc, uint32_t first_accumulates, int ks_n)
+{
+    const uint64_t hi = smem_desc_sw128(0) & 0xFFFFFFFF00000000ull;
+    const uint32_t lo_fixed = (uint32_t)(smem_desc_sw128(0) & 0xFFFFC000ull);
+    const uint32_t a_lo = lo_fixed | ((sa & 0x3FFFFu) >> 4);
+    const uint32_t b_lo = lo_fixed | ((sb & 0x3FFFFu) >> 4);
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+        if (ks < ks_n) {
+#pragma unroll
+            for (int i = 0; i < LA; ++i) {
+                const uint64_t adesc = hi | (uint64_t)(a_lo + (uint32_t)(i * ((128 * 128) >> 4) + ks * 2));
+                const uint64_t bdesc = hi | (uint64_t)(b_lo + (uint32_t)(ks * 2));
+                if (ks == 0 && i == 0) umma_i8(acc, adesc, bdesc, idesc, first_accumulates);
+                else umma_i8_acc(acc + (uint32_t)i * nt_cols, adesc, bdesc, idesc);
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void issue_k_block_n(int La, uint32_t acc, uint32_t nt_cols, uint32_t sa, uint32_t sb,
+                                                uint32_t idesc, uint32_t first_accumulates, int ks_n)
+{
+    switch (La) {
+    case 1: issue_k_block<1>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n); break;
+    case 2: issue_k_block<2>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n); break;
+    case 3: issue_k_block<3>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n); break;
+    case 4: issue_k_block<4>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n); break;
+    case 5: issue_k_block<5>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n); break;
+    case 6: issue_k_block<6>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n); break;
+    case 7: issue_k_block<7>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n); break;
+    case 8: issue_k_block<8>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n); break;
+    default: issue_k_block<9>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n); break;
+    }
+}
+
 // ------------------------------------------------------------------------------------
 // the kernel
 // ------------------------------------------------------------------------------------
@@ -273,6 +470,7 @@ constexpr int kThreads = 192;
 struct LimbParams {
     int La, Lb, NT, stages;
     int kblocks;
+    int64_t k_extent;         // K bytes per plane row (0 = unknown): a partial last K block issues fewer MMAs
     uint32_t tmem_cols;       // power of two >= (La + Lb - 1) * NT
     int64_t M, N, batches;
     int64_t a_rows_per_limb;  // batches * M
@@ -291,6 +489,14 @@ struct LimbParams {
     int k_switch, shift2;
     int64_t addend2;
     int nbuf;                 // accumulator buffers in tensor memory: 2 (ping-pong) or 1
+    // one buffer holding two sets: the epilogue hands the first set back as soon as it is drained,
+    // so the next tile's first-set MMAs overlap the rest of the epilogue
+    int split_release;
+    int wide_chunk;           // epilogue: fetch a warp's 12 or 16 columns with one wait instead of 4 or 8 at a time
+    // optional wait accounting (null = off): [0] MMA warp cycles waiting for operand stages, [1] for
+    // free accumulators, [2] MMA warp total, [3] first epilogue warp cycles waiting for accumulators,
+    // [4] its total, summed over CTAs
+    unsigned long long* wait_cycles;
     // causal skipping (optional): rows are (s, h) pairs with skip_H heads per sequence position s.
     //  skip_tiles: output tiles whose every column is beyond skip_start + s are not computed
     //              (the attention scores of masked positions are left unwritten);
@@ -345,41 +551,51 @@ __device__ __forceinline__ int64_t four_diagonals(int32_t a0, int32_t a1, int32_
     return mad_wide(a3, 1 << 24, mad_wide(a2, 1 << 16, mad_wide(a1, 1 << 8, (int64_t)a0)));
 }
 
-// One 8-column chunk of a tile whose sum fits 64 bits, diagonal count known at compile time:
-// every diagonal is fetched before the single wait and no absent diagonal costs anything.
-template <int DD>
-__device__ __forceinline__ void gather64_n(uint32_t taddr, int NT, int64_t addend, int64_t (&s)[8])
+// One chunk (CH = 8 or 4 columns) of a tile whose sum fits 64 bits, diagonal count known at
+// compile time: every diagonal is fetched before the single wait and no absent diagonal costs anything.
+struct NoHook {
+    __device__ __forceinline__ void operator()() const {}
+};
+
+// `after_loads` runs once the accumulators are in registers (before the arithmetic): the place to
+// hand the tensor-memory columns back
+template <int DD, int CH, typename Hook>
+__device__ __forceinline__ void gather64_n(uint32_t taddr, int NT, int64_t addend, int64_t (&s)[CH],
+                                           const Hook& after_loads)
 {
-    int32_t a[DD][8];
+    int32_t a[DD][CH];
 #pragma unroll
-    for (int d = 0; d < DD; ++d) tmem_ld8(taddr + (uint32_t)(d * NT), a[d]);
+    for (int d = 0; d < DD; ++d) tmem_ldn(taddr + (uint32_t)(d * NT), a[d]);
     tmem_ld_wait();
+    after_loads();
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-        int64_t lo = (int64_t)a[0][c];
+    for (int c = 0; c < CH; ++c) {
+        int64_t lo = mad_wide(a[0][c], 1, addend);
         if (DD > 1) lo = mad_wide(a[DD > 1 ? 1 : 0][c], 1 << 8, lo);
         if (DD > 2) lo = mad_wide(a[DD > 2 ? 2 : 0][c], 1 << 16, lo);
         if (DD > 3) lo = mad_wide(a[DD > 3 ? 3 : 0][c], 1 << 24, lo);
-        int64_t r = addend + lo;
         if (DD > 4) {
-            int64_t hi = (int64_t)a[DD > 4 ? 4 : 0][c];
-            if (DD > 5) hi = mad_wide(a[DD > 5 ? 5 : 0][c], 1 << 8, hi);
-            r += (int64_t)((uint64_t)hi << 32);
+            // diagonals 4 and 5 only reach the upper word
+            uint32_t hi = (uint32_t)a[DD > 4 ? 4 : 0][c];
+            if (DD > 5) hi += (uint32_t)a[DD > 5 ? 5 : 0][c] << 8;
+            lo = (int64_t)((uint64_t)lo + ((uint64_t)hi << 32));
         }
-        s[c] = r;
+        s[c] = lo;
     }
 }
 
 // false when the diagonal count has no compiled specialisation (caller uses the generic loop)
-__device__ __forceinline__ bool gather64(int D, uint32_t taddr, int NT, int64_t addend, int64_t (&s)[8])
+template <int CH, typename Hook>
+__device__ __forceinline__ bool gather64(int D, uint32_t taddr, int NT, int64_t addend, int64_t (&s)[CH],
+                                         const Hook& h)
 {
     switch (D) {
-    case 1: gather64_n<1>(taddr, NT, addend, s); return true;
-    case 2: gather64_n<2>(taddr, NT, addend, s); return true;
-    case 3: gather64_n<3>(taddr, NT, addend, s); return true;
-    case 4: gather64_n<4>(taddr, NT, addend, s); return true;
-    case 5: gather64_n<5>(taddr, NT, addend, s); return true;
-    case 6: gather64_n<6>(taddr, NT, addend, s); return true;
+    case 1: gather64_n<1, CH>(taddr, NT, addend, s, h); return true;
+    case 2: gather64_n<2, CH>(taddr, NT, addend, s, h); return true;
+    case 3: gather64_n<3, CH>(taddr, NT, addend, s, h); return true;
+    case 4: gather64_n<4, CH>(taddr, NT, addend, s, h); return true;
+    case 5: gather64_n<5, CH>(taddr, NT, addend, s, h); return true;
+    case 6: gather64_n<6, CH>(taddr, NT, addend, s, h); return true;
     default: return false;
     }
 }
@@ -641,15 +857,7 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t sa = smem_base + s * stage_bytes;
-                const uint64_t bdesc0 = smem_desc_sw128(sa + a_bytes);
-#pragma unroll
-                for (int ks = 0; ks < kBlockK / 32; ++ks) {
-                    for (int i = 0; i < La; ++i) {
-                        const uint64_t adesc = smem_desc_sw128(sa + i * (kTileM * kBlockK)) + (uint64_t)(ks * 2);
-                        umma_i8(tmem + (uint32_t)(i * p.NT), adesc, bdesc0 + (uint64_t)(ks * 2), idesc,
-                                (kb | ks | i) ? 1u : 0u);
-                    }
-                }
+                issue_k_block_n(La, tmem, (uint32_t)p.NT, sa, sa + a_bytes, idesc, kb ? 1u : 0u, kBlockK / 32);
                 umma_commit(bar_empty + 8 * s);
             }
             umma_commit(bar_accum);
@@ -699,11 +907,14 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 // run while eight epilogue warps drain tile t, the TMA pipeline keeps streaming across tile
 // boundaries, and the results leave through a shared-memory staging tile as whole rows
 // (coalesced 16-byte stores) instead of one 64-byte fragment per thread.
-constexpr int kPThreads = 320;   // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue
-constexpr int kEpiWarps = 8;
+// threads of the persistent kernel: warp 0 TMA, warp 1 MMA, then EW epilogue warps (8 or 16)
+constexpr int persistent_threads(int ew) { return 64 + 32 * ew; }
+// shared-memory staging of the epilogue warps for a tile NT columns wide
+constexpr size_t persistent_staging(int ew, int nt) { return (size_t)ew * 32 * ((nt / (ew / 4)) * 8 + 16); }
 
 struct TileCoord {
     int64_t z, m0, n0;
+    int group;       // grouped mode: the B batch of this row tile (negative: unused tile), else 0
 };
 
 __device__ __forceinline__ TileCoord decode_tile(const LimbParams& p, int64_t tile)
@@ -723,6 +934,7 @@ __device__ __forceinline__ TileCoord decode_tile(const LimbParams& p, int64_t ti
     c.z = zz;
     c.m0 = (int64_t)(panel * pm + (within - n_tile * rows_here)) * kTileM;
     c.n0 = (int64_t)n_tile * p.NT;
+    c.group = p.tile_group ? p.tile_group[panel * pm + (within - n_tile * rows_here)] : 0;
     return c;
 }
 
@@ -734,11 +946,63 @@ __device__ __forceinline__ bool tile_masked(const LimbParams& p, const TileCoord
     return c.n0 > p.skip_start + last_row / p.skip_H;
 }
 
-// one epilogue warp: rows 32 q .. 32 q + 31 of the tile, columns [c0, c0 + CW) of it
-template <bool FITS64>
+// quotients of one chunk of columns: (addend + sum_d acc_d * 2^(8 d)) >> shift, taddr = first column
+// of diagonal 0 of the set
+template <bool FITS64, int CH, typename Hook>
+__device__ __forceinline__ void chunk_quotient(int D, uint32_t taddr, int NT, int64_t addend, int shift,
+                                               int64_t (&cv)[CH], const Hook& after_loads)
+{
+    i128w sum[CH];
+    int64_t s64[CH];
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+        if (FITS64) s64[c] = addend;
+        else sum[c] = make_i128(addend);
+    }
+    const bool done64 = FITS64 && gather64<CH>(D, taddr, NT, addend, s64, after_loads);
+    for (int d0 = 0, g = 0; !done64 && d0 < D; d0 += 4, ++g) {
+        int32_t a[4][CH];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (d0 + j < D) tmem_ldn(taddr + (uint32_t)((d0 + j) * NT), a[j]);
+            else {
+#pragma unroll
+                for (int c = 0; c < CH; ++c) a[j][c] = 0;
+            }
+        }
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            const int64_t v = four_diagonals(a[0][c], a[1][c], a[2][c], a[3][c]);
+            if (FITS64) {
+                s64[c] += g ? (int64_t)((uint64_t)v << 32) : v;
+            } else {
+                i128w t;  // v * 2^(32 g)
+                if (g == 0) { t.lo = (uint64_t)v; t.hi = v >> 63; }
+                else if (g == 1) { t.lo = (uint64_t)v << 32; t.hi = v >> 32; }
+                else if (g == 2) { t.lo = 0; t.hi = v; }
+                else { t.lo = 0; t.hi = (int64_t)((uint64_t)v << 32); }
+                sum[c] = add128(sum[c], t);
+            }
+        }
+        if (d0 + 4 >= D) after_loads();
+    }
+    const int sh64 = shift >= 63 ? 63 : shift;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+        if (FITS64) cv[c] = s64[c] >> sh64;
+        else cv[c] = sar128_lo(sum[c], shift);
+    }
+}
+
+// One epilogue warp: rows 32 q .. 32 q + 31 of the tile, columns [c0, c0 + CW) of it, CH columns per
+// step.  With two sets of diagonals the first set is drained completely (its quotients parked in the
+// staging rows) before the second is touched; release_bar != 0 hands the first set back to the MMA
+// warp at that point, so the next tile's first-set MMAs run under the rest of this epilogue.
+template <bool FITS64, int CH>
 __device__ __forceinline__ void epilogue_part(const LimbParams& p, uint32_t tq, int D, const TileCoord& tc,
                                               int q, int lane, int c0, int CW, uint8_t* stage, int RS,
-                                              int set_cols)
+                                              int set_cols, uint32_t release_bar)
 {
     const int64_t m = tc.m0 + q * 32 + lane;
     const bool tail = p.addin || p.ep_div || p.causal_H;
@@ -751,7 +1015,7 @@ __device__ __forceinline__ void epilogue_part(const LimbParams& p, uint32_t tq, 
     while (lanes_per_row * 2 < CW) lanes_per_row <<= 1;
     const int rows_per_it = 32 / lanes_per_row;
     const int rl = lane / lanes_per_row, cl = (lane % lanes_per_row) * 2;
-    const int sh64 = p.shift >= 63 ? 63 : p.shift;
+    const bool two = p.k_switch != 0;
 
     if (p.addin) {
         // bring this warp's part of the addin tile in as whole rows; the 16-byte copies are
@@ -777,97 +1041,56 @@ __device__ __forceinline__ void epilogue_part(const LimbParams& p, uint32_t tq, 
         __syncwarp();
     }
 
-    for (int nc = 0; nc < CW; nc += 8) {
-        i128w sum[8];
-        int64_t s64[8];
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            if (FITS64) s64[c] = p.addend;
-            else sum[c] = make_i128(p.addend);
-        }
-        const bool done64 = FITS64 && gather64(D, tq + (uint32_t)(c0 + nc), p.NT, p.addend, s64);
-        for (int d0 = 0, g = 0; !done64 && d0 < D; d0 += 4, ++g) {
-            int32_t a[4][8];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (d0 + j < D) tmem_ld8(tq + (uint32_t)((d0 + j) * p.NT + c0 + nc), a[j]);
-                else {
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) a[j][c] = 0;
-                }
-            }
-            tmem_ld_wait();
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const int64_t v = four_diagonals(a[0][c], a[1][c], a[2][c], a[3][c]);
-                if (FITS64) {
-                    s64[c] += g ? (int64_t)((uint64_t)v << 32) : v;
-                } else {
-                    i128w t;  // v * 2^(32 g)
-                    if (g == 0) { t.lo = (uint64_t)v; t.hi = v >> 63; }
-                    else if (g == 1) { t.lo = (uint64_t)v << 32; t.hi = v >> 32; }
-                    else if (g == 2) { t.lo = 0; t.hi = v; }
-                    else { t.lo = 0; t.hi = (int64_t)((uint64_t)v << 32); }
-                    sum[c] = add128(sum[c], t);
-                }
-            }
-        }
-        int64_t cv[8];
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            if (FITS64) cv[c] = s64[c] >> sh64;
-            else cv[c] = sar128_lo(sum[c], p.shift);
-        }
-        if (p.k_switch) {
-            // second set of diagonals: its own addend and shift, then the two quotients add up
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                if (FITS64) s64[c] = p.addend2;
-                else sum[c] = make_i128(p.addend2);
-            }
-            const bool done2 = FITS64 && gather64(D, tq + (uint32_t)(set_cols + c0 + nc), p.NT, p.addend2, s64);
-            for (int d0 = 0, g = 0; !done2 && d0 < D; d0 += 4, ++g) {
-                int32_t a[4][8];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    if (d0 + j < D) tmem_ld8(tq + (uint32_t)(set_cols + (d0 + j) * p.NT + c0 + nc), a[j]);
-                    else {
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) a[j][c] = 0;
-                    }
-                }
-                tmem_ld_wait();
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const int64_t v = four_diagonals(a[0][c], a[1][c], a[2][c], a[3][c]);
-                    if (FITS64) {
-                        s64[c] += g ? (int64_t)((uint64_t)v << 32) : v;
-                    } else {
-                        i128w t;
-                        if (g == 0) { t.lo = (uint64_t)v; t.hi = v >> 63; }
-                        else if (g == 1) { t.lo = (uint64_t)v << 32; t.hi = v >> 32; }
-                        else if (g == 2) { t.lo = 0; t.hi = v; }
-                        else { t.lo = 0; t.hi = (int64_t)((uint64_t)v << 32); }
-                        sum[c] = add128(sum[c], t);
-                    }
-                }
-            }
-            const int sh2 = p.shift2 >= 63 ? 63 : p.shift2;
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const int64_t v2 = FITS64 ? (s64[c] >> sh2) : sar128_lo(sum[c], p.shift2);
-                cv[c] = (int64_t)((uint64_t)cv[c] + (uint64_t)v2);
-            }
-        }
+    // hands the first set back: re-zero the columns no first-step MMA initialises, then arrive
+    auto release_first = [&]() {
+        for (int d = p.Lb; d < D; ++d)
+            for (int c = 0; c < CW; c += 4) tmem_st4_zero(tq + (uint32_t)(d * p.NT + c0 + c));
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(release_bar);
+    };
+    // one chunk covers this warp's columns: the set can go back as soon as its accumulators are in
+    // registers, before any arithmetic
+    const bool early = two && release_bar && CH == CW;
+    for (int nc = 0; nc < CW; nc += CH) {
+        int64_t cv[CH];
+        // grouped mode: the shift belongs to the group and to the side of n_split the chunk lies on
+        // (n_split and every chunk start are multiples of 4, a chunk never straddles it when CH <= 8)
+        const int shift = p.group_shift ? p.group_shift[2 * tc.group + (nbase + nc >= p.n_split ? 1 : 0)] : p.shift;
+        if (early) chunk_quotient<FITS64, CH>(D, tq + (uint32_t)(c0 + nc), p.NT, p.addend, shift, cv, release_first);
+        else chunk_quotient<FITS64, CH>(D, tq + (uint32_t)(c0 + nc), p.NT, p.addend, shift, cv, NoHook());
         int64_t* srow_ptr = reinterpret_cast<int64_t*>(stage + lane * RS + nc * 8);
-        if (tail) {
+        if (tail && !two) {
 #pragma unroll
-            for (int c = 0; c < 8; ++c)
+            for (int c = 0; c < CH; ++c)
                 cv[c] = score_tail(p, cv[c], p.addin ? srow_ptr + c : nullptr, nbase + nc + c, srow);
         }
 #pragma unroll
-        for (int c = 0; c < 8; c += 2)
+        for (int c = 0; c < CH; c += 2)
             *reinterpret_cast<longlong2*>(srow_ptr + c) = make_longlong2(cv[c], cv[c + 1]);
+    }
+    if (two) {
+        if (release_bar && !early) release_first();
+        // second set of diagonals: its own addend and shift, then the two quotients add up
+        for (int nc = 0; nc < CW; nc += CH) {
+            int64_t v2[CH];
+            chunk_quotient<FITS64, CH>(D, tq + (uint32_t)(set_cols + c0 + nc), p.NT, p.addend2, p.shift2, v2, NoHook());
+            int64_t* srow_ptr = reinterpret_cast<int64_t*>(stage + lane * RS + nc * 8);
+#pragma unroll
+            for (int c = 0; c < CH; c += 2) {
+                const longlong2 v1 = *reinterpret_cast<const longlong2*>(srow_ptr + c);
+                v2[c] = (int64_t)((uint64_t)v2[c] + (uint64_t)v1.x);
+                v2[c + 1] = (int64_t)((uint64_t)v2[c + 1] + (uint64_t)v1.y);
+            }
+            if (tail) {
+#pragma unroll
+                for (int c = 0; c < CH; ++c) v2[c] = score_tail(p, v2[c], nullptr, nbase + nc + c, srow);
+            }
+#pragma unroll
+            for (int c = 0; c < CH; c += 2)
+                *reinterpret_cast<longlong2*>(srow_ptr + c) = make_longlong2(v2[c], v2[c + 1]);
+        }
     }
     __syncwarp();
     // write the staged rows out, whole rows at a time
@@ -892,7 +1115,8 @@ __device__ __forceinline__ void epilogue_part(const LimbParams& p, uint32_t tq, 
     __syncwarp();
 }
 
-__global__ void __launch_bounds__(kPThreads, 1)
+template <int EW>
+__global__ void __launch_bounds__(persistent_threads(EW), 1)
 limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                             const LimbParams p)
 {
@@ -917,11 +1141,14 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
     const uint32_t bar_full = smem_u32(&bars[0]);
     const uint32_t bar_empty = smem_u32(&bars[8]);
     const uint32_t bar_tfull = smem_u32(&bars[16]);    // [2]: accumulators of a tile complete
-    const uint32_t bar_tempty = smem_u32(&bars[18]);   // [2]: buffer drained and re-zeroed
+    // [2]: buffer b drained and re-zeroed; with split_release (one buffer, two sets) [0] is the
+    // first set and [1] the second
+    const uint32_t bar_tempty = smem_u32(&bars[18]);
     const int set_cols = (p.La + p.Lb - 1) * p.NT;     // one set of diagonals
     const int nsets = p.k_switch ? 2 : 1;
     const int buf_cols = nsets * set_cols;             // spacing of the two accumulator buffers
     const int64_t n_tiles_total = p.batches * p.m_tiles * p.n_tiles;
+    const bool split = p.split_release != 0;
 
     if (threadIdx.x == 0) {
         s_abort = 0;
@@ -931,7 +1158,7 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar_tfull + 8 * b, 1);
-            mbar_init(bar_tempty + 8 * b, kEpiWarps);
+            mbar_init(bar_tempty + 8 * b, EW);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -952,7 +1179,8 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             for (int64_t tile = blockIdx.x; ok && tile < n_tiles_total; tile += gridDim.x) {
                 const TileCoord tc = decode_tile(p, tile);
                 if (p.skip_tiles && tile_masked(p, tc)) continue;
-                const int64_t zb = p.b_batched ? tc.z : 0;
+                if (tc.group < 0) continue;
+                const int64_t zb = p.tile_group ? tc.group : (p.b_batched ? tc.z : 0);
                 for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
                     const int s = (int)(it % p.stages);
                     const uint32_t par = (uint32_t)((it / p.stages) & 1) ^ 1u;
@@ -984,77 +1212,141 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                                    ((uint32_t)((p.Lb * p.NT) >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
             int64_t it = 0, t = 0;
             bool ok = true;
+            const bool prof = p.wait_cycles != nullptr;
+            long long w_full = 0, w_empty = 0, t_begin = prof ? clock64() : 0, t0 = 0;
             for (int64_t tile = blockIdx.x; ok && tile < n_tiles_total; tile += gridDim.x) {
-                if (p.skip_tiles && tile_masked(p, decode_tile(p, tile))) continue;
+                if (p.skip_tiles || p.tile_group) {
+                    const TileCoord tcm = decode_tile(p, tile);
+                    if (tcm.group < 0 || (p.skip_tiles && tile_masked(p, tcm))) continue;
+                }
                 const int b = (int)(t % p.nbuf);
-                ok = mbar_wait(bar_tempty + 8 * b, (uint32_t)((t / p.nbuf) & 1), abort_flag);
+                const uint32_t tpar = (uint32_t)((t / p.nbuf) & 1);
+                if (prof) t0 = clock64();
+                ok = mbar_wait(bar_tempty + 8 * b, tpar, abort_flag);
+                if (prof) w_empty += clock64() - t0;
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t acc = tmem + (uint32_t)(b * buf_cols);
                 for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
                     const int s = (int)(it % p.stages);
+                    const bool second = p.k_switch && kb >= p.k_switch;
+                    if (split && kb == p.k_switch) {
+                        // the second set is still being drained by the previous tile's epilogue
+                        if (prof) t0 = clock64();
+                        ok = mbar_wait(bar_tempty + 8, tpar, abort_flag);
+                        if (prof) w_empty += clock64() - t0;
+                        if (!ok) break;
+                        tc_fence_after();
+                    }
+                    if (prof) t0 = clock64();
                     ok = mbar_wait(bar_full + 8 * s, (uint32_t)((it / p.stages) & 1), abort_flag);
+                    if (prof) w_full += clock64() - t0;
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t sa = smem_base + s * stage_bytes;
-                    const uint64_t bdesc0 = smem_desc_sw128(sa + a_bytes);
-                    const bool second = p.k_switch && kb >= p.k_switch;
                     const uint32_t acc_set = acc + (second ? (uint32_t)set_cols : 0u);
                     const int kb_first = second ? p.k_switch : 0;     // first K block of this set
-#pragma unroll
-                    for (int ks = 0; ks < kBlockK / 32; ++ks) {
-                        for (int i = 0; i < La; ++i) {
-                            const uint64_t adesc = smem_desc_sw128(sa + i * (kTileM * kBlockK)) + (uint64_t)(ks * 2);
-                            umma_i8(acc_set + (uint32_t)(i * p.NT), adesc, bdesc0 + (uint64_t)(ks * 2), idesc,
-                                    ((kb - kb_first) | ks | i) ? 1u : 0u);
-                        }
+                    // a partial last K block: the copy zero-fills it, no need to multiply the zeros
+                    int ks_n = kBlockK / 32;
+                    if (p.k_extent) {
+                        const int64_t left = p.k_extent - (int64_t)kb * kBlockK;
+                        if (left < kBlockK) ks_n = (int)((left + 31) >> 5);
                     }
+                    issue_k_block_n(La, acc_set, (uint32_t)p.NT, sa, sa + a_bytes, idesc,
+                                    kb != kb_first ? 1u : 0u, ks_n);
                     umma_commit(bar_empty + 8 * s);
                 }
                 if (ok) umma_commit(bar_tfull + 8 * b);
                 ++t;
             }
+            if (prof) {
+                atomicAdd(p.wait_cycles + 0, (unsigned long long)w_full);
+                atomicAdd(p.wait_cycles + 1, (unsigned long long)w_empty);
+                atomicAdd(p.wait_cycles + 2, (unsigned long long)(clock64() - t_begin));
+            }
         }
     } else {
         // ---- epilogue warps: zero the buffers, then drain tile after tile -------------------------
+        constexpr int NPART = EW / 4;           // warps sharing one lane quarter split the columns
         const int ew = warp - 2;
         const int q = warp & 3;                 // tensor-memory lane quarter of this warp
-        const int half = ew >> 2;               // which half of the tile's columns
-        const int CW = p.NT / 2, c0 = half * CW;
+        const int part = ew >> 2;
+        const int CW = p.NT / NPART, c0 = part * CW;
+        const bool ch8 = (CW & 7) == 0;
+        const int CH = ch8 ? 8 : 4;
         const int RS = CW * 8 + 16;             // staged row stride (padded against bank conflicts)
         uint8_t* stage = smem_raw + ((smem_base - smem_u32(smem_raw)) + (uint32_t)p.stages * stage_bytes) +
                          (size_t)ew * 32 * RS;
         const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
-        // columns no first-step MMA initialises: [Lb * NT, D * NT) of each buffer, this warp's half
-        for (int b = 0; b < p.nbuf; ++b) {
-            for (int st = 0; st < nsets; ++st)
-                for (int d = p.Lb; d < D; ++d)
-                    for (int c = 0; c < CW; c += 8)
-                        tmem_st8_zero(lane_base + (uint32_t)(b * buf_cols + st * set_cols + d * p.NT + c0 + c));
-            tmem_st_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
+        // columns no first-step MMA initialises: [Lb * NT, D * NT) of each set, this warp's part
+        auto zero_set = [&](uint32_t set_base) {
+            for (int d = p.Lb; d < D; ++d)
+                for (int c = 0; c < CW; c += CH) {
+                    if (ch8) tmem_st8_zero(set_base + (uint32_t)(d * p.NT + c0 + c));
+                    else tmem_st4_zero(set_base + (uint32_t)(d * p.NT + c0 + c));
+                }
+        };
+        if (split) {
+            for (int st = 0; st < 2; ++st) {
+                zero_set(lane_base + (uint32_t)(st * set_cols));
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_tempty + 8 * st);
+            }
+        } else {
+            for (int b = 0; b < p.nbuf; ++b) {
+                for (int st = 0; st < nsets; ++st) zero_set(lane_base + (uint32_t)(b * buf_cols + st * set_cols));
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
+            }
         }
         int64_t t = 0;
+        const bool prof = p.wait_cycles != nullptr && ew == 0 && lane == 0;
+        long long w_acc = 0, t_begin = prof ? clock64() : 0, t0 = 0;
         for (int64_t tile = blockIdx.x; tile < n_tiles_total; tile += gridDim.x) {
             const TileCoord tc = decode_tile(p, tile);
             if (p.skip_tiles && tile_masked(p, tc)) continue;
+            if (tc.group < 0) {
+                // unused row tile: its output is defined as zero (later passes scan the whole buffer)
+                for (int i = ew * 32 + lane; i < kTileM * p.NT; i += EW * 32) {
+                    const int64_t r = tc.m0 + i / p.NT, c = tc.n0 + i % p.NT;
+                    if (r < p.M && c < p.N) p.C[r * p.c_sm + c] = 0;
+                }
+                continue;
+            }
             const int b = (int)(t % p.nbuf);
+            if (prof) t0 = clock64();
             if (!mbar_wait(bar_tfull + 8 * b, (uint32_t)((t / p.nbuf) & 1), abort_flag)) break;
+            if (prof) w_acc += clock64() - t0;
             tc_fence_after();
             const uint32_t tq = lane_base + (uint32_t)(b * buf_cols);
-            if (p.fits64) epilogue_part<true>(p, tq, D, tc, q, lane, c0, CW, stage, RS, set_cols);
-            else epilogue_part<false>(p, tq, D, tc, q, lane, c0, CW, stage, RS, set_cols);
-            for (int st = 0; st < nsets; ++st)
-                for (int d = p.Lb; d < D; ++d)
-                    for (int c = 0; c < CW; c += 8)
-                        tmem_st8_zero(tq + (uint32_t)(st * set_cols + d * p.NT + c0 + c));
+            const uint32_t rel = split ? bar_tempty : 0u;
+            if (p.fits64) {
+                const bool wide = p.wide_chunk && !p.group_shift;   // a wide chunk could straddle n_split
+                if (EW != 12 && wide && (CW == 12 || CW == 24))
+                    epilogue_part<true, 12>(p, tq, D, tc, q, lane, c0, CW, stage, RS, set_cols, rel);
+                else if (EW == 12 && wide && CW == 16)
+                    epilogue_part<true, 16>(p, tq, D, tc, q, lane, c0, CW, stage, RS, set_cols, rel);
+                else if (ch8) epilogue_part<true, 8>(p, tq, D, tc, q, lane, c0, CW, stage, RS, set_cols, rel);
+                else epilogue_part<true, 4>(p, tq, D, tc, q, lane, c0, CW, stage, RS, set_cols, rel);
+            } else {
+                if (ch8) epilogue_part<false, 8>(p, tq, D, tc, q, lane, c0, CW, stage, RS, set_cols, rel);
+                else epilogue_part<false, 4>(p, tq, D, tc, q, lane, c0, CW, stage, RS, set_cols, rel);
+            }
+            // the set(s) this epilogue did not hand back itself
+            for (int st = split ? 1 : 0; st < nsets; ++st) zero_set(tq + (uint32_t)(st * set_cols));
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * (split ? 1 : b));
             ++t;
+        }
+        if (prof) {
+            atomicAdd(p.wait_cycles + 3, (unsigned long long)w_acc);
+            atomicAdd(p.wait_cycles + 4, (unsigned long long)(clock64() - t_begin));
         }
     }
 
@@ -1141,6 +1433,30 @@ int launch_split_t(const T* X, int8_t* planes, int L, int64_t nb, int64_t rows, 
     int64_t cap = (int64_t)sm_count() * 32;
     if (bx > cap) bx = cap;
     if (nb > 65535) return ZKDS_ERR_RANGE;
+    if (sk == 1 && !getenv("ZKDS_SPLIT_GENERIC")) {
+        int tl = 0;
+        while (tl < 8 && (1 << tl) < (Kp >> 2)) ++tl;
+        const int64_t rpb = 256 >> tl;
+        const int64_t gx = (rows + rpb - 1) / rpb;        // row groups per batch
+        if (gx * nb > 0x7fffffffll) return ZKDS_ERR_RANGE;   // the kernel's 32-bit item counter cannot wrap
+        const int z_fast = (nb > 1 && sz < sr) ? 1 : 0;
+        int64_t blocks = gx * nb;
+        if (blocks > cap) blocks = cap;
+        dim3 g2((unsigned)blocks);
+#define ZKDS_SPLIT_ROWS(LL)                                                                              \
+    split_rows_kernel<T, LL><<<g2, 256, 0, st>>>(X, planes, L, rows, K, Kp, sz, sr, div,                  \
+                                                 nb * rows * dst_pitch, overflow, absmax_out, dst_pitch, \
+                                                 valid_H, valid_start, tl, (unsigned)nb, (unsigned)gx, z_fast)
+        switch (L) {
+        case 2: ZKDS_SPLIT_ROWS(2); break;
+        case 3: ZKDS_SPLIT_ROWS(3); break;
+        case 4: ZKDS_SPLIT_ROWS(4); break;
+        case 5: ZKDS_SPLIT_ROWS(5); break;
+        default: ZKDS_SPLIT_ROWS(0); break;
+        }
+#undef ZKDS_SPLIT_ROWS
+        return check_launch();
+    }
     dim3 grid((unsigned)bx, (unsigned)nb);
     split_kernel<T><<<grid, 256, 0, st>>>(X, planes, L, rows, K, Kp, sz, sr, sk, div, nb * rows * dst_pitch,
                                           overflow, absmax_out, dst_pitch, valid_H, valid_start);
@@ -1270,6 +1586,64 @@ int planes_split(const void* X, int bits, int64_t nb, int64_t rows, int64_t K, i
     return ZKDS_ERR_ARG;
 }
 
+// Epilogue warps of the persistent kernel.  Measured on a B200: the fused attention scores (48-column
+// tile, two sets of five diagonals) run best with 12 warps (three per tensor-memory lane quarter, 16
+// columns each, fetched with one wait); plain contractions show no gain beyond 8, which also keeps
+// 168 registers per thread.  ZKDS_EPI_WARPS = 8 | 12 | 16 overrides for experiments.
+static int persistent_epilogue_warps(bool fused_scores)
+{
+    if (const char* e = getenv("ZKDS_EPI_WARPS")) {
+        const int v = atoi(e);
+        if (v == 8 || v == 12 || v == 16) return v;
+    }
+    return fused_scores ? 12 : 8;
+}
+
+static int launch_persistent(int ew, int ctas, size_t smem, cudaStream_t st, const CUtensorMap& tmA,
+                             const CUtensorMap& tmB, const LimbParams& lp_in)
+{
+    LimbParams lp = lp_in;
+    lp.wide_chunk = lp.split_release;          // the early hand-back needs the one-wait fetch
+    if (getenv("ZKDS_EPI_WIDE")) lp.wide_chunk = atoi(getenv("ZKDS_EPI_WIDE"));
+    // ZKDS_WAIT_PROFILE=1: a synchronous diagnostic run that prints where the MMA warp and the first
+    // epilogue warp spent their cycles (share of their lifetime spent waiting)
+    unsigned long long* prof = nullptr;
+    if (getenv("ZKDS_WAIT_PROFILE")) {
+        prof = (unsigned long long*)workspace(8 * sizeof(unsigned long long), 4);
+        if (prof) ZKDS_CUDA(cudaMemsetAsync(prof, 0, 8 * sizeof(unsigned long long), st));
+        lp.wait_cycles = prof;
+    }
+    struct Report {
+        unsigned long long* d; cudaStream_t st; const LimbParams* lp;
+        ~Report()
+        {
+            if (!d) return;
+            unsigned long long h[8];
+            if (cudaStreamSynchronize(st) != cudaSuccess) return;
+            if (cudaMemcpy(h, d, sizeof(h), cudaMemcpyDeviceToHost) != cudaSuccess) return;
+            fprintf(stderr, "persistent M=%lld N=%lld kblocks=%d NT=%d nbuf=%d split=%d: MMA warp waits operands "
+                            "%.1f%% accumulators %.1f%%; epilogue warp waits accumulators %.1f%%\n",
+                    (long long)lp->M, (long long)lp->N, lp->kblocks, lp->NT, lp->nbuf, lp->split_release,
+                    100.0 * h[0] / (h[2] ? h[2] : 1), 100.0 * h[1] / (h[2] ? h[2] : 1),
+                    100.0 * h[3] / (h[4] ? h[4] : 1));
+        }
+    } report{prof, st, &lp};
+    if (ew == 12) {
+        ZKDS_CUDA(cudaFuncSetAttribute(limb_gemm_persistent_kernel<12>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)(227 * 1024 - 3072)));
+        limb_gemm_persistent_kernel<12><<<ctas, persistent_threads(12), smem, st>>>(tmA, tmB, lp);
+    } else if (ew == 16) {
+        ZKDS_CUDA(cudaFuncSetAttribute(limb_gemm_persistent_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)(227 * 1024 - 3072)));
+        limb_gemm_persistent_kernel<16><<<ctas, persistent_threads(16), smem, st>>>(tmA, tmB, lp);
+    } else {
+        ZKDS_CUDA(cudaFuncSetAttribute(limb_gemm_persistent_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)(227 * 1024 - 3072)));
+        limb_gemm_persistent_kernel<8><<<ctas, persistent_threads(8), smem, st>>>(tmA, tmB, lp);
+    }
+    return check_launch();
+}
+
 int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* pre_b, cudaStream_t st)
 {
     if (pre_b) Lb = pre_b->L;
@@ -1281,17 +1655,27 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     // tile width: the B stack must fit one MMA (<= 256 columns), the diagonals tensor memory
     // (<= 512 columns), and two pipeline stages shared memory
     const size_t smem_max = 227 * 1024 - 4096;  // static barriers + alignment slack stay below the opt-in limit
+    // An MMA of M = 128 takes as long as one 256 columns wide, so the B stack (Lb * NT columns) should
+    // come close to 256; among the widths that fit, take the one that wastes the least of that time
+    // (narrow stack) and of the last column tile (padding).
     int NT = 0;
-    for (int cand : {128, 64, 32, 16}) {
+    double best = 0.0;
+    for (int cand : {16, 32, 48, 64, 80, 96, 112, 128}) {     // ties go to the narrower tile
         if (Lb * cand > 256 || D * cand > 512) continue;
         size_t stage = (size_t)La * kTileM * kBlockK + (size_t)Lb * cand * kBlockK;
         if (smem_max / stage < 2) continue;
-        NT = cand;
-        break;
+        const int64_t tiles = (p.N + cand - 1) / cand;
+        double score = ((double)p.N / (double)(tiles * cand)) * ((double)(Lb * cand) / 256.0);
+        if (smem_max / stage < 3) score *= 0.97;      // prefer three pipeline stages when it is close
+        if (score > best * 1.02) { best = score; NT = cand; }
+    }
+    if (const char* e = getenv("ZKDS_TILE_NT")) {       // experiments: force a width that fits
+        const int want = atoi(e);
+        if (want >= 16 && want % 16 == 0 && Lb * want <= 256 && D * want <= 512 &&
+            smem_max / ((size_t)La * kTileM * kBlockK + (size_t)Lb * want * kBlockK) >= 2)
+            NT = want;
     }
     if (!NT) return ZKDS_ERR_UNSUPPORTED;
-    // shrink the tile for narrow outputs (fewer wasted columns)
-    while (NT > 16 && p.N <= NT / 2) NT /= 2;
     const size_t stage = (size_t)La * kTileM * kBlockK + (size_t)Lb * NT * kBlockK;
     int stages = (int)(smem_max / stage);
     if (stages > 8) stages = 8;
@@ -1308,12 +1692,14 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     bool persistent = false;
     int pNT = 0, pstages = 0;
     size_t psmem = 0;
-    if (!p.tile_group && !p.R && !p.group_shift && !p.skip_k && (Kp + kBlockK - 1) / kBlockK <= 16 &&
-        !getenv("ZKDS_NO_PERSISTENT")) {
+    int ew = persistent_epilogue_warps(false);
+    if (ew == 12) ew = 16;          // three warps per lane quarter only divide a 48-column tile
+    if (!p.R && !p.skip_k && (Kp + kBlockK - 1) / kBlockK <= 16 && !getenv("ZKDS_NO_PERSISTENT") &&
+        !(p.tile_group && getenv("ZKDS_NO_PERSISTENT_GROUPED"))) {
         for (int cand : {64, 48, 32, 16}) {
             if (Lb * cand > 256 || 2 * D * cand > 512) continue;
             size_t st_b = (size_t)La * kTileM * kBlockK + (size_t)Lb * cand * kBlockK;
-            size_t staging = (size_t)kEpiWarps * 32 * ((cand / 2) * 8 + 16);
+            size_t staging = persistent_staging(ew, cand);
             if (smem_max < staging + 1024) continue;
             int ns = (int)((smem_max - staging - 1024) / st_b);
             if (ns < 2) continue;
@@ -1331,7 +1717,7 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
             if (want != pNT) {
                 pNT = want;
                 size_t st_b = (size_t)La * kTileM * kBlockK + (size_t)Lb * pNT * kBlockK;
-                size_t staging = (size_t)kEpiWarps * 32 * ((pNT / 2) * 8 + 16);
+                size_t staging = persistent_staging(ew, pNT);
                 int ns = (int)((smem_max - staging - 1024) / st_b);
                 pstages = ns > 8 ? 8 : ns;
                 psmem = st_b * pstages + staging + 1024;
@@ -1353,7 +1739,13 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
         ZKDS_CUDA(cudaMemsetAsync(d_absmax, 0, sizeof(uint64_t), st));
     }
     const int64_t Kp16 = Kp;
-    int rc = launch_split_t<int64_t>(p.A, pa, La, p.batches, p.M, p.K, Kp16, p.a_sz, p.a_sm, 1, p.a_div,
+    int rc;
+    if (p.softmax_lut) {
+        if (p.a_sm != p.K || p.a_sz != p.M * p.K || p.a_div != 1) return ZKDS_ERR_ARG;
+        rc = launch_softmax_planes(p.A, p.softmax_lut, pa, La, a_rows, p.K, Kp, a_rows * Kp, fl->overflow_dev,
+                                   d_absmax, p.skip_k ? p.skip_H : 0, p.softmax_S, p.skip_start, st);
+    } else
+        rc = launch_split_t<int64_t>(p.A, pa, La, p.batches, p.M, p.K, Kp16, p.a_sz, p.a_sm, 1, p.a_div,
                                      fl->overflow_dev, st, d_absmax, 0, p.skip_k ? p.skip_H : 0, p.skip_start);
     if (rc != ZKDS_OK) return rc;
     int8_t* pb;
@@ -1372,6 +1764,7 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     LimbParams lp{};
     lp.La = La; lp.Lb = Lb; lp.NT = NT; lp.stages = stages;
     lp.kblocks = (int)((Kp + kBlockK - 1) / kBlockK);
+    lp.k_extent = Kp;
     uint32_t cols = 32;
     while (cols < (uint32_t)((persistent ? 2 : 1) * D * NT)) cols <<= 1;
     lp.tmem_cols = cols;
@@ -1409,17 +1802,16 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     cudaEvent_t* ev = timing_events();
     if (ev) ZKDS_CUDA(cudaEventRecord(ev[0], st));
     if (persistent) {
-        ZKDS_CUDA(cudaFuncSetAttribute(limb_gemm_persistent_kernel,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024 - 3072)));
         if (psmem < 120 * 1024) psmem = 120 * 1024;
         int64_t total_tiles = p.batches * mt * nt_eff;
         if (total_tiles > 0x7fffffffll) return ZKDS_ERR_UNSUPPORTED;
         int ctas = sm_count();
         if (total_tiles < ctas) ctas = (int)total_tiles;
-        limb_gemm_persistent_kernel<<<ctas, kPThreads, psmem, st>>>(tmA, tmB, lp);
-    } else
+        rc = launch_persistent(ew, ctas, psmem, st, tmA, tmB, lp);
+    } else {
         limb_gemm_kernel<<<grid, kThreads, smem, st>>>(tmA, tmB, lp);
-    rc = check_launch();
+        rc = check_launch();
+    }
     if (ev) ZKDS_CUDA(cudaEventRecord(ev[1], st));
     if (ev && g_accumulate && rc == ZKDS_OK) {
         // profiling pass: wait for the kernel, add its duration and the int8 work it issued
@@ -1471,15 +1863,20 @@ int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st)
     // buffers only if the tile can still be 32 columns wide, else one buffer with the widest tile.
     int NT = 0, stages = 0, nbuf = 0;
     size_t smem = 0;
+    const int ew_pref = persistent_epilogue_warps(true);
+    int ew = ew_pref;
     for (int bufs : {2, 1}) {
         for (int cand : {64, 48, 32, 16}) {
             if (bufs == 2 && cand < 32) continue;
             if (Lb * cand > 256 || 2 * bufs * D * cand > 512) continue;
+            // three warps per lane quarter only divide a 48-column tile
+            const int ew_c = (ew_pref == 12 && cand != 48) ? 16 : ew_pref;
             size_t st_b = (size_t)La * kTileM * kBlockK + (size_t)Lb * cand * kBlockK;
-            size_t staging = (size_t)kEpiWarps * 32 * ((cand / 2) * 8 + 16);
+            size_t staging = persistent_staging(ew_c, cand);
             int ns = (int)((smem_max - staging - 1024) / st_b);
             if (ns < 2) continue;
             NT = cand;
+            ew = ew_c;
             nbuf = bufs;
             stages = ns > 8 ? 8 : ns;
             smem = st_b * stages + staging + 1024;
@@ -1528,10 +1925,12 @@ int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st)
     lp.La = La; lp.Lb = Lb; lp.NT = NT; lp.stages = stages;
     lp.k_switch = (int)(f.K1 / kBlockK);
     lp.kblocks = lp.k_switch + (int)((Kp2 + kBlockK - 1) / kBlockK);
+    lp.k_extent = pitch;
     uint32_t cols = 32;
     while (cols < (uint32_t)(2 * nbuf * D * NT)) cols <<= 1;
     lp.tmem_cols = cols;
     lp.nbuf = nbuf;
+    lp.split_release = (nbuf == 1 && !getenv("ZKDS_NO_SPLIT_RELEASE")) ? 1 : 0;
     lp.M = f.M; lp.N = f.N; lp.batches = f.batches;
     lp.a_rows_per_limb = a_rows; lp.b_rows_per_limb = b_rows;
     lp.b_batched = 1;
@@ -1550,16 +1949,13 @@ int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st)
     if (panel > mt) panel = mt;
     lp.m_tiles = mt; lp.n_tiles = nt; lp.panel_m = panel;
 
-    ZKDS_CUDA(cudaFuncSetAttribute(limb_gemm_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (int)(227 * 1024 - 3072)));
     if (smem < 120 * 1024) smem = 120 * 1024;
     const int64_t total_tiles = f.batches * mt * nt;
     int ctas = sm_count();
     if (total_tiles < ctas) ctas = (int)total_tiles;
     cudaEvent_t* ev = timing_events();
     if (ev) ZKDS_CUDA(cudaEventRecord(ev[0], st));
-    limb_gemm_persistent_kernel<<<ctas, kPThreads, smem, st>>>(tmA, tmB, lp);
-    rc = check_launch();
+    rc = launch_persistent(ew, ctas, smem, st, tmA, tmB, lp);
     if (ev) ZKDS_CUDA(cudaEventRecord(ev[1], st));
     if (ev && g_accumulate && rc == ZKDS_OK) {
         float ms = 0.f;

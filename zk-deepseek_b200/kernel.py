@@ -98,6 +98,7 @@ _sig("zkds_einsum_bshc_btc_bsht_ex", [_vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _l
 _sig("zkds_mla_scores", [_vp, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _i, _ll, _ll,
                          _i, _i, _i, _vp])
 _sig("zkds_softmax_causal", [_vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _vp])
+_sig("zkds_softmax_pv", [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _i, _ll, _i, _i, _i, _vp])
 _sig("zkds_einsum_bsht_btc_bshc_causal", [_vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _i, _i, _i, _vp])
 _sig("zkds_grouped_prepared", [_vp, _vp, _vp, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _i, _i, _vp])
 _sig("zkds_glu_q23", [_vp, _vp, _ll, _vp, _vp, _vp, _ll, _ll, _vp])
@@ -441,6 +442,31 @@ def softmax_q19_causal(R, C, start_pos=0):
         return False
     _check(rc, "softmax_q19_causal")
     return True
+
+
+def softmax_pv_fused(scores, kv, rescale=23, causal_skip=False, start_pos=0, a_limbs=0, b_limbs=0,
+                     dynamic=False):
+    """einsum_bsht_btc_bshc(softmax_q19(scores), kv, rescale) in one call: scores [B, S, H, T], kv
+    [B, T, C] -> [B, S, H, C] (model.py:911-926).  The probabilities go from the softmax kernel straight
+    into the limb planes of the contraction and are never stored as int64; `scores` is not modified.
+    causal_skip: only columns t <= start_pos + s of a row are read.  Returns None when the kernel does
+    not take the shape (use softmax_q19 and the einsum then)."""
+    _dev_i64(scores, "scores")
+    _dev_i64(kv, "kv")
+    Bn, S, H, T = scores.shape
+    Cd = kv.shape[2]
+    assert Bn == kv.shape[0] and T == kv.shape[1]
+    lut = _lut_on(EXP2_FRAC_LUT_Q19, scores.device, "softmax_init_q19")
+    out = torch.empty((Bn, S, H, Cd), dtype=torch.int64, device=scores.device)
+    flags = ALGO_LIMB | (LIMBS_DYNAMIC if dynamic else 0)
+    with torch.cuda.device(scores.device):
+        rc = lib.zkds_softmax_pv(scores.data_ptr(), kv.data_ptr(), out.data_ptr(), lut.data_ptr(), int(rescale),
+                                 Bn, S, H, T, Cd, 1 if causal_skip else 0, int(start_pos), a_limbs, b_limbs,
+                                 flags, _stream())
+    if rc == 6:
+        return None
+    _check(rc, "softmax_pv_fused")
+    return out
 
 
 def einsum_bsht_btc_bshc_causal(A, B, rescale, start_pos=0, a_limbs=3, b_limbs=0):

@@ -411,6 +411,10 @@ class MLA(nn.Module):
                                         self.softmax_scale2, causal=causal, a_limbs=al, b_limbs=bl, dynamic=dyn,
                                         skip_masked=skip)
             if scores is not None and skip:
+                ctx = K.softmax_pv_fused(scores, kv_all, 23, causal_skip=True, start_pos=0, a_limbs=3, b_limbs=bl)
+                if ctx is not None:
+                    del scores
+                    return self._finish(ctx, lim)
                 probs = torch.empty_like(scores)
                 if K.softmax_q19_causal(scores, probs, 0):
                     del scores
@@ -431,6 +435,12 @@ class MLA(nn.Module):
             scores += mask.unsqueeze(1)
         if snark:
             saveTensor(f"{d}/scores_softmax_x.bin", scores)
+        elif K.ALGO != K.ALGO_EXACT:
+            # softmax and P . KV in one call: the probabilities only ever exist as int8 limb planes
+            ctx = K.softmax_pv_fused(scores, kv_all, 23, a_limbs=3, b_limbs=bl)
+            if ctx is not None:
+                del scores
+                return self._finish(ctx, lim)
         probs = torch.empty_like(scores)
         K.softmax_q19(scores, probs)
         del scores
