@@ -360,15 +360,21 @@ int zkds_mla_scores(const int64_t* q_abs, const int64_t* kv, const int64_t* q_pe
     if (a_limbs <= 0 || b_limbs <= 0) {
         uint64_t* d = (uint64_t*)workspace(8 * sizeof(uint64_t), 5);
         if (!d) return finish(ZKDS_ERR_WORKSPACE, "zkds_mla_scores");
-        int rc = set_cuda_error(cudaMemsetAsync(d, 0, 2 * sizeof(uint64_t), st));
+        int rc = set_cuda_error(cudaMemsetAsync(d, 0, 3 * sizeof(uint64_t), st));
         if (rc == ZKDS_OK) rc = launch_absmax(q_abs, 64, B, S * H, C1, S * H * C1, C1, 1, 1, d, st);
-        if (rc == ZKDS_OK) rc = launch_absmax(q_pe, 64, B, S * H, C2, S * H * C2, C2, 1, 1, d, st);
+        if (rc == ZKDS_OK) rc = launch_absmax(q_pe, 64, B, S * H, C2, S * H * C2, C2, 1, 1, d + 2, st);
         if (rc == ZKDS_OK) rc = launch_absmax(kv, 64, B, T, C1, T * C1, C1, 1, 1, d + 1, st);
         if (rc == ZKDS_OK) rc = launch_absmax(pe, 64, B, T, C2, T * C2, C2, 1, 1, d + 1, st);
-        uint64_t h[2] = {0, 0};
+        uint64_t h[3] = {0, 0, 0};
         if (rc == ZKDS_OK) rc = set_cuda_error(cudaMemcpyAsync(h, d, sizeof(h), cudaMemcpyDeviceToHost, st));
         if (rc == ZKDS_OK) rc = set_cuda_error(cudaStreamSynchronize(st));
         if (rc != ZKDS_OK) return finish(rc, "zkds_mla_scores");
+        // the kernel may scale q_pe by 2^(rescale1 - rescale2) while splitting it (one shared set of
+        // accumulators): the limbs have to hold the scaled values
+        const int64_t dl = rescale1 - rescale2;
+        uint64_t pe_max = h[2];
+        if (dl > 0 && dl <= 8) pe_max = (pe_max >> (63 - dl)) ? ~0ull : ((pe_max + 1) << dl);
+        if (pe_max > h[0]) h[0] = pe_max;
         if (a_limbs <= 0) { a_limbs = limbs_needed(h[0]); flags &= ~ZKDS_LIMBS_DYNAMIC; }
         if (b_limbs <= 0) b_limbs = limbs_needed(h[1]);
     }

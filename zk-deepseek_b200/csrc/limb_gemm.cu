@@ -138,7 +138,7 @@ __global__ void __launch_bounds__(256)
 split_rows_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, int64_t rows, int64_t K,
                   int64_t Kp, int64_t sz, int64_t sr, int64_t div, int64_t plane_stride,
                   unsigned* overflow, unsigned long long* absmax_out, int64_t dst_pitch, int64_t valid_H,
-                  int64_t valid_start, int tpr_log2, unsigned nb, unsigned gx, int z_fast)
+                  int64_t valid_start, int tpr_log2, unsigned nb, unsigned gx, int z_fast, int shl)
 {
     uint64_t seen = 0;
     bool ovf = false;
@@ -187,6 +187,11 @@ split_rows_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, i
             for (int j = 0; j < 4; ++j) {
                 int64_t u = v[j];
                 if (div != 1) u = u / div;
+                if (shl) {
+                    const int64_t w2 = (int64_t)((uint64_t)u << shl);
+                    ovf |= (w2 >> shl) != u;      // the scaled value must still be the value
+                    u = w2;
+                }
                 const uint64_t a = (uint64_t)(u ^ (u >> 63));
                 seen = a > seen ? a : seen;
 #pragma unroll
@@ -459,6 +464,22 @@ __device__ __forceinline__ void issue_k_block_n(int La, uint32_t acc, uint32_t n
     }
 }
 
+// Merged dual accumulation, second part only: limb i of A against the lowest E - i limb tiles of the B
+// stack lands on diagonals i .. E-1 of the extra set (a handful of MMAs per tile, so a plain loop).
+__device__ __forceinline__ void issue_extra_block(int La, int E, uint32_t acc_extra, uint32_t nt_cols, uint32_t sa,
+                                                  uint32_t sb, uint32_t idesc, bool opens_set, int ks_n)
+{
+    for (int ks = 0; ks < ks_n; ++ks) {
+        for (int i = 0; i < La && i < E; ++i) {
+            const uint32_t n_i = (uint32_t)(E - i) * nt_cols;
+            const uint32_t idesc_i = (idesc & ~(0x3Fu << 17)) | ((n_i >> 3) << 17);
+            const uint64_t adesc = smem_desc_sw128(sa + (uint32_t)i * (128u * 128u)) + (uint64_t)(ks * 2);
+            const uint64_t bdesc = smem_desc_sw128(sb) + (uint64_t)(ks * 2);
+            umma_i8(acc_extra + (uint32_t)i * nt_cols, adesc, bdesc, idesc_i, (opens_set && ks == 0 && i == 0) ? 0u : 1u);
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------
 // the kernel
 // ------------------------------------------------------------------------------------
@@ -492,6 +513,12 @@ struct LimbParams {
     // one buffer holding two sets: the epilogue hands the first set back as soon as it is drained,
     // so the next tile's first-set MMAs overlap the rest of the epilogue
     int split_release;
+    // merged dual accumulation: the second part's operand A was scaled by 2^(shift - shift2) while it
+    // was split, so both parts accumulate into ONE set of diagonals T = S1 + 2^(shift-shift2) S2; the
+    // second part's lowest merged_E diagonals (all that matter modulo 2^shift) are accumulated once
+    // more into a small extra set right of the main one, which yields the carry that separates
+    // floor((S1+a1)/2^shift) + floor((S2+a2)/2^shift2) from floor((T+a1+2^(shift-shift2) a2)/2^shift)
+    int merged_E;
     int wide_chunk;           // epilogue: fetch a warp's 12 or 16 columns with one wait instead of 4 or 8 at a time
     // optional wait accounting (null = off): [0] MMA warp cycles waiting for operand stages, [1] for
     // free accumulators, [2] MMA warp total, [3] first epilogue warp cycles waiting for accumulators,
@@ -609,6 +636,19 @@ struct EpilogueCtx {
     bool row_ok, vec_ok;
 };
 
+// floor(v * 94 / 695) for |v| < 2^42 (MLA's softmax scale, model.py:897): double estimate of the
+// quotient (the product is below 2^49, exact in a double; the estimate is within one of the floor),
+// exact remainder correction.  One straight-line path for every realistic score.
+__device__ __forceinline__ int64_t scale_94_695(int64_t v)
+{
+    const int64_t t = v * 94;
+    int64_t q = __double2ll_rd((double)t * (1.0 / 695.0));
+    int64_t r = t - q * 695;
+    if (r < 0) { --q; r += 695; }
+    if (r >= 695) ++q;
+    return q;
+}
+
 // element-wise tail of the attention scores: v += *arow (the addin element, if any);
 // v = floor(v * mul / div); causal mask for column n of sequence row srow
 __device__ __forceinline__ int64_t score_tail(const LimbParams& p, int64_t v, const int64_t* arow,
@@ -616,15 +656,11 @@ __device__ __forceinline__ int64_t score_tail(const LimbParams& p, int64_t v, co
 {
     if (arow) v = (int64_t)((uint64_t)v + (uint64_t)*arow);
     if (p.ep_div) {
-        if (p.ep_mul == 94 && p.ep_div == 695) {  // MLA's softmax scale: constant divisor
-            if ((uint64_t)(v + (1 << 24)) < (uint64_t)(1 << 25)) {
-                // |v| < 2^24 (any realistic Q19 score): 32-bit multiply and constant division
-                const int32_t t = (int32_t)v * 94;
-                const int32_t qd = t / 695;
-                v = (int64_t)((t - qd * 695 < 0) ? qd - 1 : qd);
-            } else {
-                int64_t t = (int64_t)((uint64_t)v * 94ull);
-                int64_t qd = t / 695;
+        if (p.ep_mul == 94 && p.ep_div == 695) {
+            if ((uint64_t)(v + (1ll << 42)) < (uint64_t)(1ll << 43)) v = scale_94_695(v);
+            else {
+                const int64_t t = (int64_t)((uint64_t)v * 94ull);
+                const int64_t qd = t / 695;
                 v = (t - qd * 695 < 0) ? qd - 1 : qd;
             }
         } else
@@ -1050,14 +1086,17 @@ __device__ __forceinline__ void epilogue_part(const LimbParams& p, uint32_t tq, 
         __syncwarp();
         if (lane == 0) mbar_arrive(release_bar);
     };
-    // one chunk covers this warp's columns: the set can go back as soon as its accumulators are in
-    // registers, before any arithmetic
-    const bool early = two && release_bar && CH == CW;
+    // the first set can go back as soon as the accumulators of this warp's last chunk are in
+    // registers, before the arithmetic on them
+#pragma unroll 1
     for (int nc = 0; nc < CW; nc += CH) {
+        const bool early = two && release_bar && nc + CH >= CW;
         int64_t cv[CH];
         // grouped mode: the shift belongs to the group and to the side of n_split the chunk lies on
         // (n_split and every chunk start are multiples of 4, a chunk never straddles it when CH <= 8)
-        const int shift = p.group_shift ? p.group_shift[2 * tc.group + (nbase + nc >= p.n_split ? 1 : 0)] : p.shift;
+        // merged mode parks the unshifted total; the shift follows once the carry is known
+        const int shift = p.merged_E ? 0
+                          : (p.group_shift ? p.group_shift[2 * tc.group + (nbase + nc >= p.n_split ? 1 : 0)] : p.shift);
         if (early) chunk_quotient<FITS64, CH>(D, tq + (uint32_t)(c0 + nc), p.NT, p.addend, shift, cv, release_first);
         else chunk_quotient<FITS64, CH>(D, tq + (uint32_t)(c0 + nc), p.NT, p.addend, shift, cv, NoHook());
         int64_t* srow_ptr = reinterpret_cast<int64_t*>(stage + lane * RS + nc * 8);
@@ -1071,17 +1110,34 @@ __device__ __forceinline__ void epilogue_part(const LimbParams& p, uint32_t tq, 
             *reinterpret_cast<longlong2*>(srow_ptr + c) = make_longlong2(cv[c], cv[c + 1]);
     }
     if (two) {
-        if (release_bar && !early) release_first();
+
         // second set of diagonals: its own addend and shift, then the two quotients add up
+#pragma unroll 1
         for (int nc = 0; nc < CW; nc += CH) {
             int64_t v2[CH];
-            chunk_quotient<FITS64, CH>(D, tq + (uint32_t)(set_cols + c0 + nc), p.NT, p.addend2, p.shift2, v2, NoHook());
             int64_t* srow_ptr = reinterpret_cast<int64_t*>(stage + lane * RS + nc * 8);
+            if (p.merged_E) {
+                // r2 = (scaled second sum + its addend) mod 2^shift from the extra diagonals; the parked
+                // total T' carries both addends: quotient = (T' >> shift) - [T' mod 2^shift < r2]
+                chunk_quotient<FITS64, CH>(p.merged_E, tq + (uint32_t)(set_cols + c0 + nc), p.NT, p.addend2, 0, v2,
+                                           NoHook());
+                const uint32_t mask = (1u << p.shift) - 1u;
 #pragma unroll
-            for (int c = 0; c < CH; c += 2) {
-                const longlong2 v1 = *reinterpret_cast<const longlong2*>(srow_ptr + c);
-                v2[c] = (int64_t)((uint64_t)v2[c] + (uint64_t)v1.x);
-                v2[c + 1] = (int64_t)((uint64_t)v2[c + 1] + (uint64_t)v1.y);
+                for (int c = 0; c < CH; c += 2) {
+                    const longlong2 t = *reinterpret_cast<const longlong2*>(srow_ptr + c);
+                    const uint32_t r0 = (uint32_t)v2[c] & mask, r1 = (uint32_t)v2[c + 1] & mask;
+                    v2[c] = (t.x >> p.shift) - (((uint32_t)t.x & mask) < r0 ? 1 : 0);
+                    v2[c + 1] = (t.y >> p.shift) - (((uint32_t)t.y & mask) < r1 ? 1 : 0);
+                }
+            } else {
+                chunk_quotient<FITS64, CH>(D, tq + (uint32_t)(set_cols + c0 + nc), p.NT, p.addend2, p.shift2, v2,
+                                           NoHook());
+#pragma unroll
+                for (int c = 0; c < CH; c += 2) {
+                    const longlong2 v1 = *reinterpret_cast<const longlong2*>(srow_ptr + c);
+                    v2[c] = (int64_t)((uint64_t)v2[c] + (uint64_t)v1.x);
+                    v2[c + 1] = (int64_t)((uint64_t)v2[c + 1] + (uint64_t)v1.y);
+                }
             }
             if (tail) {
 #pragma unroll
@@ -1244,8 +1300,9 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t sa = smem_base + s * stage_bytes;
-                    const uint32_t acc_set = acc + (second ? (uint32_t)set_cols : 0u);
-                    const int kb_first = second ? p.k_switch : 0;     // first K block of this set
+                    const bool merged = p.merged_E != 0;
+                    const uint32_t acc_set = acc + ((second && !merged) ? (uint32_t)set_cols : 0u);
+                    const int kb_first = (second && !merged) ? p.k_switch : 0;     // first K block of this set
                     // a partial last K block: the copy zero-fills it, no need to multiply the zeros
                     int ks_n = kBlockK / 32;
                     if (p.k_extent) {
@@ -1254,6 +1311,9 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                     }
                     issue_k_block_n(La, acc_set, (uint32_t)p.NT, sa, sa + a_bytes, idesc,
                                     kb != kb_first ? 1u : 0u, ks_n);
+                    if (merged && second)
+                        issue_extra_block(La, p.merged_E, acc + (uint32_t)set_cols, (uint32_t)p.NT, sa, sa + a_bytes,
+                                          idesc, kb == p.k_switch, ks_n);
                     umma_commit(bar_empty + 8 * s);
                 }
                 if (ok) umma_commit(bar_tfull + 8 * b);
@@ -1288,7 +1348,8 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
         };
         if (split) {
             for (int st = 0; st < 2; ++st) {
-                zero_set(lane_base + (uint32_t)(st * set_cols));
+                // the extra set of the merged mode is written in full by its first MMA
+                if (!(st == 1 && p.merged_E)) zero_set(lane_base + (uint32_t)(st * set_cols));
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
@@ -1337,7 +1398,8 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                 else epilogue_part<false, 4>(p, tq, D, tc, q, lane, c0, CW, stage, RS, set_cols, rel);
             }
             // the set(s) this epilogue did not hand back itself
-            for (int st = split ? 1 : 0; st < nsets; ++st) zero_set(tq + (uint32_t)(st * set_cols));
+            for (int st = split ? 1 : 0; st < nsets; ++st)
+                if (!(st == 1 && p.merged_E)) zero_set(tq + (uint32_t)(st * set_cols));
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
@@ -1425,7 +1487,7 @@ template <typename T>
 int launch_split_t(const T* X, int8_t* planes, int L, int64_t nb, int64_t rows, int64_t K, int64_t Kp,
                    int64_t sz, int64_t sr, int64_t sk, int64_t div, unsigned* overflow, cudaStream_t st,
                    unsigned long long* absmax_out = nullptr, int64_t dst_pitch = 0, int64_t valid_H = 0,
-                   int64_t valid_start = 0)
+                   int64_t valid_start = 0, int shl = 0)
 {
     if (dst_pitch == 0) dst_pitch = Kp;
     int64_t total = rows * (Kp >> 2);
@@ -1446,7 +1508,7 @@ int launch_split_t(const T* X, int8_t* planes, int L, int64_t nb, int64_t rows, 
 #define ZKDS_SPLIT_ROWS(LL)                                                                              \
     split_rows_kernel<T, LL><<<g2, 256, 0, st>>>(X, planes, L, rows, K, Kp, sz, sr, div,                  \
                                                  nb * rows * dst_pitch, overflow, absmax_out, dst_pitch, \
-                                                 valid_H, valid_start, tl, (unsigned)nb, (unsigned)gx, z_fast)
+                                                 valid_H, valid_start, tl, (unsigned)nb, (unsigned)gx, z_fast, shl)
         switch (L) {
         case 2: ZKDS_SPLIT_ROWS(2); break;
         case 3: ZKDS_SPLIT_ROWS(3); break;
@@ -1457,6 +1519,7 @@ int launch_split_t(const T* X, int8_t* planes, int L, int64_t nb, int64_t rows, 
 #undef ZKDS_SPLIT_ROWS
         return check_launch();
     }
+    if (shl) return ZKDS_ERR_UNSUPPORTED;        // only the k-contiguous kernel scales
     dim3 grid((unsigned)bx, (unsigned)nb);
     split_kernel<T><<<grid, 256, 0, st>>>(X, planes, L, rows, K, Kp, sz, sr, sk, div, nb * rows * dst_pitch,
                                           overflow, absmax_out, dst_pitch, valid_H, valid_start);
@@ -1603,7 +1666,7 @@ static int launch_persistent(int ew, int ctas, size_t smem, cudaStream_t st, con
                              const CUtensorMap& tmB, const LimbParams& lp_in)
 {
     LimbParams lp = lp_in;
-    lp.wide_chunk = lp.split_release;          // the early hand-back needs the one-wait fetch
+    lp.wide_chunk = 0;
     if (getenv("ZKDS_EPI_WIDE")) lp.wide_chunk = atoi(getenv("ZKDS_EPI_WIDE"));
     // ZKDS_WAIT_PROFILE=1: a synchronous diagnostic run that prints where the MMA warp and the first
     // epilogue warp spent their cycles (share of their lifetime spent waiting)
@@ -1743,7 +1806,7 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     if (p.softmax_lut) {
         if (p.a_sm != p.K || p.a_sz != p.M * p.K || p.a_div != 1) return ZKDS_ERR_ARG;
         rc = launch_softmax_planes(p.A, p.softmax_lut, pa, La, a_rows, p.K, Kp, a_rows * Kp, fl->overflow_dev,
-                                   d_absmax, p.skip_k ? p.skip_H : 0, p.softmax_S, p.skip_start, st);
+                                   d_absmax, p.skip_k ? p.skip_H : 0, p.softmax_S, p.skip_start, fl->dev, st);
     } else
         rc = launch_split_t<int64_t>(p.A, pa, La, p.batches, p.M, p.K, Kp16, p.a_sz, p.a_sm, 1, p.a_div,
                                      fl->overflow_dev, st, d_absmax, 0, p.skip_k ? p.skip_H : 0, p.skip_start);
@@ -1865,10 +1928,24 @@ int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st)
     size_t smem = 0;
     const int ew_pref = persistent_epilogue_warps(true);
     int ew = ew_pref;
+    // Merged mode (see LimbParams::merged_E): one set of D diagonals plus E low diagonals of the
+    // second part instead of two full sets, so the tile can be wider (8 x 64 instead of 10 x 48 columns
+    // of tensor memory for 3 x 3 limbs): fewer, wider MMAs and less operand traffic per output.
+    const int delta = f.shift1 - f.shift2;
+    int E = 0;
+    const int64_t Kp2m = (f.K2 + 15) & ~(int64_t)15;
+    if (delta >= 0 && delta <= 8 && f.shift1 >= 1 && f.shift1 <= 31 && !getenv("ZKDS_NO_MERGED")) {
+        const int e = (f.shift1 + 7) / 8;
+        const int64_t a12 = f.addend1 + (int64_t)((uint64_t)f.addend2 << delta);
+        if (e <= Lb && e <= D && f.addend1 >= 0 && f.addend2 >= 0 && f.addend2 < (1ll << 40) &&
+            (int64_t)pairs * (f.K1 + Kp2m) < 131072 && sum_fits64(La, Lb, f.K1 + f.K2, a12))
+            E = e;
+    }
     for (int bufs : {2, 1}) {
         for (int cand : {64, 48, 32, 16}) {
             if (bufs == 2 && cand < 32) continue;
-            if (Lb * cand > 256 || 2 * bufs * D * cand > 512) continue;
+            if (E && bufs == 2) continue;                       // merged mode: one buffer, early hand-back
+            if (Lb * cand > 256 || (E ? (D + E) : 2 * bufs * D) * cand > 512) continue;
             // three warps per lane quarter only divide a 48-column tile
             const int ew_c = (ew_pref == 12 && cand != 48) ? 16 : ew_pref;
             size_t st_b = (size_t)La * kTileM * kBlockK + (size_t)Lb * cand * kBlockK;
@@ -1908,7 +1985,7 @@ int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st)
                                      fl->overflow_dev, st, d_absmax, pitch);
     if (rc == ZKDS_OK)
         rc = launch_split_t<int64_t>(f.A2, pa + f.K1, La, f.batches, f.M, f.K2, Kp2, f.M * f.K2, f.K2, 1, 1,
-                                     fl->overflow_dev, st, d_absmax, pitch);
+                                     fl->overflow_dev, st, d_absmax, pitch, 0, 0, E ? delta : 0);
     if (rc == ZKDS_OK)
         rc = launch_split_t<int64_t>(f.B1, pb, Lb, f.batches, f.N, f.K1, f.K1, f.N * f.K1, f.K1, 1, 1,
                                      fl->overflow_dev, st, nullptr, pitch);
@@ -1927,10 +2004,11 @@ int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st)
     lp.kblocks = lp.k_switch + (int)((Kp2 + kBlockK - 1) / kBlockK);
     lp.k_extent = pitch;
     uint32_t cols = 32;
-    while (cols < (uint32_t)(2 * nbuf * D * NT)) cols <<= 1;
+    while (cols < (uint32_t)((E ? (D + E) : 2 * nbuf * D) * NT)) cols <<= 1;
     lp.tmem_cols = cols;
     lp.nbuf = nbuf;
-    lp.split_release = (nbuf == 1 && !getenv("ZKDS_NO_SPLIT_RELEASE")) ? 1 : 0;
+    lp.split_release = (nbuf == 1 && (E || !getenv("ZKDS_NO_SPLIT_RELEASE"))) ? 1 : 0;
+    lp.merged_E = E;
     lp.M = f.M; lp.N = f.N; lp.batches = f.batches;
     lp.a_rows_per_limb = a_rows; lp.b_rows_per_limb = b_rows;
     lp.b_batched = 1;
@@ -1939,6 +2017,12 @@ int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st)
     lp.r_legacy = 0;
     lp.error_flag = fl->dev;
     lp.fits64 = sum_fits64(La, Lb, Kmax, f.addend1) && sum_fits64(La, Lb, Kmax, f.addend2);
+    if (E) {
+        // the parked total carries both addends; the extra set only the scaled second one
+        lp.addend2 = (int64_t)((uint64_t)f.addend2 << delta);
+        lp.addend = f.addend1 + lp.addend2;
+        lp.fits64 = 1;
+    }
     lp.a_absmax = d_absmax;
     lp.overflow_flag = fl->overflow_dev;
     lp.ep_mul = f.ep_mul; lp.ep_div = f.ep_div;
