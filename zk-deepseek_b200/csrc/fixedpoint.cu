@@ -414,80 +414,25 @@ static int launch_softmax_q19_reg(const int64_t* X, int64_t* Wout, int64_t* C, c
 // operand of the tensor-core contraction that consumes them) instead of int64 words: plane l of row
 // r lives at planes + l * plane_stride + r * Kp.  Balanced radix-256 digits as in the limb split;
 // columns from `valid` (or T) up to Kp are written as zero.  E = groups of four columns per thread.
-// STREAM: a persistent CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; thread 0 keeps `ns` rows
-// ahead in flight as bulk asynchronous copies into a shared-memory ring (one mbarrier per slot), so the
-// DRAM latency of a row is paid while earlier rows are being worked on.  Every wait is bounded; a wait
-// that runs out sets *error_flag and the CTA leaves.
-template <int E, int LL, bool STREAM>      // LL: limb count known at compile time, 0 = use L
+template <int E, int LL>      // LL: limb count known at compile time, 0 = use L
 __global__ void __launch_bounds__(kThreads)
 softmax_q19_planes_kernel(const int64_t* X, const int64_t* __restrict__ lut_g, int8_t* __restrict__ planes,
                           int L, int T, int64_t Kp, int64_t plane_stride, unsigned* overflow,
-                          unsigned long long* absmax_out, int valid_H, int valid_S, int valid_start,
-                          int64_t rows, int ns, int* error_flag)
+                          unsigned long long* absmax_out, int valid_H, int valid_S, int valid_start)
 {
-    extern __shared__ __align__(128) unsigned char ring_raw[];
-    __shared__ __align__(8) uint64_t full_bar[4];
     __shared__ uint32_t lut[256];
     __shared__ int64_t red[32];
     __shared__ uint64_t s_magic;
     for (int i = threadIdx.x; i < 256; i += kThreads) lut[i] = (uint32_t)lut_g[i];
-    const int quads_all = (int)(Kp >> 2);
-    const uint32_t row_bytes = (uint32_t)T * 8u;
-    uint32_t seen = 0;
-    bool ovf = false;
-
-    auto valid_of = [&](int64_t row) {
-        if (!valid_H) return T;
-        const int sidx = (int)(((uint64_t)row / (unsigned)valid_H) % (unsigned)valid_S);
-        return valid_start + sidx + 1 < T ? valid_start + sidx + 1 : T;
-    };
-    // bytes of a row worth copying: its valid prefix, rounded up to the 16-byte granule of the copy
-    auto copy_bytes = [&](int64_t row) { return (uint32_t)(((valid_of(row) + 3) >> 2) * 32); };
-    auto issue_copy = [&](int64_t row, int slot) {
-        const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&full_bar[slot]);
-        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(ring_raw + (size_t)slot * row_bytes);
-        const uint32_t bytes = copy_bytes(row);
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                     ::"r"(dst), "l"(X + row * T), "r"(bytes), "r"(bar)
-                     : "memory");
-    };
-    if (STREAM) {
-        if (threadIdx.x == 0) {
-            for (int i = 0; i < ns; ++i)
-                asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&full_bar[i])));
-            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            for (int i = 0; i < ns; ++i) {
-                const int64_t row = (int64_t)blockIdx.x + (int64_t)i * gridDim.x;
-                if (row < rows) issue_copy(row, i);
-            }
-        }
-        __syncthreads();
+    const longlong2* xv = reinterpret_cast<const longlong2*>(X + (int64_t)blockIdx.x * T);
+    int8_t* drow = planes + (int64_t)blockIdx.x * Kp;
+    int valid = T;
+    if (valid_H) {
+        const int sidx = (int)((blockIdx.x / (unsigned)valid_H) % (unsigned)valid_S);
+        valid = valid_start + sidx + 1 < T ? valid_start + sidx + 1 : T;
     }
-
-    int64_t it = 0;
-    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, ++it) {
-    const int slot = STREAM ? (int)(it % ns) : 0;
-    const longlong2* xv = STREAM ? reinterpret_cast<const longlong2*>(ring_raw + (size_t)slot * row_bytes)
-                                 : reinterpret_cast<const longlong2*>(X + row * T);
-    int8_t* drow = planes + row * Kp;
-    const int valid = valid_of(row);
     const int quads_valid = (valid + 3) >> 2;
-    if (STREAM) {
-        // bounded wait for this row's copy; the outcome is made uniform before anyone moves on
-        const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&full_bar[slot]);
-        const uint32_t parity = (uint32_t)((it / ns) & 1);
-        uint32_t done = 0;
-        for (uint32_t spin = 0; spin < (1u << 22) && !done; ++spin)
-            asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
-                         "selp.u32 %0, 1, 0, p;\n}\n"
-                         : "=r"(done) : "r"(bar), "r"(parity), "r"(1000u) : "memory");
-        if (!__syncthreads_and((int)done)) {
-            if (threadIdx.x == 0) *error_flag = 1;
-            break;
-        }
-    }
+    const int quads_all = (int)(Kp >> 2);
 
     int64_t v[4 * E];
     int64_t mx = INT64_MIN;
@@ -505,15 +450,6 @@ softmax_q19_planes_kernel(const int64_t* X, const int64_t* __restrict__ lut_g, i
         }
     }
     mx = block_max_i64(mx, red);
-    if (STREAM && threadIdx.x == 0) {
-        // every thread holds its part of the row in registers (the reduction synchronised the CTA):
-        // the slot can take the row `ns` steps ahead
-        const int64_t next = row + (int64_t)ns * gridDim.x;
-        if (next < rows) {
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            issue_copy(next, slot);
-        }
-    }
 
     uint32_t w[4 * E];
     uint32_t sum32 = 0;              // at most 32 weights of at most 2^19 + 1 each
@@ -544,6 +480,8 @@ softmax_q19_planes_kernel(const int64_t* X, const int64_t* __restrict__ lut_g, i
     const bool small = sumW < (1ull << 32);
     const uint32_t s32 = (uint32_t)sumW;
 
+    uint32_t seen = 0;
+    bool ovf = false;
 #pragma unroll
     for (int j = 0; j < E; ++j) {
         const int q = threadIdx.x + j * kThreads;
@@ -604,7 +542,6 @@ softmax_q19_planes_kernel(const int64_t* X, const int64_t* __restrict__ lut_g, i
                 if (LL || l < L) *reinterpret_cast<uint32_t*>(drow + 4 * q + l * plane_stride) = pl[l];
         }
     }
-    }   // rows
     if (ovf) *overflow = 1u;
     if (absmax_out) {
 #pragma unroll
@@ -624,51 +561,30 @@ bool softmax_planes_supported(const int64_t* X, int64_t rows, int64_t T, int64_t
 
 int launch_softmax_planes(const int64_t* X, const int64_t* lut, int8_t* planes, int L, int64_t rows, int64_t T,
                           int64_t Kp, int64_t plane_stride, unsigned* overflow, unsigned long long* absmax_out,
-                          int64_t valid_H, int64_t valid_S, int64_t valid_start, int* error_flag, cudaStream_t st)
+                          int64_t valid_H, int64_t valid_S, int64_t valid_start, cudaStream_t st)
 {
     if (!softmax_planes_supported(X, rows, T, Kp) || L < 1 || L > 9 || valid_H > 0x7fffffff ||
         valid_S > 0x7fffffff || valid_start > 0x7fffffff)
         return ZKDS_ERR_UNSUPPORTED;
     const int per = (int)(((Kp >> 2) + kThreads - 1) / kThreads);
+    const unsigned g = (unsigned)rows;
     const int vS = valid_S > 0 ? (int)valid_S : 1;
-    // streamed variant: a ring of 2-3 rows per CTA, as many CTAs per SM as shared memory, threads and
-    // registers allow (at most 4), one wave of persistent CTAs
-    const size_t row_bytes = (size_t)T * 8;
-    const size_t budget = 200 * 1024;
-    const bool stream = error_flag && rows >= 1024 && 2 * row_bytes <= budget && !getenv("ZKDS_SOFTMAX_NO_STREAM");
-    int ns = 1, ctas_per_sm = 1;
-    size_t smem = 0;
-    if (stream) {
-        ns = 3 * row_bytes <= 100 * 1024 ? 3 : 2;
-        ctas_per_sm = (int)(budget / (ns * row_bytes));
-        if (ctas_per_sm > 4) ctas_per_sm = 4;
-        if (ctas_per_sm < 1) ctas_per_sm = 1;
-        smem = ns * row_bytes;
-    }
-    int64_t grid = stream ? (int64_t)sm_count() * ctas_per_sm : rows;
-    if (grid > rows) grid = rows;
-    const unsigned g = (unsigned)grid;
-#define ZKDS_SP2(E, LL, S)                                                                                     \
-    do {                                                                                                       \
-        auto k = softmax_q19_planes_kernel<E, LL, S>;                                                          \
-        if (smem > 48 * 1024)                                                                                  \
-            ZKDS_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));        \
-        k<<<g, kThreads, smem, st>>>(X, lut, planes, L, (int)T, Kp, plane_stride, overflow, absmax_out,        \
-                                     (int)valid_H, vS, (int)valid_start, rows, ns, error_flag);                \
-    } while (0)
-#define ZKDS_SP(E)                                                                                             \
-    do {                                                                                                       \
-        if (L == 3 && stream) ZKDS_SP2(E, 3, true);                                                            \
-        else if (L == 3) ZKDS_SP2(E, 3, false);                                                                \
-        else if (stream) ZKDS_SP2(E, 0, true);                                                                 \
-        else ZKDS_SP2(E, 0, false);                                                                            \
+#define ZKDS_SP(E)                                                                                        \
+    do {                                                                                                  \
+        if (L == 3)                                                                                       \
+            softmax_q19_planes_kernel<E, 3><<<g, kThreads, 0, st>>>(X, lut, planes, L, (int)T, Kp,        \
+                                                                    plane_stride, overflow, absmax_out,   \
+                                                                    (int)valid_H, vS, (int)valid_start);  \
+        else                                                                                              \
+            softmax_q19_planes_kernel<E, 0><<<g, kThreads, 0, st>>>(X, lut, planes, L, (int)T, Kp,        \
+                                                                    plane_stride, overflow, absmax_out,   \
+                                                                    (int)valid_H, vS, (int)valid_start);  \
     } while (0)
     if (per <= 1) ZKDS_SP(1);
     else if (per <= 2) ZKDS_SP(2);
     else if (per <= 4) ZKDS_SP(4);
     else ZKDS_SP(8);
 #undef ZKDS_SP
-#undef ZKDS_SP2
     return check_launch();
 }
 

@@ -23,7 +23,7 @@ int launch_softmax_causal(const int64_t* X, int64_t* C, const int64_t* lut, int6
 bool softmax_planes_supported(const int64_t* X, int64_t rows, int64_t T, int64_t Kp);
 int launch_softmax_planes(const int64_t* X, const int64_t* lut, int8_t* planes, int L, int64_t rows, int64_t T,
                           int64_t Kp, int64_t plane_stride, unsigned* overflow, unsigned long long* absmax_out,
-                          int64_t valid_H, int64_t valid_S, int64_t valid_start, int* error_flag, cudaStream_t st);
+                          int64_t valid_H, int64_t valid_S, int64_t valid_start, cudaStream_t st);
 int launch_rope(const int64_t* A, const int64_t* Tb, int64_t* C, int64_t batch, int64_t S,
                 int64_t H, int64_t pairs, int shift, cudaStream_t st);
 int launch_rmsnorm(const int64_t* A, const void* W, int w_bits, const int64_t* rms_in,

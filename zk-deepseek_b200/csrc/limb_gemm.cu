@@ -641,6 +641,17 @@ struct EpilogueCtx {
 // exact remainder correction.  One straight-line path for every realistic score.
 __device__ __forceinline__ int64_t scale_94_695(int64_t v)
 {
+    if (v == (int64_t)(int32_t)v) {
+        // 32-bit tier: q0 = floor(v * ceil(94 * 2^32 / 695) / 2^32) is the floor or one above it
+        // (the constant errs by less than 1, so the product by less than |v| / 2^32 < 1/2); the
+        // remainder, exact modulo 2^32 because it is small, tells which
+        const int32_t x = (int32_t)v;
+        int32_t q = __mulhi(x, 580902052);
+        int32_t r = (int32_t)((uint32_t)x * 94u - (uint32_t)q * 695u);
+        if (r < 0) { --q; r += 695; }
+        if (r >= 695) ++q;
+        return (int64_t)q;
+    }
     const int64_t t = v * 94;
     int64_t q = __double2ll_rd((double)t * (1.0 / 695.0));
     int64_t r = t - q * 695;
@@ -1171,6 +1182,112 @@ __device__ __forceinline__ void epilogue_part(const LimbParams& p, uint32_t tq, 
     __syncwarp();
 }
 
+// Epilogue of the merged dual accumulation (one warp: rows 32 q .. 32 q + 31, its CW columns of the
+// tile, CW = 8 or 16).  The diagonals are folded into two running values per column as they arrive
+// (T' = main sum + both addends in 64 bits, r2 = extra sum + scaled second addend modulo 2^32), one
+// tensor-memory load per diagonal, so after D + E short waits everything this warp needs is in
+// registers and both sets go straight back to the MMA warp; the quotients
+// (T' >> shift) - [T' mod 2^shift < r2 mod 2^shift], the score tail, staging and the row stores then
+// run while the next tile's MMAs are already under way.
+template <int DD, int EE, int CW>
+__device__ __forceinline__ void epilogue_merged(const LimbParams& p, uint32_t tq, const TileCoord& tc, int q,
+                                                int lane, int c0, uint8_t* stage, int RS, int set_cols,
+                                                uint32_t release_main, uint32_t release_extra)
+{
+    int64_t T[CW];
+    uint32_t R[CW];
+#pragma unroll
+    for (int d = 0; d < DD; ++d) {
+        int32_t a[CW];
+        tmem_ldn(tq + (uint32_t)(d * p.NT + c0), a);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < CW; ++c) {
+            if (d == 0) T[c] = mad_wide(a[c], 1, p.addend);
+            else if (d < 4) T[c] = mad_wide(a[c], 1 << (8 * (d < 4 ? d : 0)), T[c]);
+            else T[c] = (int64_t)((uint64_t)T[c] + ((uint64_t)(uint32_t)a[c] << (8 * d)));
+        }
+    }
+#pragma unroll
+    for (int d = 0; d < EE; ++d) {
+        int32_t e[CW];
+        tmem_ldn(tq + (uint32_t)(set_cols + d * p.NT + c0), e);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < CW; ++c) {
+            if (d == 0) R[c] = (uint32_t)e[c] + (uint32_t)p.addend2;
+            else R[c] += (uint32_t)e[c] << (8 * d);
+        }
+    }
+    // re-zero the main columns no first-step MMA initialises, hand both sets back
+    for (int d = p.Lb; d < DD; ++d)
+        for (int c = 0; c < CW; c += 8) tmem_st8_zero(tq + (uint32_t)(d * p.NT + c0 + c));
+    tmem_st_wait();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) {
+        mbar_arrive(release_main);
+        mbar_arrive(release_extra);
+    }
+
+    const int64_t m = tc.m0 + q * 32 + lane;
+    const int64_t srow = p.causal_H ? m / p.causal_H : 0;
+    const int64_t nbase = tc.n0 + c0;
+    const uint32_t mask = (1u << p.shift) - 1u;
+    int64_t* srow_ptr = reinterpret_cast<int64_t*>(stage + lane * RS);
+#pragma unroll
+    for (int c = 0; c < CW; c += 2) {
+        int64_t out2[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int64_t t = T[c + h];
+            const int64_t v = (t >> p.shift) - (((uint32_t)t & mask) < (R[c + h] & mask) ? 1 : 0);
+            out2[h] = score_tail(p, v, nullptr, nbase + c + h, srow);
+        }
+        *reinterpret_cast<longlong2*>(srow_ptr + c) = make_longlong2(out2[0], out2[1]);
+    }
+    __syncwarp();
+    // write the staged rows out, whole rows at a time
+    const bool vec_ok = ((((uintptr_t)p.C) & 15) == 0) && ((p.c_sm & 1) == 0) && ((p.c_sz & 1) == 0);
+    constexpr int lanes_per_row = CW / 2;
+    constexpr int rows_per_it = 32 / lanes_per_row;
+    const int rl = lane / lanes_per_row, cl = (lane % lanes_per_row) * 2;
+    int64_t mr = tc.m0 + q * 32 + rl;
+    int64_t* dst = p.C + tc.z * p.c_sz + mr * p.c_sm + nbase + cl;
+    const uint8_t* src = stage + rl * RS + cl * 8;
+    const int64_t dstep = (int64_t)rows_per_it * p.c_sm;
+    const int sstep = rows_per_it * RS;
+    const bool full2 = vec_ok && nbase + cl + 2 <= p.N;
+#pragma unroll 4
+    for (int r0 = 0; r0 < 32; r0 += rows_per_it, mr += rows_per_it, dst += dstep, src += sstep) {
+        if (mr < p.M) {
+            const longlong2 v = *reinterpret_cast<const longlong2*>(src);
+            if (full2) *reinterpret_cast<longlong2*>(dst) = v;
+            else {
+                if (nbase + cl < p.N) dst[0] = v.x;
+                if (nbase + cl + 1 < p.N) dst[1] = v.y;
+            }
+        }
+    }
+    __syncwarp();
+}
+
+// false when the shape has no compiled specialisation (the two-pass epilogue then does the job)
+template <int CW>
+__device__ __forceinline__ bool epilogue_merged_dispatch(const LimbParams& p, int D, uint32_t tq, const TileCoord& tc,
+                                                         int q, int lane, int c0, uint8_t* stage, int RS,
+                                                         int set_cols, uint32_t rel_main, uint32_t rel_extra)
+{
+    if (p.merged_E != 3) return false;
+    switch (D) {
+    case 3: epilogue_merged<3, 3, CW>(p, tq, tc, q, lane, c0, stage, RS, set_cols, rel_main, rel_extra); return true;
+    case 4: epilogue_merged<4, 3, CW>(p, tq, tc, q, lane, c0, stage, RS, set_cols, rel_main, rel_extra); return true;
+    case 5: epilogue_merged<5, 3, CW>(p, tq, tc, q, lane, c0, stage, RS, set_cols, rel_main, rel_extra); return true;
+    case 6: epilogue_merged<6, 3, CW>(p, tq, tc, q, lane, c0, stage, RS, set_cols, rel_main, rel_extra); return true;
+    default: return false;
+    }
+}
+
 template <int EW>
 __global__ void __launch_bounds__(persistent_threads(EW), 1)
 limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -1385,6 +1502,16 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             tc_fence_after();
             const uint32_t tq = lane_base + (uint32_t)(b * buf_cols);
             const uint32_t rel = split ? bar_tempty : 0u;
+            if (p.merged_E && split && (CW == 16 || CW == 8)) {
+                const bool done = CW == 16 ? epilogue_merged_dispatch<16>(p, D, tq, tc, q, lane, c0, stage, RS, set_cols,
+                                                                          bar_tempty, bar_tempty + 8)
+                                           : epilogue_merged_dispatch<8>(p, D, tq, tc, q, lane, c0, stage, RS, set_cols,
+                                                                         bar_tempty, bar_tempty + 8);
+                if (done) {
+                    ++t;
+                    continue;
+                }
+            }
             if (p.fits64) {
                 const bool wide = p.wide_chunk && !p.group_shift;   // a wide chunk could straddle n_split
                 if (EW != 12 && wide && (CW == 12 || CW == 24))
@@ -1806,7 +1933,7 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     if (p.softmax_lut) {
         if (p.a_sm != p.K || p.a_sz != p.M * p.K || p.a_div != 1) return ZKDS_ERR_ARG;
         rc = launch_softmax_planes(p.A, p.softmax_lut, pa, La, a_rows, p.K, Kp, a_rows * Kp, fl->overflow_dev,
-                                   d_absmax, p.skip_k ? p.skip_H : 0, p.softmax_S, p.skip_start, fl->dev, st);
+                                   d_absmax, p.skip_k ? p.skip_H : 0, p.softmax_S, p.skip_start, st);
     } else
         rc = launch_split_t<int64_t>(p.A, pa, La, p.batches, p.M, p.K, Kp16, p.a_sz, p.a_sm, 1, p.a_div,
                                      fl->overflow_dev, st, d_absmax, 0, p.skip_k ? p.skip_H : 0, p.skip_start);
