@@ -1105,9 +1105,7 @@ __device__ __forceinline__ void epilogue_part(const LimbParams& p, uint32_t tq, 
         int64_t cv[CH];
         // grouped mode: the shift belongs to the group and to the side of n_split the chunk lies on
         // (n_split and every chunk start are multiples of 4, a chunk never straddles it when CH <= 8)
-        // merged mode parks the unshifted total; the shift follows once the carry is known
-        const int shift = p.merged_E ? 0
-                          : (p.group_shift ? p.group_shift[2 * tc.group + (nbase + nc >= p.n_split ? 1 : 0)] : p.shift);
+        const int shift = p.group_shift ? p.group_shift[2 * tc.group + (nbase + nc >= p.n_split ? 1 : 0)] : p.shift;
         if (early) chunk_quotient<FITS64, CH>(D, tq + (uint32_t)(c0 + nc), p.NT, p.addend, shift, cv, release_first);
         else chunk_quotient<FITS64, CH>(D, tq + (uint32_t)(c0 + nc), p.NT, p.addend, shift, cv, NoHook());
         int64_t* srow_ptr = reinterpret_cast<int64_t*>(stage + lane * RS + nc * 8);
@@ -1121,34 +1119,17 @@ __device__ __forceinline__ void epilogue_part(const LimbParams& p, uint32_t tq, 
             *reinterpret_cast<longlong2*>(srow_ptr + c) = make_longlong2(cv[c], cv[c + 1]);
     }
     if (two) {
-
         // second set of diagonals: its own addend and shift, then the two quotients add up
 #pragma unroll 1
         for (int nc = 0; nc < CW; nc += CH) {
             int64_t v2[CH];
             int64_t* srow_ptr = reinterpret_cast<int64_t*>(stage + lane * RS + nc * 8);
-            if (p.merged_E) {
-                // r2 = (scaled second sum + its addend) mod 2^shift from the extra diagonals; the parked
-                // total T' carries both addends: quotient = (T' >> shift) - [T' mod 2^shift < r2]
-                chunk_quotient<FITS64, CH>(p.merged_E, tq + (uint32_t)(set_cols + c0 + nc), p.NT, p.addend2, 0, v2,
-                                           NoHook());
-                const uint32_t mask = (1u << p.shift) - 1u;
+            chunk_quotient<FITS64, CH>(D, tq + (uint32_t)(set_cols + c0 + nc), p.NT, p.addend2, p.shift2, v2, NoHook());
 #pragma unroll
-                for (int c = 0; c < CH; c += 2) {
-                    const longlong2 t = *reinterpret_cast<const longlong2*>(srow_ptr + c);
-                    const uint32_t r0 = (uint32_t)v2[c] & mask, r1 = (uint32_t)v2[c + 1] & mask;
-                    v2[c] = (t.x >> p.shift) - (((uint32_t)t.x & mask) < r0 ? 1 : 0);
-                    v2[c + 1] = (t.y >> p.shift) - (((uint32_t)t.y & mask) < r1 ? 1 : 0);
-                }
-            } else {
-                chunk_quotient<FITS64, CH>(D, tq + (uint32_t)(set_cols + c0 + nc), p.NT, p.addend2, p.shift2, v2,
-                                           NoHook());
-#pragma unroll
-                for (int c = 0; c < CH; c += 2) {
-                    const longlong2 v1 = *reinterpret_cast<const longlong2*>(srow_ptr + c);
-                    v2[c] = (int64_t)((uint64_t)v2[c] + (uint64_t)v1.x);
-                    v2[c + 1] = (int64_t)((uint64_t)v2[c + 1] + (uint64_t)v1.y);
-                }
+            for (int c = 0; c < CH; c += 2) {
+                const longlong2 v1 = *reinterpret_cast<const longlong2*>(srow_ptr + c);
+                v2[c] = (int64_t)((uint64_t)v2[c] + (uint64_t)v1.x);
+                v2[c + 1] = (int64_t)((uint64_t)v2[c + 1] + (uint64_t)v1.y);
             }
             if (tail) {
 #pragma unroll
@@ -1187,12 +1168,13 @@ __device__ __forceinline__ void epilogue_part(const LimbParams& p, uint32_t tq, 
 // (T' = main sum + both addends in 64 bits, r2 = extra sum + scaled second addend modulo 2^32), one
 // tensor-memory load per diagonal, so after D + E short waits everything this warp needs is in
 // registers and both sets go straight back to the MMA warp; the quotients
-// (T' >> shift) - [T' mod 2^shift < r2 mod 2^shift], the score tail, staging and the row stores then
-// run while the next tile's MMAs are already under way.
+// (T' >> shift) - [T' mod 2^shift < r2 mod 2^shift], the score tail and the stores (each thread writes its
+// CW consecutive words of one row as full 32-byte sectors) then run while the next tile's MMAs are
+// already under way.
 template <int DD, int EE, int CW>
 __device__ __forceinline__ void epilogue_merged(const LimbParams& p, uint32_t tq, const TileCoord& tc, int q,
-                                                int lane, int c0, uint8_t* stage, int RS, int set_cols,
-                                                uint32_t release_main, uint32_t release_extra)
+                                                int lane, int c0, int set_cols, uint32_t release_main,
+                                                uint32_t release_extra)
 {
     int64_t T[CW];
     uint32_t R[CW];
@@ -1234,56 +1216,45 @@ __device__ __forceinline__ void epilogue_merged(const LimbParams& p, uint32_t tq
     const int64_t srow = p.causal_H ? m / p.causal_H : 0;
     const int64_t nbase = tc.n0 + c0;
     const uint32_t mask = (1u << p.shift) - 1u;
-    int64_t* srow_ptr = reinterpret_cast<int64_t*>(stage + lane * RS);
+    // each thread owns CW consecutive words of one output row: 32-byte stores (one full sector each)
+    int64_t* crow = p.C + tc.z * p.c_sz + m * p.c_sm + nbase;
+    const bool wide_ok = ((((uintptr_t)p.C) & 31) == 0) && ((p.c_sm & 3) == 0) && ((p.c_sz & 3) == 0) &&
+                         nbase + CW <= p.N;
+    if (m < p.M) {
 #pragma unroll
-    for (int c = 0; c < CW; c += 2) {
-        int64_t out2[2];
+        for (int c = 0; c < CW; c += 4) {
+            int64_t o[4];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const int64_t t = T[c + h];
-            const int64_t v = (t >> p.shift) - (((uint32_t)t & mask) < (R[c + h] & mask) ? 1 : 0);
-            out2[h] = score_tail(p, v, nullptr, nbase + c + h, srow);
-        }
-        *reinterpret_cast<longlong2*>(srow_ptr + c) = make_longlong2(out2[0], out2[1]);
-    }
-    __syncwarp();
-    // write the staged rows out, whole rows at a time
-    const bool vec_ok = ((((uintptr_t)p.C) & 15) == 0) && ((p.c_sm & 1) == 0) && ((p.c_sz & 1) == 0);
-    constexpr int lanes_per_row = CW / 2;
-    constexpr int rows_per_it = 32 / lanes_per_row;
-    const int rl = lane / lanes_per_row, cl = (lane % lanes_per_row) * 2;
-    int64_t mr = tc.m0 + q * 32 + rl;
-    int64_t* dst = p.C + tc.z * p.c_sz + mr * p.c_sm + nbase + cl;
-    const uint8_t* src = stage + rl * RS + cl * 8;
-    const int64_t dstep = (int64_t)rows_per_it * p.c_sm;
-    const int sstep = rows_per_it * RS;
-    const bool full2 = vec_ok && nbase + cl + 2 <= p.N;
-#pragma unroll 4
-    for (int r0 = 0; r0 < 32; r0 += rows_per_it, mr += rows_per_it, dst += dstep, src += sstep) {
-        if (mr < p.M) {
-            const longlong2 v = *reinterpret_cast<const longlong2*>(src);
-            if (full2) *reinterpret_cast<longlong2*>(dst) = v;
-            else {
-                if (nbase + cl < p.N) dst[0] = v.x;
-                if (nbase + cl + 1 < p.N) dst[1] = v.y;
+            for (int h = 0; h < 4; ++h) {
+                const int64_t t = T[c + h];
+                const int64_t v = (t >> p.shift) - (((uint32_t)t & mask) < (R[c + h] & mask) ? 1 : 0);
+                o[h] = score_tail(p, v, nullptr, nbase + c + h, srow);
+            }
+            if (wide_ok) {
+                asm volatile("st.global.v4.b64 [%0], {%1, %2, %3, %4};" ::"l"(crow + c), "l"(o[0]), "l"(o[1]),
+                             "l"(o[2]), "l"(o[3])
+                             : "memory");
+            } else {
+#pragma unroll
+                for (int h = 0; h < 4; ++h)
+                    if (nbase + c + h < p.N) crow[c + h] = o[h];
             }
         }
     }
-    __syncwarp();
 }
 
 // false when the shape has no compiled specialisation (the two-pass epilogue then does the job)
 template <int CW>
 __device__ __forceinline__ bool epilogue_merged_dispatch(const LimbParams& p, int D, uint32_t tq, const TileCoord& tc,
-                                                         int q, int lane, int c0, uint8_t* stage, int RS,
-                                                         int set_cols, uint32_t rel_main, uint32_t rel_extra)
+                                                         int q, int lane, int c0, int set_cols, uint32_t rel_main,
+                                                         uint32_t rel_extra)
 {
     if (p.merged_E != 3) return false;
     switch (D) {
-    case 3: epilogue_merged<3, 3, CW>(p, tq, tc, q, lane, c0, stage, RS, set_cols, rel_main, rel_extra); return true;
-    case 4: epilogue_merged<4, 3, CW>(p, tq, tc, q, lane, c0, stage, RS, set_cols, rel_main, rel_extra); return true;
-    case 5: epilogue_merged<5, 3, CW>(p, tq, tc, q, lane, c0, stage, RS, set_cols, rel_main, rel_extra); return true;
-    case 6: epilogue_merged<6, 3, CW>(p, tq, tc, q, lane, c0, stage, RS, set_cols, rel_main, rel_extra); return true;
+    case 3: epilogue_merged<3, 3, CW>(p, tq, tc, q, lane, c0, set_cols, rel_main, rel_extra); return true;
+    case 4: epilogue_merged<4, 3, CW>(p, tq, tc, q, lane, c0, set_cols, rel_main, rel_extra); return true;
+    case 5: epilogue_merged<5, 3, CW>(p, tq, tc, q, lane, c0, set_cols, rel_main, rel_extra); return true;
+    case 6: epilogue_merged<6, 3, CW>(p, tq, tc, q, lane, c0, set_cols, rel_main, rel_extra); return true;
     default: return false;
     }
 }
@@ -1502,15 +1473,19 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             tc_fence_after();
             const uint32_t tq = lane_base + (uint32_t)(b * buf_cols);
             const uint32_t rel = split ? bar_tempty : 0u;
-            if (p.merged_E && split && (CW == 16 || CW == 8)) {
-                const bool done = CW == 16 ? epilogue_merged_dispatch<16>(p, D, tq, tc, q, lane, c0, stage, RS, set_cols,
-                                                                          bar_tempty, bar_tempty + 8)
-                                           : epilogue_merged_dispatch<8>(p, D, tq, tc, q, lane, c0, stage, RS, set_cols,
-                                                                         bar_tempty, bar_tempty + 8);
-                if (done) {
-                    ++t;
-                    continue;
+            if (p.merged_E) {
+                // the launcher only merges shapes this epilogue is compiled for
+                bool done = false;
+                if (split && CW == 16)
+                    done = epilogue_merged_dispatch<16>(p, D, tq, tc, q, lane, c0, set_cols, bar_tempty, bar_tempty + 8);
+                else if (split && CW == 8)
+                    done = epilogue_merged_dispatch<8>(p, D, tq, tc, q, lane, c0, set_cols, bar_tempty, bar_tempty + 8);
+                if (!done) {
+                    if (lane == 0) *abort_flag = 1;
+                    break;
                 }
+                ++t;
+                continue;
             }
             if (p.fits64) {
                 const bool wide = p.wide_chunk && !p.group_shift;   // a wide chunk could straddle n_split
@@ -2064,19 +2039,21 @@ int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st)
     if (delta >= 0 && delta <= 8 && f.shift1 >= 1 && f.shift1 <= 31 && !getenv("ZKDS_NO_MERGED")) {
         const int e = (f.shift1 + 7) / 8;
         const int64_t a12 = f.addend1 + (int64_t)((uint64_t)f.addend2 << delta);
-        if (e <= Lb && e <= D && f.addend1 >= 0 && f.addend2 >= 0 && f.addend2 < (1ll << 40) &&
+        // the one-pass epilogue is compiled for three extra diagonals and up to six main ones
+        if (e == 3 && e <= Lb && D <= 6 && f.addend1 >= 0 && f.addend2 >= 0 && f.addend2 < (1ll << 40) &&
             (int64_t)pairs * (f.K1 + Kp2m) < 131072 && sum_fits64(La, Lb, f.K1 + f.K2, a12))
             E = e;
     }
     for (int bufs : {2, 1}) {
         for (int cand : {64, 48, 32, 16}) {
             if (bufs == 2 && cand < 32) continue;
-            if (E && bufs == 2) continue;                       // merged mode: one buffer, early hand-back
+            if (E && (bufs == 2 || cand == 48 || cand == 16)) continue;   // merged: one buffer, 8 or 16 columns per warp
             if (Lb * cand > 256 || (E ? (D + E) : 2 * bufs * D) * cand > 512) continue;
-            // three warps per lane quarter only divide a 48-column tile
-            const int ew_c = (ew_pref == 12 && cand != 48) ? 16 : ew_pref;
+            // three warps per lane quarter only divide a 48-column tile; merged mode runs 16 warps
+            const int ew_c = E ? 16 : ((ew_pref == 12 && cand != 48) ? 16 : ew_pref);
             size_t st_b = (size_t)La * kTileM * kBlockK + (size_t)Lb * cand * kBlockK;
-            size_t staging = persistent_staging(ew_c, cand);
+            // the merged epilogue stores straight from registers: no staging tile
+            size_t staging = E ? 0 : persistent_staging(ew_c, cand);
             int ns = (int)((smem_max - staging - 1024) / st_b);
             if (ns < 2) continue;
             NT = cand;
