@@ -319,3 +319,75 @@ def test_transformer_steps(M, kmod, dev):
     want, _ = orc.gemm(hn[None, -1:], model.head.weight.cpu().numpy(), 1, 256, 29)
     same(logits, want, "logits")
     kmod.device_status()
+
+
+def _small_transformer(M, a, rng, dev, batch):
+    with torch.device(dev):
+        model = M.Transformer(a)
+    model.embed.weight = t(np.rint(rng.standard_normal((a.vocab_size, a.dim)) * 2.0**31).astype(np.int64), dev)
+    model.norm.weight = t(norm_w(rng, a.dim, 15).astype(np.int64), dev)
+    model.head.weight = t(np.rint(rng.standard_normal((a.vocab_size, a.dim)) * 2.0**43 / 16).astype(np.int64), dev)
+    for i in range(a.n_layers):
+        blk = M.Block(i, a, cache_batch=batch).to(dev)
+        load_mla(blk.attn, mla_weights(rng, a), dev)
+        blk.attn_norm.weight = t(norm_w(rng, a.dim, 21), dev)
+        blk.ffn_norm.weight = t(norm_w(rng, a.dim, 23), dev)
+        if i < a.n_dense_layers:
+            load_mlp(blk.ffn, mlp_weights(rng, a.dim, a.inter_dim), dev)
+        else:
+            blk.ffn = build_moe(M, a, moe_weights(rng, a, True), dev)    # dumps write the gate bias
+        model.layers[i] = blk
+    return model
+
+
+def test_generate_loop(M, kmod, dev, tmp_path):
+    """generate() (generate.py:164-286) on a two-layer model, two prompts of different length: the
+    cached decode must give the very tokens a from-scratch prefill of every prefix gives (integer
+    arithmetic: no tolerance), prompt tokens are never overwritten, eos ends a sequence, and with
+    snark the token files appear under pos_{p}/"""
+    import importlib
+    G = importlib.import_module(M.__name__.rsplit(".", 1)[0] + ".generate")
+    a = small_args(M)
+    model = _small_transformer(M, a, np.random.default_rng(8), dev, batch=2)
+    prompts = [[5, 17, 300, 2, 41], [9, 100, 7]]
+    trace = []
+    out = G.generate(model, prompts, 4, eos_id=-5, temperature=0.0, trace=trace)
+    assert [len(o) for o in out] == [4, 4]
+    assert [s["pos"] for s in trace] == list(range(3, 9))
+    # the longer prompt's own tokens at positions 3 and 4 survive
+    assert trace[0]["next_token"][0] == prompts[0][3]
+    assert trace[1]["next_token"][0] == prompts[0][4]
+
+    # from-scratch check: every generated token equals the argmax after a fresh prefill of its prefix
+    ref = _small_transformer(M, a, np.random.default_rng(8), dev, batch=1)
+    for b, prompt in enumerate(prompts):
+        seq = list(prompt)
+        for step in range(4):
+            toks = torch.tensor([seq], dtype=torch.long, device=dev)
+            h, pos, S = ref.prep_inference(toks, 0)
+            for i in range(a.n_layers):
+                h = ref.layer_inference(i, h, pos, S)
+            nxt = int(ref.finish_inference(h).argmax(dim=-1).view(-1)[0])
+            assert nxt == out[b][step], "sequence %d, new token %d" % (b, step)
+            seq.append(nxt)
+
+    # eos: the first sequence stops at its second new token
+    model2 = _small_transformer(M, a, np.random.default_rng(8), dev, batch=2)
+    eos = out[0][1]
+    cut = G.generate(model2, prompts, 4, eos_id=eos, temperature=0.0)
+    assert cut[0] == out[0][:out[0].index(eos)]
+    assert cut[1] == (out[1][:out[1].index(eos)] if eos in out[1] else out[1])
+
+    # dumps: tokens.bin of the prefill and of the first decode step
+    model3 = _small_transformer(M, a, np.random.default_rng(8), dev, batch=1)
+    M.snark, M.zkDataDir = True, str(tmp_path)
+    try:
+        probe_trace = []
+        G.generate(model3, [prompts[1]], 2, eos_id=-5, temperature=0.0, layer_probe=True, trace=probe_trace)
+    finally:
+        M.snark, M.zkDataDir = False, "../zkdata"
+    assert np.array_equal(read_dump(os.path.join(str(tmp_path), "pos_0", "tokens.bin"), np.int64), prompts[1])
+    assert read_dump(os.path.join(str(tmp_path), "pos_3", "tokens.bin"), np.int64).tolist() == [out[1][0]]
+    # the probe of the last layer is the token the step produces
+    assert probe_trace[0]["layer_tokens"][-1] == probe_trace[0]["next_token"]
+    kmod.device_status()

@@ -274,12 +274,16 @@ __device__ __forceinline__ bool mbar_try_parked(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 
-// Bounded wait.  Returns false when the limit ran out or another role gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag)
+// Bounded wait.  Returns false when the limit ran out or another role gave up.  backoff_ns > 0: sleep
+// that long after a failed try, so a waiting warp leaves the issue slots of its scheduler to the
+// warps that have work (the price is up to backoff_ns of extra latency on the wake-up).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned backoff_ns = 0)
 {
     for (uint32_t it = 0; it < kSpinLimit; ++it) {
         if (mbar_try_parked(bar, parity)) return true;
         if ((it & 255u) == 255u && *abort_flag) return false;
+        if (backoff_ns) __nanosleep(backoff_ns);
     }
     *abort_flag = 1;
     return false;
@@ -519,6 +523,7 @@ struct LimbParams {
     // more into a small extra set right of the main one, which yields the carry that separates
     // floor((S1+a1)/2^shift) + floor((S2+a2)/2^shift2) from floor((T+a1+2^(shift-shift2) a2)/2^shift)
     int merged_E;
+    unsigned backoff;         // 1: waiting warps sleep between polls (see mbar_wait), 0: they poll back to back
     int wide_chunk;           // epilogue: fetch a warp's 12 or 16 columns with one wait instead of 4 or 8 at a time
     // optional wait accounting (null = off): [0] MMA warp cycles waiting for operand stages, [1] for
     // free accumulators, [2] MMA warp total, [3] first epilogue warp cycles waiting for accumulators,
@@ -1328,7 +1333,7 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                 for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
                     const int s = (int)(it % p.stages);
                     const uint32_t par = (uint32_t)((it / p.stages) & 1) ^ 1u;
-                    if (!mbar_wait(bar_empty + 8 * s, par, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(bar_empty + 8 * s, par, abort_flag, 96u * p.backoff)) { ok = false; break; }
                     const uint32_t full = bar_full + 8 * s;
                     mbar_expect_tx(full, tx_bytes);
                     const uint32_t sa = smem_base + s * stage_bytes;
@@ -1366,7 +1371,7 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                 const int b = (int)(t % p.nbuf);
                 const uint32_t tpar = (uint32_t)((t / p.nbuf) & 1);
                 if (prof) t0 = clock64();
-                ok = mbar_wait(bar_tempty + 8 * b, tpar, abort_flag);
+                ok = mbar_wait(bar_tempty + 8 * b, tpar, abort_flag, 24u * p.backoff);
                 if (prof) w_empty += clock64() - t0;
                 if (!ok) break;
                 tc_fence_after();
@@ -1377,13 +1382,13 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                     if (split && kb == p.k_switch) {
                         // the second set is still being drained by the previous tile's epilogue
                         if (prof) t0 = clock64();
-                        ok = mbar_wait(bar_tempty + 8, tpar, abort_flag);
+                        ok = mbar_wait(bar_tempty + 8, tpar, abort_flag, 24u * p.backoff);
                         if (prof) w_empty += clock64() - t0;
                         if (!ok) break;
                         tc_fence_after();
                     }
                     if (prof) t0 = clock64();
-                    ok = mbar_wait(bar_full + 8 * s, (uint32_t)((it / p.stages) & 1), abort_flag);
+                    ok = mbar_wait(bar_full + 8 * s, (uint32_t)((it / p.stages) & 1), abort_flag, 24u * p.backoff);
                     if (prof) w_full += clock64() - t0;
                     if (!ok) break;
                     tc_fence_after();
@@ -1468,7 +1473,7 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             }
             const int b = (int)(t % p.nbuf);
             if (prof) t0 = clock64();
-            if (!mbar_wait(bar_tfull + 8 * b, (uint32_t)((t / p.nbuf) & 1), abort_flag)) break;
+            if (!mbar_wait(bar_tfull + 8 * b, (uint32_t)((t / p.nbuf) & 1), abort_flag, 48u * p.backoff)) break;
             if (prof) w_acc += clock64() - t0;
             tc_fence_after();
             const uint32_t tq = lane_base + (uint32_t)(b * buf_cols);
@@ -1769,6 +1774,7 @@ static int launch_persistent(int ew, int ctas, size_t smem, cudaStream_t st, con
 {
     LimbParams lp = lp_in;
     lp.wide_chunk = 0;
+    lp.backoff = getenv("ZKDS_NO_BACKOFF") ? 0u : 1u;
     if (getenv("ZKDS_EPI_WIDE")) lp.wide_chunk = atoi(getenv("ZKDS_EPI_WIDE"));
     // ZKDS_WAIT_PROFILE=1: a synchronous diagnostic run that prints where the MMA warp and the first
     // epilogue warp spent their cycles (share of their lifetime spent waiting)

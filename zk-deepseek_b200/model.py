@@ -830,7 +830,7 @@ class Transformer(nn.Module):
 
     @torch.inference_mode()
     def finish_inference(self, h):
-        h = self.norm(h)[0][:, -1]          # last position of every sequence: [B, dim]
+        h = self.norm(h)[0][:, -1].contiguous()          # last position of every sequence: [B, dim]
         logits = self.head(h[None, :])      # [1, B, vocab] (B = 1 in the reference)
         if world_size > 1:
             logits = _all_gather_last(logits)
