@@ -239,6 +239,14 @@ int zkds_grouped_prepared(const int64_t* A, const void* planes, const int* tile_
                           int64_t* C, int64_t a_rescale, int64_t addend, int64_t shift,
                           const int* group_shift, int64_t n_split, int a_limbs, int flags, void* stream);
 
+/* zkds_grouped_prepared with the row gather of the expert dispatch folded into the limb split: row m of
+ * the grouped A matrix is row row_index[m] of A (int32, on the device; a negative entry is a padding row of
+ * zeros), so the gathered [n_tiles*128, K] matrix is never written (model.py:1372-1378 builds it with
+ * index_select).  a_limbs must be given (> 0).  No reference counterpart as a single entry point. */
+int zkds_grouped_gather_prepared(const int64_t* A, const int* row_index, const void* planes, const int* tile_group,
+                                 int64_t n_tiles, int64_t* C, int64_t a_rescale, int64_t addend, int64_t shift,
+                                 const int* group_shift, int64_t n_split, int a_limbs, int flags, void* stream);
+
 /* Replaces complex_int64_mul (int64_gemm.cu:274-286) with the product shift as a
  * parameter (the reference hard-codes 42). */
 int zkds_rope(const int64_t* A, const int64_t* table, int64_t* C, int64_t batch, int64_t seq,

@@ -369,6 +369,50 @@ def test_glu_gather_combine(kmod, orc, dev):
     same(y, want, "combine")
 
 
+def test_grouped_expert_gemm_with_and_without_fused_gather(kmod, orc, dev):
+    """all experts of a routed layer in one launch (model.py:1372-1378): rows grouped by expert in
+    128-row tiles, per-expert shifts left / right of n_split; the row gather as a separate pass and
+    folded into the limb split give the oracle's per-expert GEMMs"""
+    rng = np.random.default_rng(5)
+    E, N, Kd, T = 5, 96, 200, 300
+    W = rand_i64(rng, (E, N, Kd), 30).astype(np.int32)
+    x = rand_i64(rng, (T, Kd), 20)
+    shifts = rng.integers(10, 34, (E, 2)).astype(np.int32)
+    n_split = 40
+    expert_of = rng.integers(0, E, T)
+    expert_of[expert_of == 3] = 2                       # expert 3 gets no token
+    row_src, tile_group = [], []
+    for e in range(E):
+        toks = np.nonzero(expert_of == e)[0]
+        for t0 in range(0, len(toks), 128):
+            part = toks[t0:t0 + 128]
+            row_src += part.tolist() + [-1] * (128 - len(part))
+            tile_group.append(e)
+    tile_group.append(-1)                               # an unused tile: its output rows are zeros
+    row_src += [-1] * 128
+    row_src = np.array(row_src, np.int32)
+    tile_group = np.array(tile_group, np.int32)
+    want = np.zeros((len(row_src), N), np.int64)
+    for i, e in enumerate(tile_group):
+        if e < 0:
+            continue
+        rows = row_src[i * 128:(i + 1) * 128]
+        xe = np.where(rows[:, None] >= 0, x[np.maximum(rows, 0)], 0)
+        lo, _ = orc.gemm(xe[None], W[e, :n_split], 1, 1, int(shifts[e, 0]))
+        hi, _ = orc.gemm(xe[None], W[e, n_split:], 1, 1, int(shifts[e, 1]))
+        want[i * 128:(i + 1) * 128] = np.concatenate([lo[0], hi[0]], 1)
+    planes = kmod.WeightPlanes(g(W, dev))
+    xd, rs, tg, sh = g(x, dev), torch.from_numpy(row_src).to(dev), torch.from_numpy(tile_group).to(dev), g(shifts, dev)
+    separate = kmod.grouped_prepared(kmod.gather_rows(xd, rs), planes, tg, 0, a_limbs=3, dynamic=True,
+                                     group_shift=sh, n_split=n_split)
+    same(separate, want, "gather pass + grouped GEMM")
+    fused = kmod.grouped_prepared(xd, planes, tg, 0, a_limbs=3, dynamic=True, group_shift=sh, n_split=n_split,
+                                  row_index=rs)
+    same(fused, want, "gather folded into the split")
+    torch.cuda.synchronize()
+    kmod.device_status()
+
+
 # ---- the reference's own symbol names, and the reference's own kernels ------------------------------
 
 def test_reference_symbols_against_reference_kernels(libpath, reflib, orc, dev):

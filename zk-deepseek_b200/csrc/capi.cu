@@ -394,12 +394,35 @@ int zkds_mla_scores(const int64_t* q_abs, const int64_t* kv, const int64_t* q_pe
     return finish(rc, "zkds_mla_scores");
 }
 
+static int grouped_prepared(const int64_t* A, const int* row_index, const void* planes, const int* tile_group,
+                            int64_t n_tiles, int64_t* C, int64_t a_rescale, int64_t addend, int64_t shift,
+                            const int* group_shift, int64_t n_split, int a_limbs, int flags, void* stream);
+
 int zkds_grouped_prepared(const int64_t* A, const void* planes, const int* tile_group, int64_t n_tiles,
                           int64_t* C, int64_t a_rescale, int64_t addend, int64_t shift,
                           const int* group_shift, int64_t n_split, int a_limbs, int flags, void* stream)
 {
+    return grouped_prepared(A, nullptr, planes, tile_group, n_tiles, C, a_rescale, addend, shift, group_shift,
+                            n_split, a_limbs, flags, stream);
+}
+
+int zkds_grouped_gather_prepared(const int64_t* A, const int* row_index, const void* planes, const int* tile_group,
+                                 int64_t n_tiles, int64_t* C, int64_t a_rescale, int64_t addend, int64_t shift,
+                                 const int* group_shift, int64_t n_split, int a_limbs, int flags, void* stream)
+{
+    if (!row_index) return finish(ZKDS_ERR_ARG, "zkds_grouped_gather_prepared");
+    return grouped_prepared(A, row_index, planes, tile_group, n_tiles, C, a_rescale, addend, shift, group_shift,
+                            n_split, a_limbs, flags, stream);
+}
+
+static int grouped_prepared(const int64_t* A, const int* row_index, const void* planes, const int* tile_group,
+                            int64_t n_tiles, int64_t* C, int64_t a_rescale, int64_t addend, int64_t shift,
+                            const int* group_shift, int64_t n_split, int a_limbs, int flags, void* stream)
+{
     if (!planes || !tile_group || n_tiles < 0 || (group_shift && (n_split & 7)))
         return finish(ZKDS_ERR_ARG, "zkds_grouped_prepared");
+    if (row_index && a_limbs <= 0)      // measuring the range would have to follow the index too
+        return finish(ZKDS_ERR_ARG, "zkds_grouped_gather_prepared");
     const PlanesHandle* hd = (const PlanesHandle*)planes;
     Contraction p{};
     p.A = A; p.B = nullptr; p.b_bits = hd->b_bits; p.C = C; p.R = nullptr;
@@ -411,6 +434,7 @@ int zkds_grouped_prepared(const int64_t* A, const void* planes, const int* tile_
     p.addend = addend;
     p.shift = (shift < 0 || shift > 127) ? -1 : (int)shift;
     p.tile_group = tile_group;
+    p.a_row_index = row_index;
     p.group_shift = group_shift; p.n_split = n_split;
     int f = (flags & ~ZKDS_ALGO_MASK) | ZKDS_ALGO_LIMB;
     return finish(run_contraction(p, a_limbs, 0, f, ST(stream), &hd->pl), "zkds_grouped_prepared");

@@ -69,6 +69,9 @@ struct Contraction {
     // grouped mode (limb kernel only): batches == 1, A is a flat [M, K] matrix, tile_group[i]
     // gives the B batch of the i-th 128-row tile (negative: tile skipped)
     const int* tile_group;
+    // limb kernel only: row m of A is source row a_row_index[m] (negative: a row of zeros), so a row
+    // gather needs no pass of its own
+    const int* a_row_index;
     // grouped mode: shift per group, [2g] for columns < n_split, [2g+1] from n_split on (values in
     // 0..127, n_split a multiple of 8); null = the uniform shift
     const int* group_shift;

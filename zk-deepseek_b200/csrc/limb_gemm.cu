@@ -138,7 +138,8 @@ __global__ void __launch_bounds__(256)
 split_rows_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, int64_t rows, int64_t K,
                   int64_t Kp, int64_t sz, int64_t sr, int64_t div, int64_t plane_stride,
                   unsigned* overflow, unsigned long long* absmax_out, int64_t dst_pitch, int64_t valid_H,
-                  int64_t valid_start, int tpr_log2, unsigned nb, unsigned gx, int z_fast, int shl)
+                  int64_t valid_start, int tpr_log2, unsigned nb, unsigned gx, int z_fast, int shl,
+                  const int* __restrict__ row_index)
 {
     uint64_t seen = 0;
     bool ovf = false;
@@ -163,7 +164,14 @@ split_rows_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, i
             const int64_t lim = valid_start + r / valid_H + 1;
             Kv = lim < K ? lim : K;
         }
-        const T* xr = x + r * sr;
+        // row_index: plane row r is source row row_index[r] (a gather fused into the split); a negative
+        // entry is a padding row of zeros
+        int64_t rs = r;
+        if (row_index) {
+            rs = row_index[r];
+            if (rs < 0) Kv = 0;
+        }
+        const T* xr = x + (rs < 0 ? 0 : rs) * sr;
         int8_t* drow = planes + (z * rows + r) * dst_pitch;
 #pragma unroll 2
         for (int64_t qd = lane_q; qd < quads; qd += tpr) {
@@ -523,6 +531,11 @@ struct LimbParams {
     // more into a small extra set right of the main one, which yields the carry that separates
     // floor((S1+a1)/2^shift) + floor((S2+a2)/2^shift2) from floor((T+a1+2^(shift-shift2) a2)/2^shift)
     int merged_E;
+    // the epilogue that folds the diagonals as they arrive, hands tensor memory back before its
+    // arithmetic and stores from registers (epilogue_merged); set with the merged score mode.  (The same
+    // epilogue on one plain set in a single 64-column buffer measured slower than the one-tile kernel
+    // with 80-column tiles on P.KV: 8.6 against 8.0 ms.)
+    int fold_epilogue;
     unsigned backoff;         // 1: waiting warps sleep between polls (see mbar_wait), 0: they poll back to back
     int wide_chunk;           // epilogue: fetch a warp's 12 or 16 columns with one wait instead of 4 or 8 at a time
     // optional wait accounting (null = off): [0] MMA warp cycles waiting for operand stages, [1] for
@@ -1182,7 +1195,7 @@ __device__ __forceinline__ void epilogue_merged(const LimbParams& p, uint32_t tq
                                                 uint32_t release_extra)
 {
     int64_t T[CW];
-    uint32_t R[CW];
+    uint32_t R[EE ? CW : 1];
 #pragma unroll
     for (int d = 0; d < DD; ++d) {
         int32_t a[CW];
@@ -1214,13 +1227,15 @@ __device__ __forceinline__ void epilogue_merged(const LimbParams& p, uint32_t tq
     __syncwarp();
     if (lane == 0) {
         mbar_arrive(release_main);
-        mbar_arrive(release_extra);
+        if (EE) mbar_arrive(release_extra);
     }
 
     const int64_t m = tc.m0 + q * 32 + lane;
     const int64_t srow = p.causal_H ? m / p.causal_H : 0;
     const int64_t nbase = tc.n0 + c0;
-    const uint32_t mask = (1u << p.shift) - 1u;
+    const int sh = p.shift >= 63 ? 63 : p.shift;
+    const uint32_t mask = EE ? (1u << p.shift) - 1u : 0u;
+    const bool tail = p.ep_div || p.causal_H;
     // each thread owns CW consecutive words of one output row: 32-byte stores (one full sector each)
     int64_t* crow = p.C + tc.z * p.c_sz + m * p.c_sm + nbase;
     const bool wide_ok = ((((uintptr_t)p.C) & 31) == 0) && ((p.c_sm & 3) == 0) && ((p.c_sz & 3) == 0) &&
@@ -1232,8 +1247,9 @@ __device__ __forceinline__ void epilogue_merged(const LimbParams& p, uint32_t tq
 #pragma unroll
             for (int h = 0; h < 4; ++h) {
                 const int64_t t = T[c + h];
-                const int64_t v = (t >> p.shift) - (((uint32_t)t & mask) < (R[c + h] & mask) ? 1 : 0);
-                o[h] = score_tail(p, v, nullptr, nbase + c + h, srow);
+                int64_t v = t >> sh;
+                if (EE) v -= (((uint32_t)t & mask) < (R[EE ? c + h : 0] & mask) ? 1 : 0);
+                o[h] = tail ? score_tail(p, v, nullptr, nbase + c + h, srow) : v;
             }
             if (wide_ok) {
                 asm volatile("st.global.v4.b64 [%0], {%1, %2, %3, %4};" ::"l"(crow + c), "l"(o[0]), "l"(o[1]),
@@ -1248,20 +1264,24 @@ __device__ __forceinline__ void epilogue_merged(const LimbParams& p, uint32_t tq
     }
 }
 
-// false when the shape has no compiled specialisation (the two-pass epilogue then does the job)
+// false when the shape has no compiled specialisation
 template <int CW>
 __device__ __forceinline__ bool epilogue_merged_dispatch(const LimbParams& p, int D, uint32_t tq, const TileCoord& tc,
                                                          int q, int lane, int c0, int set_cols, uint32_t rel_main,
                                                          uint32_t rel_extra)
 {
-    if (p.merged_E != 3) return false;
-    switch (D) {
-    case 3: epilogue_merged<3, 3, CW>(p, tq, tc, q, lane, c0, set_cols, rel_main, rel_extra); return true;
-    case 4: epilogue_merged<4, 3, CW>(p, tq, tc, q, lane, c0, set_cols, rel_main, rel_extra); return true;
-    case 5: epilogue_merged<5, 3, CW>(p, tq, tc, q, lane, c0, set_cols, rel_main, rel_extra); return true;
-    case 6: epilogue_merged<6, 3, CW>(p, tq, tc, q, lane, c0, set_cols, rel_main, rel_extra); return true;
-    default: return false;
+#define ZKDS_EM(DD, EE) epilogue_merged<DD, EE, CW>(p, tq, tc, q, lane, c0, set_cols, rel_main, rel_extra); return true
+    if (p.merged_E == 3) {
+        switch (D) {
+        case 3: ZKDS_EM(3, 3);
+        case 4: ZKDS_EM(4, 3);
+        case 5: ZKDS_EM(5, 3);
+        case 6: ZKDS_EM(6, 3);
+        default: return false;
+        }
     }
+#undef ZKDS_EM
+    return false;
 }
 
 template <int EW>
@@ -1478,13 +1498,14 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             tc_fence_after();
             const uint32_t tq = lane_base + (uint32_t)(b * buf_cols);
             const uint32_t rel = split ? bar_tempty : 0u;
-            if (p.merged_E) {
-                // the launcher only merges shapes this epilogue is compiled for
+            if (p.fold_epilogue) {
+                // the launcher only asks for this epilogue on shapes it is compiled for
                 bool done = false;
-                if (split && CW == 16)
-                    done = epilogue_merged_dispatch<16>(p, D, tq, tc, q, lane, c0, set_cols, bar_tempty, bar_tempty + 8);
-                else if (split && CW == 8)
-                    done = epilogue_merged_dispatch<8>(p, D, tq, tc, q, lane, c0, set_cols, bar_tempty, bar_tempty + 8);
+                const uint32_t rel_extra = p.merged_E ? bar_tempty + 8 : 0u;
+                if (CW == 16)
+                    done = epilogue_merged_dispatch<16>(p, D, tq, tc, q, lane, c0, set_cols, bar_tempty, rel_extra);
+                else if (CW == 8)
+                    done = epilogue_merged_dispatch<8>(p, D, tq, tc, q, lane, c0, set_cols, bar_tempty, rel_extra);
                 if (!done) {
                     if (lane == 0) *abort_flag = 1;
                     break;
@@ -1594,7 +1615,7 @@ template <typename T>
 int launch_split_t(const T* X, int8_t* planes, int L, int64_t nb, int64_t rows, int64_t K, int64_t Kp,
                    int64_t sz, int64_t sr, int64_t sk, int64_t div, unsigned* overflow, cudaStream_t st,
                    unsigned long long* absmax_out = nullptr, int64_t dst_pitch = 0, int64_t valid_H = 0,
-                   int64_t valid_start = 0, int shl = 0)
+                   int64_t valid_start = 0, int shl = 0, const int* row_index = nullptr)
 {
     if (dst_pitch == 0) dst_pitch = Kp;
     int64_t total = rows * (Kp >> 2);
@@ -1615,7 +1636,8 @@ int launch_split_t(const T* X, int8_t* planes, int L, int64_t nb, int64_t rows, 
 #define ZKDS_SPLIT_ROWS(LL)                                                                              \
     split_rows_kernel<T, LL><<<g2, 256, 0, st>>>(X, planes, L, rows, K, Kp, sz, sr, div,                  \
                                                  nb * rows * dst_pitch, overflow, absmax_out, dst_pitch, \
-                                                 valid_H, valid_start, tl, (unsigned)nb, (unsigned)gx, z_fast, shl)
+                                                 valid_H, valid_start, tl, (unsigned)nb, (unsigned)gx, z_fast, shl, \
+                                                 row_index)
         switch (L) {
         case 2: ZKDS_SPLIT_ROWS(2); break;
         case 3: ZKDS_SPLIT_ROWS(3); break;
@@ -1626,7 +1648,7 @@ int launch_split_t(const T* X, int8_t* planes, int L, int64_t nb, int64_t rows, 
 #undef ZKDS_SPLIT_ROWS
         return check_launch();
     }
-    if (shl) return ZKDS_ERR_UNSUPPORTED;        // only the k-contiguous kernel scales
+    if (shl || row_index) return ZKDS_ERR_UNSUPPORTED;        // only the k-contiguous kernel scales or gathers
     dim3 grid((unsigned)bx, (unsigned)nb);
     split_kernel<T><<<grid, 256, 0, st>>>(X, planes, L, rows, K, Kp, sz, sr, sk, div, nb * rows * dst_pitch,
                                           overflow, absmax_out, dst_pitch, valid_H, valid_start);
@@ -1917,7 +1939,8 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
                                    d_absmax, p.skip_k ? p.skip_H : 0, p.softmax_S, p.skip_start, st);
     } else
         rc = launch_split_t<int64_t>(p.A, pa, La, p.batches, p.M, p.K, Kp16, p.a_sz, p.a_sm, 1, p.a_div,
-                                     fl->overflow_dev, st, d_absmax, 0, p.skip_k ? p.skip_H : 0, p.skip_start);
+                                     fl->overflow_dev, st, d_absmax, 0, p.skip_k ? p.skip_H : 0, p.skip_start, 0,
+                                     p.a_row_index);
     if (rc != ZKDS_OK) return rc;
     int8_t* pb;
     if (pre_b) pb = pre_b->data;
@@ -2119,6 +2142,7 @@ int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st)
     lp.nbuf = nbuf;
     lp.split_release = (nbuf == 1 && (E || !getenv("ZKDS_NO_SPLIT_RELEASE"))) ? 1 : 0;
     lp.merged_E = E;
+    lp.fold_epilogue = E ? 1 : 0;
     lp.M = f.M; lp.N = f.N; lp.batches = f.batches;
     lp.a_rows_per_limb = a_rows; lp.b_rows_per_limb = b_rows;
     lp.b_batched = 1;

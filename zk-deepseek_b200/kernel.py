@@ -101,6 +101,7 @@ _sig("zkds_softmax_causal", [_vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _vp])
 _sig("zkds_softmax_pv", [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _i, _ll, _i, _i, _i, _vp])
 _sig("zkds_einsum_bsht_btc_bshc_causal", [_vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _i, _i, _i, _vp])
 _sig("zkds_grouped_prepared", [_vp, _vp, _vp, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _i, _i, _vp])
+_sig("zkds_grouped_gather_prepared", [_vp, _vp, _vp, _vp, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _i, _i, _vp])
 _sig("zkds_glu_q23", [_vp, _vp, _ll, _vp, _vp, _vp, _ll, _ll, _vp])
 _sig("zkds_gather_rows", [_vp, _vp, _vp, _ll, _ll, _vp])
 _sig("zkds_moe_combine", [_vp, _vp, _vp, _vp, _vp, _ll, _i, _ll, _vp])
@@ -358,24 +359,36 @@ def einsum_heads_prepared(A, planes, rescale, rounding, a_limbs=0, dynamic=False
 
 
 def grouped_prepared(A, planes, tile_group, c_rescale, a_limbs=0, dynamic=False, group_shift=None,
-                     n_split=0):
+                     n_split=0, row_index=None):
     """Routed-expert linear layer: A flat (n_tiles*128, K), tile_group int32 (n_tiles,) on the
     device (expert of each 128-row tile, negative = unused) -> C (n_tiles*128, N).
     group_shift: optional int32 (experts, 2) device tensor of per-expert shifts for the output
-    columns below / from n_split; otherwise the uniform c_rescale."""
+    columns below / from n_split; otherwise the uniform c_rescale.
+    row_index: optional int32 (n_tiles*128,) device tensor; row m of the grouped matrix is then
+    A[row_index[m]] (zeros where negative) and A is the un-gathered (tokens, K) matrix: the
+    index_select of model.py:1372-1378 happens inside the limb split (a_limbs must be given)."""
     if group_shift is not None:
         assert group_shift.dtype == torch.int32 and group_shift.is_cuda and group_shift.is_contiguous()
     _dev_i64(A, "A")
     assert tile_group.dtype == torch.int32 and tile_group.is_cuda and tile_group.is_contiguous()
     n_tiles = tile_group.numel()
-    assert A.shape == (n_tiles * 128, planes.K)
     C = torch.empty((n_tiles * 128, planes.N), dtype=torch.int64, device=A.device)
+    gs = group_shift.data_ptr() if group_shift is not None else None
     with torch.cuda.device(A.device):
-        _check(lib.zkds_grouped_prepared(A.data_ptr(), planes.handle, tile_group.data_ptr(), n_tiles,
-                                         C.data_ptr(), 1, 0, int(c_rescale),
-                                         group_shift.data_ptr() if group_shift is not None else None,
-                                         int(n_split), a_limbs, _a_flags(a_limbs, dynamic), _stream()),
-               "grouped_prepared")
+        if row_index is None:
+            assert A.shape == (n_tiles * 128, planes.K)
+            _check(lib.zkds_grouped_prepared(A.data_ptr(), planes.handle, tile_group.data_ptr(), n_tiles,
+                                             C.data_ptr(), 1, 0, int(c_rescale), gs, int(n_split), a_limbs,
+                                             _a_flags(a_limbs, dynamic), _stream()), "grouped_prepared")
+        else:
+            assert row_index.dtype == torch.int32 and row_index.is_cuda and row_index.is_contiguous()
+            assert row_index.numel() == n_tiles * 128 and A.dim() == 2 and A.shape[1] == planes.K and a_limbs > 0
+            if A.shape[0] == 0:      # nothing to gather from (every index is negative): one row of zeros
+                A = torch.zeros((1, planes.K), dtype=torch.int64, device=A.device)
+            _check(lib.zkds_grouped_gather_prepared(A.data_ptr(), row_index.data_ptr(), planes.handle,
+                                                    tile_group.data_ptr(), n_tiles, C.data_ptr(), 1, 0,
+                                                    int(c_rescale), gs, int(n_split), a_limbs,
+                                                    _a_flags(a_limbs, dynamic), _stream()), "grouped_prepared")
     return C
 
 

@@ -722,9 +722,10 @@ class MoE(nn.Module):
         w13, w2, s13, s2 = self._prepared()
         lim = ACT_LIMBS if ACT_LIMBS > 0 else 5
         row_src, pos, tile_group, counts = self.route(indices)
-        xp = K.gather_rows(x, row_src)
         I = self.moe_inter_dim
-        r13 = K.grouped_prepared(xp, w13, tile_group, 0, a_limbs=lim, dynamic=True, group_shift=s13, n_split=I)
+        # the dispatch gather (model.py:1372-1378) runs inside the limb split of the first GEMM
+        r13 = K.grouped_prepared(x.contiguous(), w13, tile_group, 0, a_limbs=lim, dynamic=True, group_shift=s13,
+                                 n_split=I, row_index=row_src)
         if snark:
             h, sl = K.glu_q23(r13[:, :I], r13[:, I:], ld=2 * I, want_silu=True)
             self._dump_experts(start_pos, r13[:, :I], sl, counts)
