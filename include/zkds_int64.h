@@ -247,6 +247,18 @@ int zkds_grouped_gather_prepared(const int64_t* A, const int* row_index, const v
                                  int64_t n_tiles, int64_t* C, int64_t a_rescale, int64_t addend, int64_t shift,
                                  const int* group_shift, int64_t n_split, int a_limbs, int flags, void* stream);
 
+/* The down projection of a gated MLP with the gate folded into its limb split (model.py:1034-1049 and
+ * 1271-1281: `(silu_q23(r1) * r2) >> 23` followed by w2): C[rows, N] = (sum_k h[m,k] * W2[n,k]) >> shift with
+ * h = (silu_q23(r1) * r2) >> 23 (wrapping product, arithmetic shift) produced directly as int8 limb planes,
+ * never stored as int64.  r1, r2: rows of K words with row stride ld (both halves of a stacked w1|w3 output);
+ * lut: the Q23 table of silu_init_q23; planes: W2 (zkds_planes_create); tile_group / group_shift / n_split as
+ * in zkds_grouped_prepared (rows a multiple of 128 then) or null for a plain linear layer; a_limbs > 0.
+ * Returns ZKDS_ERR_UNSUPPORTED (silently) for odd K or ld, unaligned pointers or shapes the limb kernel
+ * declines; callers then use zkds_glu_q23 and the linear entry point. */
+int zkds_glu_prepared(const int64_t* r1, const int64_t* r2, int64_t ld, const int64_t* lut, int64_t rows,
+                      const void* planes, const int* tile_group, int64_t* C, int64_t shift,
+                      const int* group_shift, int64_t n_split, int a_limbs, int flags, void* stream);
+
 /* Replaces complex_int64_mul (int64_gemm.cu:274-286) with the product shift as a
  * parameter (the reference hard-codes 42). */
 int zkds_rope(const int64_t* A, const int64_t* table, int64_t* C, int64_t batch, int64_t seq,

@@ -369,6 +369,38 @@ def test_glu_gather_combine(kmod, orc, dev):
     same(y, want, "combine")
 
 
+@pytest.mark.parametrize("rows,n,N", [(37, 258, 70), (256, 2048, 96), (5, 16, 8)])
+def test_gated_mlp_tail_in_one_call(kmod, orc, dev, rows, n, N):
+    """(silu_q23(r1) * r2) >> 23 followed by w2 (model.py:1034-1049) with the gated product kept as limb
+    planes, against the oracle's activation and GEMM; plain and grouped (expert) form"""
+    rng = np.random.default_rng(rows + n)
+    r12 = np.rint(rng.standard_normal((rows, 2 * n)) * 2.0**24).astype(np.int64)
+    r12[0, :4] = [64 << 23, -(64 << 23), (64 << 23) - 1, 0]
+    W2 = rand_i64(rng, (N, n), 30).astype(np.int32)
+    h = (orc.act(np.ascontiguousarray(r12[:, :n]), "silu", 23) * r12[:, n:]) >> 23
+    want, _ = orc.gemm(h[None], W2, 1, 1, 31)
+    d = g(r12, dev)
+    kmod.silu_init_q23()
+    got = kmod.glu_prepared(d[:, :n], d[:, n:], kmod.WeightPlanes(g(W2, dev)), 31, ld=2 * n, a_limbs=5)
+    assert got is not None
+    same(got, want[0], "gate + down projection")
+    if rows == 256:      # two expert tiles with their own weights and shifts, one unused tile in between
+        W = np.stack([W2, rand_i64(rng, (N, n), 30).astype(np.int32)])
+        tg = torch.tensor([1, -1, 0], dtype=torch.int32, device=dev)
+        sh = g(np.array([[29, 29], [33, 33]], np.int32), dev)
+        pad = np.concatenate([r12[:128], np.zeros((128, 2 * n), np.int64), r12[128:]])
+        dp = g(pad, dev)
+        got = kmod.glu_prepared(dp[:, :n], dp[:, n:], kmod.WeightPlanes(g(W, dev)), 0, ld=2 * n, a_limbs=5,
+                                tile_group=tg, group_shift=sh, n_split=0)
+        assert got is not None
+        want_g = np.zeros((384, N), np.int64)
+        want_g[:128] = orc.gemm(h[None, :128], W[1], 1, 1, 33)[0][0]
+        want_g[256:] = orc.gemm(h[None, 128:], W[0], 1, 1, 29)[0][0]
+        same(got, want_g, "grouped gate + down projection")
+    torch.cuda.synchronize()
+    kmod.device_status()
+
+
 def test_grouped_expert_gemm_with_and_without_fused_gather(kmod, orc, dev):
     """all experts of a routed layer in one launch (model.py:1372-1378): rows grouped by expert in
     128-row tiles, per-expert shifts left / right of n_split; the row gather as a separate pass and

@@ -398,6 +398,35 @@ static int grouped_prepared(const int64_t* A, const int* row_index, const void* 
                             int64_t n_tiles, int64_t* C, int64_t a_rescale, int64_t addend, int64_t shift,
                             const int* group_shift, int64_t n_split, int a_limbs, int flags, void* stream);
 
+int zkds_glu_prepared(const int64_t* r1, const int64_t* r2, int64_t ld, const int64_t* lut, int64_t rows,
+                      const void* planes, const int* tile_group, int64_t* C, int64_t shift,
+                      const int* group_shift, int64_t n_split, int a_limbs, int flags, void* stream)
+{
+    if (!planes || rows < 0 || a_limbs <= 0 || (group_shift && (n_split & 7)) || (tile_group && (rows & 127)))
+        return finish(ZKDS_ERR_ARG, "zkds_glu_prepared");
+    if (rows == 0) return finish(ZKDS_OK, "zkds_glu_prepared");
+    if (!r1 || !r2 || !lut || !C) return finish(ZKDS_ERR_ARG, "zkds_glu_prepared");
+    const PlanesHandle* hd = (const PlanesHandle*)planes;
+    if (!glu_planes_supported(r1, r2, ld, hd->pl.K)) { t_status = ZKDS_ERR_UNSUPPORTED; return t_status; }
+    Contraction p{};
+    p.A = r1; p.B = nullptr; p.b_bits = hd->b_bits; p.C = C; p.R = nullptr;
+    p.batches = 1; p.M = rows; p.N = hd->pl.rows; p.K = hd->pl.K;
+    p.a_sz = 0; p.a_sm = ld;
+    p.b_sz = tile_group ? 1 : 0; p.b_sn = 0; p.b_sk = 0;
+    p.c_sz = 0; p.c_sm = hd->pl.rows;
+    p.a_div = 1; p.b_div = 1;
+    p.addend = 0;
+    p.shift = (shift < 0 || shift > 127) ? -1 : (int)shift;
+    p.tile_group = tile_group;
+    p.group_shift = group_shift; p.n_split = n_split;
+    p.glu_r2 = r2; p.glu_lut = lut;
+    p.dynamic_a = (flags & ZKDS_LIMBS_DYNAMIC) ? 1 : 0;
+    if (p.shift < 0) return finish(ZKDS_ERR_ARG, "zkds_glu_prepared");
+    int rc = launch_contraction_limb(p, a_limbs, 0, &hd->pl, ST(stream));
+    if (rc == ZKDS_ERR_UNSUPPORTED) { t_status = rc; return rc; }
+    return finish(rc, "zkds_glu_prepared");
+}
+
 int zkds_grouped_prepared(const int64_t* A, const void* planes, const int* tile_group, int64_t n_tiles,
                           int64_t* C, int64_t a_rescale, int64_t addend, int64_t shift,
                           const int* group_shift, int64_t n_split, int a_limbs, int flags, void* stream)

@@ -1075,6 +1075,111 @@ int launch_glu(const int64_t* r1, const int64_t* r2, int64_t ld, int64_t* h, int
     return check_launch();
 }
 
+// The gated product written as signed 8-bit limb planes (the A operand of the w2 contraction) instead
+// of int64 words: plane l of row r at planes + l * plane_stride + r * Kp, balanced radix-256 digits as
+// in the limb split, columns from n to Kp zero.  A CTA is a (rows x threads-per-row) grid, four
+// consecutive columns per thread; the largest magnitude seen goes to absmax_out, a value the L limbs
+// cannot hold raises *overflow.
+template <int LL>      // limb count known at compile time, 0 = use L
+__global__ void __launch_bounds__(kThreads)
+glu_planes_kernel(const int64_t* __restrict__ r1, const int64_t* __restrict__ r2, int64_t ld,
+                  const int64_t* __restrict__ lut_g, int8_t* __restrict__ planes, int L, int64_t rows, int64_t n,
+                  int64_t Kp, int64_t plane_stride, unsigned* overflow, unsigned long long* absmax_out,
+                  int tpr_log2)
+{
+    __shared__ int64_t lut[256];
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) lut[i] = lut_g[i];
+    __syncthreads();
+    uint64_t seen = 0;
+    bool ovf = false;
+    const int64_t quads = Kp >> 2;
+    const int tpr = 1 << tpr_log2;
+    const int lane_q = threadIdx.x & (tpr - 1);
+    const int64_t rpb = kThreads >> tpr_log2;
+    for (int64_t r = (int64_t)blockIdx.x * rpb + (threadIdx.x >> tpr_log2); r < rows;
+         r += (int64_t)gridDim.x * rpb) {
+        const int64_t* a = r1 + r * ld;
+        const int64_t* b = r2 + r * ld;
+        int8_t* drow = planes + r * Kp;
+        for (int64_t qd = lane_q; qd < quads; qd += tpr) {
+            const int64_t k0 = qd << 2;
+            int64_t v[4] = {0, 0, 0, 0};
+            if (k0 + 4 <= n) {
+                const longlong2 a0 = *reinterpret_cast<const longlong2*>(a + k0);
+                const longlong2 a1 = *reinterpret_cast<const longlong2*>(a + k0 + 2);
+                const longlong2 b0 = *reinterpret_cast<const longlong2*>(b + k0);
+                const longlong2 b1 = *reinterpret_cast<const longlong2*>(b + k0 + 2);
+                v[0] = (int64_t)((uint64_t)act_one<23, true>(a0.x, lut) * (uint64_t)b0.x) >> 23;
+                v[1] = (int64_t)((uint64_t)act_one<23, true>(a0.y, lut) * (uint64_t)b0.y) >> 23;
+                v[2] = (int64_t)((uint64_t)act_one<23, true>(a1.x, lut) * (uint64_t)b1.x) >> 23;
+                v[3] = (int64_t)((uint64_t)act_one<23, true>(a1.y, lut) * (uint64_t)b1.y) >> 23;
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (k0 + j < n)
+                        v[j] = (int64_t)((uint64_t)act_one<23, true>(a[k0 + j], lut) * (uint64_t)b[k0 + j]) >> 23;
+            }
+            constexpr int LMAX = LL ? LL : 9;
+            uint32_t w[LMAX];
+#pragma unroll
+            for (int l = 0; l < LMAX; ++l) w[l] = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                int64_t u = v[j];
+                const uint64_t mag = (uint64_t)(u ^ (u >> 63));
+                seen = mag > seen ? mag : seen;
+#pragma unroll
+                for (int l = 0; l < LMAX; ++l) {
+                    if (LL || l < L) {
+                        w[l] |= (uint32_t)(u & 0xFF) << (j * 8);
+                        u = (u >> 8) + ((u >> 7) & 1);
+                    }
+                }
+                ovf |= (u != 0);
+            }
+#pragma unroll
+            for (int l = 0; l < LMAX; ++l)
+                if (LL || l < L) *reinterpret_cast<uint32_t*>(drow + k0 + l * plane_stride) = w[l];
+        }
+    }
+    if (ovf) *overflow = 1u;
+    if (absmax_out) {
+        seen = warp_max_u64(seen);
+        if ((threadIdx.x & 31) == 0 && seen) atomicMax(absmax_out, (unsigned long long)seen);
+    }
+}
+
+bool glu_planes_supported(const int64_t* r1, const int64_t* r2, int64_t ld, int64_t n)
+{
+    return n > 0 && (n & 1) == 0 && (ld & 1) == 0 && ((((uintptr_t)r1 | (uintptr_t)r2) & 15) == 0);
+}
+
+int launch_glu_planes(const int64_t* r1, const int64_t* r2, int64_t ld, const int64_t* lut, int8_t* planes, int L,
+                      int64_t rows, int64_t n, int64_t Kp, int64_t plane_stride, unsigned* overflow,
+                      unsigned long long* absmax_out, cudaStream_t st)
+{
+    if (rows == 0) return ZKDS_OK;
+    if (!glu_planes_supported(r1, r2, ld, n) || L < 1 || L > 9 || (Kp & 3) || Kp < n) return ZKDS_ERR_UNSUPPORTED;
+    int tl = 0;
+    while (tl < 8 && (1 << tl) < (Kp >> 2)) ++tl;
+    const int64_t rpb = kThreads >> tl;
+    int64_t grid = (rows + rpb - 1) / rpb;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    if (grid > cap) grid = cap;
+#define ZKDS_GP(LL)                                                                                         \
+    glu_planes_kernel<LL><<<(unsigned)grid, kThreads, 0, st>>>(r1, r2, ld, lut, planes, L, rows, n, Kp,     \
+                                                               plane_stride, overflow, absmax_out, tl)
+    switch (L) {
+    case 2: ZKDS_GP(2); break;
+    case 3: ZKDS_GP(3); break;
+    case 4: ZKDS_GP(4); break;
+    case 5: ZKDS_GP(5); break;
+    default: ZKDS_GP(0); break;
+    }
+#undef ZKDS_GP
+    return check_launch();
+}
+
 // dst[r][:] = src[index[r]][:] for index[r] >= 0, zeros otherwise (token rows -> expert order)
 __global__ void __launch_bounds__(kThreads)
 gather_rows_kernel(const longlong2* __restrict__ src, const int* __restrict__ index,

@@ -32,6 +32,11 @@ int launch_rmsnorm(const int64_t* A, const void* W, int w_bits, const int64_t* r
 
 int launch_glu(const int64_t* r1, const int64_t* r2, int64_t ld, int64_t* h, int64_t* s1_out,
                const int64_t* lut, int64_t rows, int64_t n, cudaStream_t st);
+// (silu_q23(r1) * r2) >> 23 written as limb planes (see launch_softmax_planes for the layout)
+bool glu_planes_supported(const int64_t* r1, const int64_t* r2, int64_t ld, int64_t n);
+int launch_glu_planes(const int64_t* r1, const int64_t* r2, int64_t ld, const int64_t* lut, int8_t* planes, int L,
+                      int64_t rows, int64_t n, int64_t Kp, int64_t plane_stride, unsigned* overflow,
+                      unsigned long long* absmax_out, cudaStream_t st);
 int launch_gather_rows(const int64_t* src, const int* index, int64_t* dst, int64_t rows, int64_t cols,
                        cudaStream_t st);
 int launch_moe_combine(const int64_t* out, const int* pos, const int64_t* w, const int64_t* base,
@@ -87,6 +92,11 @@ struct Contraction {
     // (limb kernel only; softmax_S = sequence positions per batch when skip_k is set)
     const int64_t* softmax_lut;
     int64_t softmax_S;
+    // A is r1 of a gated MLP (rows of K words, row stride a_sm): the limb planes are produced from
+    // (silu_q23(A) * glu_r2) >> 23, glu_r2 with the same row stride, and the gated product never reaches
+    // memory as int64 (limb kernel only, batches == 1)
+    const int64_t* glu_r2;
+    const int64_t* glu_lut;
 };
 
 // CUDA-core path: exact for every input, any shape (gemm_exact.cu)

@@ -1937,6 +1937,10 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
         if (p.a_sm != p.K || p.a_sz != p.M * p.K || p.a_div != 1) return ZKDS_ERR_ARG;
         rc = launch_softmax_planes(p.A, p.softmax_lut, pa, La, a_rows, p.K, Kp, a_rows * Kp, fl->overflow_dev,
                                    d_absmax, p.skip_k ? p.skip_H : 0, p.softmax_S, p.skip_start, st);
+    } else if (p.glu_lut) {
+        if (p.batches != 1 || p.a_div != 1 || p.a_row_index || !p.glu_r2) return ZKDS_ERR_ARG;
+        rc = launch_glu_planes(p.A, p.glu_r2, p.a_sm, p.glu_lut, pa, La, a_rows, p.K, Kp, a_rows * Kp,
+                               fl->overflow_dev, d_absmax, st);
     } else
         rc = launch_split_t<int64_t>(p.A, pa, La, p.batches, p.M, p.K, Kp16, p.a_sz, p.a_sm, 1, p.a_div,
                                      fl->overflow_dev, st, d_absmax, 0, p.skip_k ? p.skip_H : 0, p.skip_start, 0,

@@ -101,6 +101,7 @@ _sig("zkds_softmax_causal", [_vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _vp])
 _sig("zkds_softmax_pv", [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _i, _ll, _i, _i, _i, _vp])
 _sig("zkds_einsum_bsht_btc_bshc_causal", [_vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _i, _i, _i, _vp])
 _sig("zkds_grouped_prepared", [_vp, _vp, _vp, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _i, _i, _vp])
+_sig("zkds_glu_prepared", [_vp, _vp, _ll, _vp, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _i, _i, _vp])
 _sig("zkds_grouped_gather_prepared", [_vp, _vp, _vp, _vp, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _i, _i, _vp])
 _sig("zkds_glu_q23", [_vp, _vp, _ll, _vp, _vp, _vp, _ll, _ll, _vp])
 _sig("zkds_gather_rows", [_vp, _vp, _vp, _ll, _ll, _vp])
@@ -389,6 +390,37 @@ def grouped_prepared(A, planes, tile_group, c_rescale, a_limbs=0, dynamic=False,
                                                     tile_group.data_ptr(), n_tiles, C.data_ptr(), 1, 0,
                                                     int(c_rescale), gs, int(n_split), a_limbs,
                                                     _a_flags(a_limbs, dynamic), _stream()), "grouped_prepared")
+    return C
+
+
+def glu_prepared(r1, r2, planes, c_rescale, ld=None, a_limbs=3, dynamic=True, tile_group=None,
+                 group_shift=None, n_split=0):
+    """w2 of a gated MLP with the gate inside its limb split: C = (h @ W2^T) >> c_rescale with
+    h = (silu_q23(r1) * r2) >> 23 (model.py:1034-1049, 1271-1281); h only ever exists as int8 limb
+    planes.  r1, r2: (rows, K) views sharing the row stride ld (default K); planes: prepared W2, or
+    the experts' stacked W2 together with tile_group (and group_shift) as in grouped_prepared.
+    Returns None when the kernel does not take the shape (use glu_q23 and the linear layer then)."""
+    for t_, name in ((r1, "r1"), (r2, "r2")):     # strided row views of one buffer are the normal case
+        assert t_.dtype == torch.int64 and t_.is_cuda and t_.dim() == 2 and t_.stride(1) == 1, name
+    rows, n = r1.shape
+    ld = n if ld is None else ld
+    assert r2.shape == r1.shape and n == planes.K and a_limbs > 0
+    assert rows <= 1 or (r1.stride(0) == ld and r2.stride(0) == ld)
+    lut = _lut_on(EXP2_FRAC_LUT_Q23, r1.device, "silu_init_q23")
+    if tile_group is not None:
+        assert tile_group.dtype == torch.int32 and tile_group.is_cuda and tile_group.is_contiguous()
+        assert rows == tile_group.numel() * 128
+    if group_shift is not None:
+        assert group_shift.dtype == torch.int32 and group_shift.is_cuda and group_shift.is_contiguous()
+    C = torch.empty((rows, planes.N), dtype=torch.int64, device=r1.device)
+    with torch.cuda.device(r1.device):
+        rc = lib.zkds_glu_prepared(r1.data_ptr(), r2.data_ptr(), ld, lut.data_ptr(), rows, planes.handle,
+                                   tile_group.data_ptr() if tile_group is not None else None, C.data_ptr(),
+                                   int(c_rescale), group_shift.data_ptr() if group_shift is not None else None,
+                                   int(n_split), a_limbs, _a_flags(a_limbs, dynamic), _stream())
+    if rc == 6:
+        return None
+    _check(rc, "glu_prepared")
     return C
 
 

@@ -522,6 +522,12 @@ class MLP_int(nn.Module):
             saveTensor(f"{d}/mlp_silu_x.bin", r1.contiguous().view(x.shape[0], -1, n))
             saveTensor(f"{d}/mlp_silu_y.bin", sl.view(x.shape[0], -1, n))
         else:
+            if self.parts == 1 and lim > 0 and self.w2.x_rescale == 1 and \
+                    K.limb_kernel_takes(n, lim, self.w2.planes().limbs):
+                # gate and down projection in one call: h only exists as limb planes
+                out = K.glu_prepared(r1, r2, self.w2.planes(), self.w2.shift(), ld=ld, a_limbs=lim, dynamic=True)
+                if out is not None:
+                    return out.view(*x.shape[:-1], -1)
             h = K.glu_q23(r1, r2, ld=ld)
         h = h.view(*x.shape[:-1], n)
         if self.parts > 1:
@@ -730,6 +736,10 @@ class MoE(nn.Module):
             h, sl = K.glu_q23(r13[:, :I], r13[:, I:], ld=2 * I, want_silu=True)
             self._dump_experts(start_pos, r13[:, :I], sl, counts)
         else:
+            out = K.glu_prepared(r13[:, :I], r13[:, I:], w2, 0, ld=2 * I, a_limbs=lim, dynamic=True,
+                                 tile_group=tile_group, group_shift=s2, n_split=0)
+            if out is not None:
+                return K.moe_combine(out, pos, weights.contiguous(), base)
             h = K.glu_q23(r13[:, :I], r13[:, I:], ld=2 * I)
         out = K.grouped_prepared(h, w2, tile_group, 0, a_limbs=lim, dynamic=True, group_shift=s2, n_split=0)
         return K.moe_combine(out, pos, weights.contiguous(), base)
