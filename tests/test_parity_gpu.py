@@ -255,7 +255,8 @@ def test_rope(kmod, orc, dev, shape, shift):
 # ---- RMSNorm ------------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("M,N,bits,wdt", [(64, 7168, 17, np.int32), (33, 1536, 37, np.int32),
-                                          (5, 512, 50, np.int64), (3, 7, 3, np.int32),
+                                          (5, 512, 50, np.int64), (3, 7, 3, np.int32), (1300, 1536, 20, np.int32),
+                                          (700, 7168, 33, np.int64),
                                           (2, 30001, 31, np.int64)])
 def test_rms_norm(kmod, orc, dev, M, N, bits, wdt):
     rng = np.random.default_rng(N)
