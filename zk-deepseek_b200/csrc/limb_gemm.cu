@@ -1887,7 +1887,12 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     size_t psmem = 0;
     int ew = persistent_epilogue_warps(false);
     if (ew == 12) ew = 16;          // three warps per lane quarter only divide a 48-column tile
-    if (!p.R && !p.skip_k && (Kp + kBlockK - 1) / kBlockK <= 16 && !getenv("ZKDS_NO_PERSISTENT") &&
+    // up to 8 K blocks (K <= 1024); measured: from 12 blocks on the one-tile kernel with its wider tile
+    // (a full 256-column B stack for two-limb weights) wins although it overlaps nothing
+    // (wq_b, K = 1536: 0.70 against 0.85 ms; w2 of the shared expert, K = 2048: 0.68 against 0.93 ms)
+    int64_t max_kb = 8;
+    if (const char* e = getenv("ZKDS_PERSISTENT_MAX_KB")) max_kb = atoi(e);
+    if (!p.R && !p.skip_k && (Kp + kBlockK - 1) / kBlockK <= max_kb && !getenv("ZKDS_NO_PERSISTENT") &&
         !(p.tile_group && getenv("ZKDS_NO_PERSISTENT_GROUPED"))) {
         for (int cand : {64, 48, 32, 16}) {
             if (Lb * cand > 256 || 2 * D * cand > 512) continue;
