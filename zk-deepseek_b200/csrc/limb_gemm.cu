@@ -384,19 +384,6 @@ __device__ __forceinline__ void tmem_ldn(uint32_t taddr, int32_t (&v)[16])
         : "r"(taddr)
         : "memory");
 }
-__device__ __forceinline__ void tmem_ldn(uint32_t taddr, int32_t (&v)[12])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11])
-                 : "r"(taddr + 8u)
-                 : "memory");
-}
-
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ void tmem_st8_zero(uint32_t taddr)
@@ -537,7 +524,6 @@ struct LimbParams {
     // with 80-column tiles on P.KV: 8.6 against 8.0 ms.)
     int fold_epilogue;
     unsigned backoff;         // 1: waiting warps sleep between polls (see mbar_wait), 0: they poll back to back
-    int wide_chunk;           // epilogue: fetch a warp's 12 or 16 columns with one wait instead of 4 or 8 at a time
     // optional wait accounting (null = off): [0] MMA warp cycles waiting for operand stages, [1] for
     // free accumulators, [2] MMA warp total, [3] first epilogue warp cycles waiting for accumulators,
     // [4] its total, summed over CTAs
@@ -1514,12 +1500,7 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                 continue;
             }
             if (p.fits64) {
-                const bool wide = p.wide_chunk && !p.group_shift;   // a wide chunk could straddle n_split
-                if (EW != 12 && wide && (CW == 12 || CW == 24))
-                    epilogue_part<true, 12>(p, tq, D, tc, q, lane, c0, CW, stage, RS, set_cols, rel);
-                else if (EW == 12 && wide && CW == 16)
-                    epilogue_part<true, 16>(p, tq, D, tc, q, lane, c0, CW, stage, RS, set_cols, rel);
-                else if (ch8) epilogue_part<true, 8>(p, tq, D, tc, q, lane, c0, CW, stage, RS, set_cols, rel);
+                if (ch8) epilogue_part<true, 8>(p, tq, D, tc, q, lane, c0, CW, stage, RS, set_cols, rel);
                 else epilogue_part<true, 4>(p, tq, D, tc, q, lane, c0, CW, stage, RS, set_cols, rel);
             } else {
                 if (ch8) epilogue_part<false, 8>(p, tq, D, tc, q, lane, c0, CW, stage, RS, set_cols, rel);
@@ -1778,26 +1759,23 @@ int planes_split(const void* X, int bits, int64_t nb, int64_t rows, int64_t K, i
     return ZKDS_ERR_ARG;
 }
 
-// Epilogue warps of the persistent kernel.  Measured on a B200: the fused attention scores (48-column
-// tile, two sets of five diagonals) run best with 12 warps (three per tensor-memory lane quarter, 16
-// columns each, fetched with one wait); plain contractions show no gain beyond 8, which also keeps
-// 168 registers per thread.  ZKDS_EPI_WARPS = 8 | 12 | 16 overrides for experiments.
+// Epilogue warps of the persistent kernel.  Measured on a B200: the fused attention scores run best with 16
+// (four per tensor-memory lane quarter), plain contractions show no gain beyond 8, which also keeps 168
+// registers per thread.  ZKDS_EPI_WARPS = 8 | 16 overrides for experiments.
 static int persistent_epilogue_warps(bool fused_scores)
 {
     if (const char* e = getenv("ZKDS_EPI_WARPS")) {
         const int v = atoi(e);
-        if (v == 8 || v == 12 || v == 16) return v;
+        if (v == 8 || v == 16) return v;
     }
-    return fused_scores ? 12 : 8;
+    return fused_scores ? 16 : 8;
 }
 
 static int launch_persistent(int ew, int ctas, size_t smem, cudaStream_t st, const CUtensorMap& tmA,
                              const CUtensorMap& tmB, const LimbParams& lp_in)
 {
     LimbParams lp = lp_in;
-    lp.wide_chunk = 0;
     lp.backoff = getenv("ZKDS_NO_BACKOFF") ? 0u : 1u;
-    if (getenv("ZKDS_EPI_WIDE")) lp.wide_chunk = atoi(getenv("ZKDS_EPI_WIDE"));
     // ZKDS_WAIT_PROFILE=1: a synchronous diagnostic run that prints where the MMA warp and the first
     // epilogue warp spent their cycles (share of their lifetime spent waiting)
     unsigned long long* prof = nullptr;
@@ -1821,11 +1799,7 @@ static int launch_persistent(int ew, int ctas, size_t smem, cudaStream_t st, con
                     100.0 * h[3] / (h[4] ? h[4] : 1));
         }
     } report{prof, st, &lp};
-    if (ew == 12) {
-        ZKDS_CUDA(cudaFuncSetAttribute(limb_gemm_persistent_kernel<12>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)(227 * 1024 - 3072)));
-        limb_gemm_persistent_kernel<12><<<ctas, persistent_threads(12), smem, st>>>(tmA, tmB, lp);
-    } else if (ew == 16) {
+    if (ew == 16) {
         ZKDS_CUDA(cudaFuncSetAttribute(limb_gemm_persistent_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)(227 * 1024 - 3072)));
         limb_gemm_persistent_kernel<16><<<ctas, persistent_threads(16), smem, st>>>(tmA, tmB, lp);
@@ -1886,7 +1860,6 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     int pNT = 0, pstages = 0;
     size_t psmem = 0;
     int ew = persistent_epilogue_warps(false);
-    if (ew == 12) ew = 16;          // three warps per lane quarter only divide a 48-column tile
     // up to 8 K blocks (K <= 1024); measured: from 12 blocks on the one-tile kernel with its wider tile
     // (a full 256-column B stack for two-limb weights) wins although it overlaps nothing
     // (wq_b, K = 1536: 0.70 against 0.85 ms; w2 of the shared expert, K = 2048: 0.68 against 0.93 ms)
@@ -2087,8 +2060,7 @@ int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st)
             if (bufs == 2 && cand < 32) continue;
             if (E && (bufs == 2 || cand == 48 || cand == 16)) continue;   // merged: one buffer, 8 or 16 columns per warp
             if (Lb * cand > 256 || (E ? (D + E) : 2 * bufs * D) * cand > 512) continue;
-            // three warps per lane quarter only divide a 48-column tile; merged mode runs 16 warps
-            const int ew_c = E ? 16 : ((ew_pref == 12 && cand != 48) ? 16 : ew_pref);
+            const int ew_c = E ? 16 : ew_pref;        // the one-pass merged epilogue is written for 16 warps
             size_t st_b = (size_t)La * kTileM * kBlockK + (size_t)Lb * cand * kBlockK;
             // the merged epilogue stores straight from registers: no staging tile
             size_t staging = E ? 0 : persistent_staging(ew_c, cand);
