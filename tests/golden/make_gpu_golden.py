@@ -5,7 +5,7 @@ library (built from its unmodified source by oracle/Makefile into oracle/_ref) i
 run here on seeded inputs, called through ctypes exactly as the reference's
 kernel.py does, and the inputs + outputs are stored in ref_gpu_vectors.npz.
 
-    on a GPU box:   python tests/golden/make_gpu_golden.py gpurun_out/ref_gpu_vectors.npz
+    on a GPU box:   python tests/golden/make_gpu_golden.py <output>.npz
     then copy the file to tests/golden/ref_gpu_vectors.npz
 
 check_against() replays every case through the CPU oracle (no GPU needed).
