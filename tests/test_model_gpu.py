@@ -321,7 +321,7 @@ def test_transformer_steps(M, kmod, dev):
     kmod.device_status()
 
 
-def _small_transformer(M, a, rng, dev, batch):
+def _small_transformer(M, a, rng, dev, batch, gate_bias=True):
     with torch.device(dev):
         model = M.Transformer(a)
     model.embed.weight = t(np.rint(rng.standard_normal((a.vocab_size, a.dim)) * 2.0**31).astype(np.int64), dev)
@@ -335,7 +335,7 @@ def _small_transformer(M, a, rng, dev, batch):
         if i < a.n_dense_layers:
             load_mlp(blk.ffn, mlp_weights(rng, a.dim, a.inter_dim), dev)
         else:
-            blk.ffn = build_moe(M, a, moe_weights(rng, a, True), dev)    # dumps write the gate bias
+            blk.ffn = build_moe(M, a, moe_weights(rng, a, gate_bias), dev)    # dumps write the gate bias
         model.layers[i] = blk
     return model
 
@@ -390,4 +390,37 @@ def test_generate_loop(M, kmod, dev, tmp_path):
     assert read_dump(os.path.join(str(tmp_path), "pos_3", "tokens.bin"), np.int64).tolist() == [out[1][0]]
     # the probe of the last layer is the token the step produces
     assert probe_trace[0]["layer_tokens"][-1] == probe_trace[0]["next_token"]
+    kmod.device_status()
+
+
+def test_resident_checkpoint_loader(M, kmod, dev, tmp_path):
+    """a checkpoint directory in the converted layout (embed/norm/head_int, layer-{i}, experts-{l}/{i}
+    safetensors) loaded with every layer resident generates the tokens of the model it was written from"""
+    import importlib
+    from safetensors.torch import save_file, save_model
+    G = importlib.import_module(M.__name__.rsplit(".", 1)[0] + ".generate")
+    a = small_args(M)
+    # no gate bias: like the reference, Gate only registers (and so only saves) one at dim 7168
+    model = _small_transformer(M, a, np.random.default_rng(9), dev, batch=1, gate_bias=False)
+    ck = str(tmp_path)
+    save_model(model.embed, os.path.join(ck, "embed_int.safetensors"))
+    save_model(model.norm, os.path.join(ck, "norm_int.safetensors"))
+    save_model(model.head, os.path.join(ck, "head_int.safetensors"))
+    for i, blk in enumerate(model.layers):
+        sd = {k: v.contiguous() for k, v in blk.state_dict().items()}
+        save_file(sd, os.path.join(ck, "layer-%d.safetensors" % i))
+        if isinstance(blk.ffn, M.MoE):
+            os.makedirs(os.path.join(ck, "experts-%d" % i), exist_ok=True)
+            moe, I = blk.ffn, a.moe_inter_dim
+            for j in range(a.n_routed_experts):
+                e = M.Expert_int(i, j, a.dim, I).to(dev)
+                e.w1.weight, e.w3.weight = moe.experts_w13[j, :I].clone(), moe.experts_w13[j, I:].clone()
+                e.w2.weight = moe.experts_w2[j].clone()
+                e.w1.scale, e.w3.scale, e.w2.scale = (moe.experts_shift[j, c].clone() for c in range(3))
+                save_model(e, os.path.join(ck, "experts-%d/%d.safetensors" % (i, j)))
+    loaded = G.load_resident(ck, a, dev)
+    prompts = [[11, 250, 3, 77]]
+    want = G.generate(model, prompts, 3, eos_id=-5, temperature=0.0)
+    got = G.generate(loaded, prompts, 3, eos_id=-5, temperature=0.0)
+    assert got == want
     kmod.device_status()

@@ -26,6 +26,36 @@ except ImportError:  # pragma: no cover - drop-in use with this directory first 
     import model as M
 
 
+def load_resident(ckpt_path: str, args, device="cuda", cache_batch: int = 1, prepare: bool = True):
+    """Builds a `Transformer` with every layer on `device` from a converted checkpoint directory:
+    `embed_int.safetensors`, `norm_int.safetensors`, `head_int.safetensors` (generate.py:53-60),
+    `layer-{i}.safetensors` (generate.py:344-345, loaded with strict=False as generate.py:238 does) and
+    `experts-{layer}/{i}.safetensors` (model.py:1361-1363).  The reference keeps the layer state dicts on the
+    host and rebuilds one `Block` at a time; here all of them stay resident, and with `prepare` the limb
+    planes of every static weight are built once at load instead of at first use."""
+    from safetensors.torch import load_file, load_model
+    with torch.device(device):
+        model = M.Transformer(args)
+    load_model(model.embed, os.path.join(ckpt_path, "embed_int.safetensors"))
+    load_model(model.norm, os.path.join(ckpt_path, "norm_int.safetensors"))
+    load_model(model.head, os.path.join(ckpt_path, "head_int.safetensors"))
+    for i in range(args.n_layers):
+        with torch.device(device):
+            blk = M.Block(i, args, ckpt_path, cache_batch=cache_batch)
+        blk.load_state_dict(load_file(os.path.join(ckpt_path, f"layer-{i}.safetensors"), device=str(device)),
+                            strict=False)
+        if isinstance(blk.ffn, M.MoE):
+            blk.ffn.set_experts()
+        model.layers[i] = blk
+    if prepare:
+        for mod in model.modules():
+            if isinstance(mod, M.Linear_int):
+                mod.planes()
+            elif isinstance(mod, M.MoE):
+                mod._prepared()
+    return model
+
+
 def sample(logits: torch.Tensor, temperature: float = 1.0) -> torch.Tensor:
     """generate.py:62-143 with `sample_open = False`: the argmax over the vocabulary."""
     return logits.argmax(dim=-1)
