@@ -1182,27 +1182,41 @@ __device__ __forceinline__ void epilogue_merged(const LimbParams& p, uint32_t tq
 {
     int64_t T[CW];
     uint32_t R[EE ? CW : 1];
+    // Fewer, fuller round trips to tensor memory while few values are live: the extra diagonals all at
+    // once (nothing else is held yet), then main diagonals 0 and 1 together, then one per wait.
+    if (EE) {
+        int32_t e[EE ? EE : 1][CW];
 #pragma unroll
-    for (int d = 0; d < DD; ++d) {
+        for (int d = 0; d < EE; ++d) tmem_ldn(tq + (uint32_t)(set_cols + d * p.NT + c0), e[d]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < CW; ++c) {
+            uint32_t r = (uint32_t)e[0][c] + (uint32_t)p.addend2;
+#pragma unroll
+            for (int d = 1; d < EE; ++d) r += (uint32_t)e[d][c] << (8 * d);
+            R[c] = r;
+        }
+    }
+    {
+        int32_t a0[CW], a1[CW];
+        tmem_ldn(tq + (uint32_t)c0, a0);
+        if (DD > 1) tmem_ldn(tq + (uint32_t)(p.NT + c0), a1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < CW; ++c) {
+            T[c] = mad_wide(a0[c], 1, p.addend);
+            if (DD > 1) T[c] = mad_wide(a1[c], 1 << 8, T[c]);
+        }
+    }
+#pragma unroll
+    for (int d = 2; d < DD; ++d) {
         int32_t a[CW];
         tmem_ldn(tq + (uint32_t)(d * p.NT + c0), a);
         tmem_ld_wait();
 #pragma unroll
         for (int c = 0; c < CW; ++c) {
-            if (d == 0) T[c] = mad_wide(a[c], 1, p.addend);
-            else if (d < 4) T[c] = mad_wide(a[c], 1 << (8 * (d < 4 ? d : 0)), T[c]);
+            if (d < 4) T[c] = mad_wide(a[c], 1 << (8 * (d < 4 ? d : 0)), T[c]);
             else T[c] = (int64_t)((uint64_t)T[c] + ((uint64_t)(uint32_t)a[c] << (8 * d)));
-        }
-    }
-#pragma unroll
-    for (int d = 0; d < EE; ++d) {
-        int32_t e[CW];
-        tmem_ldn(tq + (uint32_t)(set_cols + d * p.NT + c0), e);
-        tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < CW; ++c) {
-            if (d == 0) R[c] = (uint32_t)e[c] + (uint32_t)p.addend2;
-            else R[c] += (uint32_t)e[c] << (8 * d);
         }
     }
     // re-zero the main columns no first-step MMA initialises, hand both sets back
