@@ -664,6 +664,15 @@ __device__ __forceinline__ int64_t scale_94_695(int64_t v)
     return q;
 }
 
+// sequence position of row m when rows are (s, h) pairs with H heads per position; row counts are below
+// 2^31 in practice, so the division runs in 32 bits (a 64-bit division costs a few hundred instructions
+// per thread and tile)
+__device__ __forceinline__ int64_t seq_row(int64_t m, int64_t H)
+{
+    if (((uint64_t)m | (uint64_t)H) >> 32) return m / H;
+    return (int64_t)((uint32_t)m / (uint32_t)H);
+}
+
 // element-wise tail of the attention scores: v += *arow (the addin element, if any);
 // v = floor(v * mul / div); causal mask for column n of sequence row srow
 __device__ __forceinline__ int64_t score_tail(const LimbParams& p, int64_t v, const int64_t* arow,
@@ -693,7 +702,7 @@ __device__ __forceinline__ void epilogue_tile(const LimbParams& p, const Epilogu
 {
     const bool tail = p.addin || p.ep_div || p.causal_H;
     const int64_t* arow = p.addin ? p.addin + e.z * p.c_sz + e.m * p.c_sm : nullptr;
-    const int64_t srow = p.causal_H ? e.m / p.causal_H : 0;
+    const int64_t srow = p.causal_H ? seq_row(e.m, p.causal_H) : 0;
     for (int nc = 0; nc < e.NT; nc += 8) {
         i128w sum[8];
         int64_t s64[8];
@@ -1057,7 +1066,7 @@ __device__ __forceinline__ void epilogue_part(const LimbParams& p, uint32_t tq, 
 {
     const int64_t m = tc.m0 + q * 32 + lane;
     const bool tail = p.addin || p.ep_div || p.causal_H;
-    const int64_t srow = p.causal_H ? m / p.causal_H : 0;
+    const int64_t srow = p.causal_H ? seq_row(m, p.causal_H) : 0;
     const int64_t nbase = tc.n0 + c0;
     const bool vec_ok = ((((uintptr_t)p.C | (uintptr_t)p.addin) & 15) == 0) && ((p.c_sm & 1) == 0) &&
                         ((p.c_sz & 1) == 0);
@@ -1231,7 +1240,7 @@ __device__ __forceinline__ void epilogue_merged(const LimbParams& p, uint32_t tq
     }
 
     const int64_t m = tc.m0 + q * 32 + lane;
-    const int64_t srow = p.causal_H ? m / p.causal_H : 0;
+    const int64_t srow = p.causal_H ? seq_row(m, p.causal_H) : 0;
     const int64_t nbase = tc.n0 + c0;
     const int sh = p.shift >= 63 ? 63 : p.shift;
     const uint32_t mask = EE ? (1u << p.shift) - 1u : 0u;
