@@ -149,8 +149,9 @@ int zkds_gemm(const int64_t* A, const void* B, int b_bits, int64_t* C, int64_t* 
  *     the need of a shape.  Shapes the limb kernel cannot take give ZKDS_ERR_UNSUPPORTED
  *     (there is no fallback).
  *   - The first call on a device looks up the device address of that array
- *     (cudaGetSymbolAddress with the device current); make that first call outside any
- *     stream capture.
+ *     (cudaGetSymbolAddress with the device current); that first call should come before
+ *     any stream capture.  Note that EVERY call, not only the first, ends by waiting for its
+ *     stream (last point below).
  *   - Every call uses the same array, which keeps the previous call's bytes; the status words
  *     are cleared at the start of each call.  Two calls whose GPU work overlaps (different
  *     streams or threads) race on it: serialise them.

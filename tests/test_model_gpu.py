@@ -424,3 +424,39 @@ def test_resident_checkpoint_loader(M, kmod, dev, tmp_path):
     got = G.generate(loaded, prompts, 3, eos_id=-5, temperature=0.0)
     assert got == want
     kmod.device_status()
+
+
+def test_activation_beyond_the_limb_bound_is_caught(M, mo, kmod, dev):
+    """ACT_LIMBS promises |x| < 2^31 for every activation entering a GEMM.  An attn_norm weight near 2^30
+    breaks the promise (normed values reach 2^30 * x / rms): the direct inference calls raise instead of
+    returning wrong logits, generate() re-runs the step with measured limb counts and produces the tokens of
+    a model that measured from the start."""
+    import importlib
+    G = importlib.import_module(M.__name__.rsplit(".", 1)[0] + ".generate")
+    a = small_args(M)
+
+    def build():
+        model = _small_transformer(M, a, np.random.default_rng(12), dev, batch=1, gate_bias=False)
+        w = model.layers[0].attn_norm.weight
+        model.layers[0].attn_norm.weight = (w.to(torch.int64) << 9).to(torch.int32)       # 2^21 -> 2^30
+        return model
+
+    model = build()
+    toks = torch.tensor([[5, 17, 300, 2, 41, 7]], dtype=torch.long, device=dev)
+    h, pos, S = model.prep_inference(toks, 0)
+    for i in range(a.n_layers):
+        h = model.layer_inference(i, h, pos, S)
+    with pytest.raises(kmod.ZkdsError) as info:
+        model.finish_inference(h)
+    assert info.value.status == kmod.ERR_RANGE
+    kmod.device_status()                                   # the flag was cleared by the raise
+
+    trace = []
+    got = G.generate(build(), [toks[0].tolist()], 3, eos_id=-5, temperature=0.0, trace=trace)
+    assert trace[0].get("rerun_measured") is True
+    ref = build()
+    with M.measured_limbs(ref):
+        want = G.generate(ref, [toks[0].tolist()], 3, eos_id=-5, temperature=0.0)
+    assert got == want
+    assert M.ACT_LIMBS == 4
+    kmod.device_status()

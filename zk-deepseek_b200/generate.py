@@ -61,6 +61,18 @@ def sample(logits: torch.Tensor, temperature: float = 1.0) -> torch.Tensor:
     return logits.argmax(dim=-1)
 
 
+def _forward_step(model, toks, prev_pos, layer_probe):
+    """one pass over all layers; finish_inference raises ZkdsError if a kernel flagged its operands"""
+    h, start_pos, seqlen = model.prep_inference(toks, prev_pos)
+    layer_tokens = []
+    for i in range(model.args.n_layers):
+        h = model.layer_inference(i, h, start_pos, seqlen)
+        if layer_probe:
+            probe = model.head(model.norm(h)[0][:, -1].contiguous()[None, :])
+            layer_tokens.append(probe.argmax(dim=-1).view(-1).tolist())
+    return model.finish_inference(h), layer_tokens
+
+
 @torch.inference_mode()
 def generate(model, prompt_tokens: List[List[int]], max_new_tokens: int, eos_id: int,
              temperature: float = 1.0, layer_probe: bool = False,
@@ -87,14 +99,18 @@ def generate(model, prompt_tokens: List[List[int]], max_new_tokens: int, eos_id:
         if M.snark:
             os.makedirs(f"{M.zkDataDir}/pos_{prev_pos}", exist_ok=True)
             M.saveTensor(f"{M.zkDataDir}/pos_{prev_pos}/tokens.bin", tokens[0][prev_pos:cur_pos].cpu())
-        h, start_pos, seqlen = model.prep_inference(tokens[:, prev_pos:cur_pos], prev_pos)
-        layer_tokens = []
-        for i in range(args.n_layers):
-            h = model.layer_inference(i, h, start_pos, seqlen)
-            if layer_probe:
-                probe = model.head(model.norm(h)[0][:, -1].contiguous()[None, :])
-                layer_tokens.append(probe.argmax(dim=-1).view(-1).tolist())
-        logits = model.finish_inference(h)
+        rerun = False
+        try:
+            logits, layer_tokens = _forward_step(model, tokens[:, prev_pos:cur_pos], prev_pos, layer_probe)
+        except M.K.ZkdsError as err:
+            if err.status != M.K.ERR_RANGE:
+                raise
+            # an activation exceeded the limb bound promised for it (M.ACT_LIMBS, MLA.score_limbs): that
+            # pass's numbers are wrong.  The step only wrote cache rows it owns, so it is simply run again
+            # with every limb count measured on the device.
+            with M.measured_limbs(model):
+                logits, layer_tokens = _forward_step(model, tokens[:, prev_pos:cur_pos], prev_pos, layer_probe)
+            rerun = True
         next_token = (sample(logits, temperature) if temperature > 0 else logits.argmax(dim=-1)).view(-1)
         next_token = torch.where(prompt_mask[:, cur_pos], tokens[:, cur_pos], next_token)
         tokens[:, cur_pos] = next_token
@@ -102,6 +118,8 @@ def generate(model, prompt_tokens: List[List[int]], max_new_tokens: int, eos_id:
         prev_pos = cur_pos
         if trace is not None:
             step = {"pos": cur_pos, "next_token": next_token.tolist()}
+            if rerun:
+                step["rerun_measured"] = True
             if layer_probe:
                 step["layer_tokens"] = layer_tokens
             trace.append(step)

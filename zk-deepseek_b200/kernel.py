@@ -110,8 +110,15 @@ _sig("zkds_contraction_prepared", [_vp, _ll, _ll, _vp, _i, _vp, _vp, _ll, _ll, _
                                    _i, _i, _vp])
 
 
+ERR_RANGE = 2           # ZKDS_ERR_RANGE: an operand did not fit the limb count promised for it
+
+
 class ZkdsError(RuntimeError):
-    pass
+    """A library call or a finished kernel reported a non-zero status (`.status`)."""
+
+    def __init__(self, message, status=0):
+        super().__init__(message)
+        self.status = status
 
 
 def _check(status, what):
@@ -119,7 +126,7 @@ def _check(status, what):
         msg = lib.zkds_status_string(status).decode()
         if status == 3:
             msg += " (cudaError %d)" % lib.zkds_last_cuda_error()
-        raise ZkdsError("%s: %s" % (what, msg))
+        raise ZkdsError("%s: %s" % (what, msg), status)
 
 
 def _stream():
@@ -231,9 +238,12 @@ def einsum_bshc_hdc_bshd(A, B, rescale, a_limbs=0, b_limbs=0):
 
 # ---- static weights prepared once ---------------------------------------------------------
 
-def device_status(clear=True):
+def device_status(clear=True, sync=False):
     """Raises if a finished tensor-core kernel gave up a bounded wait, or if an operand did not
-    fit the limb count a caller promised through a_limbs (that call's result is wrong)."""
+    fit the limb count a caller promised through a_limbs (that call's result is wrong).  The flags
+    are written by kernels: `sync=True` first waits for torch's current stream."""
+    if sync:
+        torch.cuda.current_stream().synchronize()
     _check(lib.zkds_device_status(1 if clear else 0), "device status")
 
 

@@ -56,6 +56,12 @@ zkDataDir = "../zkdata"
 # actually used is derived on the device, data beyond the bound raises K.device_status().
 # 0 measures every activation on the device with a host synchronisation.
 ACT_LIMBS = 4
+# A result computed from an activation beyond the promised bound is wrong, and only a device flag says
+# so.  With CHECK_STATUS the flag is read wherever a result leaves the model: at the end of
+# Transformer.finish_inference (one stream synchronisation per step, where the caller reads the logits
+# anyway) and after every Block whose dumps are written.  generate() re-runs a flagged step with measured
+# limb counts instead of raising.
+CHECK_STATUS = True
 
 
 @dataclass
@@ -89,6 +95,12 @@ class ModelArgs:
     beta_fast: int = 32
     beta_slow: int = 1
     mscale: float = 1.
+
+
+def _ver(t):
+    """version counter of a weight tensor for the cache keys of its limb planes.  Tensors created under
+    torch.inference_mode() have none: they cannot be modified in place outside it either, so 0 is enough."""
+    return 0 if t.is_inference() else t._version
 
 
 def saveTensor(fileName, t):
@@ -154,7 +166,7 @@ class Linear_int(nn.Module):
 
     # -- prepared weights -------------------------------------------------------------------
     def planes(self):
-        key = (self.weight.data_ptr(), self.weight._version, self.weight.device)
+        key = (self.weight.data_ptr(), _ver(self.weight), self.weight.device)
         if self._planes is None or self._planes_key != key:
             self._planes = K.WeightPlanes(self.weight, div=self.weight_rescale)
             self._planes_key = key
@@ -162,13 +174,13 @@ class Linear_int(nn.Module):
 
     def shift(self):
         """the per-layer `scale` buffer as a Python int, read once (it is static)"""
-        key = (self.scale.data_ptr(), self.scale._version)
+        key = (self.scale.data_ptr(), _ver(self.scale))
         if self._scale_cache is None or self._scale_cache[0] != key:
             self._scale_cache = (key, int(self.scale.item()))
         return self._scale_cache[1]
 
     def _run(self, x, shift, want_remainder):
-        lim = ACT_LIMBS if self.act_limbs is None else self.act_limbs
+        lim = ACT_LIMBS if (self.act_limbs is None or ACT_LIMBS == 0) else self.act_limbs
         pl = self.planes()
         lead = x.shape[:-1]
         x3 = x.reshape(1, -1, x.shape[-1])          # every leading dimension is just more rows
@@ -344,7 +356,7 @@ class MLA(nn.Module):
 
     def _per_head_planes(self, lin, k_last):
         """limb planes of wkv_b_1 / wkv_b_2 viewed per head: [H, 128, 512]"""
-        key = (lin.weight.data_ptr(), lin.weight._version, k_last)
+        key = (lin.weight.data_ptr(), _ver(lin.weight), k_last)
         ent = self._head_planes.get(id(lin))
         if ent is None or ent[0] != key:
             w = lin.weight.view(self.n_local_heads, -1, self.kv_lora_rank)
@@ -497,8 +509,8 @@ class MLP_int(nn.Module):
         self._w13 = None
 
     def _stacked(self):
-        key = (self.w1.weight.data_ptr(), self.w1.weight._version, self.w3.weight.data_ptr(),
-               self.w3.weight._version)
+        key = (self.w1.weight.data_ptr(), _ver(self.w1.weight), self.w3.weight.data_ptr(),
+               _ver(self.w3.weight))
         if self._w13 is None or self._w13[0] != key:
             w13 = torch.cat([self.w1.weight, self.w3.weight], dim=0).contiguous()
             self._w13 = (key, K.WeightPlanes(w13))
@@ -554,7 +566,7 @@ class Gate(nn.Module):
         self._lin = None
 
     def _linear(self):
-        key = (self.weight.data_ptr(), self.weight._version, self.scale.data_ptr(), self.scale._version)
+        key = (self.weight.data_ptr(), _ver(self.weight), self.scale.data_ptr(), _ver(self.scale))
         if self._lin is None or self._lin[0] != key:
             self._lin = (key, K.WeightPlanes(self.weight), int(self.scale.item()))
         return self._lin[1], self._lin[2]
@@ -680,7 +692,7 @@ class MoE(nn.Module):
         self._planes = None
 
     def _prepared(self):
-        key = (self.experts_w13._version, self.experts_w2._version, self.experts_shift._version,
+        key = (_ver(self.experts_w13), _ver(self.experts_w2), _ver(self.experts_shift),
                self.experts_w13.data_ptr())
         if self._planes is None or self._planes[0] != key:
             sh = self.experts_shift
@@ -798,6 +810,8 @@ class Block(nn.Module):
         ffn_normed, rms = self.ffn_norm(x)
         ffned = self.ffn(start_pos, ffn_normed)
         x = x + ffned * (2 ** 8)
+        if snark and CHECK_STATUS:      # dumps of a step whose limb bound did not hold must not be trusted
+            K.device_status(sync=True)
         return x
 
 
@@ -845,4 +859,31 @@ class Transformer(nn.Module):
         logits = self.head(h[None, :])      # [1, B, vocab] (B = 1 in the reference)
         if world_size > 1:
             logits = _all_gather_last(logits)
+        if CHECK_STATUS:
+            K.device_status(sync=True)      # raises ZkdsError (status ERR_RANGE) if a limb bound did not hold
         return logits
+
+
+class measured_limbs:
+    """Context manager: every activation's limb count is measured on the device (ACT_LIMBS = 0, score
+    contractions included) instead of promised.  Slower (one host synchronisation per GEMM), never wrong;
+    generate() uses it to re-run a step whose promised bound did not hold."""
+
+    def __init__(self, model):
+        self.model = model
+
+    def __enter__(self):
+        global ACT_LIMBS
+        self.saved = (ACT_LIMBS, [(m, m.score_limbs, m.causal_skip) for m in self.model.modules()
+                                  if isinstance(m, MLA)])
+        ACT_LIMBS = 0
+        for m, _, _ in self.saved[1]:
+            m.score_limbs, m.causal_skip = (0, 0), False
+        return self
+
+    def __exit__(self, *exc):
+        global ACT_LIMBS
+        ACT_LIMBS = self.saved[0]
+        for m, sl, cs in self.saved[1]:
+            m.score_limbs, m.causal_skip = sl, cs
+        return False
