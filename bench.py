@@ -105,7 +105,7 @@ class GemmWorkload:
     metric = "int64_gemm_gops"
     unit = "Gop/s"
     M, K, N, SHIFT = 4096, 16384, 7168, 16
-    A_BITS, W_BITS = 20, 15
+    A_BITS, W_BITS, A_LIMBS = 20, 15, 3
 
     def __init__(self, torch, k, dev, rank):
         import numpy as np
@@ -119,7 +119,7 @@ class GemmWorkload:
         self.X = self.X_host.to(dev)
         self.W = self.W_host.to(dev)
         self.planes = k.WeightPlanes(self.W)          # static weights: split once
-        self.a_limbs = 3                               # |x| < 2^20 fits three signed 8-bit limbs
+        self.a_limbs = self.A_LIMBS                    # |x| < 2^20 fits three signed 8-bit limbs
         self.C_host = torch.empty((1, self.M, self.N), dtype=torch.int64).pin_memory()
         self.X_dev2 = torch.empty_like(self.X)
         self.ops = 2.0 * self.M * self.N * self.K
@@ -128,7 +128,7 @@ class GemmWorkload:
 
     def config(self):
         return {"workload": self.name, "M": self.M, "K": self.K, "N": self.N, "shift": self.SHIFT,
-                "x_range": "+-2^20", "w_range": "+-2^15 int32", "a_limbs": self.a_limbs,
+                "x_range": "+-2^%d" % self.A_BITS, "w_range": "+-2^%d int32" % self.W_BITS, "a_limbs": self.a_limbs,
                 "w_limbs": self.planes.limbs, "weights": "limb planes prepared once",
                 "l2": "inputs larger than L2 (X 537 MB, W planes %d MB)"
                       % (self.planes.limbs * self.N * self.K >> 20)}
@@ -188,6 +188,182 @@ class GemmWorkload:
         orc.gemm(X, W, 1, 1, 16)
         dt = time.time() - t0
         return 2.0 * rows * N * K / dt / 1e9, "%d of 4096 rows of X against the full W" % rows, dt
+
+
+def graph_call_us(torch, fn, calls, reps=10):
+    """GPU time of one call of `fn` in microseconds with no host in the way: `calls` consecutive calls are
+    captured in a CUDA graph on a side stream and the graph is replayed `reps` times between two events."""
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        for _ in range(3):
+            fn()
+        st.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr, stream=st):
+            for _ in range(calls):
+                fn()
+        gr.replay()
+        st.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        for _ in range(reps):
+            gr.replay()
+        e1.record(st)
+        st.synchronize()
+    return e0.elapsed_time(e1) / (calls * reps) * 1e3
+
+
+class GemmSmallMWorkload:
+    """BASELINE's first configuration, the one the reference can run on a CPU: one bit-exact int64 GEMM of
+    the wkv_a projection shape, X int64 [32, 7168] uniform in +-2^20, W [576, 7168] uniform in +-2^15 (held as
+    int64 and as int32), Y = (X W^T) >> 16, seed 0.  HBM bound: the weight is read once per call, so the
+    workload rotates over COPIES of W (together larger than L2) and every call streams its weight from HBM.
+    A step is COPIES calls through prepared limb planes (the product path of Linear_int)."""
+    name = "gemm_32x7168x576_small_m"
+    metric = "int64_gemm_gops"
+    unit = "Gop/s"
+    M, K, N, SHIFT, COPIES = 32, 7168, 576, 16, 16
+
+    def __init__(self, torch, k, dev, rank):
+        import numpy as np
+        self.torch, self.k, self.dev, self.np = torch, k, dev, np
+        rng = np.random.default_rng(0)
+        self.X_np = rng.integers(-2**20, 2**20, (1, self.M, self.K), dtype=np.int64)
+        self.W_np = rng.integers(-2**15, 2**15, (self.N, self.K), dtype=np.int64)
+        self.X = torch.from_numpy(self.X_np).to(dev)
+        w64 = torch.from_numpy(self.W_np).to(dev)
+        # the copies differ (rolled rows) so that nothing can be reused between calls
+        self.W64 = [torch.roll(w64, i, 0).contiguous() for i in range(self.COPIES)]
+        self.W32 = [w.to(torch.int32) for w in self.W64]
+        self.planes = [k.WeightPlanes(w) for w in self.W32]
+        self.a_limbs = 3
+        self.i = 0
+        self.ops = 2.0 * self.M * self.N * self.K
+        self.launches_per_step = 2 * self.COPIES
+        self.units = self.ops * self.COPIES
+        self.X_host = self.X.cpu().pin_memory()
+        self.X_in = torch.empty_like(self.X)
+        self.C_host = torch.empty((1, self.M, self.N), dtype=torch.int64).pin_memory()
+
+    def config(self):
+        return {"workload": self.name, "M": self.M, "K": self.K, "N": self.N, "shift": self.SHIFT,
+                "x_range": "+-2^20", "w_range": "+-2^15", "a_limbs": self.a_limbs, "w_limbs": self.planes[0].limbs,
+                "calls_per_step": self.COPIES,
+                "l2": "%d copies of W (%d MB of int64, %d MB of limb planes) rotate, more than L2 holds"
+                      % (self.COPIES, self.COPIES * self.N * self.K * 8 >> 20,
+                         self.COPIES * self.N * self.K * self.planes[0].limbs >> 20)}
+
+    def _prepared(self):
+        self.i = (self.i + 1) % self.COPIES
+        return self.k.linear_prepared(self.X, self.planes[self.i], self.SHIFT, a_limbs=self.a_limbs, dynamic=True)
+
+    def _legacy(self, ws):
+        self.i = (self.i + 1) % self.COPIES
+        return self.k.int64_bmm_broadcast(self.X, ws[self.i], 1, 1, self.SHIFT)
+
+    def step(self):
+        for _ in range(self.COPIES):
+            out = self._prepared()
+        return out
+
+    def step_e2e(self):
+        for _ in range(self.COPIES):
+            self.X_in.copy_(self.X_host, non_blocking=True)
+            self.i = (self.i + 1) % self.COPIES
+            C = self.k.linear_prepared(self.X_in, self.planes[self.i], self.SHIFT, a_limbs=self.a_limbs, dynamic=True)
+            self.C_host.copy_(C, non_blocking=True)
+
+    def e2e_bytes(self):
+        return self.COPIES * self.X_host.numel() * 8, self.COPIES * self.C_host.numel() * 8
+
+    def value(self, seconds_per_step, world):
+        return self.units * world / seconds_per_step / 1e9
+
+    def paths(self, peaks):
+        """GPU microseconds per call of the three ways this GEMM is reached, and what that is of the HBM
+        roofline on the algorithmic bytes 8MK + wNK + 16MN (C and R written)"""
+        torch, k = self.torch, self.k
+        out = {}
+        M, K, N = self.M, self.K, self.N
+
+        def alg(w):
+            return 8 * M * K + w * N * K + 16 * M * N
+
+        us = graph_call_us(torch, self._prepared, self.COPIES)
+        L = self.planes[0].limbs
+        out["prepared_planes"] = {"us": round(us, 2), "bytes_read_by_the_kernels": 8 * M * K + (3 * M + L * N) * K,
+                                  "GB/s_algorithmic_int32_W": round(alg(4) / us / 1e3, 1),
+                                  "frac_of_hbm_algorithmic_int32_W": round(alg(4) / us / 1e3 / peaks["hbm_gbs"], 3)}
+        for name, ws, w in (("legacy_symbol_int32_W", self.W32, 4), ("legacy_symbol_int64_W", self.W64, 8)):
+            for _ in range(3):
+                self._legacy(ws)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(2 * self.COPIES):
+                self._legacy(ws)
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) / (2 * self.COPIES) * 1e3
+            out[name] = {"us": round(us, 2), "GB/s_algorithmic": round(alg(w) / us / 1e3, 1),
+                         "frac_of_hbm_algorithmic": round(alg(w) / us / 1e3 / peaks["hbm_gbs"], 3),
+                         "note": "measures both operand ranges (a host synchronisation) and splits W on every call"}
+        return out
+
+    def roofline(self, peaks):
+        paths = self.paths(peaks)
+        pp = paths["prepared_planes"]
+        alg = 8 * self.M * self.K + 4 * self.N * self.K + 16 * self.M * self.N
+        gbs = alg / pp["us"] / 1e3
+        return {"bound": "hbm", "kernel": "split_rows_kernel + limb_gemm_kernel (split over K)",
+                "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": round(gbs / peaks["hbm_gbs"], 4), "traffic": None, "kernel_us": pp["us"],
+                "algorithmic_bytes": alg, "paths": paths,
+                "note": "algorithmic bytes = 8MK + 4NK + 16MN (int32 W) / GPU time of one call replayed from a CUDA "
+                        "graph (activation split + tensor-core kernel); the kernels read %d-limb planes of W, "
+                        "fewer bytes than the int32 weight; peak = STREAM-style copy (%s)"
+                        % (self.planes[0].limbs, peaks["source"])}
+
+    def check(self, orc):
+        C, R = self.k.linear_prepared(self.X, self.planes[0], self.SHIFT, a_limbs=self.a_limbs, want_remainder=True,
+                                      dynamic=True)
+        Co, Ro = orc.gemm(self.X_np, self.W_np, 1, 1, self.SHIFT, orc.R_LEGACY)
+        bad = int((C.cpu().numpy() != Co).sum()) + int((R.cpu().numpy() != Ro).sum())
+        C, R = self.k.int64_bmm_broadcast(self.X, self.W64[0], 1, 1, self.SHIFT)
+        return bad + int((C.cpu().numpy() != Co).sum()) + int((R.cpu().numpy() != Ro).sum())
+
+    @staticmethod
+    def cpu_sample(orc, np, seconds, rank=0):
+        """the whole GEMM (it is small) on the int128 oracle, repeated"""
+        rng = np.random.default_rng(0)
+        X = rng.integers(-2**20, 2**20, (1, 32, 7168), dtype=np.int64)
+        W = rng.integers(-2**15, 2**15, (576, 7168), dtype=np.int64)
+        orc.gemm(X, W, 1, 1, 16)
+        n, t0 = 0, time.time()
+        while time.time() - t0 < min(seconds, 3.0):
+            orc.gemm(X, W, 1, 1, 16)
+            n += 1
+        dt = (time.time() - t0) / n
+        return 2.0 * 32 * 576 * 7168 / dt / 1e9, "the full 32 x 7168 x 576 GEMM, %d repetitions" % n, dt * n
+
+
+def torch_cpu_baseline(torch, np, seconds=3.0):
+    """The reference's own CPU path for a Linear: torch.nn.functional.linear on int64 tensors (linear() takes
+    that branch for every non-fp8 weight, inference/model.py:179-181) followed by >> s, on BASELINE's first
+    configuration, where it is valid because |sum| < 2^42 stays inside the wrapping int64."""
+    rng = np.random.default_rng(0)
+    X = torch.from_numpy(rng.integers(-2**20, 2**20, (1, 32, 7168), dtype=np.int64))
+    W = torch.from_numpy(rng.integers(-2**15, 2**15, (576, 7168), dtype=np.int64))
+    torch.nn.functional.linear(X, W)
+    n, t0 = 0, time.time()
+    while time.time() - t0 < seconds:
+        Y = torch.nn.functional.linear(X, W) >> 16
+        n += 1
+    dt = (time.time() - t0) / n
+    return {"value": round(2.0 * 32 * 576 * 7168 / dt / 1e9, 3), "unit": "Gop/s", "ms_per_call": round(dt * 1e3, 3),
+            "cores": torch.get_num_threads(), "host_cpus": os.cpu_count(), "kind": "reference",
+            "sample": "torch.nn.functional.linear(X, W) >> 16 on int64 CPU tensors, 32 x 7168 x 576, %d calls" % n,
+            "checksum": int(Y.sum().item())}
 
 
 class ChainWorkload:
@@ -368,6 +544,7 @@ class MlaWorkload:
     scaling = "strong"
     collective_check = True
     T = 4096
+    SCALES = "baseline"
 
     def __init__(self, torch, k, dev, rank, T=None, scales="baseline"):
         import numpy as np
@@ -438,13 +615,22 @@ class MlaWorkload:
                               + H * T * C + H * C * v + H * v * D)
         self.launches_per_step = 0
 
+    @classmethod
+    def static_config(cls, world, scales=None, T=None):
+        """the configuration record of this workload; needs no GPU (the reference arm prints the same one)"""
+        T = T or cls.T
+        scales = scales or cls.SCALES
+        D, q, C, R, H, nope, v = 7168, 1536, 512, 64, 128, 128, 128
+        ops = 2.0 * T * (D * q + q * H * (nope + R) + D * (C + R) + H * nope * C + H * T * (C + R)
+                         + H * T * C + H * C * v + H * v * D)
+        base = scales == "baseline"
+        return {"workload": cls.name, "tokens": T, "dim": D, "heads": H, "q_lora": q, "kv_lora": C, "scales": scales,
+                "shift": 16 if base else 30, "act_limbs_bound": 3 if base else 4,
+                "score_limbs_bound": [3, 3] if base else [5, 5], "heads_per_gpu": H // world,
+                "useful_ops_per_step": ops, "l2": "activations and score tensors (up to 17 GB) far exceed L2"}
+
     def config(self):
-        a = self.args
-        return {"workload": self.name, "tokens": self.T, "dim": a.dim, "heads": a.n_heads,
-                "q_lora": a.q_lora_rank, "kv_lora": a.kv_lora_rank, "scales": self.scales,
-                "shift": self.shift, "act_limbs_bound": self.act_limbs, "score_limbs_bound": self.score_limbs,
-                "heads_per_gpu": a.n_heads // self.world, "useful_ops_per_step": self.ops,
-                "l2": "activations and score tensors (up to 17 GB) far exceed L2"}
+        return self.static_config(self.world, self.scales, self.T)
 
     def step(self):
         return self.attn(self.x, 0, self.freqs, self.mask)
@@ -486,12 +672,16 @@ class MlaWorkload:
                         "durations; peak = 2 x sustained cuBLAS bf16 (%s)" % peaks["source"]}
 
     def check(self, orc):
-        """the layer against the numpy restatement of MLA.forward on the first 48 tokens"""
+        """Rows of the ACTUAL T-token pass against the numpy restatement of MLA.forward: three groups of four
+        consecutive query tokens (first, middle, last) x every head, each against the whole cache before it.
+        The oracle takes the cache rows before a group from the GPU (it recomputes and compares the group's
+        own rows and 16 rows elsewhere), so every contraction of the full-extent run is covered: the 2^31-word
+        score tensor, the last column tiles, K = T in P.KV."""
         np, torch, a = self.np, self.torch, self.args
-        S = 48
-        at = self.attn
-        mask = torch.full((S, S), -(64 << 36), dtype=torch.int64, device=self.dev).triu_(1)
-        got = self.attn(self.x[:, :S].contiguous(), 0, self.freqs[:S], mask).cpu().numpy()
+        at, T = self.attn, self.T
+        got = self.step()                       # with N > 1 every rank joins the collectives here
+        kv_gpu = at.kv_cache[0, :T].cpu().numpy()
+        pe_gpu = at.pe_cache[0, :T].cpu().numpy()
 
         def full(name):          # head / column slices of the ranks -> the whole weight
             w = getattr(at, name).weight
@@ -508,33 +698,61 @@ class MlaWorkload:
             return None
         from oracle import model_oracle as mo
         p.update(wkv_b_1_scale=self.shift, wkv_b_2_scale=self.shift, wo_scale=self.shift)
-        x = self.x[:, :S].cpu().numpy()
-        kv = np.zeros((1, S, a.kv_lora_rank), np.int64)
-        pe = np.zeros((1, S, a.qk_rope_head_dim), np.int64)
         sq, skv = (self.shift, self.shift) if self.scales == "baseline" else (30, 29)
-        want = mo.mla_forward(p, x, 0, self.freqs[:S].cpu().numpy(), mo.causal_mask(S), kv, pe, a.n_heads,
-                              s_q=sq, s_kv=skv)
-        return int((got != want).sum())
+        freqs = self.freqs.cpu().numpy()
+        S = 4
+        bad = 0
+        for st in sorted({0, max(0, T // 2 - 2), max(0, T - S)}):
+            end = st + S
+            kv = np.zeros((1, end, a.kv_lora_rank), np.int64)
+            pe = np.zeros((1, end, a.qk_rope_head_dim), np.int64)
+            kv[0, :st], pe[0, :st] = kv_gpu[:st], pe_gpu[:st]
+            mask = np.where(np.arange(end)[None, :] > (st + np.arange(S))[:, None], mo.MASK_VALUE, 0).astype(np.int64)
+            x = self.x[:, st:end].cpu().numpy()
+            want = mo.mla_forward(p, x, st, freqs[st:end], mask, kv, pe, a.n_heads, s_q=sq, s_kv=skv)
+            bad += int((got[:, st:end].cpu().numpy() != want).sum())
+            bad += int((kv[0, st:end] != kv_gpu[st:end]).sum()) + int((pe[0, st:end] != pe_gpu[st:end]).sum())
+        rows = np.random.default_rng(9).choice(T, 16, replace=False)
+        for r in rows:
+            x = self.x[:, r:r + 1].cpu().numpy()
+            kvr = mo.rms_norm(mo.linear(x, p["wkv_a1"], skv)[0], p["kv_norm"])[0]
+            per = mo.rotary(mo.linear(x, p["wkv_a2"], skv)[0][:, :, None, :], freqs[r:r + 1])[:, :, 0]
+            bad += int((kvr[0, 0] != kv_gpu[r]).sum()) + int((per[0, 0] != pe_gpu[r]).sum())
+        return bad
 
     @staticmethod
     def cpu_sample(orc, np, seconds, rank=0):
-        """the layer's contractions and softmax on a token sample (full K and T extents)"""
-        S, T, H = 4, 4096, 128
+        """the layer's contractions and softmax for a sample of query tokens (full K and T extents, operands at
+        the workload's magnitudes).  The sample grows until it uses about `seconds`; tokens/s of the sample is
+        what a full 4096-token pass would give, since every query token costs the same."""
+        T, H = 4096, 128
         rng = np.random.default_rng(5)
         ri = lambda shape, b: np.rint(rng.standard_normal(shape) * 2.0**b).astype(np.int64)
-        x = ri((1, S, 7168), 16)
-        t0 = time.time()
-        for (n, kk) in ((1536, 7168), (24576, 1536), (576, 7168), (7168, 16384)):
-            orc.gemm(ri((1, S, kk), 16), ri((n, kk), 12).astype(np.int32), 1, 1, 16)
-        q = ri((1, S, H, 512), 16)
-        kv = ri((1, T, 512), 16)
-        sc = orc.einsum_bshc_btc_bsht(q, kv, 23) + orc.einsum_bshc_btc_bsht(ri((1, S, H, 64), 16), ri((1, T, 64), 16), 21)
-        pr = orc.softmax(sc * 94 // 695, 19)
-        ctx = orc.einsum_bsht_btc_bshc(pr, kv, 23)
-        orc.einsum_bshc_hdc_bshd(ctx, ri((H, 128, 512), 12).astype(np.int32), 16)
-        orc.einsum_bshd_hdc_bshc(ri((1, S, H, 128), 16), ri((H, 128, 512), 12).astype(np.int32), 16)
-        dt = time.time() - t0
-        return S / dt, "%d of 4096 query tokens against the full 4096-token cache and full weights" % S, dt
+        wi = lambda n, kk: np.rint(rng.standard_normal((n, kk)) * 2.0**16 / math.sqrt(kk)).astype(np.int32)
+        ws = [wi(n, kk) for (n, kk) in ((1536, 7168), (24576, 1536), (576, 7168), (7168, 16384))]
+        wh = [np.rint(rng.standard_normal((H, 128, 512)) * 2.0**16 / math.sqrt(512)).astype(np.int32) for _ in range(2)]
+        kv, pe = ri((1, T, 512), 16), ri((1, T, 64), 16)
+
+        def run(S):
+            t0 = time.time()
+            for w in ws:
+                orc.gemm(ri((1, S, w.shape[1]), 16), w, 1, 1, 16)
+            sc = orc.einsum_bshc_btc_bsht(ri((1, S, H, 512), 16), kv, 23) + \
+                orc.einsum_bshc_btc_bsht(ri((1, S, H, 64), 16), pe, 21)
+            pr = orc.softmax(sc * 94 // 695, 19)
+            ctx = orc.einsum_bsht_btc_bshc(pr, kv, 23)
+            orc.einsum_bshc_hdc_bshd(ctx, wh[0], 16)
+            orc.einsum_bshd_hdc_bshc(ri((1, S, H, 128), 16), wh[1], 16)
+            return time.time() - t0
+
+        dt = run(4)
+        S = int(max(4, min(64, 4 * 0.8 * seconds / max(dt, 1e-3))))
+        if S > 4:
+            dt = run(S)
+        else:
+            S = 4
+        return S / dt, ("%d of 4096 query tokens against the full 4096-token cache and the full weights; "
+                        "tokens/s of the sample (a 4096-token pass was not run on the CPU)" % S), dt
 
 
 class MoeWorkload:
@@ -667,16 +885,23 @@ class MoeWorkload:
                         "cuBLAS bf16 (%s)" % peaks["source"]}
 
     def check(self, orc):
-        """four tokens against the numpy restatement of MoE.forward (the GPU's expert choice is
-        passed on so that a score tie cannot make the two differ)"""
+        """Tokens of the ACTUAL pass (all T tokens routed, so experts receive several 128-row tiles each) against
+        the numpy restatement of MoE.forward: eight tokens spread over the batch, each through the gate, the
+        shared expert and its eight routed experts.  The GPU's expert choice is passed on so that a score tie
+        cannot make the two differ."""
         np, a, moe = self.np, self.args, self.moe
-        I = a.moe_inter_dim
-        xs = self.x[:, :4].contiguous()
-        got = moe(0, xs).cpu().numpy()          # with N > 1 every rank joins the all-to-all here
+        got_all = self.step()                   # with N > 1 every rank joins the all-to-all here
         if orc is None:
             return None
         from oracle import model_oracle as mo
-        idx = moe.gate(0, xs.view(-1, a.dim))[1].cpu().numpy()
+        Tl = self.T_local
+        sample = sorted({0, 1, Tl // 3, Tl // 2, Tl // 2 + 1, (2 * Tl) // 3, Tl - 2, Tl - 1})
+        idx_all = moe.gate(0, self.x.view(-1, a.dim))[1]
+        counts = self.torch.bincount(idx_all.flatten(), minlength=self.E)
+        self.max_rows_per_expert = int(counts.max().item())
+        xs = self.x[:, sample].contiguous()
+        got = got_all[:, sample].cpu().numpy()
+        idx = idx_all[sample].cpu().numpy()
         sh = self.SHIFT
         mlp = lambda m: {"w1": m.w1.weight.cpu().numpy(), "w3": m.w3.weight.cpu().numpy(),
                          "w2": m.w2.weight.cpu().numpy(), "w1_scale": sh, "w3_scale": sh, "w2_scale": sh}
@@ -937,6 +1162,18 @@ class DecodeWorkload:
         return 1.0 / (dt * 5.3), "GEMVs of one dense layer for one token, scaled to 4 layers + head", dt
 
 
+class GemmWideRangeWorkload(GemmWorkload):
+    """The same `wo`-shaped GEMM with wide operands: X uniform in +-2^36, W over the whole int32 range,
+    shift 30.  Sums reach 2^81, so the accumulation must be wider than int64; five activation limbs against
+    five weight limbs (25 limb pairs instead of 9)."""
+    name = "gemm_wo_4096x16384x7168_wide_operands"
+    A_BITS, W_BITS, A_LIMBS, SHIFT = 36, 31, 5, 30
+
+    @staticmethod
+    def cpu_sample(orc, np, seconds, rank=0):
+        return GemmWorkload.cpu_sample(orc, np, seconds, rank)
+
+
 class GemmProfWorkload(GemmWorkload):
     """Smaller GEMM of the same kernel for profiler captures (inputs still exceed L2)."""
     name = "gemm_4096x8192x4096"
@@ -961,6 +1198,7 @@ class MlaRefScaleWorkload(MlaWorkload):
     """The MLA layer at the reference's fixed-point magnitudes (activations 2^21, int32 weights
     2^30/sqrt(fan_in), shifts 29-31): more limbs per operand than the 2^16 configuration."""
     name = "mla_layer_prefill_4096_reference_scales"
+    SCALES = "reference"
 
     def __init__(self, torch, k, dev, rank):
         super().__init__(torch, k, dev, rank, scales="reference")
@@ -994,7 +1232,8 @@ class MlaSmallWorkload(MlaWorkload):
         return MlaWorkload.cpu_sample(orc, np, seconds, rank)
 
 
-WORKLOADS = {"gemm": GemmWorkload, "gemm_prof": GemmProfWorkload, "chain": ChainWorkload,
+WORKLOADS = {"gemm": GemmWorkload, "gemm_prof": GemmProfWorkload, "gemm_cfg1": GemmSmallMWorkload,
+             "gemm_wide": GemmWideRangeWorkload, "chain": ChainWorkload,
              "chain_prof": ChainProfWorkload, "mla": MlaWorkload, "mla_ref": MlaRefScaleWorkload,
              "mla_small": MlaSmallWorkload, "mla_causal": MlaCausalSkipWorkload, "moe": MoeWorkload,
              "moe_small": MoeSmallWorkload, "decode": DecodeWorkload}
@@ -1003,14 +1242,139 @@ DEFAULT_WORKLOAD = "mla"
 
 # --------------------------------------------------------------------------------------------
 
+def _timed_steps(torch, w, n):
+    for _ in range(3):
+        w.step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        w.step()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e-3 / n
+
+
+def reference_kernels_on_this_gpu(torch, np):
+    """The reference's own CUDA kernels (its unmodified int64_gemm.cu compiled for this GPU by oracle/Makefile,
+    otherwise only a checker) timed with CUDA events inside the limits they work in: BASELINE's first
+    configuration, and the two score contractions + Q19 softmax of 16 heads at T = 1024."""
+    import ctypes
+    path = os.path.join(ROOT, "oracle", "_ref", "libint64gemm_ref.so")
+    if not os.path.exists(path):
+        return {"unavailable": "oracle/_ref/libint64gemm_ref.so was not built where this repository was packed"}
+    L = ctypes.CDLL(path)
+    vp, ll, ci = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int
+    L.int64_64_bmm_broadcast_launcher.argtypes = [vp, vp, vp, vp, ll, ll, ll, ci, ci, ci, ci]
+    L.int64_32_bmm_broadcast_launcher.argtypes = [vp, vp, vp, vp, ll, ll, ll, ci, ci, ci, ci]
+    L.einsum_bshc_btc_bsht.argtypes = [vp, vp, vp, ll, ci, ci, ci, ci, ci]
+    L.softmax_q19.argtypes = [vp, vp, vp, ci, ci, ci, ci]
+    L.softmax_init_q19.argtypes = [vp]
+    dev = torch.device("cuda", torch.cuda.current_device())
+
+    def timed(fn, n):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()                      # the reference launches on the legacy default stream
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    rng = np.random.default_rng(0)
+    X = torch.from_numpy(rng.integers(-2**20, 2**20, (1, 32, 7168), dtype=np.int64)).to(dev)
+    W = torch.from_numpy(rng.integers(-2**15, 2**15, (576, 7168), dtype=np.int64)).to(dev)
+    W32 = W.to(torch.int32)
+    C, R = torch.empty((1, 32, 576), dtype=torch.int64, device=dev), torch.empty((1, 32, 576), dtype=torch.int64, device=dev)
+    out = {"kind": "reference_cuda", "library": "oracle/_ref/libint64gemm_ref.so (the reference's int64_gemm.cu, nvcc -arch=sm_100)"}
+    with torch.cuda.stream(torch.cuda.default_stream()):
+        for name, fn, w in (("gemm_32x7168x576_int64_W", L.int64_64_bmm_broadcast_launcher, W),
+                            ("gemm_32x7168x576_int32_W", L.int64_32_bmm_broadcast_launcher, W32)):
+            ms = timed(lambda: fn(X.data_ptr(), w.data_ptr(), C.data_ptr(), R.data_ptr(), 1, 1, 16, 1, 32, 7168, 576), 5)
+            out[name] = {"ms": round(ms, 4), "Gop/s": round(2.0 * 32 * 576 * 7168 / ms / 1e6, 1)}
+        S, H, T = 64, 16, 1024
+        q = torch.from_numpy(rng.integers(-2**16, 2**16, (1, S, H, 512), dtype=np.int64)).to(dev)
+        kv = torch.from_numpy(rng.integers(-2**16, 2**16, (1, T, 512), dtype=np.int64)).to(dev)
+        qp = torch.from_numpy(rng.integers(-2**16, 2**16, (1, S, H, 64), dtype=np.int64)).to(dev)
+        pe = torch.from_numpy(rng.integers(-2**16, 2**16, (1, T, 64), dtype=np.int64)).to(dev)
+        s1, s2 = torch.empty((1, S, H, T), dtype=torch.int64, device=dev), torch.empty((1, S, H, T), dtype=torch.int64, device=dev)
+        probs = torch.empty_like(s1)
+        lut = torch.zeros(256, dtype=torch.int64)
+        L.softmax_init_q19(lut.data_ptr())
+        lut = lut.to(dev)
+
+        def scores():
+            L.einsum_bshc_btc_bsht(q.data_ptr(), kv.data_ptr(), s1.data_ptr(), 23, 1, S, H, T, 512)
+            L.einsum_bshc_btc_bsht(qp.data_ptr(), pe.data_ptr(), s2.data_ptr(), 21, 1, S, H, T, 64)
+            sc = (s1 + s2) * 94 // 695
+            L.softmax_q19(sc.data_ptr(), probs.data_ptr(), lut.data_ptr(), 1, S, H, T)
+
+        ms = timed(scores, 3)
+        out["scores_softmax_64q_16h_T1024"] = {"ms": round(ms, 4),
+                                               "Gop/s": round(2.0 * S * H * T * 576 / ms / 1e6, 1),
+                                               "note": "two score einsums, torch glue (s1+s2)*94//695, softmax_q19"}
+    return out
+
+
+def default_line_extras(torch, k, dev, rank, peaks, np, wl):
+    """Parts of the default line beside the MLA layer: the int64 GEMM at a tensor-bound projection shape in
+    two operand ranges, BASELINE's first (small-M, HBM-bound) configuration, the layer at the reference's own
+    magnitudes, and the reference's CUDA kernels on this GPU."""
+    out = {}
+    torch.cuda.empty_cache()
+    for key, cls in (("int64_gemm", GemmWorkload), ("int64_gemm_wide_operands", GemmWideRangeWorkload)):
+        gw = cls(torch, k, dev, rank)
+        sec = _timed_steps(torch, gw, 10)
+        out[key] = {"metric": gw.metric, "value": round(gw.value(sec, 1), 1), "unit": gw.unit, "workload": gw.name,
+                    "config": gw.config(), "ms": round(sec * 1e3, 4), "roofline": gw.roofline(peaks)}
+        k.device_status(sync=True)
+        del gw
+        torch.cuda.empty_cache()
+    sw = GemmSmallMWorkload(torch, k, dev, rank)
+    sec = _timed_steps(torch, sw, 10)
+    out["int64_gemm_small_m"] = {"metric": sw.metric, "value": round(sw.value(sec, 1), 1), "unit": sw.unit,
+                                 "workload": sw.name, "config": sw.config(),
+                                 "us_per_call_host_launched": round(sec * 1e6 / sw.COPIES, 2),
+                                 "roofline": sw.roofline(peaks)}
+    k.device_status(sync=True)
+    del sw
+    torch.cuda.empty_cache()
+    # the same layer at the reference's fixed-point magnitudes (more limbs per operand)
+    old_limbs = wl.M.ACT_LIMBS
+    wl.attn = None
+    torch.cuda.empty_cache()
+    rw = MlaRefScaleWorkload(torch, k, dev, rank)
+    sec = _timed_steps(torch, rw, 3)
+    out["value_reference_scales"] = {"metric": rw.metric, "value": round(rw.value(sec, 1), 2), "unit": rw.unit,
+                                     "workload": rw.name, "config": rw.config(), "ms_per_step": round(sec * 1e3, 3),
+                                     "roofline": rw.roofline(peaks)}
+    k.device_status(sync=True)
+    del rw
+    wl.M.ACT_LIMBS = old_limbs
+    torch.cuda.empty_cache()
+    try:
+        out["reference_kernels_b200"] = reference_kernels_on_this_gpu(torch, np)
+    except Exception as err:  # noqa: BLE001 - a baseline, never fatal
+        out["reference_kernels_b200"] = {"unavailable": repr(err)}
+    return out
+
+
 def run_reference(args, rank, world):
-    """The reference has no CPU implementation of this path (its kernels are CUDA only); the
-    CPU arm is the OpenMP int128 oracle on every host thread, on a bounded sample per step."""
+    """The reference has no CPU implementation of this path beyond torch's int64 `F.linear` (its kernels are
+    CUDA only, its library is built as a checker under oracle/_ref).  The CPU arm is the OpenMP int128 oracle
+    (`kind: "port"`), the same arithmetic the reference's kernels perform, on every host thread, on a bounded
+    sample of the workload per step; the torch `F.linear` path is timed beside it on BASELINE's first
+    configuration, the only one where wrapping int64 is exact."""
     if rank != 0:
         return
     import numpy as np
     from oracle import oracle as orc
     orc.build()
+    # torch.distributed.run exports OMP_NUM_THREADS=1: use every core for every N all the same
+    cores = os.cpu_count() or 1
+    orc.set_threads(cores)
     wl = WORKLOADS[args.workload]
     vals = []
     budget = 60.0 / max(1, args.steps + args.warmup)
@@ -1020,16 +1384,23 @@ def run_reference(args, rank, world):
         if i >= args.warmup:
             vals.append((v, dt))
     value = statistics.mean(v for v, _ in vals)
+    config = wl.static_config(world) if hasattr(wl, "static_config") else {"workload": wl.name}
     line = {"impl": "reference", "metric": wl.metric, "value": round(value, 3), "unit": wl.unit,
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(1e3 * statistics.mean(d for _, d in vals), 3),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int64",
-            "data": "synthetic", "config": {"workload": wl.name},
+            "higher_is_better": True, "scaling": getattr(wl, "scaling", "weak"), "vs_baseline": None,
+            "dtype": "int64", "data": "synthetic", "config": config,
             "cpu_baseline": {"value": round(value, 3), "unit": wl.unit, "cores": orc.num_threads(),
                              "kind": "port", "sample": desc},
             "e2e": {"value": round(value, 3), "unit": wl.unit, "h2d_bytes_per_step": 0,
                     "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
+    try:
+        import torch
+        torch.set_num_threads(cores)
+        line["cpu_baseline_torch"] = torch_cpu_baseline(torch, np, 2.0)
+    except Exception as err:  # noqa: BLE001 - the arm must still print its line
+        line["cpu_baseline_torch"] = {"unavailable": repr(err)}
     print(json.dumps(line), flush=True)
 
 
@@ -1041,6 +1412,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--no-extras", action="store_true",
+                    help="default workload only: leave out the GEMM, small-M, reference-scale and reference-kernel parts")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -1118,29 +1491,19 @@ def main():
             orc.build()
         mismatches = wl.check(orc)          # every rank takes part in the collectives
         barrier()
-    gemm_part = None
-    if args.workload in ("mla", "mla_ref", "moe") and rank == 0:
-        # the other half of the headline metric: the bit-exact int64 GEMM alone, same kernel
-        wl.x_host = None
-        torch.cuda.empty_cache()
-        gw = GemmProfWorkload(torch, k, dev, rank)
-        for _ in range(3):
-            gw.step()
-        torch.cuda.synchronize()
-        ev0.record()
-        for _ in range(10):
-            gw.step()
-        ev1.record()
-        torch.cuda.synchronize()
-        gsec = ev0.elapsed_time(ev1) * 1e-4
-        gemm_part = {"metric": gw.metric, "value": round(gw.value(gsec, 1), 1), "unit": gw.unit,
-                     "workload": gw.name, "ms": round(gsec * 1e3, 4), "roofline": gw.roofline(peaks)}
-        del gw
+    extras = {}
     if rank == 0:
         from oracle import oracle as orc
         orc.build()
+        orc.set_threads(os.cpu_count() or 1)      # torch.distributed.run exports OMP_NUM_THREADS=1
         if world == 1 or not getattr(wl, "collective_check", False):
             mismatches = wl.check(orc)
+    if args.workload == DEFAULT_WORKLOAD and world == 1 and not args.no_extras:
+        # the rest of the headline metric and the configurations the default workload does not cover
+        wl.x_host = None
+        extras = default_line_extras(torch, k, dev, rank, peaks, np, wl)
+        extras["cpu_baseline_torch"] = torch_cpu_baseline(torch, np, 2.0)
+    if rank == 0:
         cpu_v, cpu_desc, _ = (wl.cpu_sample(orc, np, args.cpu_seconds)
                                 if world == 1 and args.cpu_seconds > 0 else (None, None, 0))
         launches = wl.launches_per_step * args.steps
@@ -1155,8 +1518,7 @@ def main():
                 "gpu_launches": launches,
                 "roofline": roof,
                 "clocks": clocks, "mismatched_words_vs_oracle": mismatches}
-        if gemm_part is not None:
-            line["int64_gemm"] = gemm_part
+        line.update(extras)
         if cpu_v is not None:
             line["cpu_baseline"] = {"value": round(cpu_v, 3), "unit": wl.unit,
                                     "cores": orc.num_threads(), "kind": "port", "sample": cpu_desc}

@@ -66,6 +66,10 @@ class RefLib:
             getattr(L, n).argtypes = [vp, vp, vp, i, i, i]
         for n in ("softmax_init_q21", "softmax_init_q19", "silu_init_q25", "silu_init_q23"):
             getattr(L, n).argtypes = [vp]
+        # exported by the reference, bound nowhere in its kernel.py (int64_gemm.cu:126,173,215)
+        L.bf16_to_int32_2d.argtypes = [vp, vp, i, i, i]
+        L.wkv_b_bf16_to_int32.argtypes = [vp, vp, i, i]
+        L.float32_to_int64_2d.argtypes = [vp, vp, i, i, i]
 
 
 @pytest.fixture(scope="session")

@@ -34,11 +34,11 @@ def fx():
     return z, meta
 
 
-def check_against_fixture(fx, name, out, files, what):
+def check_against_fixture(fx, name, out, files, what, outputs=True):
     z, meta = fx
     rec = meta["cases"][name]
     problems = []
-    for k, r in rec["outputs"].items():
+    for k, r in rec["outputs"].items() if outputs else ():
         if k == "freqs" and k not in out:
             continue
         v = np.ascontiguousarray(out[k])
@@ -115,3 +115,71 @@ def test_reference_model_runs_on_this_library(dev, tmp_path):
                         "--arms", "ref,so,py", "--out", str(tmp_path / "again.npz"), "--keep", str(tmp_path)],
                        capture_output=True, text=True)
     assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
+
+
+def _write_converted_checkpoint(ck, a, w):
+    """the converted layout generate.py reads: embed/norm/head_int.safetensors, layer-{i}.safetensors with
+    Block's state-dict keys (convert2.py:13-32,591), experts-{layer}/{i}.safetensors"""
+    import torch
+    from safetensors.torch import save_file
+    tt = lambda x: torch.from_numpy(np.ascontiguousarray(x))
+    sc = lambda v: torch.tensor(v, dtype=torch.int32)
+    for name in ("embed", "norm", "head"):
+        save_file({"weight": tt(w[name])}, os.path.join(ck, name + "_int.safetensors"))
+
+    def mlp(prefix, p, sd):
+        for n in ("w1", "w2", "w3"):
+            sd[prefix + n + ".weight"] = tt(p[n])
+            sd[prefix + n + ".scale"] = sc(p[n + "_scale"])
+
+    for i, p in enumerate(w["layers"]):
+        sd = {"attn_norm.weight": tt(p["attn_norm"]), "ffn_norm.weight": tt(p["ffn_norm"]),
+              "attn.q_norm.weight": tt(p["attn"]["q_norm"]), "attn.kv_norm.weight": tt(p["attn"]["kv_norm"])}
+        for n in ("wq_a", "wq_b1", "wq_b2", "wkv_a1", "wkv_a2", "wkv_b_1", "wkv_b_2", "wo"):
+            sd["attn.%s.weight" % n] = tt(p["attn"][n])
+            if n + "_scale" in p["attn"]:
+                sd["attn.%s.scale" % n] = sc(p["attn"][n + "_scale"])
+        f = p["ffn"]
+        if "experts" in f:
+            sd["ffn.gate.weight"], sd["ffn.gate.scale"] = tt(f["gate"]["weight"]), sc(f["gate"]["scale"])
+            sd["ffn.gate.bias"] = tt(f["gate"]["bias"])
+            mlp("ffn.shared_experts.", f["shared"], sd)
+            mc.write_experts(ck, i, f["experts"])
+        else:
+            mlp("ffn.", f, sd)
+        save_file(sd, os.path.join(ck, "layer-%d.safetensors" % i))
+
+
+@pytest.mark.gpu
+def test_generate_from_a_converted_checkpoint_gives_the_reference_tokens(fx, kmod, dev, tmp_path):
+    """load_resident + generate() (this repository's generate.py) on the `tf` case: the tokens and the
+    pos_{p}/tokens.bin files are those of the reference's model.py driven by its own token loop"""
+    M = importlib.import_module(PKG + ".model")
+    G = importlib.import_module(PKG + ".generate")
+    c = mc.CASES["tf"]
+    w, x = mc.case_data("tf")
+    ck = str(tmp_path / "ckpt")
+    os.makedirs(ck)
+    a = M.ModelArgs(**c["args"])
+    _write_converted_checkpoint(ck, a, w)
+    model = G.load_resident(ck, a, dev)
+    want = fx[0]["tf/out/tokens"]
+    prompt = [int(v) for v in x["prompt"]]
+    zk = str(tmp_path / "zk")
+    M.snark, M.zkDataDir = True, zk
+    try:
+        trace = []
+        got = G.generate(model, [prompt], c["new_tokens"], eos_id=-5, temperature=0.0, trace=trace)
+    finally:
+        M.snark, M.zkDataDir = False, "../zkdata"
+    assert got == [want[len(prompt):].tolist()]
+    assert not any(s.get("rerun_measured") for s in trace)
+    pos = 0
+    for n in (len(prompt), 1, 1):
+        toks = np.fromfile(os.path.join(zk, "pos_%d" % pos, "tokens.bin"), np.int64)
+        assert np.array_equal(toks, want[pos:pos + n])
+        pos += n
+    # the layer dumps written on the way are the reference's too
+    dumps = mc.normalise_dumps({k: v for k, v in mc.read_dumps(zk).items() if not k.endswith("tokens.bin")})
+    check_against_fixture(fx, "tf", {}, dumps, "dumps written under generate()", outputs=False)
+    kmod.device_status()

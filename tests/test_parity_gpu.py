@@ -584,3 +584,123 @@ def test_golden_vectors_from_the_reference_replay_on_the_gpu(kmod, orc, dev):
 
     bad = mk.check_against(np.load(path), GpuAsOracle())
     assert not bad, bad
+
+
+# ---- small M: the weight-streaming shapes (BASELINE config 1, decode) ----------------------------
+
+@pytest.mark.parametrize("M", [1, 7, 32, 64])
+@pytest.mark.parametrize("K,N", [(7168, 576), (2048, 1536), (1536, 200)])
+@pytest.mark.parametrize("abits,bbits,s", [(20, 15, 16), (36, 31, 30), (47, 31, 33)])
+def test_small_m_gemm_split_over_k(kmod, orc, dev, M, K, N, abits, bbits, s):
+    """Few output tiles and a deep K: the K range is split over CTAs that add their int32 diagonals before
+    the shift.  Sums reach 2^80 (beyond int64) in the wide ranges.  Through prepared planes (promised and
+    measured limb counts) and through the reference symbol's wrapper, twice each: the second call finds the
+    partial-sum scratch as the first one left it."""
+    rng = np.random.default_rng(M * 7 + K + N + s)
+    A = rand_i64(rng, (1, M, K), abits)
+    B = rand_i64(rng, (N, K), bbits).astype(np.int32)
+    Co, Ro = orc.gemm(A, B, 1, 1, s, orc.R_LEGACY)
+    Ad, Bd = g(A, dev), g(B, dev)
+    planes = kmod.WeightPlanes(Bd)
+    la = (abits + 8) // 8                  # signed 8-bit limbs that cover |x| < 2^abits
+    for rep in range(2):
+        C, R = kmod.int64_bmm_broadcast(Ad, Bd, 1, 1, s)
+        same(C, Co, "legacy C, call %d" % rep)
+        same(R, Ro, "legacy R, call %d" % rep)
+        if la <= 5:
+            C, R = kmod.linear_prepared(Ad, planes, s, a_limbs=la, want_remainder=True, dynamic=True)
+            same(C, Co, "prepared dynamic C, call %d" % rep)
+            same(R, Ro, "prepared dynamic R, call %d" % rep)
+            C = kmod.linear_prepared(Ad, planes, s, a_limbs=0)
+            same(C, Co, "prepared measured C, call %d" % rep)
+        # (wider activations do not fit the tensor-core kernel's shared memory; with prepared planes there is no
+        # other kernel to fall back to, the reference-named wrapper above falls back to the exact one)
+    kmod.device_status()
+
+
+def test_small_m_gemm_batched_and_int64_weights(kmod, orc, dev):
+    """batch > 1 with a shared int64 weight and divisors (the head projection's form, model.py:1517-1519),
+    interleaved with a shape of another tile geometry so that the shared partial-sum scratch is reused
+    under a different layout"""
+    rng = np.random.default_rng(77)
+    A = rand_i64(rng, (3, 9, 3000), 30)
+    B = rand_i64(rng, (333, 3000), 43)
+    A2 = rand_i64(rng, (1, 64, 7168), 21)
+    B2 = rand_i64(rng, (1536, 7168), 17).astype(np.int32)
+    want = orc.gemm(A, B, 1, 256, 29, orc.R_LEGACY)
+    want2 = orc.gemm(A2, B2, 1, 1, 30, orc.R_LEGACY)
+    for rep in range(3):
+        C, R = kmod.int64_bmm_broadcast(g(A, dev), g(B, dev), 1, 256, 29)
+        same(C, want[0], "batched C %d" % rep)
+        same(R, want[1], "batched R %d" % rep)
+        C, R = kmod.int64_bmm_broadcast(g(A2, dev), g(B2, dev), 1, 1, 30)
+        same(C, want2[0], "wq_a-shaped C %d" % rep)
+        same(R, want2[1], "wq_a-shaped R %d" % rep)
+    kmod.device_status()
+
+
+def test_small_m_against_the_reference_kernels(libpath, reflib, dev):
+    """config 1 and a decode-shaped projection through the reference's symbols of both libraries"""
+    ours, ref = type(reflib)(libpath).lib, reflib.lib
+    rng = np.random.default_rng(0)
+    for (M, K, N, ab, bb, s, w64) in ((32, 7168, 576, 20, 15, 16, True), (32, 7168, 576, 20, 15, 16, False),
+                                      (64, 7168, 1536, 21, 30, 30, False), (7, 2048, 7168, 23, 29, 29, False),
+                                      (1, 16384, 300, 36, 31, 31, False)):
+        A = g(rand_i64(rng, (1, M, K), ab), dev)
+        B = rand_i64(rng, (N, K), bb)
+        B = g(B if w64 else B.astype(np.int32), dev)
+        name = "int64_64_bmm_broadcast_launcher" if w64 else "int64_32_bmm_broadcast_launcher"
+        res = []
+        for L in (ours, ref):
+            C = torch.zeros((1, M, N), dtype=torch.int64, device=dev)
+            R = torch.zeros_like(C)
+            getattr(L, name)(A.data_ptr(), B.data_ptr(), C.data_ptr(), R.data_ptr(), 1, 1, s, 1, M, K, N)
+            torch.cuda.synchronize()
+            res.append((C.cpu().numpy(), R.cpu().numpy()))
+        assert np.array_equal(res[0][0], res[1][0]) and np.array_equal(res[0][1], res[1][1]), (M, K, N)
+
+
+# ---- float -> fixed converters (exported by the reference, called by nothing in it) ------------------
+
+def test_converters_against_the_reference_kernels(libpath, reflib, dev):
+    """bf16_to_int32_2d, wkv_b_bf16_to_int32, float32_to_int64_2d (int64_gemm.cu:92-221) over every bf16 bit
+    pattern and a sample of float32 patterns.  Compared wherever the reference is defined: it divides by
+    `1 << -e` evaluated in 32-bit int, which is zero (a division by zero) from e <= -32 on."""
+    ours, ref = type(reflib)(libpath).lib, reflib.lib
+    bits = np.arange(65536, dtype=np.uint16)
+    ex0 = ((bits.astype(np.int64) >> 7) & 0xFF) - 127
+    src = torch.from_numpy(bits.view(np.int16).copy()).to(dev)
+    for rescale in (0, 19, 31, 40):
+        outs = []
+        for L in (ours, ref):
+            o = torch.zeros(65536, dtype=torch.int32, device=dev)
+            L.bf16_to_int32_2d(src.data_ptr(), o.data_ptr(), 256, 256, rescale)
+            torch.cuda.synchronize()
+            outs.append(o.cpu().numpy())
+        ok = ex0 + rescale > -32
+        assert np.array_equal(outs[0][ok], outs[1][ok]), "bf16_to_int32_2d rescale %d" % rescale
+    outs = []
+    for L in (ours, ref):
+        o = torch.zeros(65536, dtype=torch.int32, device=dev)
+        L.wkv_b_bf16_to_int32(src.data_ptr(), o.data_ptr(), 64, 1024)
+        torch.cuda.synchronize()
+        outs.append(o.cpu().numpy())
+    ok = (ex0 + 25 > -32) | (ex0 >= -1)
+    assert np.array_equal(outs[0][ok], outs[1][ok]), "wkv_b_bf16_to_int32"
+
+    rng = np.random.default_rng(5)
+    f = np.concatenate([rng.integers(0, 2**32, 200000, dtype=np.uint64).astype(np.uint32),
+                        np.array([0, 0x80000000, 1, 0x00800000, 0x3F800000, 0xBF800000, 0x7F7FFFFF, 0x7F800000,
+                                  0xFFFFFFFF, 0x4B000000], np.uint32)])
+    f = np.resize(f, (500, 420)).copy()
+    exf = ((f.astype(np.int64) >> 23) & 0xFF) - 127
+    srcf = torch.from_numpy(f.view(np.int32)).to(dev)
+    for rescale in (0, 19, 31, 40):
+        outs = []
+        for L in (ours, ref):
+            o = torch.zeros(f.shape, dtype=torch.int64, device=dev)
+            L.float32_to_int64_2d(srcf.data_ptr(), o.data_ptr(), f.shape[0], f.shape[1], rescale)
+            torch.cuda.synchronize()
+            outs.append(o.cpu().numpy())
+        ok = exf + rescale > -32
+        assert np.array_equal(outs[0][ok], outs[1][ok]), "float32_to_int64_2d rescale %d" % rescale

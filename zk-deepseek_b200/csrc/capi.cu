@@ -5,6 +5,7 @@
 #include <math.h>
 #include <stdio.h>
 #include <mutex>
+#include <stdlib.h>
 
 #include "../../include/zkds_int64.h"
 #include "common.cuh"
@@ -25,7 +26,7 @@ int set_cuda_error(cudaError_t e)
 int check_launch() { return set_cuda_error(cudaGetLastError()); }
 
 static constexpr int kMaxDevices = 64;
-static constexpr int kSlots = 6;
+static constexpr int kSlots = 8;
 
 struct Arena {
     void* ptr[kSlots] = {};
@@ -34,6 +35,32 @@ struct Arena {
 };
 static Arena g_arena[kMaxDevices];
 static std::mutex g_mu;
+
+const Switches& switches()
+{
+    static const Switches sw = [] {
+        Switches v{};
+        auto on = [](const char* n) { return getenv(n) != nullptr; };
+        auto num = [](const char* n, int dflt) { const char* e = getenv(n); return e ? atoi(e) : dflt; };
+        v.wait_profile = on("ZKDS_WAIT_PROFILE");
+        v.trace = on("ZKDS_TRACE");
+        v.no_persistent = on("ZKDS_NO_PERSISTENT");
+        v.no_persistent_grouped = on("ZKDS_NO_PERSISTENT_GROUPED");
+        v.no_merged = on("ZKDS_NO_MERGED");
+        v.no_split_release = on("ZKDS_NO_SPLIT_RELEASE");
+        v.no_backoff = on("ZKDS_NO_BACKOFF");
+        v.no_split_k = on("ZKDS_NO_SPLIT_K");
+        v.split_generic = on("ZKDS_SPLIT_GENERIC");
+        v.softmax_generic = on("ZKDS_SOFTMAX_GENERIC");
+        v.rms_staged = on("ZKDS_RMS_STAGED");
+        v.rms_nostage = on("ZKDS_RMS_NOSTAGE");
+        v.epi_warps = num("ZKDS_EPI_WARPS", 0);
+        v.tile_nt = num("ZKDS_TILE_NT", 0);
+        v.persistent_max_kb = num("ZKDS_PERSISTENT_MAX_KB", -1);
+        return v;
+    }();
+    return sw;
+}
 
 int sm_count()
 {
@@ -48,8 +75,11 @@ int sm_count()
     return g_arena[dev].sms;
 }
 
-void* workspace(size_t bytes, int slot)
+void* workspace(size_t bytes, int slot) { return workspace_fresh(bytes, slot, nullptr); }
+
+void* workspace_fresh(size_t bytes, int slot, size_t* fresh_bytes)
 {
+    if (fresh_bytes) *fresh_bytes = 0;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
     if (slot < 0 || slot >= kSlots) return nullptr;
@@ -76,6 +106,7 @@ void* workspace(size_t bytes, int slot)
     }
     a.ptr[slot] = p;
     a.cap[slot] = want;
+    if (fresh_bytes) *fresh_bytes = want;
     return p;
 }
 

@@ -630,7 +630,7 @@ int launch_softmax(const int64_t* X, int64_t* Wout, int64_t* C, const int64_t* l
     if (rows > 0x7fffffffll) return ZKDS_ERR_RANGE;
     if (frac == 19) {
         const bool vec = (T % 2 == 0) && ((((uintptr_t)X | (uintptr_t)C | (uintptr_t)Wout) & 15) == 0);
-        if (vec && T >= 64 && T <= 2 * 16 * kThreads && !getenv("ZKDS_SOFTMAX_GENERIC"))
+        if (vec && T >= 64 && T <= 2 * 16 * kThreads && !switches().softmax_generic)
             return launch_softmax_q19_reg(X, Wout, C, lut, rows, T, st);
         return launch_softmax_t<19>(X, Wout, C, lut, rows, T, st);
     }
@@ -996,10 +996,10 @@ static int launch_rmsnorm_t(const int64_t* A, const WT* W, const int64_t* rms_in
                             cudaStream_t st)
 {
     if (fused && (N & 1) == 0 && N <= 16 * kRegThreads && ((((uintptr_t)A | (uintptr_t)C) & 15) == 0) &&
-        !getenv("ZKDS_RMS_STAGED"))
+        !switches().rms_staged)
         return launch_rmsnorm_reg<WT>(A, W, rms_out, C, M, N, eps, dim, st);
     size_t row_bytes = (size_t)N * 8;
-    bool stage = fused && row_bytes <= 200 * 1024 && !getenv("ZKDS_RMS_NOSTAGE");
+    bool stage = fused && row_bytes <= 200 * 1024 && !switches().rms_nostage;
     size_t smem = stage ? row_bytes : 0;
 #define ZKDS_RMS(F, S)                                                                       \
     do {                                                                                     \

@@ -9,6 +9,26 @@ namespace zkds {
 
 int sm_count();  // SM count of the current device (cached per device)
 
+// Diagnostic switches, read from the environment ONCE (first use) and constant for the life of the
+// process; all off by default.  They exist so that one run on one GPU can compare two variants.
+struct Switches {
+    bool wait_profile;            // ZKDS_WAIT_PROFILE: the persistent kernel reports where its warps waited
+    bool trace;                   // ZKDS_TRACE: one line per timed launch
+    bool no_persistent;           // ZKDS_NO_PERSISTENT
+    bool no_persistent_grouped;   // ZKDS_NO_PERSISTENT_GROUPED
+    bool no_merged;               // ZKDS_NO_MERGED
+    bool no_split_release;        // ZKDS_NO_SPLIT_RELEASE
+    bool no_backoff;              // ZKDS_NO_BACKOFF
+    bool no_split_k;              // ZKDS_NO_SPLIT_K: few-tile GEMMs keep one CTA per output tile
+    bool split_generic;           // ZKDS_SPLIT_GENERIC
+    bool softmax_generic;         // ZKDS_SOFTMAX_GENERIC
+    bool rms_staged, rms_nostage; // ZKDS_RMS_STAGED, ZKDS_RMS_NOSTAGE
+    int epi_warps;                // ZKDS_EPI_WARPS = 8 | 16 (0: default)
+    int tile_nt;                  // ZKDS_TILE_NT = forced tile width (0: default)
+    int persistent_max_kb;        // ZKDS_PERSISTENT_MAX_KB (negative: default)
+};
+const Switches& switches();
+
 // ---- streaming fixed-point kernels (fixedpoint.cu) ---------------------------
 int launch_act(const int64_t* X, int64_t* C, const int64_t* lut, int64_t n, int frac, int silu,
                cudaStream_t st);
@@ -170,5 +190,8 @@ int launch_f32_to_int64(const uint32_t* in, int64_t* out, int rows, int cols, in
 // scratch memory owned by the library, one arena per device, grown on demand and
 // reused by the next call (capi.cu).  Returns null when the allocation fails.
 void* workspace(size_t bytes, int slot);
+// same; *fresh_bytes is the size of the block when this call had to allocate it (its contents are then
+// undefined), 0 when the block of an earlier call is returned with whatever that call left in it
+void* workspace_fresh(size_t bytes, int slot, size_t* fresh_bytes);
 
 }  // namespace zkds

@@ -139,7 +139,7 @@ split_rows_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, i
                   int64_t Kp, int64_t sz, int64_t sr, int64_t div, int64_t plane_stride,
                   unsigned* overflow, unsigned long long* absmax_out, int64_t dst_pitch, int64_t valid_H,
                   int64_t valid_start, int tpr_log2, unsigned nb, unsigned gx, int z_fast, int shl,
-                  const int* __restrict__ row_index)
+                  const int* __restrict__ row_index, unsigned kseg, int64_t seg_quads)
 {
     uint64_t seen = 0;
     bool ovf = false;
@@ -151,8 +151,13 @@ split_rows_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, i
     const int lane_q = threadIdx.x & (tpr - 1);
     const int64_t rpb = 256 >> tpr_log2;
     const bool vec = sizeof(T) == 8 && ((((uintptr_t)X) & 15) == 0) && ((sr & 1) == 0) && ((sz & 1) == 0);
-    const unsigned items = nb * gx;
-    for (unsigned item = blockIdx.x; item < items; item += gridDim.x) {
+    // few rows (decode): a row is cut into kseg segments of seg_quads quads so that the launch still has
+    // a CTA for every SM
+    const unsigned items = nb * gx * kseg;
+    for (unsigned it = blockIdx.x; it < items; it += gridDim.x) {
+        const unsigned seg = it % kseg, item = it / kseg;
+        const int64_t q_begin = (int64_t)seg * seg_quads;
+        const int64_t q_end = q_begin + seg_quads < quads ? q_begin + seg_quads : quads;
         const unsigned zi = z_fast ? item % nb : item / gx;
         const unsigned bx = z_fast ? item / nb : item - zi * gx;
         const int64_t z = zi;
@@ -174,7 +179,7 @@ split_rows_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, i
         const T* xr = x + (rs < 0 ? 0 : rs) * sr;
         int8_t* drow = planes + (z * rows + r) * dst_pitch;
 #pragma unroll 2
-        for (int64_t qd = lane_q; qd < quads; qd += tpr) {
+        for (int64_t qd = q_begin + lane_q; qd < q_end; qd += tpr) {
             const int64_t k0 = qd << 2;
             int64_t v[4];
             if (k0 >= Kv) {
@@ -394,6 +399,14 @@ __device__ __forceinline__ void tmem_st8_zero(uint32_t taddr)
         : "memory");
 }
 
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const int32_t (&v)[8])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(v[0]),
+        "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+        : "memory");
+}
+
 __device__ __forceinline__ void tmem_st4_zero(uint32_t taddr)
 {
     const uint32_t z = 0;
@@ -427,7 +440,8 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr)
 // for the K block that opens a set of accumulators (its very first MMA then overwrites).
 template <int LA>
 __device__ __forceinline__ void issue_k_block(uint32_t acc, uint32_t nt_cols, uint32_t sa, uint32_t sb,
-                                              uint32_t idesc, uint32_t first_accumulates, int ks_n)
+                                              uint32_t idesc, uint32_t first_accumulates, int ks_n,
+                                              uint32_t a_stride16 = (128 * 128) >> 4)
 {
     const uint64_t hi = smem_desc_sw128(0) & 0xFFFFFFFF00000000ull;
     const uint32_t lo_fixed = (uint32_t)(smem_desc_sw128(0) & 0xFFFFC000ull);
@@ -438,7 +452,7 @@ __device__ __forceinline__ void issue_k_block(uint32_t acc, uint32_t nt_cols, ui
         if (ks < ks_n) {
 #pragma unroll
             for (int i = 0; i < LA; ++i) {
-                const uint64_t adesc = hi | (uint64_t)(a_lo + (uint32_t)(i * ((128 * 128) >> 4) + ks * 2));
+                const uint64_t adesc = hi | (uint64_t)(a_lo + (uint32_t)i * a_stride16 + (uint32_t)(ks * 2));
                 const uint64_t bdesc = hi | (uint64_t)(b_lo + (uint32_t)(ks * 2));
                 if (ks == 0 && i == 0) umma_i8(acc, adesc, bdesc, idesc, first_accumulates);
                 else umma_i8_acc(acc + (uint32_t)i * nt_cols, adesc, bdesc, idesc);
@@ -448,18 +462,19 @@ __device__ __forceinline__ void issue_k_block(uint32_t acc, uint32_t nt_cols, ui
 }
 
 __device__ __forceinline__ void issue_k_block_n(int La, uint32_t acc, uint32_t nt_cols, uint32_t sa, uint32_t sb,
-                                                uint32_t idesc, uint32_t first_accumulates, int ks_n)
+                                                uint32_t idesc, uint32_t first_accumulates, int ks_n,
+                                                uint32_t a_stride16 = (128 * 128) >> 4)
 {
     switch (La) {
-    case 1: issue_k_block<1>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n); break;
-    case 2: issue_k_block<2>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n); break;
-    case 3: issue_k_block<3>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n); break;
-    case 4: issue_k_block<4>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n); break;
-    case 5: issue_k_block<5>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n); break;
-    case 6: issue_k_block<6>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n); break;
-    case 7: issue_k_block<7>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n); break;
-    case 8: issue_k_block<8>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n); break;
-    default: issue_k_block<9>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n); break;
+    case 1: issue_k_block<1>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n, a_stride16); break;
+    case 2: issue_k_block<2>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n, a_stride16); break;
+    case 3: issue_k_block<3>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n, a_stride16); break;
+    case 4: issue_k_block<4>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n, a_stride16); break;
+    case 5: issue_k_block<5>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n, a_stride16); break;
+    case 6: issue_k_block<6>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n, a_stride16); break;
+    case 7: issue_k_block<7>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n, a_stride16); break;
+    case 8: issue_k_block<8>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n, a_stride16); break;
+    default: issue_k_block<9>(acc, nt_cols, sa, sb, idesc, first_accumulates, ks_n, a_stride16); break;
     }
 }
 
@@ -486,6 +501,8 @@ __device__ __forceinline__ void issue_extra_block(int La, int E, uint32_t acc_ex
 constexpr int kTileM = 128;
 constexpr int kBlockK = 128;   // bytes (= int8 elements) of K per pipeline stage
 constexpr int kThreads = 192;
+constexpr int kSplitTilesMax = 128;       // split-K: output tiles per launch (one arrival counter each)
+constexpr size_t kSplitHeader = 1024;     // bytes reserved for the counters in front of the partial sums
 
 struct LimbParams {
     int La, Lb, NT, stages;
@@ -550,6 +567,18 @@ struct LimbParams {
     const int64_t* addin;
     int64_t ep_mul, ep_div;
     int64_t causal_H, causal_start, mask_value;
+    // split-K (one-tile kernel, few output tiles, deep K: the weight-streaming shapes of decode).
+    // ksplit CTAs share an output tile, each accumulates kb_per_split K blocks; they add their shares of
+    // the sums (integers: exact in any order) to partial[tile][word][column][row], and the CTA that
+    // arrives last at tile_counter[tile] reads the totals back, shifts and stores them and leaves both
+    // arrays zeroed for the next launch.
+    int ksplit, kb_per_split;
+    unsigned long long* partial;
+    unsigned* tile_counter;
+    // one-tile kernel, M <= 64: the A box holds only a_box_rows (32 or 64) of the MMA's 128 rows, and the
+    // limb tiles lie that close together in shared memory.  The MMA still reads 128 rows per limb; what it
+    // finds beyond the box (the next limb, the B stack) lands in accumulator rows nobody stores.  0 = 128.
+    int a_box_rows;
 };
 
 __device__ __forceinline__ int limbs_needed_dev(unsigned long long maxabs)
@@ -694,51 +723,11 @@ __device__ __forceinline__ int64_t score_tail(const LimbParams& p, int64_t v, co
     return v;
 }
 
-// Reads the diagonals of one 128 x NT tile back from tensor memory, recombines them
-// (sum_d acc_d * 2^(8 d)), shifts and stores.  FITS64: the launcher proved |sum| < 2^62, so the
-// recombination runs in one 64-bit word instead of two.
+// shift, remainder, element-wise tail and store of one 8-column chunk whose sums are complete
 template <bool FITS64>
-__device__ __forceinline__ void epilogue_tile(const LimbParams& p, const EpilogueCtx& e)
+__device__ __forceinline__ void finish_chunk(const LimbParams& p, const EpilogueCtx& e, int nc, const int64_t (&s64)[8],
+                                             const i128w (&sum)[8], bool tail, const int64_t* arow, int64_t srow)
 {
-    const bool tail = p.addin || p.ep_div || p.causal_H;
-    const int64_t* arow = p.addin ? p.addin + e.z * p.c_sz + e.m * p.c_sm : nullptr;
-    const int64_t srow = p.causal_H ? seq_row(e.m, p.causal_H) : 0;
-    for (int nc = 0; nc < e.NT; nc += 8) {
-        i128w sum[8];
-        int64_t s64[8];
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            if (FITS64) s64[c] = p.addend;
-            else sum[c] = make_i128(p.addend);
-        }
-        for (int d0 = 0, g = 0; d0 < e.D; d0 += 4, ++g) {
-            int32_t a[4][8];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (d0 + j < e.D) tmem_ld8(e.tq + (uint32_t)((d0 + j) * e.NT + nc), a[j]);
-                else {
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) a[j][c] = 0;
-                }
-            }
-            tmem_ld_wait();
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const int64_t v = four_diagonals(a[0][c], a[1][c], a[2][c], a[3][c]);
-                if (FITS64) {
-                    // the sum fits 62 bits, so it has at most 6 diagonals: g <= 1 here
-                    s64[c] += g ? (int64_t)((uint64_t)v << 32) : v;
-                } else {
-                    i128w t;  // v * 2^(32 g)
-                    if (g == 0) { t.lo = (uint64_t)v; t.hi = v >> 63; }
-                    else if (g == 1) { t.lo = (uint64_t)v << 32; t.hi = v >> 32; }
-                    else if (g == 2) { t.lo = 0; t.hi = v; }
-                    else { t.lo = 0; t.hi = (int64_t)((uint64_t)v << 32); }
-                    sum[c] = add128(sum[c], t);
-                }
-            }
-        }
-        if (!e.row_ok) continue;
         int64_t cv[8], rv[8];
         const int64_t n = e.n0 + nc;
         const int shift = p.group_shift ? p.group_shift[2 * e.group + (n >= p.n_split ? 1 : 0)] : p.shift;
@@ -784,7 +773,209 @@ __device__ __forceinline__ void epilogue_tile(const LimbParams& p, const Epilogu
                     if (e.rrow) e.rrow[n + c] = rv[c];
                 }
         }
+}
+
+// Reads the diagonals of one 128 x NT tile back from tensor memory, recombines them
+// (sum_d acc_d * 2^(8 d)), shifts and stores.  FITS64: the launcher proved |sum| < 2^62, so the
+// recombination runs in one 64-bit word instead of two.
+// sum_d acc_d * 2^(8 d) + addend of one 8-column chunk, diagonals read back from tensor memory
+template <bool FITS64>
+__device__ __forceinline__ void gather_chunk(const EpilogueCtx& e, int nc, int64_t addend, int64_t (&s64)[8],
+                                             i128w (&sum)[8])
+{
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        if (FITS64) s64[c] = addend;
+        else sum[c] = make_i128(addend);
     }
+    for (int d0 = 0, g = 0; d0 < e.D; d0 += 4, ++g) {
+        int32_t a[4][8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (d0 + j < e.D) tmem_ld8(e.tq + (uint32_t)((d0 + j) * e.NT + nc), a[j]);
+            else {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) a[j][c] = 0;
+            }
+        }
+        tmem_ld_wait();
+        if (g >= 4) continue;         // diagonals from 16 on only reach bits beyond the 128 kept
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const int64_t v = four_diagonals(a[0][c], a[1][c], a[2][c], a[3][c]);
+            if (FITS64) {
+                // the sum fits 62 bits, so it has at most 6 diagonals: g <= 1 here
+                s64[c] += g ? (int64_t)((uint64_t)v << 32) : v;
+            } else {
+                i128w t;  // v * 2^(32 g)
+                if (g == 0) { t.lo = (uint64_t)v; t.hi = v >> 63; }
+                else if (g == 1) { t.lo = (uint64_t)v << 32; t.hi = v >> 32; }
+                else if (g == 2) { t.lo = 0; t.hi = v; }
+                else { t.lo = 0; t.hi = (int64_t)((uint64_t)v << 32); }
+                sum[c] = add128(sum[c], t);
+            }
+        }
+    }
+}
+
+template <bool FITS64>
+__device__ __forceinline__ void epilogue_tile(const LimbParams& p, const EpilogueCtx& e)
+{
+    const bool tail = p.addin || p.ep_div || p.causal_H;
+    const int64_t* arow = p.addin ? p.addin + e.z * p.c_sz + e.m * p.c_sm : nullptr;
+    const int64_t srow = p.causal_H ? seq_row(e.m, p.causal_H) : 0;
+    for (int nc = 0; nc < e.NT; nc += 8) {
+        i128w sum[8];
+        int64_t s64[8];
+        gather_chunk<FITS64>(e, nc, p.addend, s64, sum);
+        if (!e.row_ok) continue;
+        finish_chunk<FITS64>(p, e, nc, s64, sum, tail, arow, srow);
+    }
+}
+
+// The same for sums that fit 62 bits with the diagonal count known at compile time (DD <= 6), software
+// pipelined: the accumulators of the next CW columns are requested before the current ones are shifted and
+// stored, so the tensor-memory round trip hides behind the arithmetic and the stores of the previous step.
+template <int DD, int CW>
+__device__ __forceinline__ void fetch_cols(const EpilogueCtx& e, int nc, int32_t (&a)[DD][CW])
+{
+#pragma unroll
+    for (int d = 0; d < DD; ++d) tmem_ldn(e.tq + (uint32_t)(d * e.NT + nc), a[d]);
+}
+
+// tot != nullptr: split-K, the recombined sums (no addend) are added to the tile's totals instead
+template <int DD, int CW>
+__device__ __forceinline__ void finish_cols(const LimbParams& p, const EpilogueCtx& e, int nc, const int32_t (&a)[DD][CW],
+                                            bool tail, const int64_t* arow, int64_t srow, unsigned long long* tot)
+{
+    if (!e.row_ok) return;
+    const int64_t addend = tot ? 0 : p.addend;
+#pragma unroll
+    for (int h = 0; h < CW; h += 8) {
+        int64_t s64[8];
+        i128w unused[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            int64_t lo = mad_wide(a[0][h + c], 1, addend);
+            if (DD > 1) lo = mad_wide(a[DD > 1 ? 1 : 0][h + c], 1 << 8, lo);
+            if (DD > 2) lo = mad_wide(a[DD > 2 ? 2 : 0][h + c], 1 << 16, lo);
+            if (DD > 3) lo = mad_wide(a[DD > 3 ? 3 : 0][h + c], 1 << 24, lo);
+            if (DD > 4) {
+                uint32_t hi = (uint32_t)a[DD > 4 ? 4 : 0][h + c];
+                if (DD > 5) hi += (uint32_t)a[DD > 5 ? 5 : 0][h + c] << 8;
+                lo = (int64_t)((uint64_t)lo + ((uint64_t)hi << 32));
+            }
+            s64[c] = lo;
+        }
+        if (tot) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                if (s64[c]) atomicAdd(tot + (int64_t)(nc + h + c) * kTileM, (unsigned long long)s64[c]);
+        } else
+            finish_chunk<true>(p, e, nc + h, s64, unused, tail, arow, srow);
+    }
+}
+
+template <int DD, int CW>
+__device__ __forceinline__ void epilogue_tile_pipelined(const LimbParams& p, const EpilogueCtx& e, unsigned long long* tot)
+{
+    const bool tail = p.addin || p.ep_div || p.causal_H;
+    const int64_t* arow = p.addin ? p.addin + e.z * p.c_sz + e.m * p.c_sm : nullptr;
+    const int64_t srow = p.causal_H ? seq_row(e.m, p.causal_H) : 0;
+    int32_t a0[DD][CW], a1[DD][CW];
+    fetch_cols<DD, CW>(e, 0, a0);
+    for (int nc = 0; nc < e.NT; nc += 2 * CW) {
+        tmem_ld_wait();
+        const bool more1 = nc + CW < e.NT;
+        if (more1) fetch_cols<DD, CW>(e, nc + CW, a1);
+        finish_cols<DD, CW>(p, e, nc, a0, tail, arow, srow, tot);
+        if (more1) {
+            tmem_ld_wait();
+            if (nc + 2 * CW < e.NT) fetch_cols<DD, CW>(e, nc + 2 * CW, a0);
+            finish_cols<DD, CW>(p, e, nc + CW, a1, tail, arow, srow, tot);
+        }
+    }
+}
+
+// false when the tile has no compiled pipelined epilogue (the caller then uses epilogue_tile)
+__device__ __forceinline__ bool epilogue_tile_fast(const LimbParams& p, const EpilogueCtx& e, unsigned long long* tot = nullptr)
+{
+    if (!p.fits64) return false;
+    switch (e.D) {
+    case 2: epilogue_tile_pipelined<2, 16>(p, e, tot); return true;
+    case 3: epilogue_tile_pipelined<3, 16>(p, e, tot); return true;
+    case 4: epilogue_tile_pipelined<4, 16>(p, e, tot); return true;
+    case 5: epilogue_tile_pipelined<5, 8>(p, e, tot); return true;
+    case 6: epilogue_tile_pipelined<6, 8>(p, e, tot); return true;
+    default: return false;
+    }
+}
+
+// Split-K.  A CTA's share of a tile's sums, recombined from its diagonals, is added to the tile's totals in
+// global memory, totals[word][column][row of the tile]: one 64-bit word when the sum fits 62 bits, else the low
+// 55 bits and the rest (the launcher checked that the rest fits a word; sums of up to 256 shares of 55 bits
+// stay below 2^63).  Integer sums: exact in any order.
+constexpr int kSplitLowBits = 55;
+template <bool FITS64>
+__device__ __forceinline__ void add_partials_tile(const LimbParams& p, const EpilogueCtx& e, unsigned long long* tot)
+{
+    for (int nc = 0; nc < e.NT; nc += 8) {
+        i128w sum[8];
+        int64_t s64[8];
+        gather_chunk<FITS64>(e, nc, 0, s64, sum);
+        if (!e.row_ok) continue;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            unsigned long long* w = tot + (int64_t)(nc + c) * kTileM;
+            if (FITS64) {
+                if (s64[c]) atomicAdd(w, (unsigned long long)s64[c]);
+            } else {
+                const unsigned long long lo = sum[c].lo & ((1ull << kSplitLowBits) - 1ull);
+                const unsigned long long hi = (unsigned long long)sar128_lo(sum[c], kSplitLowBits);
+                if (lo) atomicAdd(w, lo);
+                if (hi) atomicAdd(w + (int64_t)e.NT * kTileM, hi);
+            }
+        }
+    }
+}
+
+// The last CTA of a split-K tile: one 8-column chunk of one row from the totals.  Every word is requested
+// before the first is used (one round trip to L2 per chunk) and written back as zero, the state the next
+// launch expects.
+template <bool FITS64>
+__device__ __forceinline__ void epilogue_totals_chunk(const LimbParams& p, const EpilogueCtx& e, unsigned long long* col0,
+                                                      int nc)
+{
+    if (!e.row_ok) return;
+    unsigned long long lo[8], hi[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        lo[c] = __ldcg(col0 + (int64_t)(nc + c) * kTileM);
+        hi[c] = FITS64 ? 0ull : __ldcg(col0 + (int64_t)(e.NT + nc + c) * kTileM);
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        __stcg(col0 + (int64_t)(nc + c) * kTileM, 0ull);
+        if (!FITS64) __stcg(col0 + (int64_t)(e.NT + nc + c) * kTileM, 0ull);
+    }
+    i128w sum[8];
+    int64_t s64[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        if (FITS64) s64[c] = (int64_t)lo[c] + p.addend;
+        else {
+            i128w t;       // hi * 2^55 + lo + addend
+            t.lo = hi[c] << kSplitLowBits;
+            t.hi = (int64_t)hi[c] >> (64 - kSplitLowBits);
+            i128w l;
+            l.lo = lo[c]; l.hi = 0;
+            sum[c] = add128(add128(t, l), make_i128(p.addend));
+        }
+    }
+    const bool tail = p.addin || p.ep_div || p.causal_H;
+    const int64_t* arow = p.addin ? p.addin + e.z * p.c_sz + e.m * p.c_sm : nullptr;
+    const int64_t srow = p.causal_H ? seq_row(e.m, p.causal_H) : 0;
+    finish_chunk<FITS64>(p, e, nc, s64, sum, tail, arow, srow);
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -795,7 +986,9 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     __shared__ __align__(8) uint64_t bars[2 * 8 + 2];
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
+    __shared__ int s_last;
 
+    const long long t_cta0 = p.wait_cycles ? clock64() : 0;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int group = 0;
     if (p.tile_group) {
@@ -819,7 +1012,8 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         } else La = need;
     }
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t a_bytes = (uint32_t)p.La * kTileM * kBlockK;
+    const uint32_t a_limb_bytes = (uint32_t)(p.a_box_rows ? p.a_box_rows : kTileM) * kBlockK;
+    const uint32_t a_bytes = (uint32_t)p.La * a_limb_bytes;
     const uint32_t b_bytes = (uint32_t)p.Lb * p.NT * kBlockK;
     const uint32_t stage_bytes = a_bytes + b_bytes;
     const uint32_t bar_full = smem_u32(&bars[0]);
@@ -827,14 +1021,18 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t bar_zeroed = smem_u32(&bars[16]);
     const uint32_t bar_accum = smem_u32(&bars[17]);
 
+    // split-K: consecutive CTAs share an output tile and take consecutive K slices of it
+    int64_t bx = blockIdx.x;
+    int split = 0;
+    if (p.ksplit > 1) { split = (int)(bx % p.ksplit); bx /= p.ksplit; }
     // tiles are walked panel by panel: panel_m row tiles x all column tiles, rows fastest, so the
     // A tiles of a panel and the B tile in flight stay in L2 while the panel is swept
     int64_t m_tile, n_tile;
     if (p.tile_group) { m_tile = blockIdx.x; n_tile = blockIdx.y; }
     else {
         const int64_t per_panel = p.panel_m * p.n_tiles;
-        const int64_t panel = blockIdx.x / per_panel;
-        const int64_t within = blockIdx.x - panel * per_panel;
+        const int64_t panel = bx / per_panel;
+        const int64_t within = bx - panel * per_panel;
         const int64_t rows_here = (p.m_tiles - panel * p.panel_m < p.panel_m) ? p.m_tiles - panel * p.panel_m
                                                                               : p.panel_m;
         n_tile = within / rows_here;
@@ -845,6 +1043,11 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int64_t n0 = n_tile * p.NT;
     const int64_t z = blockIdx.z;
     int kb_end = p.kblocks;
+    int kb_begin = 0;
+    if (p.ksplit > 1) {
+        kb_begin = split * p.kb_per_split;
+        kb_end = kb_begin + p.kb_per_split < p.kblocks ? kb_begin + p.kb_per_split : p.kblocks;
+    }
     if (p.skip_k) {
         // rows of this tile see nothing beyond column skip_start + s_max: later K blocks are all zero
         int64_t last_row = m0 + kTileM - 1;
@@ -876,30 +1079,31 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // ---- TMA producer -------------------------------------------------------------
         if (lane == 0) {
             const int64_t zb = p.tile_group ? group : (p.b_batched ? z : 0);
-            const uint32_t tx_bytes = (uint32_t)La * kTileM * kBlockK + b_bytes;
+            const uint32_t tx_bytes = (uint32_t)La * a_limb_bytes + b_bytes;
             int armed = 0;
-            for (int kb = 0; kb < kb_end; ++kb) {
-                const int s = kb % p.stages;
-                const uint32_t par = ((kb / p.stages) & 1) ^ 1;
+            for (int kb = kb_begin; kb < kb_end; ++kb) {
+                const int it = kb - kb_begin;
+                const int s = it % p.stages;
+                const uint32_t par = ((it / p.stages) & 1) ^ 1;
                 if (!mbar_wait(bar_empty + 8 * s, par, abort_flag)) break;
                 const uint32_t full = bar_full + 8 * s;
                 mbar_expect_tx(full, tx_bytes);
                 const uint32_t sa = smem_base + s * stage_bytes;
                 const uint32_t sb = sa + a_bytes;
                 for (int i = 0; i < La; ++i)
-                    tma_load_2d(sa + i * (kTileM * kBlockK), &tmA, kb * kBlockK,
+                    tma_load_2d(sa + i * a_limb_bytes, &tmA, kb * kBlockK,
                                 (int)(i * p.a_rows_per_limb + z * p.M + m0), full);
                 for (int j = 0; j < p.Lb; ++j)
                     tma_load_2d(sb + j * (p.NT * kBlockK), &tmB, kb * kBlockK,
                                 (int)(j * p.b_rows_per_limb + zb * p.N + n0), full);
-                armed = kb + 1;
+                armed = it + 1;
             }
             if (*abort_flag) {
                 // leave no copy in flight: wait (bounded) for every stage that was armed and
                 // that no consumer waited for
-                for (int kb = (armed > p.stages ? armed - p.stages : 0); kb < armed; ++kb)
+                for (int i = (armed > p.stages ? armed - p.stages : 0); i < armed; ++i)
                     for (uint32_t it = 0; it < kSpinLimit; ++it)
-                        if (mbar_try(bar_full + 8 * (kb % p.stages), (kb / p.stages) & 1)) break;
+                        if (mbar_try(bar_full + 8 * (i % p.stages), (i / p.stages) & 1)) break;
             }
         }
     } else if (warp == 1) {
@@ -911,13 +1115,15 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                    | ((uint32_t)(kTileM >> 4) << 24);        // M
             bool ok = mbar_wait(bar_zeroed, 0, abort_flag);
             tc_fence_after();
-            for (int kb = 0; ok && kb < kb_end; ++kb) {
-                const int s = kb % p.stages;
-                ok = mbar_wait(bar_full + 8 * s, (kb / p.stages) & 1, abort_flag);
+            for (int kb = kb_begin; ok && kb < kb_end; ++kb) {
+                const int it = kb - kb_begin;
+                const int s = it % p.stages;
+                ok = mbar_wait(bar_full + 8 * s, (it / p.stages) & 1, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t sa = smem_base + s * stage_bytes;
-                issue_k_block_n(La, tmem, (uint32_t)p.NT, sa, sa + a_bytes, idesc, kb ? 1u : 0u, kBlockK / 32);
+                issue_k_block_n(La, tmem, (uint32_t)p.NT, sa, sa + a_bytes, idesc, it ? 1u : 0u, kBlockK / 32,
+                                a_limb_bytes >> 4);
                 umma_commit(bar_empty + 8 * s);
             }
             umma_commit(bar_accum);
@@ -934,8 +1140,34 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_zeroed);
 
+        const bool prof = p.wait_cycles != nullptr && warp == 2 && lane == 0;
+        long long ph0 = prof ? clock64() : 0, ph1 = 0, ph2 = 0, ph3 = 0;
         const bool ok = mbar_wait(bar_accum, 0, abort_flag);
         tc_fence_after();
+        if (prof) ph1 = clock64();
+        if (p.wait_cycles != nullptr && warp == 2 && ok) {
+            // latency probes (diagnostic runs only): one 8-column load, four of them, one 16-column load,
+            // each followed by a wait
+            int32_t t8[8], u8[4][8], t16[16];
+            long long c0 = clock64();
+            tmem_ld8(tq, t8);
+            tmem_ld_wait();
+            long long c1 = clock64();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) tmem_ld8(tq + (uint32_t)(8 * j), u8[j]);
+            tmem_ld_wait();
+            long long c2 = clock64();
+            tmem_ldn(tq, t16);
+            tmem_ld_wait();
+            long long c3 = clock64();
+            int keep = t8[0] ^ u8[3][7] ^ t16[15];
+            if (lane == 0) {
+                atomicMax(p.wait_cycles + 13, (unsigned long long)(c1 - c0));
+                atomicMax(p.wait_cycles + 14, (unsigned long long)(c2 - c1));
+                atomicMax(p.wait_cycles + 15, (unsigned long long)(c3 - c2) + (keep == 0x7fffffff ? 1ull : 0ull));
+            }
+            if (prof) ph1 = clock64();
+        }
         const int64_t m = m0 + q * 32 + lane;
         int64_t* crow = p.C + z * p.c_sz + m * p.c_sm;
         int64_t* rrow = p.R ? p.R + z * p.c_sz + m * p.c_sm : nullptr;
@@ -945,9 +1177,69 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         EpilogueCtx ec;
         ec.tq = tq; ec.D = D; ec.NT = p.NT; ec.m = m; ec.n0 = n0; ec.z = z; ec.group = group;
         ec.crow = crow; ec.rrow = rrow; ec.row_ok = row_ok; ec.vec_ok = vec_ok;
-        if (ok) {
-            if (p.fits64) epilogue_tile<true>(p, ec);
-            else epilogue_tile<false>(p, ec);
+        bool finish = ok;
+        if (p.ksplit > 1) {
+            // add this CTA's share of the sums to the tile's totals (rows beyond M hold nothing)
+            const int64_t tile_id = z * (p.m_tiles * p.n_tiles) + bx;
+            unsigned long long* tile_tot = p.partial + tile_id * (2ll * p.NT * kTileM);
+            if (ok && m0 + q * 32 < p.M) {
+                if (!epilogue_tile_fast(p, ec, tile_tot + q * 32 + lane)) {
+                    if (p.fits64) add_partials_tile<true>(p, ec, tile_tot + q * 32 + lane);
+                    else add_partials_tile<false>(p, ec, tile_tot + q * 32 + lane);
+                }
+            }
+            if (prof) ph2 = clock64();
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (warp == 2 && lane == 0) {
+                // a CTA that gave up a wait does not count: the tile then stays unfinished and the
+                // error word tells the host
+                s_last = 0;
+                if (ok) s_last = atomicAdd(p.tile_counter + tile_id, 1u) == (unsigned)(p.ksplit - 1) ? 1 : 0;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            finish = false;
+            if (prof) ph3 = clock64();
+            if (s_last) {
+                // the last CTA of the tile: every (32-row group, 8-column chunk) of the totals is one unit
+                // of work for any of the four warps (the totals are in global memory, not tied to lanes)
+                __threadfence();
+                if (warp == 2 && lane == 0) p.tile_counter[tile_id] = 0u;
+                int64_t rows_here = p.M - m0;
+                if (rows_here > kTileM) rows_here = kTileM;
+                const int chunks = p.NT >> 3;
+                const int units = (int)((rows_here + 31) >> 5) * chunks;
+                for (int u = q; u < units; u += 4) {
+                    const int rg = u / chunks, nc = (u - rg * chunks) << 3;
+                    EpilogueCtx eu = ec;
+                    eu.m = m0 + rg * 32 + lane;
+                    eu.row_ok = eu.m < p.M;
+                    eu.crow = p.C + z * p.c_sz + eu.m * p.c_sm;
+                    eu.rrow = p.R ? p.R + z * p.c_sz + eu.m * p.c_sm : nullptr;
+                    unsigned long long* col0 = tile_tot + rg * 32 + lane;
+                    if (p.fits64) epilogue_totals_chunk<true>(p, eu, col0, nc);
+                    else epilogue_totals_chunk<false>(p, eu, col0, nc);
+                }
+            }
+        }
+        if (finish) {
+            if (!epilogue_tile_fast(p, ec)) {
+                if (p.fits64) epilogue_tile<true>(p, ec);
+                else epilogue_tile<false>(p, ec);
+            }
+        }
+        if (prof) {
+            // longest phase over the CTAs: [8] start -> accumulators complete, [9] partials added, [10] fence and
+            // arrival counter, [11] epilogue (last CTA of a tile), [12] CTA lifetime from its first instruction
+            const long long ph4 = clock64();
+            atomicMax(p.wait_cycles + 8, (unsigned long long)(ph1 - ph0));
+            if (p.ksplit > 1) {
+                atomicMax(p.wait_cycles + 9, (unsigned long long)(ph2 - ph1));
+                atomicMax(p.wait_cycles + 10, (unsigned long long)(ph3 - ph2));
+                if (s_last) atomicMax(p.wait_cycles + 11, (unsigned long long)(ph4 - ph3));
+            } else
+                atomicMax(p.wait_cycles + 11, (unsigned long long)(ph4 - ph1));
+            atomicMax(p.wait_cycles + 12, (unsigned long long)(ph4 - t_cta0));
         }
     }
 
@@ -1627,21 +1919,29 @@ int launch_split_t(const T* X, int8_t* planes, int L, int64_t nb, int64_t rows, 
     int64_t cap = (int64_t)sm_count() * 32;
     if (bx > cap) bx = cap;
     if (nb > 65535) return ZKDS_ERR_RANGE;
-    if (sk == 1 && !getenv("ZKDS_SPLIT_GENERIC")) {
+    if (sk == 1 && !switches().split_generic) {
         int tl = 0;
         while (tl < 8 && (1 << tl) < (Kp >> 2)) ++tl;
         const int64_t rpb = 256 >> tl;
         const int64_t gx = (rows + rpb - 1) / rpb;        // row groups per batch
         if (gx * nb > 0x7fffffffll) return ZKDS_ERR_RANGE;   // the kernel's 32-bit item counter cannot wrap
         const int z_fast = (nb > 1 && sz < sr) ? 1 : 0;
-        int64_t blocks = gx * nb;
+        int64_t kseg = 1, seg_quads = Kp >> 2;
+        const int64_t per_row = ((Kp >> 2) + (1 << tl) - 1) >> tl;      // quads each thread of a row walks
+        if (gx * nb < 2 * (int64_t)sm_count() && per_row > 1) {
+            kseg = (2 * (int64_t)sm_count() + gx * nb - 1) / (gx * nb);
+            if (kseg > per_row) kseg = per_row;
+            seg_quads = ((per_row + kseg - 1) / kseg) << tl;
+            kseg = ((Kp >> 2) + seg_quads - 1) / seg_quads;
+        }
+        int64_t blocks = gx * nb * kseg;
         if (blocks > cap) blocks = cap;
         dim3 g2((unsigned)blocks);
 #define ZKDS_SPLIT_ROWS(LL)                                                                              \
     split_rows_kernel<T, LL><<<g2, 256, 0, st>>>(X, planes, L, rows, K, Kp, sz, sr, div,                  \
                                                  nb * rows * dst_pitch, overflow, absmax_out, dst_pitch, \
                                                  valid_H, valid_start, tl, (unsigned)nb, (unsigned)gx, z_fast, shl, \
-                                                 row_index)
+                                                 row_index, (unsigned)kseg, seg_quads)
         switch (L) {
         case 2: ZKDS_SPLIT_ROWS(2); break;
         case 3: ZKDS_SPLIT_ROWS(3); break;
@@ -1733,6 +2033,26 @@ float limb_last_kernel_ms()
     return ms;
 }
 
+// Share of a launch's (row tile x column tile x K block) work that is issued under causal skipping
+// (LimbParams::skip_tiles / skip_k): what the timing records count as int8 operations.
+static double issued_share(int64_t M, int64_t N, int64_t K, int NT, int skip_tiles, int skip_k, int64_t H,
+                           int64_t start)
+{
+    if ((!skip_tiles && !skip_k) || H <= 0) return 1.0;
+    const int64_t mt = (M + kTileM - 1) / kTileM, nt = (N + NT - 1) / NT, kb = (K + kBlockK - 1) / kBlockK;
+    double issued = 0.0;
+    for (int64_t t = 0; t < mt; ++t) {
+        int64_t last = t * kTileM + kTileM - 1;
+        if (last > M - 1) last = M - 1;
+        const int64_t s_max = last / H;
+        int64_t cols = nt, blocks = kb;
+        if (skip_tiles) { cols = (start + s_max) / NT + 1; if (cols > nt) cols = nt; }
+        if (skip_k) { blocks = (start + s_max + 1 + kBlockK - 1) / kBlockK; if (blocks > kb) blocks = kb; if (blocks < 1) blocks = 1; }
+        issued += (double)cols * (double)blocks;
+    }
+    return issued / ((double)mt * (double)nt * (double)kb);
+}
+
 static cudaEvent_t* timing_events()
 {
     int dev = 0;
@@ -1787,10 +2107,8 @@ int planes_split(const void* X, int bits, int64_t nb, int64_t rows, int64_t K, i
 // registers per thread.  ZKDS_EPI_WARPS = 8 | 16 overrides for experiments.
 static int persistent_epilogue_warps(bool fused_scores)
 {
-    if (const char* e = getenv("ZKDS_EPI_WARPS")) {
-        const int v = atoi(e);
-        if (v == 8 || v == 16) return v;
-    }
+    const int v = switches().epi_warps;
+    if (v == 8 || v == 16) return v;
     return fused_scores ? 16 : 8;
 }
 
@@ -1798,11 +2116,11 @@ static int launch_persistent(int ew, int ctas, size_t smem, cudaStream_t st, con
                              const CUtensorMap& tmB, const LimbParams& lp_in)
 {
     LimbParams lp = lp_in;
-    lp.backoff = getenv("ZKDS_NO_BACKOFF") ? 0u : 1u;
+    lp.backoff = switches().no_backoff ? 0u : 1u;
     // ZKDS_WAIT_PROFILE=1: a synchronous diagnostic run that prints where the MMA warp and the first
     // epilogue warp spent their cycles (share of their lifetime spent waiting)
     unsigned long long* prof = nullptr;
-    if (getenv("ZKDS_WAIT_PROFILE")) {
+    if (switches().wait_profile) {
         prof = (unsigned long long*)workspace(8 * sizeof(unsigned long long), 4);
         if (prof) ZKDS_CUDA(cudaMemsetAsync(prof, 0, 8 * sizeof(unsigned long long), st));
         lp.wait_cycles = prof;
@@ -1859,8 +2177,8 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
         if (smem_max / stage < 3) score *= 0.97;      // prefer three pipeline stages when it is close
         if (score > best * 1.02) { best = score; NT = cand; }
     }
-    if (const char* e = getenv("ZKDS_TILE_NT")) {       // experiments: force a width that fits
-        const int want = atoi(e);
+    if (switches().tile_nt) {       // experiments: force a width that fits
+        const int want = switches().tile_nt;
         if (want >= 16 && want % 16 == 0 && Lb * want <= 256 && D * want <= 512 &&
             smem_max / ((size_t)La * kTileM * kBlockK + (size_t)Lb * want * kBlockK) >= 2)
             NT = want;
@@ -1887,9 +2205,9 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     // (a full 256-column B stack for two-limb weights) wins although it overlaps nothing
     // (wq_b, K = 1536: 0.70 against 0.85 ms; w2 of the shared expert, K = 2048: 0.68 against 0.93 ms)
     int64_t max_kb = 8;
-    if (const char* e = getenv("ZKDS_PERSISTENT_MAX_KB")) max_kb = atoi(e);
-    if (!p.R && !p.skip_k && (Kp + kBlockK - 1) / kBlockK <= max_kb && !getenv("ZKDS_NO_PERSISTENT") &&
-        !(p.tile_group && getenv("ZKDS_NO_PERSISTENT_GROUPED"))) {
+    if (switches().persistent_max_kb >= 0) max_kb = switches().persistent_max_kb;
+    if (!p.R && !p.skip_k && (Kp + kBlockK - 1) / kBlockK <= max_kb && !switches().no_persistent &&
+        !(p.tile_group && switches().no_persistent_grouped)) {
         for (int cand : {64, 48, 32, 16}) {
             if (Lb * cand > 256 || 2 * D * cand > 512) continue;
             size_t st_b = (size_t)La * kTileM * kBlockK + (size_t)Lb * cand * kBlockK;
@@ -1956,12 +2274,26 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
         if (rc != ZKDS_OK) return rc;
     }
 
+    // few rows (decode, the small-M GEMM): a smaller A box, more pipeline stages
+    int a_box = kTileM;
+    if (!persistent && !p.tile_group && p.M <= 64) {
+        const int want = p.M <= 32 ? 32 : 64;
+        // the MMA of the last limb reads 128 rows from its tile's start: that must stay inside the stage
+        if ((size_t)(kTileM - want) * kBlockK <= (size_t)Lb * NT * kBlockK) a_box = want;
+    }
+    size_t stage_bytes = stage;
+    if (a_box != kTileM) {
+        stage_bytes = (size_t)La * a_box * kBlockK + (size_t)Lb * NT * kBlockK;
+        stages = (int)(smem_max / stage_bytes);
+        if (stages > 8) stages = 8;
+    }
     CUtensorMap tmA, tmB;
-    if (!make_plane_map(&tmA, pa, (int64_t)La * a_rows, Kp, kTileM)) return ZKDS_ERR_UNSUPPORTED;
+    if (!make_plane_map(&tmA, pa, (int64_t)La * a_rows, Kp, a_box)) return ZKDS_ERR_UNSUPPORTED;
     if (!make_plane_map(&tmB, pb, (int64_t)Lb * b_rows, Kp, NT)) return ZKDS_ERR_UNSUPPORTED;
 
     LimbParams lp{};
     lp.La = La; lp.Lb = Lb; lp.NT = NT; lp.stages = stages;
+    lp.a_box_rows = a_box == kTileM ? 0 : a_box;
     lp.kblocks = (int)((Kp + kBlockK - 1) / kBlockK);
     lp.k_extent = Kp;
     uint32_t cols = 32;
@@ -1984,7 +2316,32 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     lp.addin = p.addin; lp.ep_mul = p.ep_mul; lp.ep_div = p.ep_div;
     lp.causal_H = p.causal_H; lp.causal_start = p.causal_start; lp.mask_value = p.mask_value;
 
-    size_t smem = stage * stages + 1024;
+    // split-K for the weight-streaming shapes (few output tiles, deep K): see LimbParams::ksplit
+    lp.ksplit = 1;
+    const int64_t tiles_total = p.batches * mt * nt_eff;
+    if (!persistent && !p.tile_group && !p.skip_k && !p.skip_tiles && lp.kblocks >= 2 && !switches().no_split_k &&
+        tiles_total * 2 <= sm_count() && tiles_total <= kSplitTilesMax && 8 * (La + Lb) + 18 <= 116) {
+        int want = (int)(sm_count() / tiles_total);
+        if (want > lp.kblocks) want = lp.kblocks;
+        const int per = (lp.kblocks + want - 1) / want;
+        const int ks = (lp.kblocks + per - 1) / per;
+        if (ks > 1) {
+            const size_t words = (size_t)tiles_total * 2 * NT * kTileM;
+            size_t fresh = 0;
+            uint8_t* ws = (uint8_t*)workspace_fresh(kSplitHeader + words * sizeof(uint64_t), 6, &fresh);
+            if (!ws) return ZKDS_ERR_WORKSPACE;
+            // the kernel leaves the block zeroed; it has to be cleared when it is new, and after a launch
+            // that gave up a wait (its tiles were never finished)
+            if (fresh) ZKDS_CUDA(cudaMemsetAsync(ws, 0, fresh, st));
+            else if (fl->host[0]) ZKDS_CUDA(cudaMemsetAsync(ws, 0, kSplitHeader + words * sizeof(uint64_t), st));
+            lp.ksplit = ks;
+            lp.kb_per_split = per;
+            lp.tile_counter = (unsigned*)ws;
+            lp.partial = (unsigned long long*)(ws + kSplitHeader);
+        }
+    }
+
+    size_t smem = stage_bytes * stages + 1024;
     // more than half the shared memory per CTA keeps one CTA per SM, so its tensor-memory
     // allocation can never wait for a co-resident CTA
     if (smem < 120 * 1024) smem = 120 * 1024;
@@ -1997,7 +2354,7 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     lp.m_tiles = mt; lp.n_tiles = nt_eff; lp.panel_m = panel;
     if (mt * nt_eff > 0x7fffffffll) return ZKDS_ERR_UNSUPPORTED;
     dim3 grid = p.tile_group ? dim3((unsigned)mt, (unsigned)nt_eff, 1)
-                             : dim3((unsigned)(mt * nt_eff), 1, (unsigned)p.batches);
+                             : dim3((unsigned)(mt * nt_eff * lp.ksplit), 1, (unsigned)p.batches);
     cudaEvent_t* ev = timing_events();
     if (ev) ZKDS_CUDA(cudaEventRecord(ev[0], st));
     if (persistent) {
@@ -2008,8 +2365,24 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
         if (total_tiles < ctas) ctas = (int)total_tiles;
         rc = launch_persistent(ew, ctas, psmem, st, tmA, tmB, lp);
     } else {
+        unsigned long long* prof = nullptr;
+        if (switches().wait_profile) {
+            prof = (unsigned long long*)workspace(32 * sizeof(unsigned long long), 4);
+            if (prof) ZKDS_CUDA(cudaMemsetAsync(prof, 0, 32 * sizeof(unsigned long long), st));
+            lp.wait_cycles = prof;
+        }
         limb_gemm_kernel<<<grid, kThreads, smem, st>>>(tmA, tmB, lp);
         rc = check_launch();
+        if (prof && rc == ZKDS_OK) {
+            unsigned long long h[32];
+            ZKDS_CUDA(cudaStreamSynchronize(st));
+            ZKDS_CUDA(cudaMemcpy(h, prof, sizeof(h), cudaMemcpyDeviceToHost));
+            fprintf(stderr, "one-tile M=%lld N=%lld kblocks=%d NT=%d stages=%d ksplit=%d ctas=%u: longest phase in cycles: "
+                            "accumulate %llu, add partials %llu, fence+counter %llu, epilogue %llu, CTA lifetime %llu; "
+                            "tcgen05.ld + wait: x8 %llu, 4 x x8 %llu, x16 %llu\n",
+                    (long long)lp.M, (long long)lp.N, lp.kblocks, lp.NT, lp.stages, lp.ksplit, grid.x * grid.z, h[8], h[9],
+                    h[10], h[11], h[12], h[13], h[14], h[15]);
+        }
     }
     if (ev) ZKDS_CUDA(cudaEventRecord(ev[1], st));
     if (ev && g_accumulate && rc == ZKDS_OK) {
@@ -2024,7 +2397,7 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
             int need = limbs_needed(h);
             if (need < la_used) la_used = need;
         }
-        if (getenv("ZKDS_TRACE"))
+        if (switches().trace)
             fprintf(stderr, "limb_gemm batches=%lld M=%lld N=%lld K=%lld La=%d(%d) Lb=%d NT=%d stages=%d fits64=%d tail=%d: %.3f ms\n",
                     (long long)p.batches, (long long)p.M, (long long)p.N, (long long)p.K, la_used, La, Lb, NT,
                     stages, lp.fits64, (p.addin || p.ep_div || p.causal_H) ? 1 : 0, ms);
@@ -2034,7 +2407,8 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
             r.v[4] = la_used; r.v[5] = Lb; r.v[6] = ms; r.v[7] = (p.tile_group ? 1.0 : 0.0) + (p.b_sz ? 2.0 : 0.0);
         }
         g_tot_ms += ms;
-        g_tot_ops += 2.0 * (double)la_used * Lb * (double)p.batches * (double)p.M * (double)p.N * (double)p.K;
+        g_tot_ops += 2.0 * (double)la_used * Lb * (double)p.batches * (double)p.M * (double)p.N * (double)p.K *
+                     issued_share(p.M, p.N, p.K, NT, p.skip_tiles, p.skip_k, p.skip_H, p.skip_start);
         g_tot_launches += 1;
     }
     return rc;
@@ -2051,7 +2425,7 @@ int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st)
 {
     if (La < 1 || Lb < 1 || La > 9 || Lb > 9) return ZKDS_ERR_UNSUPPORTED;
     if (f.K1 <= 0 || f.K2 <= 0 || (f.K1 % kBlockK) != 0) return ZKDS_ERR_UNSUPPORTED;
-    if (getenv("ZKDS_NO_PERSISTENT")) return ZKDS_ERR_UNSUPPORTED;
+    if (switches().no_persistent) return ZKDS_ERR_UNSUPPORTED;
     const int D = La + Lb - 1;
     const int pairs = La < Lb ? La : Lb;
     const int64_t Kmax = f.K1 > f.K2 ? f.K1 : f.K2;
@@ -2070,7 +2444,7 @@ int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st)
     const int delta = f.shift1 - f.shift2;
     int E = 0;
     const int64_t Kp2m = (f.K2 + 15) & ~(int64_t)15;
-    if (delta >= 0 && delta <= 8 && f.shift1 >= 1 && f.shift1 <= 31 && !getenv("ZKDS_NO_MERGED")) {
+    if (delta >= 0 && delta <= 8 && f.shift1 >= 1 && f.shift1 <= 31 && !switches().no_merged) {
         const int e = (f.shift1 + 7) / 8;
         const int64_t a12 = f.addend1 + (int64_t)((uint64_t)f.addend2 << delta);
         // the one-pass epilogue is compiled for three extra diagonals and up to six main ones
@@ -2144,7 +2518,7 @@ int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st)
     while (cols < (uint32_t)((E ? (D + E) : 2 * nbuf * D) * NT)) cols <<= 1;
     lp.tmem_cols = cols;
     lp.nbuf = nbuf;
-    lp.split_release = (nbuf == 1 && (E || !getenv("ZKDS_NO_SPLIT_RELEASE"))) ? 1 : 0;
+    lp.split_release = (nbuf == 1 && (E || !switches().no_split_release)) ? 1 : 0;
     lp.merged_E = E;
     lp.fold_epilogue = E ? 1 : 0;
     lp.M = f.M; lp.N = f.N; lp.batches = f.batches;
@@ -2190,7 +2564,7 @@ int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st)
             int need = limbs_needed(h);
             if (need < la_used) la_used = need;
         }
-        if (getenv("ZKDS_TRACE"))
+        if (switches().trace)
             fprintf(stderr, "scores_fused batches=%lld M=%lld N=%lld K=%lld+%lld La=%d(%d) Lb=%d NT=%d stages=%d fits64=%d: %.3f ms\n",
                     (long long)f.batches, (long long)f.M, (long long)f.N, (long long)f.K1, (long long)f.K2,
                     la_used, La, Lb, NT, stages, lp.fits64, ms);
@@ -2200,7 +2574,8 @@ int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st)
             r.v[4] = la_used; r.v[5] = Lb; r.v[6] = ms; r.v[7] = 2.0;
         }
         g_tot_ms += ms;
-        g_tot_ops += 2.0 * (double)la_used * Lb * (double)f.batches * (double)f.M * (double)f.N * (double)(f.K1 + f.K2);
+        g_tot_ops += 2.0 * (double)la_used * Lb * (double)f.batches * (double)f.M * (double)f.N * (double)(f.K1 + f.K2) *
+                     issued_share(f.M, f.N, f.K1 + f.K2, NT, f.skip_tiles, 0, f.causal_H, f.causal_start);
         g_tot_launches += 1;
     }
     return rc;
