@@ -500,7 +500,8 @@ __device__ __forceinline__ void issue_extra_block(int La, int E, uint32_t acc_ex
 
 constexpr int kTileM = 128;
 constexpr int kBlockK = 128;   // bytes (= int8 elements) of K per pipeline stage
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;            // one-tile kernel: two warps per tensor-memory lane quarter, half the columns each
+constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr int kSplitTilesMax = 128;       // split-K: output tiles per launch (one arrival counter each)
 constexpr size_t kSplitHeader = 1024;     // bytes reserved for the counters in front of the partial sums
 
@@ -663,6 +664,7 @@ __device__ __forceinline__ bool gather64(int D, uint32_t taddr, int NT, int64_t 
 struct EpilogueCtx {
     uint32_t tq;
     int D, NT, group;
+    int nc_begin, nc_end;     // columns of the tile this warp handles (multiples of 8)
     int64_t m, n0, z;
     int64_t* crow;
     int64_t* rrow;
@@ -824,7 +826,7 @@ __device__ __forceinline__ void epilogue_tile(const LimbParams& p, const Epilogu
     const bool tail = p.addin || p.ep_div || p.causal_H;
     const int64_t* arow = p.addin ? p.addin + e.z * p.c_sz + e.m * p.c_sm : nullptr;
     const int64_t srow = p.causal_H ? seq_row(e.m, p.causal_H) : 0;
-    for (int nc = 0; nc < e.NT; nc += 8) {
+    for (int nc = e.nc_begin; nc < e.nc_end; nc += 8) {
         i128w sum[8];
         int64_t s64[8];
         gather_chunk<FITS64>(e, nc, p.addend, s64, sum);
@@ -883,15 +885,15 @@ __device__ __forceinline__ void epilogue_tile_pipelined(const LimbParams& p, con
     const int64_t* arow = p.addin ? p.addin + e.z * p.c_sz + e.m * p.c_sm : nullptr;
     const int64_t srow = p.causal_H ? seq_row(e.m, p.causal_H) : 0;
     int32_t a0[DD][CW], a1[DD][CW];
-    fetch_cols<DD, CW>(e, 0, a0);
-    for (int nc = 0; nc < e.NT; nc += 2 * CW) {
+    fetch_cols<DD, CW>(e, e.nc_begin, a0);
+    for (int nc = e.nc_begin; nc < e.nc_end; nc += 2 * CW) {
         tmem_ld_wait();
-        const bool more1 = nc + CW < e.NT;
+        const bool more1 = nc + CW < e.nc_end;
         if (more1) fetch_cols<DD, CW>(e, nc + CW, a1);
         finish_cols<DD, CW>(p, e, nc, a0, tail, arow, srow, tot);
         if (more1) {
             tmem_ld_wait();
-            if (nc + 2 * CW < e.NT) fetch_cols<DD, CW>(e, nc + 2 * CW, a0);
+            if (nc + 2 * CW < e.nc_end) fetch_cols<DD, CW>(e, nc + 2 * CW, a0);
             finish_cols<DD, CW>(p, e, nc + CW, a1, tail, arow, srow, tot);
         }
     }
@@ -902,9 +904,9 @@ __device__ __forceinline__ bool epilogue_tile_fast(const LimbParams& p, const Ep
 {
     if (!p.fits64) return false;
     switch (e.D) {
-    case 2: epilogue_tile_pipelined<2, 16>(p, e, tot); return true;
-    case 3: epilogue_tile_pipelined<3, 16>(p, e, tot); return true;
-    case 4: epilogue_tile_pipelined<4, 16>(p, e, tot); return true;
+    case 2: epilogue_tile_pipelined<2, 8>(p, e, tot); return true;
+    case 3: epilogue_tile_pipelined<3, 8>(p, e, tot); return true;
+    case 4: epilogue_tile_pipelined<4, 8>(p, e, tot); return true;
     case 5: epilogue_tile_pipelined<5, 8>(p, e, tot); return true;
     case 6: epilogue_tile_pipelined<6, 8>(p, e, tot); return true;
     default: return false;
@@ -919,7 +921,7 @@ constexpr int kSplitLowBits = 55;
 template <bool FITS64>
 __device__ __forceinline__ void add_partials_tile(const LimbParams& p, const EpilogueCtx& e, unsigned long long* tot)
 {
-    for (int nc = 0; nc < e.NT; nc += 8) {
+    for (int nc = e.nc_begin; nc < e.nc_end; nc += 8) {
         i128w sum[8];
         int64_t s64[8];
         gather_chunk<FITS64>(e, nc, 0, s64, sum);
@@ -1063,7 +1065,7 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
         }
-        mbar_init(bar_zeroed, 4);
+        mbar_init(bar_zeroed, kEpiWarps);
         mbar_init(bar_accum, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1131,10 +1133,12 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     } else {
         // ---- accumulator zeroing, then epilogue -------------------------------------------
         const int q = warp & 3;  // tensor-memory lane quarter this warp may touch
+        const int part = (warp - 2) >> 2;                 // which of the quarter's kEpiWarps / 4 warps
+        constexpr int kParts = kEpiWarps / 4;
         const uint32_t tq = tmem + ((uint32_t)(q * 32) << 16);
         // the first MMA (limb 0, first K step) overwrites its Lb * NT columns; only the columns the
         // later limbs extend into must start at zero
-        for (int c = p.Lb * p.NT; c < D * p.NT; c += 8) tmem_st8_zero(tq + (uint32_t)c);
+        for (int c = p.Lb * p.NT + 8 * part; c < D * p.NT; c += 8 * kParts) tmem_st8_zero(tq + (uint32_t)c);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
@@ -1145,29 +1149,6 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const bool ok = mbar_wait(bar_accum, 0, abort_flag);
         tc_fence_after();
         if (prof) ph1 = clock64();
-        if (p.wait_cycles != nullptr && warp == 2 && ok) {
-            // latency probes (diagnostic runs only): one 8-column load, four of them, one 16-column load,
-            // each followed by a wait
-            int32_t t8[8], u8[4][8], t16[16];
-            long long c0 = clock64();
-            tmem_ld8(tq, t8);
-            tmem_ld_wait();
-            long long c1 = clock64();
-#pragma unroll
-            for (int j = 0; j < 4; ++j) tmem_ld8(tq + (uint32_t)(8 * j), u8[j]);
-            tmem_ld_wait();
-            long long c2 = clock64();
-            tmem_ldn(tq, t16);
-            tmem_ld_wait();
-            long long c3 = clock64();
-            int keep = t8[0] ^ u8[3][7] ^ t16[15];
-            if (lane == 0) {
-                atomicMax(p.wait_cycles + 13, (unsigned long long)(c1 - c0));
-                atomicMax(p.wait_cycles + 14, (unsigned long long)(c2 - c1));
-                atomicMax(p.wait_cycles + 15, (unsigned long long)(c3 - c2) + (keep == 0x7fffffff ? 1ull : 0ull));
-            }
-            if (prof) ph1 = clock64();
-        }
         const int64_t m = m0 + q * 32 + lane;
         int64_t* crow = p.C + z * p.c_sz + m * p.c_sm;
         int64_t* rrow = p.R ? p.R + z * p.c_sz + m * p.c_sm : nullptr;
@@ -1176,6 +1157,11 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                             ((p.c_sz & 1) == 0);
         EpilogueCtx ec;
         ec.tq = tq; ec.D = D; ec.NT = p.NT; ec.m = m; ec.n0 = n0; ec.z = z; ec.group = group;
+        {   // the quarter's warps take consecutive column ranges (multiples of 8)
+            const int chunks = p.NT >> 3, per = (chunks + kParts - 1) / kParts;
+            ec.nc_begin = 8 * per * part < p.NT ? 8 * per * part : p.NT;
+            ec.nc_end = 8 * per * (part + 1) < p.NT ? 8 * per * (part + 1) : p.NT;
+        }
         ec.crow = crow; ec.rrow = rrow; ec.row_ok = row_ok; ec.vec_ok = vec_ok;
         bool finish = ok;
         if (p.ksplit > 1) {
@@ -1190,14 +1176,14 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
             if (prof) ph2 = clock64();
             __threadfence();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps) : "memory");
             if (warp == 2 && lane == 0) {
                 // a CTA that gave up a wait does not count: the tile then stays unfinished and the
                 // error word tells the host
                 s_last = 0;
                 if (ok) s_last = atomicAdd(p.tile_counter + tile_id, 1u) == (unsigned)(p.ksplit - 1) ? 1 : 0;
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps) : "memory");
             finish = false;
             if (prof) ph3 = clock64();
             if (s_last) {
@@ -1209,7 +1195,7 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (rows_here > kTileM) rows_here = kTileM;
                 const int chunks = p.NT >> 3;
                 const int units = (int)((rows_here + 31) >> 5) * chunks;
-                for (int u = q; u < units; u += 4) {
+                for (int u = warp - 2; u < units; u += kEpiWarps) {
                     const int rg = u / chunks, nc = (u - rg * chunks) << 3;
                     EpilogueCtx eu = ec;
                     eu.m = m0 + rg * 32 + lane;
@@ -2378,10 +2364,9 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
             ZKDS_CUDA(cudaStreamSynchronize(st));
             ZKDS_CUDA(cudaMemcpy(h, prof, sizeof(h), cudaMemcpyDeviceToHost));
             fprintf(stderr, "one-tile M=%lld N=%lld kblocks=%d NT=%d stages=%d ksplit=%d ctas=%u: longest phase in cycles: "
-                            "accumulate %llu, add partials %llu, fence+counter %llu, epilogue %llu, CTA lifetime %llu; "
-                            "tcgen05.ld + wait: x8 %llu, 4 x x8 %llu, x16 %llu\n",
+                            "accumulate %llu, add partials %llu, fence+counter %llu, epilogue %llu, CTA lifetime %llu\n",
                     (long long)lp.M, (long long)lp.N, lp.kblocks, lp.NT, lp.stages, lp.ksplit, grid.x * grid.z, h[8], h[9],
-                    h[10], h[11], h[12], h[13], h[14], h[15]);
+                    h[10], h[11], h[12]);
         }
     }
     if (ev) ZKDS_CUDA(cudaEventRecord(ev[1], st));
