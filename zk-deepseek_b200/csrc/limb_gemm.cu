@@ -674,6 +674,18 @@ struct EpilogueCtx {
 // floor(v * 94 / 695) for |v| < 2^42 (MLA's softmax scale, model.py:897): double estimate of the
 // quotient (the product is below 2^49, exact in a double; the estimate is within one of the floor),
 // exact remainder correction.  One straight-line path for every realistic score.
+// the tier for |v| >= 2^31 (out of line: the epilogues that inline the 32-bit tier sixteen times per thread
+// must stay small enough for the instruction cache)
+__device__ __noinline__ int64_t scale_94_695_wide(int64_t v)
+{
+    const int64_t t = v * 94;
+    int64_t q = __double2ll_rd((double)t * (1.0 / 695.0));
+    int64_t r = t - q * 695;
+    if (r < 0) { --q; r += 695; }
+    if (r >= 695) ++q;
+    return q;
+}
+
 __device__ __forceinline__ int64_t scale_94_695(int64_t v)
 {
     if (v == (int64_t)(int32_t)v) {
@@ -687,12 +699,7 @@ __device__ __forceinline__ int64_t scale_94_695(int64_t v)
         if (r >= 695) ++q;
         return (int64_t)q;
     }
-    const int64_t t = v * 94;
-    int64_t q = __double2ll_rd((double)t * (1.0 / 695.0));
-    int64_t r = t - q * 695;
-    if (r < 0) { --q; r += 695; }
-    if (r >= 695) ++q;
-    return q;
+    return scale_94_695_wide(v);
 }
 
 // sequence position of row m when rows are (s, h) pairs with H heads per position; row counts are below
@@ -704,6 +711,12 @@ __device__ __forceinline__ int64_t seq_row(int64_t m, int64_t H)
     return (int64_t)((uint32_t)m / (uint32_t)H);
 }
 
+// floor(v * mul / div) with a wrapping product, any operands (out of line: rare)
+__device__ __noinline__ int64_t scale_general(int64_t v, int64_t mul, int64_t div)
+{
+    return floor_div_i64((int64_t)((uint64_t)v * (uint64_t)mul), div);
+}
+
 // element-wise tail of the attention scores: v += *arow (the addin element, if any);
 // v = floor(v * mul / div); causal mask for column n of sequence row srow
 __device__ __forceinline__ int64_t score_tail(const LimbParams& p, int64_t v, const int64_t* arow,
@@ -711,15 +724,10 @@ __device__ __forceinline__ int64_t score_tail(const LimbParams& p, int64_t v, co
 {
     if (arow) v = (int64_t)((uint64_t)v + (uint64_t)*arow);
     if (p.ep_div) {
-        if (p.ep_mul == 94 && p.ep_div == 695) {
-            if ((uint64_t)(v + (1ll << 42)) < (uint64_t)(1ll << 43)) v = scale_94_695(v);
-            else {
-                const int64_t t = (int64_t)((uint64_t)v * 94ull);
-                const int64_t qd = t / 695;
-                v = (t - qd * 695 < 0) ? qd - 1 : qd;
-            }
-        } else
-            v = floor_div_i64((int64_t)((uint64_t)v * (uint64_t)p.ep_mul), p.ep_div);
+        if (p.ep_mul == 94 && p.ep_div == 695 && (uint64_t)(v + (1ll << 42)) < (uint64_t)(1ll << 43))
+            v = scale_94_695(v);
+        else
+            v = scale_general(v, p.ep_mul, p.ep_div);
     }
     if (p.causal_H && n > p.causal_start + srow) v = (int64_t)((uint64_t)v + (uint64_t)p.mask_value);
     return v;
