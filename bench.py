@@ -536,8 +536,10 @@ class MlaWorkload:
     norm weights near 2^16, every runtime shift 16 (the layer's fixed-point scale); the shifts the
     reference hard-codes stay (scores 23 / 21, RoPE 42, softmax Q19).  `scales="reference"` uses the
     reference's magnitudes instead (activations 2^21, weights 2^30/sqrt(fan_in), shifts 29-31).
-    With N GPUs the heads are split N ways (wq_b, wkv_b, attention per head local) and wo is
-    column-split after an all-gather: strong scaling of the same 4096 tokens."""
+    With N GPUs every rank holds 4096 / N consecutive tokens: the down projections, norms and wo run on the
+    local tokens, the attention core on all tokens for 128 / N heads, with one all-gather of the normed
+    latents and one all-to-all of the attention output between the two layouts (MLA.seq_parallel): strong
+    scaling of the same 4096 tokens, input and output distributed over the ranks."""
     name = "mla_layer_prefill_4096"
     metric = "int64_mla_layer_tokens_per_s"
     unit = "tokens/s"
@@ -570,7 +572,7 @@ class MlaWorkload:
             xs, wb, nb, shift, self.act_limbs, self.score_limbs = 21, 30, 19, 30, 4, (5, 5)
         self.shift = shift
         with torch.device(dev):
-            attn = M.MLA(0, a)
+            attn = M.MLA(0, a, seq_parallel=self.world > 1)
         g = torch.Generator(device=dev).manual_seed(5)          # same weights on every rank
         H, Hl = a.n_heads, a.n_heads // self.world
         r = M.rank
@@ -592,8 +594,7 @@ class MlaWorkload:
         attn.kv_norm.weight = norm_weight(a.kv_lora_rank)
         attn.wkv_b_1.weight = weight(H * a.qk_nope_head_dim, a.kv_lora_rank, heads(a.qk_nope_head_dim))
         attn.wkv_b_2.weight = weight(H * a.v_head_dim, a.kv_lora_rank, heads(a.v_head_dim))
-        wo_cols = a.dim // self.world
-        attn.wo.weight = weight(a.dim, H * a.v_head_dim, (r * wo_cols, (r + 1) * wo_cols))
+        attn.wo.weight = weight(a.dim, H * a.v_head_dim)        # whole on every rank: wo runs on the rank's tokens
         for lin in (attn.wq_a, attn.wq_b1, attn.wq_b2, attn.wkv_a1, attn.wkv_a2):
             lin.res_rescale = shift if scales == "baseline" else lin.res_rescale
         for lin in (attn.wkv_b_1, attn.wkv_b_2, attn.wo):
@@ -601,7 +602,11 @@ class MlaWorkload:
         attn.score_limbs = self.score_limbs
         self.attn = attn
         gx = torch.Generator(device=dev).manual_seed(55)
-        self.x = _normal_i(torch, gx, (1, self.T, a.dim), 2.0**xs, dev, torch.int64)
+        x_all = _normal_i(torch, gx, (1, self.T, a.dim), 2.0**xs, dev, torch.int64)
+        # N > 1: every rank holds T / N consecutive tokens (input and output), see MLA.seq_parallel
+        self.T_local = self.T // self.world
+        self.x = x_all[:, r * self.T_local:(r + 1) * self.T_local].contiguous() if self.world > 1 else x_all
+        del x_all
         self.freqs = M.precompute_freqs_cis(a).to(dev)
         self.mask = torch.full((self.T, self.T), -(64 << 36), dtype=torch.int64, device=dev).triu_(1)
         self.mask._zkds_causal = True
@@ -640,13 +645,13 @@ class MlaWorkload:
         if self.x_host is None:
             self.x_host = self.x.cpu().pin_memory()
             self.x_in = torch.empty_like(self.x)
-            self.out_host = torch.empty((1, self.T, self.args.dim), dtype=torch.int64).pin_memory()
+            self.out_host = torch.empty((1, self.T_local, self.args.dim), dtype=torch.int64).pin_memory()
         self.x_in.copy_(self.x_host, non_blocking=True)
         out = self.attn(self.x_in, 0, self.freqs, self.mask)
         self.out_host.copy_(out, non_blocking=True)
 
     def e2e_bytes(self):
-        n = 8 * self.T * self.args.dim
+        n = 8 * self.T * self.args.dim            # over all ranks: each copies its T / N tokens in and out
         return n, n
 
     def value(self, seconds_per_step, world):
@@ -680,12 +685,20 @@ class MlaWorkload:
         np, torch, a = self.np, self.torch, self.args
         at, T = self.attn, self.T
         got = self.step()                       # with N > 1 every rank joins the collectives here
+        x_all = self.x
+        if self.world > 1:                      # token blocks of the ranks -> the whole input and output
+            import torch.distributed as dist
+            full = torch.empty((T, a.dim), dtype=torch.int64, device=self.dev)
+            dist.all_gather_into_tensor(full, got[0].contiguous())
+            got = full[None]
+            x_all = torch.empty((1, T, a.dim), dtype=torch.int64, device=self.dev)
+            dist.all_gather_into_tensor(x_all[0], self.x[0].contiguous())
         kv_gpu = at.kv_cache[0, :T].cpu().numpy()
         pe_gpu = at.pe_cache[0, :T].cpu().numpy()
 
         def full(name):          # head / column slices of the ranks -> the whole weight
             w = getattr(at, name).weight
-            if self.world == 1 or name in ("wq_a", "wkv_a1", "wkv_a2", "q_norm", "kv_norm"):
+            if self.world == 1 or name in ("wq_a", "wkv_a1", "wkv_a2", "q_norm", "kv_norm", "wo"):
                 return w.cpu().numpy()
             import torch.distributed as dist
             parts = [torch.empty_like(w) for _ in range(self.world)]
@@ -708,13 +721,13 @@ class MlaWorkload:
             pe = np.zeros((1, end, a.qk_rope_head_dim), np.int64)
             kv[0, :st], pe[0, :st] = kv_gpu[:st], pe_gpu[:st]
             mask = np.where(np.arange(end)[None, :] > (st + np.arange(S))[:, None], mo.MASK_VALUE, 0).astype(np.int64)
-            x = self.x[:, st:end].cpu().numpy()
+            x = x_all[:, st:end].cpu().numpy()
             want = mo.mla_forward(p, x, st, freqs[st:end], mask, kv, pe, a.n_heads, s_q=sq, s_kv=skv)
             bad += int((got[:, st:end].cpu().numpy() != want).sum())
             bad += int((kv[0, st:end] != kv_gpu[st:end]).sum()) + int((pe[0, st:end] != pe_gpu[st:end]).sum())
         rows = np.random.default_rng(9).choice(T, 16, replace=False)
         for r in rows:
-            x = self.x[:, r:r + 1].cpu().numpy()
+            x = x_all[:, r:r + 1].cpu().numpy()
             kvr = mo.rms_norm(mo.linear(x, p["wkv_a1"], skv)[0], p["kv_norm"])[0]
             per = mo.rotary(mo.linear(x, p["wkv_a2"], skv)[0][:, :, None, :], freqs[r:r + 1])[:, :, 0]
             bad += int((kvr[0, 0] != kv_gpu[r]).sum()) + int((per[0, 0] != pe_gpu[r]).sum())
@@ -865,7 +878,14 @@ class MoeWorkload:
         self.torch.cuda.synchronize()
         recs = k.kernel_timing_records()
         k.kernel_timing(False)
-        pairs_local = self.T_local * 8 if self.world == 1 else None
+        pairs_local = self.T_local * 8
+        if self.world > 1:
+            # (token, expert) pairs whose expert this rank owns: counted over every rank's routing
+            import torch.distributed as dist
+            idx = self.moe.gate(0, self.x.view(-1, self.args.dim))[1]
+            owners = self.torch.bincount((idx // (self.E // self.world)).flatten(), minlength=self.world)
+            dist.all_reduce(owners)
+            pairs_local = int(owners[self.M.rank].item())
         ms = sum(r["ms"] for r in recs)
         ops = 0.0
         for r in recs:

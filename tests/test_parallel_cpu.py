@@ -13,15 +13,19 @@ from conftest import PKG, ROOT
 
 
 class FakeMoE:
-    """experts_forward stand-in: out = rows * (expert id + 1) * weight (int64, wrapping)"""
+    """experts_forward stand-in: out = rows * sum over the row's local experts of (expert id + 1) * weight
+    (int64, wrapping); a row arrives once per owner rank with the other ranks' experts set to -1"""
     n_routed_experts = 8
 
-    def experts_forward(self, start_pos, rows, weights, indices, base=None):
-        assert indices.shape == (rows.shape[0], 1) and weights.shape == indices.shape
+    def experts_forward(self, start_pos, rows, weights, indices, base=None, max_pairs=None):
+        assert max_pairs is not None and int(((indices >= 0)).sum()) == max_pairs
+        assert indices.shape == weights.shape and indices.shape[0] == rows.shape[0]
         lo = self.n_routed_experts // dist.get_world_size() * dist.get_rank()
         hi = lo + self.n_routed_experts // dist.get_world_size()
-        assert bool(((indices >= lo) & (indices < hi)).all()), "a row reached a rank that does not own its expert"
-        return rows * (indices + 1) * weights
+        local = (indices >= lo) & (indices < hi)
+        assert bool((local | (indices == -1)).all()), "an expert id of another rank was not masked"
+        assert bool(local.any(1).all()), "a row reached a rank that owns none of its experts"
+        return rows * ((indices + 1) * weights * local).sum(1, keepdim=True)
 
 
 def _worker(rank, world, port, T, out):
@@ -36,7 +40,8 @@ def _worker(rank, world, port, T, out):
         indices = torch.stack([torch.randperm(FakeMoE.n_routed_experts, generator=g)[:k] for _ in range(T[rank])]) \
             if T[rank] else torch.zeros((0, k), dtype=torch.int64)
         weights = torch.randint(1, 50, (T[rank], k), generator=g, dtype=torch.int64)
-        y = par.expert_parallel_forward(FakeMoE(), 0, x, weights, indices)
+        y, side = par.expert_parallel_forward(FakeMoE(), 0, x, weights, indices, before_sync=lambda: 7)
+        assert side == 7
         want = (x[:, None, :] * (indices + 1)[:, :, None] * weights[:, :, None]).sum(1)
         out[rank] = bool(torch.equal(y, want))
     finally:
@@ -55,8 +60,9 @@ def test_expert_parallel_dispatch_and_combine(T):
 def test_dispatch_plan_orders_rows_by_destination():
     sys.path.insert(0, ROOT)
     par = importlib.import_module(PKG + ".parallel")
-    idx = torch.tensor([[0, 5], [7, 2], [3, 4]])
-    order, counts = par.dispatch_plan(idx, 8, 2)
-    assert counts.tolist() == [3, 3]
-    dest = (idx.flatten() // 4)[order]
-    assert dest.tolist() == sorted(dest.tolist())
+    idx = torch.tensor([[0, 5], [7, 6], [3, 4], [1, 2]])          # tokens 1 and 3 keep both experts on one rank
+    order, counts, dest = par.dispatch_plan(idx, 8, 2)
+    assert counts.tolist() == [[3, 4], [3, 4]]                      # rows (one per token and owner rank), pairs
+    assert dest.tolist() == [[0, 1], [1, 1], [0, 1], [0, 0]]
+    pairs = order[:6].tolist()                                      # r * T + t, by rank then token
+    assert pairs == [0 * 4 + 0, 0 * 4 + 2, 0 * 4 + 3, 1 * 4 + 0, 1 * 4 + 1, 1 * 4 + 2]

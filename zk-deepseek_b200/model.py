@@ -314,9 +314,16 @@ def apply_rotary_emb(x: torch.Tensor, freqs_cis: torch.Tensor) -> torch.Tensor:
 class MLA(nn.Module):
     """Absorbed multi-head latent attention in int64 (model.py:652-957)."""
 
-    def __init__(self, layer_id, args: ModelArgs, cache_batch: int = 1):
+    def __init__(self, layer_id, args: ModelArgs, cache_batch: int = 1, seq_parallel: bool = False):
         super().__init__()
         self.layer_id = layer_id
+        # With world_size > 1: False keeps the reference's layout (every rank sees all tokens, heads and
+        # output columns are split, two all-gathers).  True is the prefill layout for one sequence: every
+        # rank holds S / world_size consecutive tokens, the down projections, their norms and wo run on the
+        # local tokens with whole weights, the attention core runs on all tokens for the local heads, and
+        # the two layouts are exchanged with one small all-gather (normed latents) and one all-to-all
+        # (attention output).  Exact either way: no sum is ever split.
+        self.seq_parallel = seq_parallel
         self.dim, self.n_heads = args.dim, args.n_heads
         self.n_local_heads = args.n_heads // world_size
         self.q_lora_rank, self.kv_lora_rank = args.q_lora_rank, args.kv_lora_rank
@@ -339,7 +346,8 @@ class MLA(nn.Module):
                                                         self.n_heads * self.qk_nope_head_dim, 1, 1, i32)
         self.wkv_b_2 = ColumnParallelLinear_rescale_int(layer_id, self.kv_lora_rank,
                                                         self.n_heads * self.v_head_dim, 1, 1, i32)
-        self.wo = RowParallelLinear_rescale_int(layer_id, self.n_heads * self.v_head_dim, self.dim, 1, 1, 1, i32)
+        self.wo = RowParallelLinear_rescale_int(layer_id, self.n_heads * self.v_head_dim, self.dim, 1, 1, 1, i32,
+                                                parallel=not seq_parallel)
         self.softmax_scale1, self.softmax_scale2 = 94, 695
         # the reference keeps one sequence (model.py:740-744); cache_batch > 1 serves batched decode
         self.register_buffer("kv_cache", torch.zeros(cache_batch, args.max_seq_len, self.kv_lora_rank,
@@ -365,9 +373,12 @@ class MLA(nn.Module):
         return ent[1]
 
     def forward(self, x, start_pos, freqs_cis, mask):
+        if self.seq_parallel and world_size > 1:
+            return self._forward_seq_parallel(x, start_pos, freqs_cis, mask)
         bsz, seqlen, _ = x.size()
         end_pos = start_pos + seqlen
         lim = ACT_LIMBS
+        d = None
         q_down, q_down_rem = self.wq_a(x)
         if snark:
             d = _dump_dir(start_pos, self.layer_id)
@@ -397,7 +408,44 @@ class MLA(nn.Module):
             saveTensor(f"{d}/wkv_a1_r.bin", kv_rem)
         k_pe, _ = self.wkv_a2(x)
         k_pe = apply_rotary_emb(k_pe.unsqueeze(2), freqs_cis)
+        kv_normed, rms = self.kv_norm(kv)
+        ctx = self._core(q_nope, q_pe, kv_normed, k_pe.squeeze(2), bsz, seqlen, start_pos, mask, d)
+        return self._finish(ctx, lim)
 
+    def _forward_seq_parallel(self, x, start_pos, freqs_cis, mask):
+        """x [1, S / world_size, dim]: this rank's consecutive tokens of one sequence; freqs_cis and mask
+        cover all S tokens.  Returns the layer output for the same local tokens."""
+        if snark:
+            raise NotImplementedError("the zkdata dumps are written from the one-GPU layout")
+        bsz, s_loc, _ = x.size()
+        assert bsz == 1
+        S = s_loc * world_size
+        fr_loc = freqs_cis[rank * s_loc:(rank + 1) * s_loc]
+        q_normed, _ = self.q_norm(self.wq_a(x)[0])
+        kv_normed, _ = self.kv_norm(self.wkv_a1(x)[0])
+        k_pe = apply_rotary_emb(self.wkv_a2(x)[0].unsqueeze(2), fr_loc).squeeze(2)
+        qr, C = self.q_lora_rank, self.kv_lora_rank
+        local = torch.cat([q_normed, kv_normed, k_pe], dim=-1)[0].contiguous()         # [s_loc, q + C + rope]
+        full = torch.empty((S, local.shape[1]), dtype=torch.int64, device=x.device)
+        dist.all_gather_into_tensor(full, local)         # token blocks in rank order: the whole [S, .] matrix
+        q_all = full[:, :qr].contiguous()[None]
+        q_nope = self.wq_b1(q_all).view(1, S, self.n_local_heads, self.qk_nope_head_dim)
+        q_pe = self.wq_b2(q_all).view(1, S, self.n_local_heads, self.qk_rope_head_dim)
+        q_pe = apply_rotary_emb(q_pe, freqs_cis)
+        ctx = self._core(q_nope, q_pe, full[:, qr:qr + C][None], full[:, qr + C:][None], 1, S, start_pos, mask, None)
+        out = self._project_heads(ctx, ACT_LIMBS)                                       # [1, S, local heads * v]
+        # head-split -> token-split: rank j receives its token block from every rank's heads
+        cols = out.shape[-1]
+        recv = torch.empty((world_size, s_loc, cols), dtype=torch.int64, device=x.device)
+        dist.all_to_all_single(recv, out.view(world_size, s_loc, cols))
+        del out
+        rows = recv.permute(1, 0, 2).reshape(1, s_loc, world_size * cols)               # heads in rank order
+        return self.wo(rows)
+
+    def _core(self, q_nope, q_pe, kv_normed, k_pe, bsz, seqlen, start_pos, mask, d):
+        """caches, scores, softmax, P . KV for the local heads: returns ctx [b, s, h, c]"""
+        end_pos = start_pos + seqlen
+        lim = ACT_LIMBS
         # q_nope . W_uk per head  (einsum_bshd_hdc_bshc, weight [H, D, C]: K is the middle axis)
         shift1 = self.wkv_b_1.shift()
         if lim > 0 and K.limb_kernel_takes(self.qk_nope_head_dim, lim, 5):
@@ -406,9 +454,8 @@ class MLA(nn.Module):
         else:
             w1 = self.wkv_b_1.weight.view(self.n_local_heads, -1, self.kv_lora_rank)
             q_abs = K.einsum_bshd_hdc_bshc(q_nope.contiguous(), w1.contiguous(), shift1)
-        kv_normed, rms = self.kv_norm(kv)
         self.kv_cache[:bsz, start_pos:end_pos] = kv_normed
-        self.pe_cache[:bsz, start_pos:end_pos] = k_pe.squeeze(2)
+        self.pe_cache[:bsz, start_pos:end_pos] = k_pe
         kv_all = self.kv_cache[:bsz, :end_pos].contiguous()
         pe_all = self.pe_cache[:bsz, :end_pos].contiguous()
 
@@ -426,13 +473,13 @@ class MLA(nn.Module):
                 ctx = K.softmax_pv_fused(scores, kv_all, 23, causal_skip=True, start_pos=0, a_limbs=3, b_limbs=bl)
                 if ctx is not None:
                     del scores
-                    return self._finish(ctx, lim)
+                    return ctx
                 probs = torch.empty_like(scores)
                 if K.softmax_q19_causal(scores, probs, 0):
                     del scores
                     ctx = K.einsum_bsht_btc_bshc_causal(probs, kv_all, 23, 0, a_limbs=3, b_limbs=bl)
                     del probs
-                    return self._finish(ctx, lim)
+                    return ctx
                 # softmax shape not taken by the causal kernel: recompute the scores in full
                 scores = K.mla_scores_fused(q_abs, kv_all, q_pe.contiguous(), pe_all, 23, 21, self.softmax_scale1,
                                             self.softmax_scale2, causal=causal, a_limbs=al, b_limbs=bl,
@@ -452,7 +499,7 @@ class MLA(nn.Module):
             ctx = K.softmax_pv_fused(scores, kv_all, 23, a_limbs=3, b_limbs=bl)
             if ctx is not None:
                 del scores
-                return self._finish(ctx, lim)
+                return ctx
         probs = torch.empty_like(scores)
         K.softmax_q19(scores, probs)
         del scores
@@ -461,10 +508,17 @@ class MLA(nn.Module):
         # probabilities are in [0, 2^19]: three limbs
         ctx = K.einsum_bsht_btc_bshc(probs, kv_all, 23, a_limbs=3 if dyn else 0, b_limbs=bl)
         del probs
-        return self._finish(ctx, lim)
+        return ctx
 
     def _finish(self, ctx, lim):
         """ctx [b, s, h, c] -> per-head W_uv, concatenate heads, output projection"""
+        out = self._project_heads(ctx, lim)
+        if world_size > 1:
+            out = _all_gather_last(out)      # heads of every rank, then a column-split wo
+        return self.wo(out)
+
+    def _project_heads(self, ctx, lim):
+        """ctx [b, s, h, c] -> per-head W_uv -> [b, s, h * v]"""
         shift2 = self.wkv_b_2.shift()
         if lim > 0 and K.limb_kernel_takes(self.kv_lora_rank, lim, 5):
             out = K.einsum_heads_prepared(ctx, self._per_head_planes(self.wkv_b_2, True), shift2, False,
@@ -472,10 +526,7 @@ class MLA(nn.Module):
         else:
             w2 = self.wkv_b_2.weight.view(self.n_local_heads, -1, self.kv_lora_rank)
             out = K.einsum_bshc_hdc_bshd(ctx, w2.contiguous(), shift2)
-        out = out.flatten(2)
-        if world_size > 1:
-            out = _all_gather_last(out)      # heads of every rank, then a column-split wo
-        return self.wo(out)
+        return out.flatten(2)
 
 
 def _is_causal_mask(mask, seqlen):
@@ -701,10 +752,12 @@ class MoE(nn.Module):
             self._planes = (key, K.WeightPlanes(self.experts_w13), K.WeightPlanes(self.experts_w2), s13, s2)
         return self._planes[1:]
 
-    def route(self, indices):
+    def route(self, indices, max_pairs=None):
         """rows sorted by local expert and padded to 128 per expert.  Returns
         row_src int32 [R] (token of each row, -1 = padding), pos int32 [T, k] (row of each
-        (token, slot), -1 = not a local expert), tile_group int32 [R / 128]."""
+        (token, slot), -1 = not a local expert), tile_group int32 [R / 128].
+        max_pairs: a bound on the (token, slot) pairs that name a local expert when the caller knows one
+        smaller than T * k (expert parallelism: most slots of a received row belong to other ranks)."""
         T, k = indices.shape
         E = self.n_local_experts
         dev = indices.device
@@ -719,7 +772,7 @@ class MoE(nn.Module):
         pad_end = torch.cumsum(padded, 0)
         pad_start = pad_end - padded
         start = torch.cumsum(counts, 0) - counts
-        n_tiles = (T * k + E * 127) // 128
+        n_tiles = ((T * k if max_pairs is None else min(T * k, max_pairs)) + E * 127) // 128
         R = n_tiles * 128
         ar = torch.arange(T * k, device=dev)
         valid = skey < E
@@ -735,11 +788,11 @@ class MoE(nn.Module):
         tile_group = torch.where(tile_start < pad_end[-1], g, torch.full_like(g, -1)).to(torch.int32)
         return row_src, pos.view(T, k), tile_group, counts
 
-    def experts_forward(self, start_pos, x, weights, indices, base=None):
+    def experts_forward(self, start_pos, x, weights, indices, base=None, max_pairs=None):
         """sum over the local experts of expert(x) * w // 2^23, added to `base`"""
         w13, w2, s13, s2 = self._prepared()
         lim = ACT_LIMBS if ACT_LIMBS > 0 else 5
-        row_src, pos, tile_group, counts = self.route(indices)
+        row_src, pos, tile_group, counts = self.route(indices, max_pairs)
         I = self.moe_inter_dim
         # the dispatch gather (model.py:1372-1378) runs inside the limb split of the first GEMM
         r13 = K.grouped_prepared(x.contiguous(), w13, tile_group, 0, a_limbs=lim, dynamic=True, group_shift=s13,
@@ -768,14 +821,18 @@ class MoE(nn.Module):
             row += (c + 127) // 128 * 128
 
     def forward(self, start_pos: int, x: torch.Tensor) -> torch.Tensor:
-        z = self.shared_experts(start_pos, x)
         shape = x.size()
-        x = x.view(-1, self.dim)
-        weights, indices = self.gate(start_pos, x)
         if world_size > 1 and self.token_parallel:
             from . import parallel
-            y = parallel.expert_parallel_forward(self, start_pos, x, weights, indices)
+            x2 = x.view(-1, self.dim)
+            weights, indices = self.gate(start_pos, x2)
+            # the shared expert runs while the dispatch counts travel to the host
+            y, z = parallel.expert_parallel_forward(self, start_pos, x2, weights, indices,
+                                                    before_sync=lambda: self.shared_experts(start_pos, x))
             return (y + z.view(-1, self.dim)).view(shape)
+        z = self.shared_experts(start_pos, x)
+        x = x.view(-1, self.dim)
+        weights, indices = self.gate(start_pos, x)
         if world_size > 1:
             y = self.experts_forward(start_pos, x, weights, indices)
             dist.all_reduce(y)                        # model.py:1381-1382
