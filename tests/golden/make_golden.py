@@ -44,7 +44,9 @@ def ref_luts():
 
 
 if __name__ == "__main__":
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("ZKDS_REFERENCE", "")
+    if not os.path.isdir(ref_root):
+        sys.exit("usage: make_golden.py <reference checkout>   (or set ZKDS_REFERENCE)")
     json.dump(ts_tables(ref_root), open(os.path.join(HERE, "ts_tables.json"), "w"))
     json.dump(ref_luts(), open(os.path.join(HERE, "ref_luts.json"), "w"))
     print("wrote ts_tables.json, ref_luts.json")

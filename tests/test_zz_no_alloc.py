@@ -7,7 +7,7 @@ its limb planes and status words in a fixed 64 MiB device array inside the libra
 
 This file is collected last on purpose: if it fails, every other test has already run.
 Checked here, through the C ABI: two calls in a row give word-for-word the output of the
-allocating entry point zkds_gemm (the second call is smaller, so stale bytes of the first would
+allocating entry point zkds_gemm and of the CPU oracle (the second call is smaller, so stale bytes of the first would
 show), a shape beyond the fixed capacity is refused, and the second call changes the amount of
 free device memory by nothing.
 """
@@ -52,7 +52,7 @@ def _run(fn, A, B, s, a_limbs, b_limbs, flags):
     return rc, C.cpu().numpy(), R.cpu().numpy()
 
 
-def test_noalloc_gemm_matches_the_allocating_entry_point_twice_in_a_row(libpath, dev):
+def test_noalloc_gemm_matches_the_allocating_entry_point_twice_in_a_row(libpath, dev, orc):
     lib = _bind(libpath)
     rng = np.random.default_rng(2025)
     LIMB = 2           # ZKDS_ALGO_LIMB: both entry points on the tensor-core kernel
@@ -74,6 +74,10 @@ def test_noalloc_gemm_matches_the_allocating_entry_point_twice_in_a_row(libpath,
         assert rc1 == 0
         assert np.array_equal(C1, C0), "call %d: quotient differs" % n
         assert np.array_equal(R1, R0), "call %d: remainder differs" % n
+        # and both are what the CPU oracle computes (flags = 2: remainder sum mod 2^s)
+        Co, Ro = orc.gemm(A.cpu().numpy(), B.cpu().numpy(), 1, 1, s, orc.R_MATH)
+        assert np.array_equal(C1, Co), "call %d: quotient differs from the oracle" % n
+        assert np.array_equal(R1, Ro), "call %d: remainder differs from the oracle" % n
 
 
 def test_noalloc_gemm_rejects_what_does_not_fit(libpath, dev):
