@@ -317,7 +317,9 @@ class GemmSmallMWorkload:
         gbs = alg / pp["us"] / 1e3
         return {"bound": "hbm", "kernel": "split_rows_kernel + limb_gemm_kernel (split over K)",
                 "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": round(gbs / peaks["hbm_gbs"], 4), "traffic": None, "kernel_us": pp["us"],
+                "frac": round(gbs / peaks["hbm_gbs"], 4), "traffic": 15200000, "kernel_us": pp["us"],
+                "traffic_note": "ncu dram__bytes_read + dram__bytes_write of one call: 13.3 MB tensor-core kernel "
+                                "(weight and activation planes) + 1.9 MB activation split; the outputs stay in L2",
                 "algorithmic_bytes": alg, "paths": paths,
                 "note": "algorithmic bytes = 8MK + 4NK + 16MN (int32 W) / GPU time of one call replayed from a CUDA "
                         "graph (activation split + tensor-core kernel); the kernels read %d-limb planes of W, "
@@ -569,7 +571,9 @@ class MlaWorkload:
         if scales == "baseline":
             xs, wb, nb, shift, self.act_limbs, self.score_limbs = 16, 16, 16, 16, 3, (3, 3)
         else:
-            xs, wb, nb, shift, self.act_limbs, self.score_limbs = 21, 30, 19, 30, 4, (5, 5)
+            # |q| and |kv| stay below 2^31 at these magnitudes (2^19 and 2^23 fixed-point scales): four limbs each,
+            # promised; the split passes verify it on the device and k.device_status() would report a miss
+            xs, wb, nb, shift, self.act_limbs, self.score_limbs = 21, 30, 19, 30, 4, (4, 4)
         self.shift = shift
         with torch.device(dev):
             attn = M.MLA(0, a, seq_parallel=self.world > 1)
@@ -631,7 +635,7 @@ class MlaWorkload:
         base = scales == "baseline"
         return {"workload": cls.name, "tokens": T, "dim": D, "heads": H, "q_lora": q, "kv_lora": C, "scales": scales,
                 "shift": 16 if base else 30, "act_limbs_bound": 3 if base else 4,
-                "score_limbs_bound": [3, 3] if base else [5, 5], "heads_per_gpu": H // world,
+                "score_limbs_bound": [3, 3] if base else [4, 4], "heads_per_gpu": H // world,
                 "useful_ops_per_step": ops, "l2": "activations and score tensors (up to 17 GB) far exceed L2"}
 
     def config(self):
@@ -669,9 +673,16 @@ class MlaWorkload:
         self.launches_per_step = 2 * n + 3 + 5
         int8_peak = 2.0 * peaks["bf16_tflops_sustained"]
         achieved = ops / (ms * 1e-3) / 1e12
+        # DRAM bytes of the step's largest launch, the fused score kernel: dram__bytes_read + dram__bytes_write of
+        # one ncu capture of the 1024-token case (1.413 GB per launch), scaled by (T / 1024)^2 like its output
+        H = self.args.n_heads // self.world
+        traffic = 1.4128e9 * (self.T / 1024.0) ** 2 * (H / 128.0)
+        alg = 8.0 * self.T * H * self.T + 3.0 * 576 * (self.T * H + self.T)
         return {"bound": "tensor", "kernel": "limb_gemm_kernel (%d launches per step)" % n,
                 "achieved": round(achieved, 1), "peak": round(int8_peak, 1), "unit": "TFLOP/s",
-                "frac": round(achieved / int8_peak, 4), "traffic": None, "kernel_ms": round(ms, 3),
+                "frac": round(achieved / int8_peak, 4), "traffic": round(traffic), "kernel_ms": round(ms, 3),
+                "traffic_note": "fused score launch, DRAM read + write scaled from an ncu capture at 1024 tokens; its "
+                                "algorithmic bytes (scores written once, limb planes read once) are %d" % round(alg),
                 "int8_ops_per_step": ops,
                 "note": "sum over the step's tensor-core launches of limb pairs x 2MNK / sum of their CUDA-event "
                         "durations; peak = 2 x sustained cuBLAS bf16 (%s)" % peaks["source"]}
@@ -978,13 +989,23 @@ class DecodeWorkload:
     unit = "tokens/s"
     scaling = "weak"
     BATCH, CACHE, LAYERS, DENSE = 64, 2048, 4, 3
+    SHARDED = False      # True: the N GPUs share ONE model and ONE batch (see DecodeShardedWorkload)
 
     def __init__(self, torch, k, dev, rank, experts=256, vocab=129280, inter=18432):
         import numpy as np
+        import torch.distributed as dist
         self.torch, self.k, self.dev, self.np, self.rank = torch, k, dev, np, rank
         M = importlib.import_module(PKG + ".model")
         self.M = M
-        M.world_size, M.rank = 1, 0               # every GPU decodes its own 64 sequences
+        if self.SHARDED and dist.is_initialized():
+            M.world_size, M.rank = dist.get_world_size(), dist.get_rank()
+        else:
+            M.world_size, M.rank = 1, 0           # every GPU decodes its own 64 sequences
+        W, R = M.world_size, M.rank
+        self.world = W
+
+        def part(n):                               # this rank's slice of n rows
+            return (R * (n // W), (R + 1) * (n // W))
         a = M.ModelArgs(max_seq_len=self.CACHE + 512, vocab_size=vocab, dim=7168, inter_dim=inter,
                         moe_inter_dim=2048, n_layers=self.LAYERS, n_dense_layers=self.DENSE, n_heads=128,
                         n_routed_experts=experts, n_shared_experts=1, n_activated_experts=8, n_expert_groups=8,
@@ -994,8 +1015,10 @@ class DecodeWorkload:
         sh = 16
         g = torch.Generator(device=dev).manual_seed(7)
 
-        def weight(out_f, in_f, gen=g):
-            return _normal_i(torch, gen, (out_f, in_f), 2.0**16 / math.sqrt(in_f), dev, torch.int32)
+        def weight(out_f, in_f, gen=g, rows=None):
+            # every rank draws the whole tensor from the same generator state and keeps its rows
+            w = _normal_i(torch, gen, (out_f, in_f), 2.0**16 / math.sqrt(in_f), dev, torch.int32)
+            return w if rows is None or W == 1 else w[rows[0]:rows[1]].contiguous()
 
         def norm_weight(n, dtype=torch.int32):
             return (2**16 + _normal_i(torch, g, (n,), 2.0**8, dev, torch.int64)).to(dtype)
@@ -1005,9 +1028,12 @@ class DecodeWorkload:
 
         with torch.device(dev):
             model = M.Transformer(a)
-        model.embed.weight = _normal_i(torch, g, (vocab, a.dim), 2.0**16, dev, torch.int64)
+        M.world_size, M.rank = W, R               # Transformer() reads them from torch.distributed
+        vlo, vhi = part(vocab)
+        model.embed.weight = _normal_i(torch, g, (vocab, a.dim), 2.0**16, dev, torch.int64)[vlo:vhi].contiguous()
         model.norm.weight = norm_weight(a.dim, torch.int64)
-        model.head.weight = _normal_i(torch, g, (vocab, a.dim), 2.0**16 / math.sqrt(a.dim), dev, torch.int64)
+        model.head.weight = _normal_i(torch, g, (vocab, a.dim), 2.0**16 / math.sqrt(a.dim), dev,
+                                      torch.int64)[vlo:vhi].contiguous()
         model.head.weight_rescale = 1
         model.head.res_rescale = sh
         D, I = a.dim, a.moe_inter_dim
@@ -1018,14 +1044,14 @@ class DecodeWorkload:
             H = a.n_heads
             at.wq_a.weight = weight(a.q_lora_rank, D)
             at.q_norm.weight = norm_weight(a.q_lora_rank)
-            at.wq_b1.weight = weight(H * a.qk_nope_head_dim, a.q_lora_rank)
-            at.wq_b2.weight = weight(H * a.qk_rope_head_dim, a.q_lora_rank)
+            at.wq_b1.weight = weight(H * a.qk_nope_head_dim, a.q_lora_rank, rows=part(H * a.qk_nope_head_dim))
+            at.wq_b2.weight = weight(H * a.qk_rope_head_dim, a.q_lora_rank, rows=part(H * a.qk_rope_head_dim))
             at.wkv_a1.weight = weight(a.kv_lora_rank, D)
             at.wkv_a2.weight = weight(a.qk_rope_head_dim, D)
             at.kv_norm.weight = norm_weight(a.kv_lora_rank)
-            at.wkv_b_1.weight = weight(H * a.qk_nope_head_dim, a.kv_lora_rank)
-            at.wkv_b_2.weight = weight(H * a.v_head_dim, a.kv_lora_rank)
-            at.wo.weight = weight(D, H * a.v_head_dim)
+            at.wkv_b_1.weight = weight(H * a.qk_nope_head_dim, a.kv_lora_rank, rows=part(H * a.qk_nope_head_dim))
+            at.wkv_b_2.weight = weight(H * a.v_head_dim, a.kv_lora_rank, rows=part(H * a.v_head_dim))
+            at.wo.weight = weight(D, H * a.v_head_dim, rows=part(D))       # output columns split, full K
             for lin in (at.wq_a, at.wq_b1, at.wq_b2, at.wkv_a1, at.wkv_a2):
                 lin.res_rescale = sh
             for lin in (at.wkv_b_1, at.wkv_b_2, at.wo):
@@ -1040,7 +1066,7 @@ class DecodeWorkload:
             if i < a.n_dense_layers:
                 for name, (o, n_in) in (("w1", (inter, D)), ("w3", (inter, D)), ("w2", (D, inter))):
                     lin = getattr(blk.ffn, name)
-                    lin.weight = weight(o, n_in)
+                    lin.weight = weight(o, n_in, rows=part(o))
                     lin.scale = scale()
             else:
                 moe = blk.ffn
@@ -1049,16 +1075,17 @@ class DecodeWorkload:
                 moe.gate.bias = torch.abs(_normal_i(torch, g, (experts,), 2.0**18, dev, torch.int64)).to(torch.int32)
                 for name, (o, n_in) in (("w1", (I, D)), ("w3", (I, D)), ("w2", (D, I))):
                     lin = getattr(moe.shared_experts, name)
-                    lin.weight = weight(o, n_in)
+                    lin.weight = weight(o, n_in, rows=part(o))
                     lin.scale = scale()
-                for j in range(experts):
-                    moe.experts_w13[j, :I] = weight(I, D)
-                    moe.experts_w13[j, I:] = weight(I, D)
-                    moe.experts_w2[j] = weight(D, I)
+                for j in range(moe.n_local_experts):          # each expert from its own seed: any rank can make it
+                    ge = torch.Generator(device=dev).manual_seed(7000 + moe.experts_start_idx + j)
+                    moe.experts_w13[j, :I] = weight(I, D, gen=ge)
+                    moe.experts_w13[j, I:] = weight(I, D, gen=ge)
+                    moe.experts_w2[j] = weight(D, I, gen=ge)
                 moe.experts_shift.fill_(sh)
             model.layers[i] = blk
         self.model = model
-        gt = torch.Generator(device=dev).manual_seed(70 + rank)
+        gt = torch.Generator(device=dev).manual_seed(70 + (0 if self.SHARDED else rank))
         self.tokens = torch.randint(0, vocab, (self.BATCH, 1), generator=gt, device=dev)
         self.pos = self.CACHE
         M.ACT_LIMBS = 3
@@ -1103,7 +1130,7 @@ class DecodeWorkload:
         return self.BATCH * 8, self.BATCH * 8
 
     def value(self, seconds_per_step, world):
-        return self.BATCH * world / seconds_per_step
+        return self.BATCH * (1 if self.SHARDED else world) / seconds_per_step
 
     def roofline(self, peaks):
         k = self.k
@@ -1116,7 +1143,7 @@ class DecodeWorkload:
         # weight bytes each tensor-core launch streams: its B limb planes (N x K x limbs)
         wbytes = 0.0
         for r in recs:
-            nb = self.args.n_routed_experts if r["grouped"] else (r["batches"] if r["b_batched"] else 1)
+            nb = (self.args.n_routed_experts // self.world) if r["grouped"] else (r["batches"] if r["b_batched"] else 1)
             wbytes += float(nb) * r["N"] * r["K"] * r["lb"]
         self.launches_per_step = 2 * len(recs) + 40
         gbs = wbytes / (ms * 1e-3) / 1e9
@@ -1180,6 +1207,46 @@ class DecodeWorkload:
         dt = time.time() - t0
         # one dense layer per token; the 4-layer model + head costs about 5.3x that
         return 1.0 / (dt * 5.3), "GEMVs of one dense layer for one token, scaled to 4 layers + head", dt
+
+
+class DecodeShardedWorkload(DecodeWorkload):
+    """The same decode with ONE model and ONE batch of 64 sequences spread over the N GPUs (strong scaling):
+    attention heads, the dense MLPs' and the shared expert's hidden and output columns, the routed experts
+    (256 / N per GPU, integer all-reduce of their weighted sums as in model.py:1381-1382) and the vocabulary
+    rows of embedding and head are split; every output column keeps its full K, so the tokens are those of one
+    GPU.  Collectives per step: all-reduce of the embedding, all-gathers of attention output / MLP hidden /
+    projection outputs, all-reduce of the routed sums, all-gather of the logits."""
+    name = "decode_sharded_4_layers_batch64_cache2048"
+    scaling = "strong"
+    SHARDED = True
+    collective_check = True
+
+    def check(self, orc):
+        """the logits of this rank's vocabulary slice against the oracle's head GEMM on the step's final hidden
+        state, and every rank's next tokens identical (they all hold the gathered logits)"""
+        import torch.distributed as dist
+        torch, m = self.torch, self.model
+        pos = self.pos if self.pos < self.args.max_seq_len else self.CACHE
+        h, p, S = m.prep_inference(self.tokens, pos)
+        for i in range(self.args.n_layers):
+            h = m.layer_inference(i, h, p, S)
+        logits = m.finish_inference(h)                       # gathered over the ranks
+        self.pos += 1
+        tok = logits[0].argmax(-1)
+        if self.world > 1:
+            both = [torch.empty_like(tok) for _ in range(self.world)]
+            dist.all_gather(both, tok)
+            same = all(bool(torch.equal(both[0], t)) for t in both)
+        else:
+            same = True
+        if orc is None:
+            return None
+        hn = m.norm(h)[0][:, -1].contiguous()
+        n = m.head.weight.shape[0]
+        want, _ = orc.gemm(hn[None].cpu().numpy(), m.head.weight[:2048].cpu().numpy(), 1, 1, 16)
+        lo = self.M.rank * n
+        bad = int((logits[:, :, lo:lo + 2048].cpu().numpy() != want).sum())
+        return bad + (0 if same else 1)
 
 
 class GemmWideRangeWorkload(GemmWorkload):
@@ -1256,7 +1323,7 @@ WORKLOADS = {"gemm": GemmWorkload, "gemm_prof": GemmProfWorkload, "gemm_cfg1": G
              "gemm_wide": GemmWideRangeWorkload, "chain": ChainWorkload,
              "chain_prof": ChainProfWorkload, "mla": MlaWorkload, "mla_ref": MlaRefScaleWorkload,
              "mla_small": MlaSmallWorkload, "mla_causal": MlaCausalSkipWorkload, "moe": MoeWorkload,
-             "moe_small": MoeSmallWorkload, "decode": DecodeWorkload}
+             "moe_small": MoeSmallWorkload, "decode": DecodeWorkload, "decode_sharded": DecodeShardedWorkload}
 DEFAULT_WORKLOAD = "mla"
 
 

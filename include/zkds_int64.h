@@ -19,6 +19,15 @@
  * All pointers are device pointers unless a comment says HOST.  Tensors are
  * dense and row-major in the shapes given.  No entry point synchronises the
  * device except where a comment says so.
+ *
+ * Concurrency.  The contraction entry points keep their scratch (limb planes of the
+ * operands they split, range words, split-K partial sums) in ONE arena per device,
+ * owned by the library and reused by the next call.  Calls on one device must
+ * therefore be issued from one host thread at a time and on one stream (or on
+ * streams the caller orders with events so that two calls never overlap on the
+ * GPU): two calls in flight at once would overwrite each other's planes.  Calls on
+ * different devices are independent.  Prepared weight planes (zkds_planes_create)
+ * are read-only afterwards and may be shared freely.
  */
 #ifndef ZKDS_INT64_H
 #define ZKDS_INT64_H

@@ -66,3 +66,40 @@ def test_dispatch_plan_orders_rows_by_destination():
     assert dest.tolist() == [[0, 1], [1, 1], [0, 1], [0, 0]]
     pairs = order[:6].tolist()                                      # r * T + t, by rank then token
     assert pairs == [0 * 4 + 0, 0 * 4 + 2, 0 * 4 + 3, 1 * 4 + 0, 1 * 4 + 1, 1 * 4 + 2]
+
+
+def _vocab_worker(rank, world, port, out):
+    """vocabulary-parallel embedding (masked lookup + all_reduce, model.py:104-150) and the gather of the
+    logits' vocabulary slices (model.py:1577-1580) on CPU ranks"""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    sys.path.insert(0, ROOT)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        M = importlib.import_module(PKG + ".model")
+        M.world_size, M.rank = world, rank
+        vocab, dim, B = 64, 12, 5
+        g = torch.Generator().manual_seed(7)                      # the same table and tokens on every rank
+        table = torch.randint(-2**40, 2**40, (vocab, dim), generator=g, dtype=torch.int64)
+        tokens = torch.randint(0, vocab, (B, 9), generator=g)
+        emb = M.ParallelEmbedding(vocab, dim)
+        assert emb.weight.shape == (vocab // world, dim)
+        emb.weight = table[rank * (vocab // world):(rank + 1) * (vocab // world)].clone()
+        got = emb(tokens.clone())
+        ok = bool(torch.equal(got, torch.nn.functional.embedding(tokens, table)))
+        # logits: every rank holds the columns of its vocabulary slice; gathered in rank order
+        logits_full = torch.randint(-2**30, 2**30, (1, B, vocab), generator=g, dtype=torch.int64)
+        part = logits_full[..., rank * (vocab // world):(rank + 1) * (vocab // world)].contiguous()
+        gathered = M._all_gather_last(part)
+        ok = ok and bool(torch.equal(gathered, logits_full))
+        ok = ok and bool(torch.equal(gathered.argmax(-1), logits_full.argmax(-1)))
+        out[rank] = ok
+    finally:
+        dist.destroy_process_group()
+
+
+def test_vocab_parallel_embedding_and_logits_gather():
+    mgr = mp.Manager()
+    out = mgr.dict()
+    port = 29900 + os.getpid() % 90
+    mp.spawn(_vocab_worker, args=(2, port, out), nprocs=2, join=True)
+    assert dict(out) == {0: True, 1: True}

@@ -119,6 +119,7 @@ int launch_contraction_exact(const Contraction& p, cudaStream_t st)
             q.B = (const char*)p.B + z0 * p.b_sz * (p.b_bits / 8);
             q.C = p.C + z0 * p.c_sz;
             q.R = p.R ? p.R + z0 * p.c_sz : nullptr;
+            q.addin = p.addin ? p.addin + z0 * p.c_sz : nullptr;     // same layout as C
             int rc = launch_contraction_exact(q, st);
             if (rc != ZKDS_OK) return rc;
         }
