@@ -341,6 +341,17 @@ int zkds_gather_rows(const int64_t* src, const int* index, int64_t* dst, int64_t
 int zkds_moe_combine(const int64_t* out, const int* pos, const int64_t* w, const int64_t* base,
                      int64_t* y, int64_t tokens, int slots, int64_t cols, void* stream);
 
+/* Gate.forward after the sigmoid (replaces the torch ops of model.py:1140-1211): scores = sigma + bias
+ * (bias int32, may be null); with n_groups > 1 the score of a group is the sum of its two largest scores
+ * (its largest when bias is null), the topk_groups best groups stay and the others are masked with -(2^42);
+ * indices [tokens][topk] = the topk best experts in descending order of score, lower index on ties;
+ * raw_weights = sigma[indices]; weights = ((raw * 2^23) // sum raw) * 5 // 2 (floor divisions).
+ * sigma [tokens][experts] int64.  Returns ZKDS_ERR_UNSUPPORTED (silently) for experts > 1024 or not a
+ * multiple of n_groups, n_groups > 32, topk > 32. */
+int zkds_gate_select(const int64_t* sigma, const int32_t* bias, int64_t tokens, int experts, int n_groups,
+                     int topk_groups, int topk, int64_t* indices, int64_t* raw_weights, int64_t* weights,
+                     void* stream);
+
 /* Replaces the four *_init_* functions.  HOST table of 256 entries.
  * kind: 0 softmax Q19, 1 softmax Q21, 2 silu Q23, 3 silu Q25. */
 int zkds_lut(int64_t* host_lut, int kind);

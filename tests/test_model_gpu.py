@@ -460,3 +460,45 @@ def test_activation_beyond_the_limb_bound_is_caught(M, mo, kmod, dev):
     assert got == want
     assert M.ACT_LIMBS == 4
     kmod.device_status()
+
+
+@pytest.mark.parametrize("E,groups,keep,topk,with_bias", [(256, 8, 4, 8, True), (256, 8, 4, 8, False),
+                                                          (16, 4, 2, 4, False), (64, 1, 1, 6, True), (32, 8, 4, 8, True)])
+def test_fused_gate_selection(M, mo, kmod, dev, E, groups, keep, topk, with_bias):
+    """K.gate_select against the reference's torch ops (run here on the same tensors) and the numpy oracle:
+    the same weights always; the same experts, in the same order when no two scores of a row are equal; with
+    deliberately tied scores still a valid top-k of the masked scores and the lower index first."""
+    rng = np.random.default_rng(E + topk)
+    T = 300
+    bias = (2**20 + rng.integers(-2**19, 2**19, E, dtype=np.int64)).astype(np.int32) if with_bias else None
+    # scores (sigma + bias) that are distinct within a row, so that torch.topk's order is defined
+    distinct = np.stack([rng.permutation(E) for _ in range(T)]).astype(np.int64) * 2**14 + \
+        rng.integers(0, 2**14, (T, E), dtype=np.int64) + 2**21
+    sig = distinct - (bias.astype(np.int64) if with_bias else 0)
+    sg, bg = t(sig, dev), (t(bias, dev) if with_bias else None)
+    w, idx, raw = kmod.gate_select(sg, bg, groups, keep, topk)
+    # the reference's ops (model.py:1140-1211)
+    scores = sg + bg if with_bias else sg
+    if groups > 1:
+        s3 = scores.view(T, groups, -1)
+        gsc = s3.topk(2, dim=-1)[0].sum(-1) if with_bias else s3.amax(-1)
+        gi = gsc.topk(keep, dim=-1)[1]
+        gm = s3.new_ones(T, groups, dtype=torch.bool).scatter_(1, gi, False)
+        scores = s3.masked_fill(gm.unsqueeze(-1), -(1 << 42)).flatten(1)
+    ti = torch.topk(scores, topk, dim=-1)[1]
+    tw = sg.gather(1, ti)
+    same(raw, tw.cpu().numpy(), "raw weights")
+    same(idx, ti.cpu().numpy(), "indices")
+    same(w, ((tw * (2 ** 23)) // tw.sum(-1, keepdim=True) * 5 // 2).cpu().numpy(), "weights")
+    # oracle
+    original, biased = sig, (sig + bias.astype(np.int64) if with_bias else sig)
+    oi, masked = mo.gate_select(biased, groups, keep, topk, with_bias)
+    same(idx, oi, "indices vs oracle")
+    same(w, mo.gate_weights(original, oi)[0], "weights vs oracle")
+    # ties: quantise the scores so that many are equal
+    sig2 = (sig >> 19) << 19
+    w2, idx2, raw2 = kmod.gate_select(t(sig2, dev), None, groups, keep, topk)
+    oi2, masked2 = mo.gate_select(sig2, groups, keep, topk, False)
+    same(idx2, oi2, "tied scores: the lower index first, as the oracle's stable sort")
+    check_selection(masked2, idx2.cpu().numpy())
+    kmod.device_status()

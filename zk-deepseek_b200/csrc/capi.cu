@@ -713,6 +713,17 @@ int zkds_moe_combine(const int64_t* out, const int* pos, const int64_t* w, const
     return finish(rc, "zkds_moe_combine");
 }
 
+int zkds_gate_select(const int64_t* sigma, const int32_t* bias, int64_t tokens, int experts, int n_groups,
+                     int topk_groups, int topk, int64_t* indices, int64_t* raw_weights, int64_t* weights, void* stream)
+{
+    int rc = (tokens < 0 || (tokens && (!sigma || !indices || !raw_weights || !weights)))
+                 ? ZKDS_ERR_ARG
+                 : launch_gate_select(sigma, bias, tokens, experts, n_groups, topk_groups, topk, indices, raw_weights,
+                                      weights, ST(stream));
+    if (rc == ZKDS_ERR_UNSUPPORTED) { t_status = rc; return rc; }       // silent: the caller falls back
+    return finish(rc, "zkds_gate_select");
+}
+
 int zkds_lut(int64_t* host_lut, int kind) { return finish(make_lut(host_lut, kind), "zkds_lut"); }
 
 // ---- the reference's 21 symbols ---------------------------------------------------

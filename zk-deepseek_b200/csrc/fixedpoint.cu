@@ -1242,4 +1242,126 @@ int launch_moe_combine(const int64_t* out, const int* pos, const int64_t* w, con
     return check_launch();
 }
 
+// ------------------------------------------------------------------------------
+// gate: bias, grouped top-k selection, weights (Gate.forward, model.py:1140-1211), one warp per token
+// ------------------------------------------------------------------------------
+// scores = sigma + bias; per group the sum of its two largest scores (the largest when there is no bias);
+// the topk_groups best groups stay, the others are out; the topk best remaining experts, in descending
+// order of score; raw = sigma[idx]; w = ((raw * 2^23) // sum raw) * 5 // 2.  Ties go to the lower index
+// (the set torch.topk's radix select takes; the order among equal scores is unspecified there).
+namespace {
+
+__device__ __forceinline__ int64_t floor_div_gate(int64_t a, int64_t b)
+{
+    if (b == 0) return 0;          // an all-zero weight row: torch would raise; defined as 0 here
+    int64_t q = a / b, r = a % b;
+    return (r != 0 && ((r < 0) != (b < 0))) ? q - 1 : q;
+}
+
+constexpr int kGateMaxE = 1024;          // experts per token held in shared memory per warp
+constexpr int kGateWarps = 4;
+
+struct Top2 { int64_t a, b; };           // a >= b
+
+__device__ __forceinline__ Top2 top2_merge(Top2 x, Top2 y)
+{
+    Top2 r;
+    if (x.a >= y.a) { r.a = x.a; r.b = x.b >= y.a ? x.b : y.a; }
+    else { r.a = y.a; r.b = y.b >= x.a ? y.b : x.a; }
+    return r;
+}
+
+__global__ void __launch_bounds__(32 * kGateWarps)
+gate_select_kernel(const int64_t* __restrict__ sig, const int32_t* __restrict__ bias, int64_t T, int E, int n_groups,
+                   int topk_groups, int topk, int64_t* __restrict__ indices, int64_t* __restrict__ raw_out,
+                   int64_t* __restrict__ w_out)
+{
+    extern __shared__ int64_t gate_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t t = (int64_t)blockIdx.x * kGateWarps + warp;
+    if (t >= T) return;
+    int64_t* sc = gate_smem + (size_t)warp * E;
+    const int64_t* srow = sig + t * E;
+    for (int e = lane; e < E; e += 32) sc[e] = srow[e] + (bias ? (int64_t)bias[e] : 0);
+    __syncwarp();
+    const int gs = E / n_groups;
+    if (n_groups > 1) {
+        // group score in lane g (n_groups <= 32)
+        int64_t gscore = INT64_MIN;
+        for (int g = 0; g < n_groups; ++g) {
+            Top2 m{INT64_MIN, INT64_MIN};
+            for (int i = lane; i < gs; i += 32) m = top2_merge(m, Top2{sc[g * gs + i], INT64_MIN});
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                Top2 y{__shfl_xor_sync(0xffffffffu, m.a, o), __shfl_xor_sync(0xffffffffu, m.b, o)};
+                m = top2_merge(m, y);
+            }
+            const int64_t v = bias ? (int64_t)((uint64_t)m.a + (uint64_t)m.b) : m.a;
+            if (lane == g) gscore = v;
+        }
+        // keep the topk_groups best groups (lower index on ties), mask the rest
+        unsigned kept = 0;
+        for (int r = 0; r < topk_groups; ++r) {
+            int64_t v = (lane < n_groups && !((kept >> lane) & 1u)) ? gscore : INT64_MIN;
+            int idx = lane;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const int64_t ov = __shfl_xor_sync(0xffffffffu, v, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+                if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+            }
+            kept |= 1u << idx;
+        }
+        for (int e = lane; e < E; e += 32)
+            if (!((kept >> (e / gs)) & 1u)) sc[e] = -(1ll << 42);           // model.py:1186
+        __syncwarp();
+    }
+    // topk experts, descending; lower index on ties
+    int64_t raw_sum = 0, my_raw = 0;
+    int my_idx = 0;
+    for (int r = 0; r < topk; ++r) {
+        int64_t v = INT64_MIN;
+        int idx = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const int64_t x = sc[e];
+            if (x > v) { v = x; idx = e; }                                   // ascending e: first maximum kept
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const int64_t ov = __shfl_xor_sync(0xffffffffu, v, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+        }
+        const int64_t raw = srow[idx];
+        raw_sum += raw;
+        if (lane == r) { my_raw = raw; my_idx = idx; }
+        if (lane == 0) sc[idx] = INT64_MIN;                                  // taken (below the group mask value)
+        __syncwarp();
+    }
+    if (lane < topk) {
+        indices[t * topk + lane] = my_idx;
+        raw_out[t * topk + lane] = my_raw;
+        // floor divisions of torch's `//` (model.py:1207, 1210); the wrapping products of int64 tensors
+        int64_t w = floor_div_gate((int64_t)((uint64_t)my_raw << 23), raw_sum);
+        w = floor_div_gate((int64_t)((uint64_t)w * 5ull), 2);
+        w_out[t * topk + lane] = w;
+    }
+}
+
+}  // namespace
+
+int launch_gate_select(const int64_t* sig, const int32_t* bias, int64_t T, int E, int n_groups, int topk_groups,
+                       int topk, int64_t* indices, int64_t* raw, int64_t* w, cudaStream_t st)
+{
+    if (T == 0) return ZKDS_OK;
+    if (E <= 0 || E > kGateMaxE || n_groups < 1 || n_groups > 32 || E % n_groups || topk < 1 || topk > 32 ||
+        topk_groups < 1 || topk_groups > n_groups || (int64_t)topk > (int64_t)topk_groups * (E / n_groups))
+        return ZKDS_ERR_UNSUPPORTED;
+    const int64_t blocks = (T + kGateWarps - 1) / kGateWarps;
+    if (blocks > 0x7fffffffll) return ZKDS_ERR_RANGE;
+    gate_select_kernel<<<(unsigned)blocks, 32 * kGateWarps, (size_t)kGateWarps * E * sizeof(int64_t), st>>>(
+        sig, bias, T, E, n_groups, topk_groups, topk, indices, raw, w);
+    return check_launch();
+}
+
 }  // namespace zkds

@@ -59,6 +59,10 @@ int launch_glu_planes(const int64_t* r1, const int64_t* r2, int64_t ld, const in
                       unsigned long long* absmax_out, cudaStream_t st);
 int launch_gather_rows(const int64_t* src, const int* index, int64_t* dst, int64_t rows, int64_t cols,
                        cudaStream_t st);
+// Gate.forward after the sigmoid (model.py:1140-1211): bias, grouped top-k selection, gathered and
+// normalised weights; one warp per token.  ZKDS_ERR_UNSUPPORTED for shapes it does not take.
+int launch_gate_select(const int64_t* sig, const int32_t* bias, int64_t T, int E, int n_groups, int topk_groups,
+                       int topk, int64_t* indices, int64_t* raw, int64_t* w, cudaStream_t st);
 int launch_moe_combine(const int64_t* out, const int* pos, const int64_t* w, const int64_t* base,
                        int64_t* y, int64_t tokens, int slots, int64_t cols, cudaStream_t st);
 

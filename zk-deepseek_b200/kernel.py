@@ -106,6 +106,7 @@ _sig("zkds_grouped_gather_prepared", [_vp, _vp, _vp, _vp, _ll, _vp, _ll, _ll, _l
 _sig("zkds_glu_q23", [_vp, _vp, _ll, _vp, _vp, _vp, _ll, _ll, _vp])
 _sig("zkds_gather_rows", [_vp, _vp, _vp, _ll, _ll, _vp])
 _sig("zkds_moe_combine", [_vp, _vp, _vp, _vp, _vp, _ll, _i, _ll, _vp])
+_sig("zkds_gate_select", [_vp, _vp, _ll, _i, _i, _i, _i, _vp, _vp, _vp, _vp])
 _sig("zkds_contraction_prepared", [_vp, _ll, _ll, _vp, _i, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _ll,
                                    _i, _i, _vp])
 
@@ -480,6 +481,28 @@ def mla_scores_fused(q_abs, kv, q_pe, pe, rescale1=23, rescale2=21, mul=94, div=
         return None
     _check(rc, "mla_scores_fused")
     return out
+
+
+def gate_select(sigma, bias, n_groups, topk_groups, topk):
+    """The gate after its sigmoid (model.py:1140-1211) in one kernel: sigma int64 [T, E], bias int32 [E] or
+    None -> (weights int64 [T, topk], indices int64 [T, topk], raw int64 [T, topk]) with
+    raw = sigma[indices] and weights = ((raw * 2^23) // sum raw) * 5 // 2.  Experts in descending order of
+    sigma + bias, lower index on ties.  Returns None for shapes the kernel does not take."""
+    _dev_i64(sigma, "sigma")
+    T, E = sigma.shape
+    if bias is not None and (bias.dtype != torch.int32 or not bias.is_contiguous() or bias.numel() != E):
+        return None
+    idx = torch.empty((T, topk), dtype=torch.int64, device=sigma.device)
+    raw = torch.empty_like(idx)
+    w = torch.empty_like(idx)
+    with torch.cuda.device(sigma.device):
+        rc = lib.zkds_gate_select(sigma.data_ptr(), bias.data_ptr() if bias is not None else None, T, E,
+                                  int(n_groups), int(topk_groups), int(topk), idx.data_ptr(), raw.data_ptr(),
+                                  w.data_ptr(), _stream())
+    if rc == 6:
+        return None
+    _check(rc, "gate_select")
+    return w, idx, raw
 
 
 def softmax_q19_causal(R, C, start_pos=0):

@@ -62,6 +62,10 @@ ACT_LIMBS = 4
 # anyway) and after every Block whose dumps are written.  generate() re-runs a flagged step with measured
 # limb counts instead of raising.
 CHECK_STATUS = True
+# Gate: bias, grouped top-k selection and weights in one kernel (K.gate_select) instead of the reference's
+# torch ops.  Same experts and weights; under score ties the kernel takes the lower index, which is the set
+# torch.topk takes, while the ORDER torch gives equal scores is unspecified (False keeps the torch ops).
+FUSED_GATE = True
 
 
 @dataclass
@@ -649,6 +653,14 @@ class Gate(nn.Module):
             saveTensor(f"{d}/gate_original_scores.bin", original_scores.contiguous())
             saveTensor(f"{d}/gate_bias.bin", self.bias.view(torch.uint32))
         T = scores.size(0)
+        fused = K.gate_select(original_scores.contiguous(), self.bias, self.n_groups, self.topk_groups, self.topk) \
+            if FUSED_GATE else None
+        if fused is not None:
+            weights, indices, raw = fused
+            if snark:
+                saveTensor(f"{d}/gate_indices.bin", indices)
+                saveTensor(f"{d}/gate_weights.bin", raw)
+            return weights, indices
         if self.n_groups > 1:
             scores = scores.view(T, self.n_groups, -1)
             if self.bias is None:
