@@ -2047,6 +2047,20 @@ static double issued_share(int64_t M, int64_t N, int64_t K, int NT, int skip_til
     return issued / ((double)mt * (double)nt * (double)kb);
 }
 
+// The opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of the kernel: set once.
+template <typename K>
+static int allow_big_smem(K kernel, bool (&done)[64])
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (!done[dev]) {
+        ZKDS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024 - 3072)));
+        done[dev] = true;
+    }
+    return ZKDS_OK;
+}
+static bool g_attr_onetile[64], g_attr_p16[64], g_attr_p8[64];
+
 static cudaEvent_t* timing_events()
 {
     int dev = 0;
@@ -2135,12 +2149,10 @@ static int launch_persistent(int ew, int ctas, size_t smem, cudaStream_t st, con
         }
     } report{prof, st, &lp};
     if (ew == 16) {
-        ZKDS_CUDA(cudaFuncSetAttribute(limb_gemm_persistent_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)(227 * 1024 - 3072)));
+        { int rc_a = allow_big_smem(limb_gemm_persistent_kernel<16>, g_attr_p16); if (rc_a != ZKDS_OK) return rc_a; }
         limb_gemm_persistent_kernel<16><<<ctas, persistent_threads(16), smem, st>>>(tmA, tmB, lp);
     } else {
-        ZKDS_CUDA(cudaFuncSetAttribute(limb_gemm_persistent_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)(227 * 1024 - 3072)));
+        { int rc_a = allow_big_smem(limb_gemm_persistent_kernel<8>, g_attr_p8); if (rc_a != ZKDS_OK) return rc_a; }
         limb_gemm_persistent_kernel<8><<<ctas, persistent_threads(8), smem, st>>>(tmA, tmB, lp);
     }
     return check_launch();
@@ -2339,8 +2351,7 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     // more than half the shared memory per CTA keeps one CTA per SM, so its tensor-memory
     // allocation can never wait for a co-resident CTA
     if (smem < 120 * 1024) smem = 120 * 1024;
-    ZKDS_CUDA(cudaFuncSetAttribute(limb_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (int)(227 * 1024 - 3072)));
+    { int rc_a = allow_big_smem(limb_gemm_kernel, g_attr_onetile); if (rc_a != ZKDS_OK) return rc_a; }
     // panel height: the A limb tiles of one panel should stay L2 resident (~32 MB)
     int64_t panel = (32ll << 20) / ((int64_t)La * kTileM * Kp);
     if (panel < 1) panel = 1;
@@ -2693,8 +2704,7 @@ int launch_gemm_noalloc(const Contraction& p, int La, int Lb, cudaStream_t st)
 
     size_t smem = stage * stages + 1024;
     if (smem < 120 * 1024) smem = 120 * 1024;
-    ZKDS_CUDA(cudaFuncSetAttribute(limb_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (int)(227 * 1024 - 3072)));
+    { int rc_a = allow_big_smem(limb_gemm_kernel, g_attr_onetile); if (rc_a != ZKDS_OK) return rc_a; }
     lp.m_tiles = mt; lp.n_tiles = nt; lp.panel_m = mt;
     if (mt * nt > 0x7fffffffll) return ZKDS_ERR_UNSUPPORTED;
     dim3 grid((unsigned)(mt * nt), 1, (unsigned)p.batches);

@@ -134,6 +134,25 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+class _NoSwitch:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_SWITCH = _NoSwitch()
+
+
+def _on(device):
+    """context that makes `device` current for a library call; nothing to do (and nothing to pay: the guard
+    costs several microseconds per call) when it already is"""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _NO_SWITCH
+    return torch.cuda.device(device)
+
+
 def _dev_i64(t, name):
     if t.dtype != torch.int64:
         raise TypeError("%s must be int64, got %s" % (name, t.dtype))
@@ -178,7 +197,7 @@ def int64_bmm_broadcast(A, B, a_rescale, b_rescale, c_rescale, a_limbs=0, b_limb
     C = torch.empty((Bdim, M, N), dtype=torch.int64, device=A.device)
     R = torch.empty((Bdim, M, N), dtype=torch.int64, device=A.device)
     flags = ALGO | (REMAINDER_LEGACY if LEGACY_REMAINDER else 0)
-    with torch.cuda.device(A.device):
+    with _on(A.device):
         _check(lib.zkds_gemm(A.data_ptr(), B.data_ptr(), 32 if B.dtype == torch.int32 else 64,
                              C.data_ptr(), R.data_ptr(), int(a_rescale), int(b_rescale),
                              int(c_rescale), Bdim, M, K, N, a_limbs, b_limbs, flags, _stream()),
@@ -191,7 +210,7 @@ def _einsum(fn_name, A, B, out_shape, rescale, dims, a_limbs, b_limbs):
     if not B.is_cuda or not B.is_contiguous():
         raise ValueError("B must be a contiguous CUDA tensor")
     C = torch.empty(out_shape, dtype=torch.int64, device=A.device)
-    with torch.cuda.device(A.device):
+    with _on(A.device):
         _check(getattr(lib, fn_name)(A.data_ptr(), B.data_ptr(), C.data_ptr(), int(rescale), *dims,
                                      a_limbs, b_limbs, ALGO, _stream()), fn_name)
     return C
@@ -316,7 +335,7 @@ class WeightPlanes:
         self.nb, self.N, self.K = nb, rows, K
         self.device = W.device
         h = _vp()
-        with torch.cuda.device(W.device):
+        with _on(W.device):
             _check(lib.zkds_planes_create(W.data_ptr(), 32 if W.dtype == torch.int32 else 64, nb, rows,
                                           K, s_batch, s_row, s_k, int(div), limbs, ctypes.byref(h),
                                           _stream()), "zkds_planes_create")
@@ -345,7 +364,7 @@ def linear_prepared(A, planes, c_rescale, a_rescale=1, a_limbs=0, want_remainder
     C = torch.empty((Bdim, M, planes.N), dtype=torch.int64, device=A.device)
     R = torch.empty_like(C) if want_remainder else None
     flags = (REMAINDER_LEGACY if LEGACY_REMAINDER else 0) | _a_flags(a_limbs, dynamic)
-    with torch.cuda.device(A.device):
+    with _on(A.device):
         _check(lib.zkds_contraction_prepared(A.data_ptr(), M * K, K, planes.handle, 0, C.data_ptr(),
                                              R.data_ptr() if want_remainder else None, M * planes.N,
                                              planes.N, Bdim, M, int(a_rescale), 0, int(c_rescale),
@@ -362,7 +381,7 @@ def einsum_heads_prepared(A, planes, rescale, rounding, a_limbs=0, dynamic=False
     assert H == planes.nb and K == planes.K
     N = planes.N
     C = torch.empty((Bn, S, H, N), dtype=torch.int64, device=A.device)
-    with torch.cuda.device(A.device):
+    with _on(A.device):
         _check(lib.zkds_contraction_prepared(A.data_ptr(), K, H * K, planes.handle, 1, C.data_ptr(), None,
                                              N, H * N, H, Bn * S, 1, int(rescale) // 2 if rounding else 0,
                                              int(rescale), a_limbs, _a_flags(a_limbs, dynamic), _stream()),
@@ -386,7 +405,7 @@ def grouped_prepared(A, planes, tile_group, c_rescale, a_limbs=0, dynamic=False,
     n_tiles = tile_group.numel()
     C = torch.empty((n_tiles * 128, planes.N), dtype=torch.int64, device=A.device)
     gs = group_shift.data_ptr() if group_shift is not None else None
-    with torch.cuda.device(A.device):
+    with _on(A.device):
         if row_index is None:
             assert A.shape == (n_tiles * 128, planes.K)
             _check(lib.zkds_grouped_prepared(A.data_ptr(), planes.handle, tile_group.data_ptr(), n_tiles,
@@ -424,7 +443,7 @@ def glu_prepared(r1, r2, planes, c_rescale, ld=None, a_limbs=3, dynamic=True, ti
     if group_shift is not None:
         assert group_shift.dtype == torch.int32 and group_shift.is_cuda and group_shift.is_contiguous()
     C = torch.empty((rows, planes.N), dtype=torch.int64, device=r1.device)
-    with torch.cuda.device(r1.device):
+    with _on(r1.device):
         rc = lib.zkds_glu_prepared(r1.data_ptr(), r2.data_ptr(), ld, lut.data_ptr(), rows, planes.handle,
                                    tile_group.data_ptr() if tile_group is not None else None, C.data_ptr(),
                                    int(c_rescale), group_shift.data_ptr() if group_shift is not None else None,
@@ -449,7 +468,7 @@ def attention_scores_fused(A, KV, rescale, addin=None, mul=0, div=0, causal=Fals
         _dev_i64(addin, "addin")
         assert tuple(addin.shape) == (Bn, S, H, T)
     C = torch.empty((Bn, S, H, T), dtype=torch.int64, device=A.device)
-    with torch.cuda.device(A.device):
+    with _on(A.device):
         _check(lib.zkds_einsum_bshc_btc_bsht_ex(A.data_ptr(), KV.data_ptr(), C.data_ptr(), int(rescale), Bn,
                                                 S, H, T, Cd, addin.data_ptr() if addin is not None else None,
                                                 int(mul), int(div), 1 if causal else 0, int(start_pos),
@@ -471,7 +490,7 @@ def mla_scores_fused(q_abs, kv, q_pe, pe, rescale1=23, rescale2=21, mul=94, div=
     T, C2 = kv.shape[1], q_pe.shape[3]
     assert kv.shape == (Bn, T, C1) and q_pe.shape == (Bn, S, H, C2) and pe.shape == (Bn, T, C2)
     out = torch.empty((Bn, S, H, T), dtype=torch.int64, device=q_abs.device)
-    with torch.cuda.device(q_abs.device):
+    with _on(q_abs.device):
         rc = lib.zkds_mla_scores(q_abs.data_ptr(), kv.data_ptr(), q_pe.data_ptr(), pe.data_ptr(), out.data_ptr(),
                                  Bn, S, H, T, C1, C2, int(rescale1), int(rescale2), int(mul), int(div),
                                  1 if causal else 0, int(start_pos), int(mask_value), a_limbs, b_limbs,
@@ -495,7 +514,7 @@ def gate_select(sigma, bias, n_groups, topk_groups, topk):
     idx = torch.empty((T, topk), dtype=torch.int64, device=sigma.device)
     raw = torch.empty_like(idx)
     w = torch.empty_like(idx)
-    with torch.cuda.device(sigma.device):
+    with _on(sigma.device):
         rc = lib.zkds_gate_select(sigma.data_ptr(), bias.data_ptr() if bias is not None else None, T, E,
                                   int(n_groups), int(topk_groups), int(topk), idx.data_ptr(), raw.data_ptr(),
                                   w.data_ptr(), _stream())
@@ -513,7 +532,7 @@ def softmax_q19_causal(R, C, start_pos=0):
     _dev_i64(C, "C")
     Bn, S, H, T = R.shape
     lut = _lut_on(EXP2_FRAC_LUT_Q19, R.device, "softmax_init_q19")
-    with torch.cuda.device(R.device):
+    with _on(R.device):
         rc = lib.zkds_softmax_causal(R.data_ptr(), C.data_ptr(), lut.data_ptr(), Bn, S, H, T, int(start_pos),
                                      _stream())
     if rc == 6:
@@ -537,7 +556,7 @@ def softmax_pv_fused(scores, kv, rescale=23, causal_skip=False, start_pos=0, a_l
     lut = _lut_on(EXP2_FRAC_LUT_Q19, scores.device, "softmax_init_q19")
     out = torch.empty((Bn, S, H, Cd), dtype=torch.int64, device=scores.device)
     flags = ALGO_LIMB | (LIMBS_DYNAMIC if dynamic else 0)
-    with torch.cuda.device(scores.device):
+    with _on(scores.device):
         rc = lib.zkds_softmax_pv(scores.data_ptr(), kv.data_ptr(), out.data_ptr(), lut.data_ptr(), int(rescale),
                                  Bn, S, H, T, Cd, 1 if causal_skip else 0, int(start_pos), a_limbs, b_limbs,
                                  flags, _stream())
@@ -555,7 +574,7 @@ def einsum_bsht_btc_bshc_causal(A, B, rescale, start_pos=0, a_limbs=3, b_limbs=0
     Cd = B.shape[2]
     assert Bn == B.shape[0] and T == B.shape[1]
     C = torch.empty((Bn, S, H, Cd), dtype=torch.int64, device=A.device)
-    with torch.cuda.device(A.device):
+    with _on(A.device):
         _check(lib.zkds_einsum_bsht_btc_bshc_causal(A.data_ptr(), B.data_ptr(), C.data_ptr(), int(rescale), Bn, S,
                                                     H, T, Cd, int(start_pos), a_limbs, b_limbs, 0, _stream()),
                "einsum_bsht_btc_bshc_causal")
@@ -571,7 +590,7 @@ def glu_q23(r1, r2, ld=None, want_silu=False):
     lut = _lut_on(EXP2_FRAC_LUT_Q23, r1.device, "silu_init_q23")
     h = torch.empty((rows, n), dtype=torch.int64, device=r1.device)
     s1 = torch.empty_like(h) if want_silu else None
-    with torch.cuda.device(r1.device):
+    with _on(r1.device):
         _check(lib.zkds_glu_q23(r1.data_ptr(), r2.data_ptr(), ld, h.data_ptr(),
                                 s1.data_ptr() if want_silu else None, lut.data_ptr(), rows, n, _stream()),
                "glu_q23")
@@ -586,7 +605,7 @@ def gather_rows(src, index):
     if src.shape[0] == 0:       # nothing to gather from (a rank that received no rows): all padding
         return torch.zeros((rows, cols), dtype=torch.int64, device=src.device)
     dst = torch.empty((rows, cols), dtype=torch.int64, device=src.device)
-    with torch.cuda.device(src.device):
+    with _on(src.device):
         _check(lib.zkds_gather_rows(src.data_ptr(), index.data_ptr(), dst.data_ptr(), rows, cols, _stream()),
                "gather_rows")
     return dst
@@ -600,7 +619,7 @@ def moe_combine(out, pos, w, base=None):
     tokens, slots = pos.shape
     cols = out.shape[-1]
     y = torch.empty((tokens, cols), dtype=torch.int64, device=out.device)
-    with torch.cuda.device(out.device):
+    with _on(out.device):
         _check(lib.zkds_moe_combine(out.data_ptr(), pos.data_ptr(), w.data_ptr(),
                                     base.data_ptr() if base is not None else None, y.data_ptr(), tokens,
                                     slots, cols, _stream()), "moe_combine")
@@ -620,7 +639,7 @@ def complex_int64_mul_broadcast(A, B, shift=42):
     batch, seq, head, pairs = A.shape[0], A.shape[1], A.shape[2], A.shape[3]
     assert B.numel() == seq * pairs * 2, "table must hold one entry per (seq, pair)"
     C = torch.empty(A.shape, dtype=torch.int64, device=A.device)
-    with torch.cuda.device(A.device):
+    with _on(A.device):
         _check(lib.zkds_rope(A.data_ptr(), B.data_ptr(), C.data_ptr(), batch, seq, head, pairs,
                              int(shift), _stream()), "complex_int64_mul_broadcast")
     return C
@@ -639,7 +658,7 @@ def rms_norm_int64_device(A, W, eps, dim):
     M, N = A.shape
     C = torch.empty((M, N), dtype=torch.int64, device=A.device)
     rms = torch.empty((M,), dtype=torch.int64, device=A.device)
-    with torch.cuda.device(A.device):
+    with _on(A.device):
         _check(lib.zkds_rms_norm(A.data_ptr(), W.data_ptr(), 32 if W.dtype == torch.int32 else 64,
                                  C.data_ptr(), rms.data_ptr(), M, N, int(eps), int(dim), _stream()),
                "RMS_Norm_int64")
@@ -661,7 +680,7 @@ def rms_norm_apply(A, W, rms):
     _dev_i64(rms, "rms")
     M, N = A.shape
     C = torch.empty((M, N), dtype=torch.int64, device=A.device)
-    with torch.cuda.device(A.device):
+    with _on(A.device):
         _check(lib.zkds_rms_norm_apply(A.data_ptr(), W.data_ptr(),
                                        32 if W.dtype == torch.int32 else 64, rms.data_ptr(),
                                        C.data_ptr(), M, N, _stream()), "rms_norm_apply")
@@ -732,7 +751,7 @@ def _softmax(R, C, lut, frac, what):
     T = R.shape[-1]
     rows = R.numel() // T if T else 0
     w = R.data_ptr() if SOFTMAX_WRITES_WEIGHTS else None
-    with torch.cuda.device(R.device):
+    with _on(R.device):
         _check(lib.zkds_softmax(R.data_ptr(), w, C.data_ptr(), lut.data_ptr(), rows, T, frac,
                                 _stream()), what)
 
@@ -750,7 +769,7 @@ def softmax_q19(R, C):
 def _act(R, C, lut, frac, silu, what):
     _dev_i64(R, "R")
     _dev_i64(C, "C")
-    with torch.cuda.device(R.device):
+    with _on(R.device):
         _check(lib.zkds_act(R.data_ptr(), C.data_ptr(), lut.data_ptr(), R.numel(), frac, silu,
                             _stream()), what)
 
