@@ -183,3 +183,18 @@ def test_generate_from_a_converted_checkpoint_gives_the_reference_tokens(fx, kmo
     dumps = mc.normalise_dumps({k: v for k, v in mc.read_dumps(zk).items() if not k.endswith("tokens.bin")})
     check_against_fixture(fx, "tf", {}, dumps, "dumps written under generate()", outputs=False)
     kmod.device_status()
+
+
+@pytest.mark.gpu
+def test_asynchronous_dump_writer_gives_the_same_files(fx, kmod, dev, tmp_path):
+    """kernel.ASYNC_DUMPS: dumps leave through pinned buffers and a writer thread; after flush_dumps() the
+    files are byte for byte the reference's (the `tf` case: scores dumped before softmax overwrites them)"""
+    M = importlib.import_module(PKG + ".model")
+    kmod.ASYNC_DUMPS = True
+    try:
+        out, _ = mc.run_case(M, kmod, "tf", dev, str(tmp_path))
+        kmod.flush_dumps()
+    finally:
+        kmod.ASYNC_DUMPS = False
+    dumps = mc.read_dumps(os.path.join(str(tmp_path), "zkdata_tf"))
+    check_against_fixture(fx, "tf", out, mc.normalise_dumps(dumps), "asynchronous dumps vs reference model.py")

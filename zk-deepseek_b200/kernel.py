@@ -687,13 +687,70 @@ def rms_norm_apply(A, W, rms):
     return C
 
 
+# zkdata dumps.  ASYNC_DUMPS = False writes every file before saveTensor returns, as the reference does (a
+# device-to-host copy that stalls the host on the GPU at every dump site).  True: the copy into a pinned host
+# buffer is queued on the CURRENT stream (so it reads the tensor exactly where the call stands, before any
+# later kernel can overwrite it, e.g. softmax_q19 clobbering its input) and a writer thread stores the file
+# once the copy's event has fired; flush_dumps() returns when every file is on disk.  Same bytes either way.
+ASYNC_DUMPS = False
+_DUMP_QUEUE = None
+_DUMP_THREAD = None
+_DUMP_ERRORS = []
+_PINNED_FREE = {}            # bytes -> [pinned uint8 tensors]: cudaHostAlloc is slow, buffers are reused
+
+
+def _dump_worker():
+    while True:
+        item = _DUMP_QUEUE.get()
+        try:
+            if item is None:
+                return
+            fileName, buf, nbytes, event = item
+            event.synchronize()
+            with open(fileName, "wb") as f:
+                f.write(buf.numpy()[:nbytes].tobytes())
+            _PINNED_FREE.setdefault(buf.numel(), []).append(buf)
+        except Exception as err:  # noqa: BLE001 - reported by flush_dumps
+            _DUMP_ERRORS.append(err)
+        finally:
+            _DUMP_QUEUE.task_done()
+
+
+def flush_dumps():
+    """waits until every dump queued by saveTensor is written; raises the first error a write met"""
+    if _DUMP_QUEUE is not None:
+        _DUMP_QUEUE.join()
+    if _DUMP_ERRORS:
+        err = _DUMP_ERRORS[0]
+        del _DUMP_ERRORS[:]
+        raise err
+
+
 def saveTensor(fileName, t):
     """Raw little-endian C-order dump, no header (kernel.py:553-565)."""
+    global _DUMP_QUEUE, _DUMP_THREAD
     t = t.detach()
-    if t.device.type != "cpu":
-        t = t.cpu()
-    with open(fileName, "wb") as f:
-        f.write(t.contiguous().numpy().tobytes(order="C"))
+    if not (ASYNC_DUMPS and t.device.type == "cuda"):
+        if t.device.type != "cpu":
+            t = t.cpu()
+        with open(fileName, "wb") as f:
+            f.write(t.contiguous().numpy().tobytes(order="C"))
+        return
+    import queue
+    import threading
+    if _DUMP_QUEUE is None:
+        _DUMP_QUEUE = queue.Queue()
+        _DUMP_THREAD = threading.Thread(target=_dump_worker, daemon=True)
+        _DUMP_THREAD.start()
+    src = t.contiguous().view(-1).view(torch.uint8)
+    nbytes = src.numel()
+    size = max(4096, 1 << (max(nbytes, 1) - 1).bit_length())          # size classes: powers of two
+    free = _PINNED_FREE.get(size)
+    buf = free.pop() if free else torch.empty(size, dtype=torch.uint8, pin_memory=True)
+    buf[:nbytes].copy_(src, non_blocking=True)                        # stream-ordered read of the tensor
+    event = torch.cuda.Event()
+    event.record()
+    _DUMP_QUEUE.put((fileName, buf, nbytes, event))
 
 
 # ---- lookup tables --------------------------------------------------------------------
