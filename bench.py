@@ -829,7 +829,11 @@ class MoeWorkload:
     """One DeepSeek-V3 MoE layer in int64 fixed point (MoE.forward, inference/model.py:1325-1383):
     dim 7168, 256 routed experts + 1 shared expert, moe_inter_dim 2048, sigmoid gate with top-8
     routing over 8 groups / 4 kept, route scale 2.5.  8192 tokens ~ N(0, 2^16); int32 gate,
-    shared and expert weights ~ N(0, 2^16/sqrt(fan_in)); int32 gate bias >= 0; every shift 16.
+    shared and expert weights ~ N(0, 2^16/sqrt(fan_in)); every shift 16 except the gate's, which is 9 so
+    that its logits have a standard deviation of about 1.0 in Q23 (what the sigmoid reads); int32 gate bias
+    >= 0 of about 0.004.  Like the trained model's balancing bias this leaves the expert load even (a bias
+    that outweighs the spread of the scores would send every token to the same eight experts); the load the
+    gate actually produced is reported in config.routing.
     With N GPUs the experts are split 256/N per GPU and the 8192 tokens N ways; rows travel to the
     experts' owners and back with NCCL all-to-all (strong scaling)."""
     name = "moe_layer_8192_tokens"
@@ -839,7 +843,7 @@ class MoeWorkload:
     unit = "tokens/s"
     scaling = "strong"
     collective_check = True
-    T, E, SHIFT = 8192, 256, 16
+    T, E, SHIFT, GATE_SHIFT = 8192, 256, 16, 9
 
     def __init__(self, torch, k, dev, rank, T=None, E=None):
         import numpy as np
@@ -870,8 +874,8 @@ class MoeWorkload:
             return _normal_i(torch, gen, (out_f, in_f), 2.0**16 / math.sqrt(in_f), dev, torch.int32)
 
         moe.gate.weight = weight(g, self.E, D)
-        moe.gate.scale = torch.tensor(sh, dtype=torch.int32, device=dev)
-        moe.gate.bias = torch.abs(_normal_i(torch, g, (self.E,), 2.0**18, dev, torch.int64)).to(torch.int32)
+        moe.gate.scale = torch.tensor(self.GATE_SHIFT, dtype=torch.int32, device=dev)
+        moe.gate.bias = torch.abs(_normal_i(torch, g, (self.E,), 2.0**15, dev, torch.int64)).to(torch.int32)
         for name, (o, i) in (("w1", (I, D)), ("w3", (I, D)), ("w2", (D, I))):
             lin = getattr(moe.shared_experts, name)
             lin.weight = weight(g, o, i)
@@ -895,6 +899,21 @@ class MoeWorkload:
         pairs = self.T * a.n_activated_experts
         self.ops = 2.0 * 3 * D * I * (pairs + self.T) + 2.0 * self.T * D * self.E
         self.launches_per_step = 0
+        self.routing = self._expert_load()
+
+    def _expert_load(self):
+        """rows per expert and per GPU that the gate produces for the whole batch (every rank's tokens)"""
+        import torch.distributed as dist
+        idx = self.moe.gate(0, self.x.view(-1, self.args.dim))[1]
+        rows = self.torch.bincount(idx.flatten(), minlength=self.E)
+        if self.world > 1:
+            dist.all_reduce(rows)
+        per_gpu = rows.view(self.world, -1).sum(1)
+        mean_e = float(rows.sum().item()) / self.E
+        return {"experts_hit": int((rows > 0).sum().item()),
+                "rows_per_expert_max_over_mean": round(float(rows.max().item()) / mean_e, 3),
+                "rows_per_expert_min": int(rows.min().item()),
+                "rows_per_gpu_max_over_mean": round(float(per_gpu.max().item()) * self.world / float(rows.sum().item()), 3)}
 
     def expert_weights(self, global_id):
         """(w1, w3, w2) of one routed expert, seeded by its global id (same on every rank)"""
@@ -906,8 +925,8 @@ class MoeWorkload:
         a = self.args
         return {"workload": self.name, "tokens": self.T, "tokens_per_gpu": self.T_local, "dim": a.dim,
                 "routed_experts": self.E, "experts_per_gpu": self.E // self.world, "top_k": 8,
-                "moe_inter_dim": a.moe_inter_dim, "shift": self.SHIFT, "act_limbs_bound": 3,
-                "useful_ops_per_step": self.ops, "weights": "resident limb planes, all experts",
+                "moe_inter_dim": a.moe_inter_dim, "shift": self.SHIFT, "gate_shift": self.GATE_SHIFT,
+                "act_limbs_bound": 3, "routing": self.routing, "useful_ops_per_step": self.ops, "weights": "resident limb planes, all experts",
                 "l2": "expert weights (45 GB int32) and token rows far exceed L2"}
 
     def step(self):
@@ -985,7 +1004,8 @@ class MoeWorkload:
             w1, w3, w2 = self.expert_weights(int(e))
             experts[e] = {"w1": w1.cpu().numpy(), "w3": w3.cpu().numpy(), "w2": w2.cpu().numpy(),
                           "w1_scale": sh, "w3_scale": sh, "w2_scale": sh}
-        p = {"gate": {"weight": moe.gate.weight.cpu().numpy(), "scale": sh, "bias": moe.gate.bias.cpu().numpy()},
+        p = {"gate": {"weight": moe.gate.weight.cpu().numpy(), "scale": self.GATE_SHIFT,
+                      "bias": moe.gate.bias.cpu().numpy()},
              "shared": mlp(moe.shared_experts), "experts": experts}
         want, _, _ = mo.moe_forward(p, xs.cpu().numpy(), 8, 4, 8, indices=idx)
         return int((got != want).sum())
@@ -1001,7 +1021,7 @@ class MoeWorkload:
         wg = ri((256, D), 9).astype(np.int32)
         x = ri((1, S, D), 16)
         t0 = time.time()
-        orc.act(orc.gemm(x, wg, 1, 1, 16)[0], "sigmoid", 23)
+        orc.act(orc.gemm(x, wg, 1, 1, 9)[0], "sigmoid", 23)
         for _ in range(9):                       # shared + 8 routed experts per token
             r = orc.gemm(x, w13, 1, 1, 16)[0]
             h = (orc.act(np.ascontiguousarray(r[..., :I]), "silu", 23) * r[..., I:]) >> 23
@@ -1115,8 +1135,10 @@ class DecodeWorkload:
             else:
                 moe = blk.ffn
                 moe.gate.weight = weight(experts, D)
-                moe.gate.scale = scale()
-                moe.gate.bias = torch.abs(_normal_i(torch, g, (experts,), 2.0**18, dev, torch.int64)).to(torch.int32)
+                # shift 9: logits with a standard deviation near 1.0 in Q23 and a small bias, so that the 64
+                # tokens spread over the experts as they do in the trained model (see config.experts_hit)
+                moe.gate.scale = torch.tensor(9, dtype=torch.int32, device=dev)
+                moe.gate.bias = torch.abs(_normal_i(torch, g, (experts,), 2.0**15, dev, torch.int64)).to(torch.int32)
                 for name, (o, n_in) in (("w1", (I, D)), ("w3", (I, D)), ("w2", (D, I))):
                     lin = getattr(moe.shared_experts, name)
                     lin.weight = weight(o, n_in, rows=part(o))
@@ -1186,17 +1208,25 @@ class DecodeWorkload:
         ms = sum(r["ms"] for r in recs)
         # weight bytes each tensor-core launch streams: its B limb planes (N x K x limbs)
         wbytes = 0.0
+        hit = [int((blk.ffn.last_counts > 0).sum().item()) for blk in self.model.layers
+               if getattr(blk.ffn, "last_counts", None) is not None]
+        self.experts_hit = hit
+        grouped = [r for r in recs if r["grouped"]]
         for r in recs:
-            nb = (self.args.n_routed_experts // self.world) if r["grouped"] else (r["batches"] if r["b_batched"] else 1)
+            # a grouped launch reads the planes of the experts that received a row (two launches per MoE layer)
+            nb = (hit[grouped.index(r) // 2] if r["grouped"] and len(grouped) == 2 * len(hit) else
+                  (self.args.n_routed_experts // self.world) if r["grouped"] else
+                  (r["batches"] if r["b_batched"] else 1))
             wbytes += float(nb) * r["N"] * r["K"] * r["lb"]
         self.launches_per_step = 2 * len(recs) + 40
         gbs = wbytes / (ms * 1e-3) / 1e9
         return {"bound": "hbm", "kernel": "limb_gemm kernels of one decode step (%d launches)" % len(recs),
                 "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": round(gbs / peaks["hbm_gbs"], 4), "traffic": None, "kernel_ms": round(ms, 3),
-                "weight_plane_bytes_per_step": wbytes,
+                "weight_plane_bytes_per_step": wbytes, "experts_hit_per_moe_layer": hit,
+                "launches": [{kk: (round(v, 4) if kk == "ms" else v) for kk, v in r.items()} for r in recs],
                 "note": "algorithmic bytes = limb planes of the B operand of every tensor-core launch (weights, "
-                        "all 256 experts' planes counted for the grouped launches, latent caches); peak = "
+                        "for the grouped launches the planes of the experts that received at least one row, latent caches); peak = "
                         "STREAM-style copy (%s)" % peaks["source"]}
 
     def check(self, orc):

@@ -79,6 +79,16 @@ int zkds_device_status(int clear);
                                    contents are undefined).  Only for callers that never read masked
                                    scores: zkds_softmax_causal / zkds_einsum_bsht_btc_bshc_causal. */
 
+#define ZKDS_GROUP_ROWS_32 32    /* grouped entry points (tile_group != null): the caller promises that no group */
+#define ZKDS_GROUP_ROWS_64 64    /* holds more than 32 (64) rows, i.e. only the first 32 (64) rows of every
+                                   128-row tile are tokens and the rest is padding.  The kernel then fetches
+                                   only those rows of A (decode: a few rows per expert, the weights stream
+                                   from HBM and the A tiles from L2, so a smaller A box is less L2 traffic and
+                                   a deeper pipeline); padding rows come out as zero rows do.  A tile that
+                                   breaks the promise loses its rows beyond the bound silently: callers derive
+                                   the bound from the shape (a token names an expert at most once, so a group
+                                   has at most as many rows as there are tokens). */
+
 /* =============================================================================
  * Group 1 — the reference's symbols (same names, same argument lists)
  * ========================================================================== */

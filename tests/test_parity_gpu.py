@@ -446,6 +446,60 @@ def test_grouped_expert_gemm_with_and_without_fused_gather(kmod, orc, dev):
     kmod.device_status()
 
 
+@pytest.mark.parametrize("T", [7, 32, 64])
+def test_grouped_expert_gemm_with_few_rows_per_expert(kmod, orc, dev, T):
+    """decode: every expert receives a handful of rows (at most one per token).  With the caller's bound on
+    the rows of a group the kernel fetches only the first 32 / 64 rows of every 128-row tile; the result,
+    padding rows included, is that of the launch without the bound and the oracle's, for the first expert GEMM
+    (fused gather, deep K) and for the gated down projection (zkds_glu_prepared)."""
+    rng = np.random.default_rng(50 + T)
+    E, I, Kd, k = 12, 1040, 1100, 4        # both contractions deeper than the persistent kernel takes
+    W13 = rand_i64(rng, (E, 2 * I, Kd), 15).astype(np.int32)
+    W2 = rand_i64(rng, (E, 80, I), 15).astype(np.int32)
+    x = rand_i64(rng, (T, Kd), 12)          # keeps the gated product within the three limbs promised below
+    # every token names k distinct experts; expert E-1 stays empty
+    choice = np.stack([rng.choice(E - 1, k, replace=False) for _ in range(T)])
+    row_src, tile_group = [], []
+    for e in range(E):
+        toks = np.nonzero((choice == e).any(1))[0]
+        if len(toks) == 0:
+            continue
+        assert len(toks) <= T
+        row_src += toks.tolist() + [-1] * (128 - len(toks))
+        tile_group.append(e)
+    tile_group.append(-1)
+    row_src += [-1] * 128
+    row_src, tile_group = np.array(row_src, np.int32), np.array(tile_group, np.int32)
+    sh13 = rng.integers(12, 20, (E, 2)).astype(np.int32)
+    sh2 = np.repeat(rng.integers(10, 18, (E, 1)), 2, axis=1).astype(np.int32)
+    want13 = np.zeros((len(row_src), 2 * I), np.int64)
+    want2 = np.zeros((len(row_src), 80), np.int64)
+    for i, e in enumerate(tile_group):
+        if e < 0:
+            continue
+        rows = row_src[i * 128:(i + 1) * 128]
+        xe = np.where(rows[:, None] >= 0, x[np.maximum(rows, 0)], 0)
+        lo, _ = orc.gemm(xe[None], W13[e, :I], 1, 1, int(sh13[e, 0]))
+        hi, _ = orc.gemm(xe[None], W13[e, I:], 1, 1, int(sh13[e, 1]))
+        want13[i * 128:(i + 1) * 128] = np.concatenate([lo[0], hi[0]], 1)
+        h = (orc.act(np.ascontiguousarray(lo), "silu", 23) * hi) >> 23
+        want2[i * 128:(i + 1) * 128] = orc.gemm(h, W2[e], 1, 1, int(sh2[e, 0]))[0][0]
+    p13, p2 = kmod.WeightPlanes(g(W13, dev)), kmod.WeightPlanes(g(W2, dev))
+    xd, rs, tg = g(x, dev), torch.from_numpy(row_src).to(dev), torch.from_numpy(tile_group).to(dev)
+    s13, s2 = g(sh13, dev), g(sh2, dev)
+    kmod.silu_init_q23()
+    for bound in (None, T):
+        r13 = kmod.grouped_prepared(xd, p13, tg, 0, a_limbs=3, dynamic=True, group_shift=s13, n_split=I,
+                                    row_index=rs, max_group_rows=bound)
+        same(r13, want13, "w13, bound %s" % bound)
+        out = kmod.glu_prepared(r13[:, :I], r13[:, I:], p2, 0, ld=2 * I, a_limbs=3, dynamic=True, tile_group=tg,
+                                group_shift=s2, n_split=0, max_group_rows=bound)
+        assert out is not None
+        same(out, want2, "w2, bound %s" % bound)
+    torch.cuda.synchronize()
+    kmod.device_status()
+
+
 # ---- the reference's own symbol names, and the reference's own kernels ------------------------------
 
 def test_reference_symbols_against_reference_kernels(libpath, reflib, orc, dev):

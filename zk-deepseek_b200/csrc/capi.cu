@@ -452,6 +452,7 @@ int zkds_glu_prepared(const int64_t* r1, const int64_t* r2, int64_t ld, const in
     p.group_shift = group_shift; p.n_split = n_split;
     p.glu_r2 = r2; p.glu_lut = lut;
     p.dynamic_a = (flags & ZKDS_LIMBS_DYNAMIC) ? 1 : 0;
+    p.group_rows = !tile_group ? 0 : (flags & ZKDS_GROUP_ROWS_32) ? 32 : (flags & ZKDS_GROUP_ROWS_64) ? 64 : 0;
     if (p.shift < 0) return finish(ZKDS_ERR_ARG, "zkds_glu_prepared");
     int rc = launch_contraction_limb(p, a_limbs, 0, &hd->pl, ST(stream));
     if (rc == ZKDS_ERR_UNSUPPORTED) { t_status = rc; return rc; }
@@ -496,6 +497,7 @@ static int grouped_prepared(const int64_t* A, const int* row_index, const void* 
     p.tile_group = tile_group;
     p.a_row_index = row_index;
     p.group_shift = group_shift; p.n_split = n_split;
+    p.group_rows = (flags & ZKDS_GROUP_ROWS_32) ? 32 : (flags & ZKDS_GROUP_ROWS_64) ? 64 : 0;
     int f = (flags & ~ZKDS_ALGO_MASK) | ZKDS_ALGO_LIMB;
     return finish(run_contraction(p, a_limbs, 0, f, ST(stream), &hd->pl), "zkds_grouped_prepared");
 }

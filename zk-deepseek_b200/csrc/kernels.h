@@ -98,6 +98,10 @@ struct Contraction {
     // grouped mode (limb kernel only): batches == 1, A is a flat [M, K] matrix, tile_group[i]
     // gives the B batch of the i-th 128-row tile (negative: tile skipped)
     const int* tile_group;
+    // grouped mode, 0 / 32 / 64: the caller promises that only the first 32 (64) rows of every 128-row tile
+    // hold data (no group has more rows than that); the kernel then loads only those rows of A and the other
+    // rows of a tile come out as zero rows would
+    int group_rows;
     // limb kernel only: row m of A is source row a_row_index[m] (negative: a row of zeros), so a row
     // gather needs no pass of its own
     const int* a_row_index;

@@ -576,9 +576,11 @@ struct LimbParams {
     int ksplit, kb_per_split;
     unsigned long long* partial;
     unsigned* tile_counter;
-    // one-tile kernel, M <= 64: the A box holds only a_box_rows (32 or 64) of the MMA's 128 rows, and the
-    // limb tiles lie that close together in shared memory.  The MMA still reads 128 rows per limb; what it
-    // finds beyond the box (the next limb, the B stack) lands in accumulator rows nobody stores.  0 = 128.
+    // one-tile kernel, M <= 64 or grouped tiles with at most that many rows each: the A box holds only
+    // a_box_rows (32 or 64) of the MMA's 128 rows, and the limb tiles lie that close together in shared
+    // memory.  The MMA still reads 128 rows per limb; what it finds beyond the box (the next limb, the B stack)
+    // lands in accumulator rows nobody stores (M <= 64) or that are zeroed before the epilogue reads them
+    // (grouped tiles: their padding rows are stored, as the result of zero rows).  0 = 128.
     int a_box_rows;
 };
 
@@ -1161,6 +1163,7 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int64_t* crow = p.C + z * p.c_sz + m * p.c_sm;
         int64_t* rrow = p.R ? p.R + z * p.c_sz + m * p.c_sm : nullptr;
         const bool row_ok = ok && m < p.M;
+        const bool beyond_box = p.tile_group && p.a_box_rows && q * 32 >= p.a_box_rows;
         const bool vec_ok = ((((uintptr_t)p.C | (uintptr_t)p.R) & 15) == 0) && ((p.c_sm & 1) == 0) &&
                             ((p.c_sz & 1) == 0);
         EpilogueCtx ec;
@@ -1171,6 +1174,13 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             ec.nc_end = 8 * per * (part + 1) < p.NT ? 8 * per * (part + 1) : p.NT;
         }
         ec.crow = crow; ec.rrow = rrow; ec.row_ok = row_ok; ec.vec_ok = vec_ok;
+        if (beyond_box && ok) {
+            // padding rows of a grouped tile whose A box stops short of them: the MMAs summed whatever follows
+            // the box in shared memory into these lanes.  Every warp clears the columns it is about to read.
+            for (int d = 0; d < D; ++d)
+                for (int c = ec.nc_begin; c < ec.nc_end; c += 8) tmem_st8_zero(tq + (uint32_t)(d * p.NT + c));
+            tmem_st_wait();
+        }
         bool finish = ok;
         if (p.ksplit > 1) {
             // add this CTA's share of the sums to the tile's totals (rows beyond M hold nothing)
@@ -2282,8 +2292,8 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
 
     // few rows (decode, the small-M GEMM): a smaller A box, more pipeline stages
     int a_box = kTileM;
-    if (!persistent && !p.tile_group && p.M <= 64) {
-        const int want = p.M <= 32 ? 32 : 64;
+    if (!persistent && (p.tile_group ? p.group_rows != 0 : p.M <= 64)) {
+        const int want = p.tile_group ? p.group_rows : p.M <= 32 ? 32 : 64;
         // the MMA of the last limb reads 128 rows from its tile's start: that must stay inside the stage
         if ((size_t)(kTileM - want) * kBlockK <= (size_t)Lb * NT * kBlockK) a_box = want;
     }

@@ -34,6 +34,7 @@ ALGO_AUTO, ALGO_EXACT, ALGO_LIMB = 0, 1, 2
 REMAINDER_LEGACY = 4
 LIMBS_DYNAMIC = 8
 CAUSAL_SKIP = 16
+GROUP_ROWS_32, GROUP_ROWS_64 = 32, 64
 
 # Remainder flavour of int64_bmm_broadcast.  True reproduces the reference binary:
 # exact for c_rescale <= 31, the low 32 bits of the sum above that
@@ -389,15 +390,26 @@ def einsum_heads_prepared(A, planes, rescale, rounding, a_limbs=0, dynamic=False
     return C
 
 
+def _group_rows_flag(max_rows):
+    """flag for a promised bound on the rows of every group (None or > 64: no promise)"""
+    if max_rows is None or max_rows > 64:
+        return 0
+    return GROUP_ROWS_32 if max_rows <= 32 else GROUP_ROWS_64
+
+
 def grouped_prepared(A, planes, tile_group, c_rescale, a_limbs=0, dynamic=False, group_shift=None,
-                     n_split=0, row_index=None):
+                     n_split=0, row_index=None, max_group_rows=None):
     """Routed-expert linear layer: A flat (n_tiles*128, K), tile_group int32 (n_tiles,) on the
     device (expert of each 128-row tile, negative = unused) -> C (n_tiles*128, N).
     group_shift: optional int32 (experts, 2) device tensor of per-expert shifts for the output
     columns below / from n_split; otherwise the uniform c_rescale.
     row_index: optional int32 (n_tiles*128,) device tensor; row m of the grouped matrix is then
     A[row_index[m]] (zeros where negative) and A is the un-gathered (tokens, K) matrix: the
-    index_select of model.py:1372-1378 happens inside the limb split (a_limbs must be given)."""
+    index_select of model.py:1372-1378 happens inside the limb split (a_limbs must be given).
+    max_group_rows: a bound on the rows of every group that the caller can prove (decode: a token names an
+    expert at most once, so no expert has more rows than there are tokens); up to 64 the kernel then fetches
+    only the first 32 / 64 rows of every tile."""
+    gflag = _group_rows_flag(max_group_rows)
     if group_shift is not None:
         assert group_shift.dtype == torch.int32 and group_shift.is_cuda and group_shift.is_contiguous()
     _dev_i64(A, "A")
@@ -410,7 +422,7 @@ def grouped_prepared(A, planes, tile_group, c_rescale, a_limbs=0, dynamic=False,
             assert A.shape == (n_tiles * 128, planes.K)
             _check(lib.zkds_grouped_prepared(A.data_ptr(), planes.handle, tile_group.data_ptr(), n_tiles,
                                              C.data_ptr(), 1, 0, int(c_rescale), gs, int(n_split), a_limbs,
-                                             _a_flags(a_limbs, dynamic), _stream()), "grouped_prepared")
+                                             _a_flags(a_limbs, dynamic) | gflag, _stream()), "grouped_prepared")
         else:
             assert row_index.dtype == torch.int32 and row_index.is_cuda and row_index.is_contiguous()
             assert row_index.numel() == n_tiles * 128 and A.dim() == 2 and A.shape[1] == planes.K and a_limbs > 0
@@ -419,12 +431,12 @@ def grouped_prepared(A, planes, tile_group, c_rescale, a_limbs=0, dynamic=False,
             _check(lib.zkds_grouped_gather_prepared(A.data_ptr(), row_index.data_ptr(), planes.handle,
                                                     tile_group.data_ptr(), n_tiles, C.data_ptr(), 1, 0,
                                                     int(c_rescale), gs, int(n_split), a_limbs,
-                                                    _a_flags(a_limbs, dynamic), _stream()), "grouped_prepared")
+                                                    _a_flags(a_limbs, dynamic) | gflag, _stream()), "grouped_prepared")
     return C
 
 
 def glu_prepared(r1, r2, planes, c_rescale, ld=None, a_limbs=3, dynamic=True, tile_group=None,
-                 group_shift=None, n_split=0):
+                 group_shift=None, n_split=0, max_group_rows=None):
     """w2 of a gated MLP with the gate inside its limb split: C = (h @ W2^T) >> c_rescale with
     h = (silu_q23(r1) * r2) >> 23 (model.py:1034-1049, 1271-1281); h only ever exists as int8 limb
     planes.  r1, r2: (rows, K) views sharing the row stride ld (default K); planes: prepared W2, or
@@ -447,7 +459,9 @@ def glu_prepared(r1, r2, planes, c_rescale, ld=None, a_limbs=3, dynamic=True, ti
         rc = lib.zkds_glu_prepared(r1.data_ptr(), r2.data_ptr(), ld, lut.data_ptr(), rows, planes.handle,
                                    tile_group.data_ptr() if tile_group is not None else None, C.data_ptr(),
                                    int(c_rescale), group_shift.data_ptr() if group_shift is not None else None,
-                                   int(n_split), a_limbs, _a_flags(a_limbs, dynamic), _stream())
+                                   int(n_split), a_limbs,
+                                   _a_flags(a_limbs, dynamic) | (_group_rows_flag(max_group_rows) if tile_group is not None else 0),
+                                   _stream())
     if rc == 6:
         return None
     _check(rc, "glu_prepared")

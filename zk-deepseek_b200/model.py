@@ -721,6 +721,7 @@ class MoE(nn.Module):
         # True: every rank holds its own tokens; rows travel to the experts' owners and back with
         # all-to-all, gate and shared expert run on the local tokens with whole weights.
         self.token_parallel = token_parallel
+        self.last_counts = None
         self.dim, self.moe_inter_dim = args.dim, args.moe_inter_dim
         assert args.n_routed_experts % world_size == 0
         self.n_routed_experts = args.n_routed_experts
@@ -805,20 +806,24 @@ class MoE(nn.Module):
         w13, w2, s13, s2 = self._prepared()
         lim = ACT_LIMBS if ACT_LIMBS > 0 else 5
         row_src, pos, tile_group, counts = self.route(indices, max_pairs)
+        self.last_counts = counts          # rows per local expert of the latest call (device tensor, not read here)
         I = self.moe_inter_dim
+        # a token names an expert at most once: no expert receives more rows than there are token rows
+        few = x.shape[0] if x.shape[0] <= 64 else None
         # the dispatch gather (model.py:1372-1378) runs inside the limb split of the first GEMM
         r13 = K.grouped_prepared(x.contiguous(), w13, tile_group, 0, a_limbs=lim, dynamic=True, group_shift=s13,
-                                 n_split=I, row_index=row_src)
+                                 n_split=I, row_index=row_src, max_group_rows=few)
         if snark:
             h, sl = K.glu_q23(r13[:, :I], r13[:, I:], ld=2 * I, want_silu=True)
             self._dump_experts(start_pos, r13[:, :I], sl, counts)
         else:
             out = K.glu_prepared(r13[:, :I], r13[:, I:], w2, 0, ld=2 * I, a_limbs=lim, dynamic=True,
-                                 tile_group=tile_group, group_shift=s2, n_split=0)
+                                 tile_group=tile_group, group_shift=s2, n_split=0, max_group_rows=few)
             if out is not None:
                 return K.moe_combine(out, pos, weights.contiguous(), base)
             h = K.glu_q23(r13[:, :I], r13[:, I:], ld=2 * I)
-        out = K.grouped_prepared(h, w2, tile_group, 0, a_limbs=lim, dynamic=True, group_shift=s2, n_split=0)
+        out = K.grouped_prepared(h, w2, tile_group, 0, a_limbs=lim, dynamic=True, group_shift=s2, n_split=0,
+                                 max_group_rows=few)
         return K.moe_combine(out, pos, weights.contiguous(), base)
 
     def _dump_experts(self, start_pos, r1, sl, counts):
