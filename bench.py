@@ -926,7 +926,11 @@ class MoeWorkload:
         return {"workload": self.name, "tokens": self.T, "tokens_per_gpu": self.T_local, "dim": a.dim,
                 "routed_experts": self.E, "experts_per_gpu": self.E // self.world, "top_k": 8,
                 "moe_inter_dim": a.moe_inter_dim, "shift": self.SHIFT, "gate_shift": self.GATE_SHIFT,
-                "act_limbs_bound": 3, "routing": self.routing, "useful_ops_per_step": self.ops, "weights": "resident limb planes, all experts",
+                "act_limbs_bound": 3, "routing": self.routing, "useful_ops_per_step": self.ops,
+                "exchange": ("none (one GPU)" if self.world == 1 else
+                             "peer memory: rows read in place by the owner's limb split, results stored into the "
+                             "home GPU's slots, flag barriers" if self.M.PEER_EXPERTS else
+                             "NCCL all-to-all of packed rows"), "weights": "resident limb planes, all experts",
                 "l2": "expert weights (45 GB int32) and token rows far exceed L2"}
 
     def step(self):
@@ -1573,6 +1577,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--moe-exchange", default="peer", choices=["peer", "nccl"],
+                    help="expert-parallel MoE on N > 1 GPUs: rows and results over peer memory inside the expert "
+                         "kernels (default) or NCCL all-to-all of packed rows")
+    ap.add_argument("--op-profile", default=None, metavar="FILE",
+                    help="after the timed steps, run three more under torch.profiler and write rank 0's table of "
+                         "CUDA time per operator and kernel to FILE (where a multi-rank step's time goes; the "
+                         "timed numbers are taken before it)")
     ap.add_argument("--no-extras", action="store_true",
                     help="default workload only: leave out the GEMM, small-M, reference-scale and reference-kernel parts")
     args = ap.parse_args()
@@ -1598,6 +1609,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     k = importlib.import_module(PKG + ".kernel")
     peaks = measured_peaks()
+    importlib.import_module(PKG + ".model").PEER_EXPERTS = args.moe_exchange == "peer"
     wl = WORKLOADS[args.workload](torch, k, dev, rank)
 
     def barrier():
@@ -1628,6 +1640,28 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     sec_per_step = float(t.item()) / args.steps
+
+    if args.op_profile:
+        from torch.profiler import profile, ProfilerActivity
+        barrier()
+        from torch.profiler import schedule
+        # two steps with the profiler attached but not recording (its start-up differs per rank and would
+        # show up as waiting inside the first collective), then three recorded ones
+        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA],
+                     schedule=schedule(wait=0, warmup=2, active=3)) as prof:
+            for i in range(5):
+                if i == 2:
+                    torch.cuda.synchronize()
+                    barrier()
+                wl.step()
+                if i == 4:
+                    torch.cuda.synchronize()
+                prof.step()
+        if rank == 0:
+            with open(args.op_profile, "w") as f:
+                f.write("three steps of %s on %d GPU(s), rank 0\n" % (wl.name, world))
+                f.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=25, max_name_column_width=70))
+        barrier()
 
     # ---- end to end through the drop-in module with host buffers -------------------------------
     for _ in range(3):

@@ -279,6 +279,48 @@ int zkds_glu_prepared(const int64_t* r1, const int64_t* r2, int64_t ld, const in
                       const void* planes, const int* tile_group, int64_t* C, int64_t shift,
                       const int* group_shift, int64_t n_split, int a_limbs, int flags, void* stream);
 
+/* ---- expert parallelism over peer memory (no reference counterpart: the reference sums every rank's expert
+ * outputs with a full-tensor all_reduce, model.py:1381-1382).  One process per GPU; the buffers named "of
+ * every GPU" are symmetric allocations that each process has mapped (peer pointers, plain loads and stores
+ * over NVLink, no multicast).  A layer then runs: publish the local token rows -> zkds_peer_barrier -> the
+ * owner's grouped GEMMs, whose limb split reads the rows of every GPU in place
+ * (zkds_grouped_gather_parts_prepared) -> zkds_moe_combine_peer writes each token's weighted sum into its home
+ * GPU -> zkds_peer_barrier -> zkds_moe_sum_slots on the home GPU.  No row is packed, sent or unpacked by a
+ * separate collective. */
+
+/* zkds_grouped_gather_prepared with the source rows spread over n_parts (<= 16) buffers of rows_per_part rows
+ * each (parts: host array of device pointers, e.g. the token rows of every GPU): row_index[m] = g names row
+ * g % rows_per_part of parts[g / rows_per_part]; negative or beyond the parts = a row of zeros. */
+int zkds_grouped_gather_parts_prepared(const int64_t* const* parts, int n_parts, int64_t rows_per_part,
+                                       const int* row_index, const void* planes, const int* tile_group,
+                                       int64_t n_tiles, int64_t* C, int64_t shift, const int* group_shift,
+                                       int64_t n_split, int a_limbs, int flags, void* stream);
+
+/* zkds_moe_combine for the owner of some experts: tokens = n_parts * tokens_per_part gathered tokens, pos
+ * [tokens, slots] (row of `out` for each (token, slot), -1 = expert of another GPU), w [tokens, slots].  For
+ * every token g with at least one local expert, sum_slot floor(out[pos] * w / 2^23) is stored at
+ * slot_bases[g / tokens_per_part] + ((g % tokens_per_part) * n_parts + my_part) * cols: the slot of this owner
+ * in the token's home GPU (slot_bases: host array of the n_parts GPUs' slot buffers,
+ * [tokens_per_part, n_parts, cols] int64 each, 16-byte aligned).  Other tokens' slots are not written. */
+int zkds_moe_combine_peer(const int64_t* out, const int* pos, const int64_t* w, int64_t tokens, int slots,
+                          int64_t cols, int64_t tokens_per_part, int64_t* const* slot_bases, int n_parts,
+                          int my_part, void* stream);
+
+/* The home GPU's side: y[t] = base[t] (or 0) + sum over the owners q of token t's experts, each once, of
+ * slot_rows[t][q]; q = indices[t][slot] / experts_per_part (indices [tokens, slots] int64 global expert ids).
+ * Only slots that an owner wrote in this round are read. */
+int zkds_moe_sum_slots(const int64_t* base, const int64_t* slot_rows, const int64_t* indices, int64_t tokens,
+                       int slots, int64_t cols, int n_parts, int experts_per_part, int64_t* y, void* stream);
+
+/* Barrier between the n_parts GPUs on `stream`: flag_bases[i] = GPU i's array of n_parts 64-bit flags
+ * (zero-initialised once, peer-mapped); epoch must grow by one with every call, the same on all GPUs.  Work
+ * queued before the call on any GPU is complete and visible to work queued after it on every GPU.  The wait
+ * is bounded (4 s): on expiry *status (device or mapped host word) becomes 1, the kernel returns and
+ * the caller reports the error; nothing spins for ever.  Every GPU must run its kernel concurrently, so the
+ * participants are different GPUs, never several processes on one. */
+int zkds_peer_barrier(uint64_t* const* flag_bases, int n_parts, int my_part, uint64_t epoch, uint32_t* status,
+                      void* stream);
+
 /* Replaces complex_int64_mul (int64_gemm.cu:274-286) with the product shift as a
  * parameter (the reference hard-codes 42). */
 int zkds_rope(const int64_t* A, const int64_t* table, int64_t* C, int64_t batch, int64_t seq,

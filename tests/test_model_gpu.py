@@ -231,6 +231,49 @@ def test_moe_layer_small(M, mo, kmod, dev):
     kmod.device_status()
 
 
+def test_expert_parallel_over_peer_memory_one_rank(M, mo, kmod, dev):
+    """The peer-memory expert-parallel path (rows read in place by the owner's limb split, weighted sums written
+    into the home GPU's slots, flag barriers) with a process group of one rank: this GPU is its own peer, so the
+    symmetric buffers, the multi-buffer gather, the slot write, the slot sum and the barrier kernel all run.  The
+    result is the MoE layer's and the oracle's.  More ranks: bench.py --workload moe --gpus N checks rows of the
+    actual pass against the oracle."""
+    import importlib
+    import os
+    import socket
+    import torch.distributed as dist
+    par = importlib.import_module(M.__name__.rsplit(".", 1)[0] + ".parallel")
+    a = small_args(M)
+    rng = np.random.default_rng(31)
+    p = moe_weights(rng, a, with_bias=False)
+    moe = build_moe(M, a, p, dev)
+    started = False
+    if not dist.is_initialized():
+        with socket.socket() as so:
+            so.bind(("127.0.0.1", 0))
+            port = so.getsockname()[1]
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device(dev))
+        started = True
+    try:
+        for T in (300, 40, 300):          # the second call has fewer tokens than the buffers hold
+            x = np.rint(rng.standard_normal((1, T, a.dim)) * 2.0**23).astype(np.int64)
+            xg = t(x, dev).view(-1, a.dim)
+            w_gpu, idx_gpu = moe.gate(0, xg)
+            y, _ = par.expert_parallel_forward_peer(
+                moe, kmod, 0, xg.contiguous(), w_gpu, idx_gpu,
+                before_sync=lambda: moe.shared_experts(0, xg[None]).view(-1, a.dim).contiguous())
+            want, _, _ = mo.moe_forward(p, x, a.n_expert_groups, a.n_limited_groups, a.n_activated_experts,
+                                        indices=idx_gpu.cpu().numpy())
+            same(y[None], want, "peer path, T=%d" % T)
+            same(moe(0, xg[None]), want, "single-GPU path, T=%d" % T)
+        par.peer_exchange(None, 1, a.dim, xg.device).raise_if_timed_out()
+        kmod.device_status()
+    finally:
+        if started:
+            par._exchanges.clear()
+            dist.destroy_process_group()
+
+
 def test_gate_with_bias_dim_7168(M, mo, kmod, dev):
     """the gate bias exists only for dim == 7168 (model.py:1093): grouped top-2-sum selection"""
     a = small_args(M, dim=7168, n_routed_experts=256, n_expert_groups=8, n_limited_groups=4,

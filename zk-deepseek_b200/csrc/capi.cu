@@ -715,6 +715,67 @@ int zkds_moe_combine(const int64_t* out, const int* pos, const int64_t* w, const
     return finish(rc, "zkds_moe_combine");
 }
 
+int zkds_grouped_gather_parts_prepared(const int64_t* const* parts, int n_parts, int64_t rows_per_part,
+                                       const int* row_index, const void* planes, const int* tile_group,
+                                       int64_t n_tiles, int64_t* C, int64_t shift, const int* group_shift,
+                                       int64_t n_split, int a_limbs, int flags, void* stream)
+{
+    if (!parts || n_parts < 1 || n_parts > kMaxRowParts || rows_per_part <= 0 || !row_index || !planes ||
+        !tile_group || n_tiles < 0 || a_limbs <= 0 || (group_shift && (n_split & 7)))
+        return finish(ZKDS_ERR_ARG, "zkds_grouped_gather_parts_prepared");
+    const PlanesHandle* hd = (const PlanesHandle*)planes;
+    Contraction p{};
+    p.A = parts[0]; p.B = nullptr; p.b_bits = hd->b_bits; p.C = C; p.R = nullptr;
+    p.batches = 1; p.M = n_tiles * 128; p.N = hd->pl.rows; p.K = hd->pl.K;
+    p.a_sz = 0; p.a_sm = hd->pl.K;
+    p.b_sz = 1; p.b_sn = 0; p.b_sk = 0;
+    p.c_sz = 0; p.c_sm = hd->pl.rows;
+    p.a_div = 1; p.b_div = 1;
+    p.addend = 0;
+    p.shift = (shift < 0 || shift > 127) ? -1 : (int)shift;
+    p.tile_group = tile_group;
+    p.a_row_index = row_index;
+    p.a_n_parts = n_parts; p.a_rows_per_part = rows_per_part;
+    for (int i = 0; i < n_parts; ++i) {
+        if (!parts[i]) return finish(ZKDS_ERR_ARG, "zkds_grouped_gather_parts_prepared");
+        p.a_parts[i] = parts[i];
+    }
+    p.group_shift = group_shift; p.n_split = n_split;
+    p.group_rows = (flags & ZKDS_GROUP_ROWS_32) ? 32 : (flags & ZKDS_GROUP_ROWS_64) ? 64 : 0;
+    int f = (flags & ~ZKDS_ALGO_MASK) | ZKDS_ALGO_LIMB;
+    return finish(run_contraction(p, a_limbs, 0, f, ST(stream), &hd->pl), "zkds_grouped_gather_parts_prepared");
+}
+
+int zkds_moe_combine_peer(const int64_t* out, const int* pos, const int64_t* w, int64_t tokens, int slots,
+                          int64_t cols, int64_t tokens_per_part, int64_t* const* slot_bases, int n_parts,
+                          int my_part, void* stream)
+{
+    int rc = (tokens < 0 || cols < 0 || !slot_bases || (tokens && cols && (!out || !pos || !w)))
+                 ? ZKDS_ERR_ARG
+                 : launch_moe_combine_peer(out, pos, w, tokens, slots, cols, tokens_per_part, slot_bases, n_parts,
+                                           my_part, ST(stream));
+    return finish(rc, "zkds_moe_combine_peer");
+}
+
+int zkds_moe_sum_slots(const int64_t* base, const int64_t* slot_rows, const int64_t* indices, int64_t tokens,
+                       int slots, int64_t cols, int n_parts, int experts_per_part, int64_t* y, void* stream)
+{
+    int rc = (tokens < 0 || cols < 0 || (tokens && cols && (!slot_rows || !indices || !y)))
+                 ? ZKDS_ERR_ARG
+                 : launch_moe_sum_slots(base, slot_rows, indices, tokens, slots, cols, n_parts, experts_per_part, y,
+                                        ST(stream));
+    return finish(rc, "zkds_moe_sum_slots");
+}
+
+int zkds_peer_barrier(uint64_t* const* flag_bases, int n_parts, int my_part, uint64_t epoch, uint32_t* status,
+                      void* stream)
+{
+    int rc = !flag_bases ? ZKDS_ERR_ARG
+                         : launch_peer_barrier((unsigned long long* const*)flag_bases, n_parts, my_part,
+                                               (unsigned long long)epoch, (unsigned*)status, ST(stream));
+    return finish(rc, "zkds_peer_barrier");
+}
+
 int zkds_gate_select(const int64_t* sigma, const int32_t* bias, int64_t tokens, int experts, int n_groups,
                      int topk_groups, int topk, int64_t* indices, int64_t* raw_weights, int64_t* weights, void* stream)
 {

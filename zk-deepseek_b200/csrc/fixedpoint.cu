@@ -1243,6 +1243,155 @@ int launch_moe_combine(const int64_t* out, const int* pos, const int64_t* w, con
 }
 
 // ------------------------------------------------------------------------------
+// expert parallelism over peer memory: the owner of a token's experts writes the weighted sum of their outputs
+// straight into the token's home GPU, one slot per (token, owner); the home GPU adds the slots it expects
+// ------------------------------------------------------------------------------
+struct PeerSlots {
+    int64_t* base[kMaxRowParts];
+};
+
+// token g = part * tokens_per_part + t of the gathered batch; rows with no local expert are not touched.
+// slot row of (t, my_part) on the home GPU: base[part] + (t * n_parts + my_part) * cols.
+__global__ void __launch_bounds__(kThreads)
+moe_combine_peer_kernel(const longlong2* __restrict__ out, const int* __restrict__ pos, const int64_t* __restrict__ w,
+                        int slots, int64_t cols2, int64_t tokens_per_part, int n_parts, int my_part,
+                        const PeerSlots peers)
+{
+    const int64_t g = blockIdx.x;
+    __shared__ int s_any;
+    if (threadIdx.x == 0) {
+        int any = 0;
+        for (int s = 0; s < slots; ++s) any |= pos[g * slots + s] >= 0;
+        s_any = any;
+    }
+    __syncthreads();
+    if (!s_any) return;
+    const int64_t part = g / tokens_per_part, t = g - part * tokens_per_part;
+    if (part >= n_parts) return;
+    longlong2* dst = reinterpret_cast<longlong2*>(peers.base[part]) + (t * n_parts + my_part) * cols2;
+    for (int64_t c = threadIdx.x; c < cols2; c += kThreads) {
+        longlong2 acc = make_longlong2(0, 0);
+        for (int s = 0; s < slots; ++s) {
+            const int r = pos[g * slots + s];
+            if (r < 0) continue;
+            const int64_t ws = w[g * slots + s];
+            const longlong2 v = out[(int64_t)r * cols2 + c];
+            acc.x = (int64_t)((uint64_t)acc.x + (uint64_t)((int64_t)((uint64_t)v.x * (uint64_t)ws) >> 23));
+            acc.y = (int64_t)((uint64_t)acc.y + (uint64_t)((int64_t)((uint64_t)v.y * (uint64_t)ws) >> 23));
+        }
+        dst[c] = acc;
+    }
+}
+
+int launch_moe_combine_peer(const int64_t* out, const int* pos, const int64_t* w, int64_t tokens, int slots,
+                            int64_t cols, int64_t tokens_per_part, int64_t* const* slot_bases, int n_parts,
+                            int my_part, cudaStream_t st)
+{
+    if (tokens == 0 || cols == 0) return ZKDS_OK;
+    if ((cols & 1) || tokens > 0x7fffffffll || n_parts < 1 || n_parts > kMaxRowParts || my_part < 0 ||
+        my_part >= n_parts || tokens_per_part <= 0 || tokens > tokens_per_part * n_parts || slots < 1 ||
+        (((uintptr_t)out) & 15) != 0)
+        return ZKDS_ERR_ARG;
+    PeerSlots peers{};
+    for (int i = 0; i < n_parts; ++i) {
+        if (!slot_bases[i] || (((uintptr_t)slot_bases[i]) & 15) != 0) return ZKDS_ERR_ARG;
+        peers.base[i] = slot_bases[i];
+    }
+    moe_combine_peer_kernel<<<(unsigned)tokens, kThreads, 0, st>>>(
+        reinterpret_cast<const longlong2*>(out), pos, w, slots, cols / 2, tokens_per_part, n_parts, my_part, peers);
+    return check_launch();
+}
+
+// y[t] = base[t] + sum over the owners q of token t's experts (each owner once) of slot_rows[t][q]
+__global__ void __launch_bounds__(kThreads)
+moe_sum_slots_kernel(const longlong2* __restrict__ base, const longlong2* __restrict__ slot_rows,
+                     const int64_t* __restrict__ indices, int slots, int64_t cols2, int n_parts,
+                     int experts_per_part, longlong2* __restrict__ y)
+{
+    const int64_t t = blockIdx.x;
+    __shared__ unsigned s_owners;
+    if (threadIdx.x == 0) {
+        unsigned m = 0;
+        for (int s = 0; s < slots; ++s) {
+            const int64_t e = indices[t * slots + s];
+            const int64_t q = e >= 0 ? e / experts_per_part : -1;
+            if (q >= 0 && q < n_parts) m |= 1u << q;
+        }
+        s_owners = m;
+    }
+    __syncthreads();
+    const unsigned owners = s_owners;
+    const longlong2* rows = slot_rows + t * n_parts * cols2;
+    for (int64_t c = threadIdx.x; c < cols2; c += kThreads) {
+        longlong2 acc = base ? base[t * cols2 + c] : make_longlong2(0, 0);
+        for (int q = 0; q < n_parts; ++q) {
+            if (!((owners >> q) & 1u)) continue;
+            const longlong2 v = rows[q * cols2 + c];
+            acc.x = (int64_t)((uint64_t)acc.x + (uint64_t)v.x);
+            acc.y = (int64_t)((uint64_t)acc.y + (uint64_t)v.y);
+        }
+        y[t * cols2 + c] = acc;
+    }
+}
+
+int launch_moe_sum_slots(const int64_t* base, const int64_t* slot_rows, const int64_t* indices, int64_t tokens,
+                         int slots, int64_t cols, int n_parts, int experts_per_part, int64_t* y, cudaStream_t st)
+{
+    if (tokens == 0 || cols == 0) return ZKDS_OK;
+    if ((cols & 1) || tokens > 0x7fffffffll || n_parts < 1 || n_parts > kMaxRowParts || experts_per_part < 1 ||
+        slots < 1 || ((((uintptr_t)base | (uintptr_t)slot_rows | (uintptr_t)y) & 15) != 0))
+        return ZKDS_ERR_ARG;
+    moe_sum_slots_kernel<<<(unsigned)tokens, kThreads, 0, st>>>(
+        reinterpret_cast<const longlong2*>(base), reinterpret_cast<const longlong2*>(slot_rows), indices, slots,
+        cols / 2, n_parts, experts_per_part, reinterpret_cast<longlong2*>(y));
+    return check_launch();
+}
+
+// Barrier between the GPUs of one node over peer-mapped flag words.  Every GPU owns n_parts 64-bit flags;
+// GPU i announces epoch e by storing e into flag i of every GPU (its own included) and then waits until all
+// of its own flags have reached e.  Epochs only grow, so a flag never has to be reset.  The wait is bounded
+// (four seconds of the global timer): when it runs out the kernel sets *status and returns, the stream
+// carries on with whatever data is there and the host reports the error from the status word.
+struct PeerFlags {
+    unsigned long long* base[kMaxRowParts];
+};
+
+__global__ void __launch_bounds__(32)
+peer_barrier_kernel(const PeerFlags peers, int n_parts, int my_part, unsigned long long epoch, unsigned* status)
+{
+    const int i = threadIdx.x;
+    if (i < n_parts) {
+        // the writes of every earlier kernel of this stream are ordered before the announcement
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(peers.base[i] + my_part), "l"(epoch) : "memory");
+        const unsigned long long* mine = peers.base[my_part] + i;
+        unsigned long long t0, now, seen = 0;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        for (;;) {
+            asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(mine) : "memory");
+            if (seen >= epoch) break;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (now - t0 > 4000000000ull) { atomicExch(status, 1u); break; }
+            __nanosleep(200);
+        }
+        __threadfence_system();
+    }
+}
+
+int launch_peer_barrier(unsigned long long* const* flag_bases, int n_parts, int my_part, unsigned long long epoch,
+                        unsigned* status, cudaStream_t st)
+{
+    if (n_parts < 1 || n_parts > kMaxRowParts || my_part < 0 || my_part >= n_parts || !status) return ZKDS_ERR_ARG;
+    PeerFlags peers{};
+    for (int i = 0; i < n_parts; ++i) {
+        if (!flag_bases[i] || (((uintptr_t)flag_bases[i]) & 7) != 0) return ZKDS_ERR_ARG;
+        peers.base[i] = flag_bases[i];
+    }
+    peer_barrier_kernel<<<1, 32, 0, st>>>(peers, n_parts, my_part, epoch, status);
+    return check_launch();
+}
+
+// ------------------------------------------------------------------------------
 // gate: bias, grouped top-k selection, weights (Gate.forward, model.py:1140-1211), one warp per token
 // ------------------------------------------------------------------------------
 // scores = sigma + bias; per group the sum of its two largest scores (the largest when there is no bias);

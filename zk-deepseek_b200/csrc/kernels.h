@@ -65,6 +65,15 @@ int launch_gate_select(const int64_t* sig, const int32_t* bias, int64_t T, int E
                        int topk, int64_t* indices, int64_t* raw, int64_t* w, cudaStream_t st);
 int launch_moe_combine(const int64_t* out, const int* pos, const int64_t* w, const int64_t* base,
                        int64_t* y, int64_t tokens, int slots, int64_t cols, cudaStream_t st);
+// expert parallelism over peer memory (see include/zkds_int64.h)
+constexpr int kMaxRowParts = 16;
+int launch_moe_combine_peer(const int64_t* out, const int* pos, const int64_t* w, int64_t tokens, int slots,
+                            int64_t cols, int64_t tokens_per_part, int64_t* const* slot_bases, int n_parts,
+                            int my_part, cudaStream_t st);
+int launch_moe_sum_slots(const int64_t* base, const int64_t* slot_rows, const int64_t* indices, int64_t tokens,
+                         int slots, int64_t cols, int n_parts, int experts_per_part, int64_t* y, cudaStream_t st);
+int launch_peer_barrier(unsigned long long* const* flag_bases, int n_parts, int my_part, unsigned long long epoch,
+                        unsigned* status, cudaStream_t st);
 
 // ---- contractions ---------------------------------------------------------------
 // One batched contraction  C[z][m][n] = (addend + sum_k A(z,m,k) * B(z,n,k)) >> shift
@@ -105,6 +114,13 @@ struct Contraction {
     // limb kernel only: row m of A is source row a_row_index[m] (negative: a row of zeros), so a row
     // gather needs no pass of its own
     const int* a_row_index;
+    // with a_row_index: the source rows lie in a_n_parts (<= kMaxRowParts) pieces of a_rows_per_part rows each
+    // (piece i at a_parts[i], which may be another GPU's memory mapped into this process): row g is row
+    // g % a_rows_per_part of piece g / a_rows_per_part; an index beyond the pieces reads as a row of zeros.
+    // 0 pieces: all rows at A.
+    const void* a_parts[16];
+    int a_n_parts;
+    int64_t a_rows_per_part;
     // grouped mode: shift per group, [2g] for columns < n_split, [2g+1] from n_split on (values in
     // 0..127, n_split a multiple of 8); null = the uniform shift
     const int* group_shift;

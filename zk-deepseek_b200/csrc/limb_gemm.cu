@@ -133,13 +133,21 @@ split_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, int64_
 // The k-contiguous case of split_kernel without any integer division: a CTA of 256 threads is a
 // (256 / tpr) x tpr grid, tpr = threads per row (a power of two), and walks whole rows; every
 // thread converts four consecutive k per step, two steps in flight.
+// source rows spread over several buffers (expert parallelism: the token rows of every rank, read in place over
+// peer mappings): row g of the gathered matrix is row g % rows_per_part of base[g / rows_per_part]
+struct RowParts {
+    const void* base[kMaxRowParts];
+    int n;
+    int64_t rows_per_part;
+};
+
 template <typename T, int LL>     // LL: limb count known at compile time, 0 = use L
 __global__ void __launch_bounds__(256)
 split_rows_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, int64_t rows, int64_t K,
                   int64_t Kp, int64_t sz, int64_t sr, int64_t div, int64_t plane_stride,
                   unsigned* overflow, unsigned long long* absmax_out, int64_t dst_pitch, int64_t valid_H,
                   int64_t valid_start, int tpr_log2, unsigned nb, unsigned gx, int z_fast, int shl,
-                  const int* __restrict__ row_index, unsigned kseg, int64_t seg_quads)
+                  const int* __restrict__ row_index, unsigned kseg, int64_t seg_quads, const RowParts parts)
 {
     uint64_t seen = 0;
     bool ovf = false;
@@ -150,7 +158,8 @@ split_rows_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, i
     const int tpr = 1 << tpr_log2;
     const int lane_q = threadIdx.x & (tpr - 1);
     const int64_t rpb = 256 >> tpr_log2;
-    const bool vec = sizeof(T) == 8 && ((((uintptr_t)X) & 15) == 0) && ((sr & 1) == 0) && ((sz & 1) == 0);
+    bool vec = sizeof(T) == 8 && ((((uintptr_t)X) & 15) == 0) && ((sr & 1) == 0) && ((sz & 1) == 0);
+    for (int i = 0; i < parts.n; ++i) vec = vec && (((uintptr_t)parts.base[i]) & 15) == 0;
     // few rows (decode): a row is cut into kseg segments of seg_quads quads so that the launch still has
     // a CTA for every SM
     const unsigned items = nb * gx * kseg;
@@ -177,6 +186,13 @@ split_rows_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, i
             if (rs < 0) Kv = 0;
         }
         const T* xr = x + (rs < 0 ? 0 : rs) * sr;
+        if (parts.n && rs >= 0) {
+            const int64_t part = rs / parts.rows_per_part;
+            if (part < parts.n)
+                xr = reinterpret_cast<const T*>(parts.base[part]) + (rs - part * parts.rows_per_part) * sr;
+            else
+                Kv = 0;             // an index beyond the pieces: zeros, never an address outside them
+        }
         int8_t* drow = planes + (z * rows + r) * dst_pitch;
 #pragma unroll 2
         for (int64_t qd = q_begin + lane_q; qd < q_end; qd += tpr) {
@@ -1915,9 +1931,13 @@ template <typename T>
 int launch_split_t(const T* X, int8_t* planes, int L, int64_t nb, int64_t rows, int64_t K, int64_t Kp,
                    int64_t sz, int64_t sr, int64_t sk, int64_t div, unsigned* overflow, cudaStream_t st,
                    unsigned long long* absmax_out = nullptr, int64_t dst_pitch = 0, int64_t valid_H = 0,
-                   int64_t valid_start = 0, int shl = 0, const int* row_index = nullptr)
+                   int64_t valid_start = 0, int shl = 0, const int* row_index = nullptr,
+                   const RowParts* row_parts = nullptr)
 {
     if (dst_pitch == 0) dst_pitch = Kp;
+    RowParts parts{};
+    if (row_parts) parts = *row_parts;
+    if (parts.n && (!row_index || sk != 1 || switches().split_generic)) return ZKDS_ERR_UNSUPPORTED;
     int64_t total = rows * (Kp >> 2);
     int64_t bx = (total + 255) / 256;
     int64_t cap = (int64_t)sm_count() * 32;
@@ -1945,7 +1965,7 @@ int launch_split_t(const T* X, int8_t* planes, int L, int64_t nb, int64_t rows, 
     split_rows_kernel<T, LL><<<g2, 256, 0, st>>>(X, planes, L, rows, K, Kp, sz, sr, div,                  \
                                                  nb * rows * dst_pitch, overflow, absmax_out, dst_pitch, \
                                                  valid_H, valid_start, tl, (unsigned)nb, (unsigned)gx, z_fast, shl, \
-                                                 row_index, (unsigned)kseg, seg_quads)
+                                                 row_index, (unsigned)kseg, seg_quads, parts)
         switch (L) {
         case 2: ZKDS_SPLIT_ROWS(2); break;
         case 3: ZKDS_SPLIT_ROWS(3); break;
@@ -2276,10 +2296,18 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
         if (p.batches != 1 || p.a_div != 1 || p.a_row_index || !p.glu_r2) return ZKDS_ERR_ARG;
         rc = launch_glu_planes(p.A, p.glu_r2, p.a_sm, p.glu_lut, pa, La, a_rows, p.K, Kp, a_rows * Kp,
                                fl->overflow_dev, d_absmax, st);
-    } else
+    } else {
+        RowParts parts{};
+        if (p.a_n_parts > 0) {
+            if (p.a_n_parts > kMaxRowParts || p.a_rows_per_part <= 0 || !p.a_row_index) return ZKDS_ERR_ARG;
+            parts.n = p.a_n_parts;
+            parts.rows_per_part = p.a_rows_per_part;
+            for (int i = 0; i < parts.n; ++i) parts.base[i] = p.a_parts[i];
+        }
         rc = launch_split_t<int64_t>(p.A, pa, La, p.batches, p.M, p.K, Kp16, p.a_sz, p.a_sm, 1, p.a_div,
                                      fl->overflow_dev, st, d_absmax, 0, p.skip_k ? p.skip_H : 0, p.skip_start, 0,
-                                     p.a_row_index);
+                                     p.a_row_index, parts.n ? &parts : nullptr);
+    }
     if (rc != ZKDS_OK) return rc;
     int8_t* pb;
     if (pre_b) pb = pre_b->data;

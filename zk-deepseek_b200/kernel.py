@@ -108,6 +108,10 @@ _sig("zkds_glu_q23", [_vp, _vp, _ll, _vp, _vp, _vp, _ll, _ll, _vp])
 _sig("zkds_gather_rows", [_vp, _vp, _vp, _ll, _ll, _vp])
 _sig("zkds_moe_combine", [_vp, _vp, _vp, _vp, _vp, _ll, _i, _ll, _vp])
 _sig("zkds_gate_select", [_vp, _vp, _ll, _i, _i, _i, _i, _vp, _vp, _vp, _vp])
+_sig("zkds_grouped_gather_parts_prepared", [_vp, _i, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _ll, _i, _i, _vp])
+_sig("zkds_moe_combine_peer", [_vp, _vp, _vp, _ll, _i, _ll, _ll, _vp, _i, _i, _vp])
+_sig("zkds_moe_sum_slots", [_vp, _vp, _vp, _ll, _i, _ll, _i, _i, _vp, _vp])
+_sig("zkds_peer_barrier", [_vp, _i, _i, ctypes.c_ulonglong, _vp, _vp])
 _sig("zkds_contraction_prepared", [_vp, _ll, _ll, _vp, _i, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _ll,
                                    _i, _i, _vp])
 
@@ -638,6 +642,74 @@ def moe_combine(out, pos, w, base=None):
                                     base.data_ptr() if base is not None else None, y.data_ptr(), tokens,
                                     slots, cols, _stream()), "moe_combine")
     return y
+
+
+# ---- expert parallelism over peer memory ------------------------------------------------
+
+def _ptr_array(ptrs):
+    return (ctypes.c_void_p * len(ptrs))(*[int(p_) for p_ in ptrs])
+
+
+def grouped_gather_parts_prepared(part_ptrs, rows_per_part, row_index, planes, tile_group, c_rescale, a_limbs,
+                                  dynamic=True, group_shift=None, n_split=0, max_group_rows=None):
+    """grouped_prepared(row_index=...) whose source rows lie in len(part_ptrs) buffers of rows_per_part rows
+    each (device addresses; the token rows of every GPU, read in place): row_index[m] = g names row
+    g % rows_per_part of buffer g // rows_per_part.  The caller keeps the buffers alive and synchronised."""
+    assert row_index.dtype == torch.int32 and row_index.is_cuda and row_index.is_contiguous()
+    assert tile_group.dtype == torch.int32 and tile_group.is_cuda and tile_group.is_contiguous()
+    n_tiles = tile_group.numel()
+    assert row_index.numel() == n_tiles * 128 and a_limbs > 0
+    if group_shift is not None:
+        assert group_shift.dtype == torch.int32 and group_shift.is_cuda and group_shift.is_contiguous()
+    C = torch.empty((n_tiles * 128, planes.N), dtype=torch.int64, device=row_index.device)
+    with _on(row_index.device):
+        _check(lib.zkds_grouped_gather_parts_prepared(
+            _ptr_array(part_ptrs), len(part_ptrs), int(rows_per_part), row_index.data_ptr(), planes.handle,
+            tile_group.data_ptr(), n_tiles, C.data_ptr(), int(c_rescale),
+            group_shift.data_ptr() if group_shift is not None else None, int(n_split), a_limbs,
+            _a_flags(a_limbs, dynamic) | _group_rows_flag(max_group_rows), _stream()), "grouped_gather_parts_prepared")
+    return C
+
+
+def moe_combine_peer(out, pos, w, tokens_per_part, slot_ptrs, my_part):
+    """the owner's half of the combine: for every gathered token with a local expert, the weighted sum of its
+    local experts' rows goes to slot (token, my_part) of the token's home GPU (slot_ptrs: device addresses of
+    the GPUs' [tokens_per_part, parts, cols] slot buffers)."""
+    _dev_i64(out, "out")
+    _dev_i64(w, "w")
+    assert pos.dtype == torch.int32 and pos.is_cuda and pos.is_contiguous()
+    tokens, slots = pos.shape
+    with _on(out.device):
+        _check(lib.zkds_moe_combine_peer(out.data_ptr(), pos.data_ptr(), w.data_ptr(), tokens, slots, out.shape[-1],
+                                         int(tokens_per_part), _ptr_array(slot_ptrs), len(slot_ptrs), int(my_part),
+                                         _stream()), "moe_combine_peer")
+
+
+def moe_sum_slots(base, slot_rows, indices, experts_per_part):
+    """the home GPU's half: y[t] = base[t] + the slots of the owners of token t's experts
+    (slot_rows [tokens, parts, cols], indices [tokens, k] int64 global expert ids)."""
+    _dev_i64(slot_rows, "slot_rows")
+    _dev_i64(indices, "indices")
+    tokens, parts, cols = slot_rows.shape
+    assert indices.shape[0] == tokens
+    if base is not None:
+        _dev_i64(base, "base")
+        assert base.shape == (tokens, cols)
+    y = torch.empty((tokens, cols), dtype=torch.int64, device=slot_rows.device)
+    with _on(slot_rows.device):
+        _check(lib.zkds_moe_sum_slots(base.data_ptr() if base is not None else None, slot_rows.data_ptr(),
+                                      indices.data_ptr(), tokens, indices.shape[1], cols, parts,
+                                      int(experts_per_part), y.data_ptr(), _stream()), "moe_sum_slots")
+    return y
+
+
+def peer_barrier(flag_ptrs, my_part, epoch, status):
+    """barrier between the GPUs on the current stream (flag_ptrs: device addresses of every GPU's flag array;
+    status: int32 device tensor that becomes 1 if the bounded wait ran out)."""
+    assert status.dtype == torch.int32 and status.is_cuda
+    with _on(status.device):
+        _check(lib.zkds_peer_barrier(_ptr_array(flag_ptrs), len(flag_ptrs), int(my_part), int(epoch),
+                                     status.data_ptr(), _stream()), "peer_barrier")
 
 
 # ---- RoPE ----------------------------------------------------------------------------

@@ -66,6 +66,9 @@ CHECK_STATUS = True
 # torch ops.  Same experts and weights; under score ties the kernel takes the lower index, which is the set
 # torch.topk takes, while the ORDER torch gives equal scores is unspecified (False keeps the torch ops).
 FUSED_GATE = True
+# token-parallel MoE on GPUs of one node: rows and results move over peer memory inside the expert kernels
+# (parallel.expert_parallel_forward_peer); False = NCCL all-to-all of packed rows
+PEER_EXPERTS = True
 
 
 @dataclass
@@ -801,18 +804,28 @@ class MoE(nn.Module):
         tile_group = torch.where(tile_start < pad_end[-1], g, torch.full_like(g, -1)).to(torch.int32)
         return row_src, pos.view(T, k), tile_group, counts
 
-    def experts_forward(self, start_pos, x, weights, indices, base=None, max_pairs=None):
-        """sum over the local experts of expert(x) * w // 2^23, added to `base`"""
+    def experts_forward(self, start_pos, x, weights, indices, base=None, max_pairs=None, parts=None, combine=None):
+        """sum over the local experts of expert(x) * w // 2^23, added to `base`.
+        parts = (device addresses, rows per buffer): the token rows lie in several buffers (every rank's rows,
+        read in place; `indices` then covers all of them) instead of x.  combine(out, pos): what to do with the
+        experts' output rows instead of the local weighted sum."""
         w13, w2, s13, s2 = self._prepared()
         lim = ACT_LIMBS if ACT_LIMBS > 0 else 5
         row_src, pos, tile_group, counts = self.route(indices, max_pairs)
         self.last_counts = counts          # rows per local expert of the latest call (device tensor, not read here)
         I = self.moe_inter_dim
         # a token names an expert at most once: no expert receives more rows than there are token rows
-        few = x.shape[0] if x.shape[0] <= 64 else None
+        n_rows = indices.shape[0]
+        few = n_rows if n_rows <= 64 else None
+        finish = combine if combine is not None else (
+            lambda out, pos: K.moe_combine(out, pos, weights.contiguous(), base))
         # the dispatch gather (model.py:1372-1378) runs inside the limb split of the first GEMM
-        r13 = K.grouped_prepared(x.contiguous(), w13, tile_group, 0, a_limbs=lim, dynamic=True, group_shift=s13,
-                                 n_split=I, row_index=row_src, max_group_rows=few)
+        if parts is not None:
+            r13 = K.grouped_gather_parts_prepared(parts[0], parts[1], row_src, w13, tile_group, 0, a_limbs=lim,
+                                                  dynamic=True, group_shift=s13, n_split=I, max_group_rows=few)
+        else:
+            r13 = K.grouped_prepared(x.contiguous(), w13, tile_group, 0, a_limbs=lim, dynamic=True, group_shift=s13,
+                                     n_split=I, row_index=row_src, max_group_rows=few)
         if snark:
             h, sl = K.glu_q23(r13[:, :I], r13[:, I:], ld=2 * I, want_silu=True)
             self._dump_experts(start_pos, r13[:, :I], sl, counts)
@@ -820,11 +833,11 @@ class MoE(nn.Module):
             out = K.glu_prepared(r13[:, :I], r13[:, I:], w2, 0, ld=2 * I, a_limbs=lim, dynamic=True,
                                  tile_group=tile_group, group_shift=s2, n_split=0, max_group_rows=few)
             if out is not None:
-                return K.moe_combine(out, pos, weights.contiguous(), base)
+                return finish(out, pos)
             h = K.glu_q23(r13[:, :I], r13[:, I:], ld=2 * I)
         out = K.grouped_prepared(h, w2, tile_group, 0, a_limbs=lim, dynamic=True, group_shift=s2, n_split=0,
                                  max_group_rows=few)
-        return K.moe_combine(out, pos, weights.contiguous(), base)
+        return finish(out, pos)
 
     def _dump_experts(self, start_pos, r1, sl, counts):
         d = _dump_dir(start_pos, self.layer_id)
@@ -843,6 +856,13 @@ class MoE(nn.Module):
             from . import parallel
             x2 = x.view(-1, self.dim)
             weights, indices = self.gate(start_pos, x2)
+            if PEER_EXPERTS and x2.is_cuda and not snark:
+                # rows read and results written over peer memory by the expert kernels themselves; the shared
+                # expert runs while the pair count travels to the host and is added by the slot sum
+                y, _ = parallel.expert_parallel_forward_peer(
+                    self, K, start_pos, x2.contiguous(), weights, indices,
+                    before_sync=lambda: self.shared_experts(start_pos, x).view(-1, self.dim).contiguous())
+                return y.view(shape)
             # the shared expert runs while the dispatch counts travel to the host
             y, z = parallel.expert_parallel_forward(self, start_pos, x2, weights, indices,
                                                     before_sync=lambda: self.shared_experts(start_pos, x))
