@@ -930,7 +930,8 @@ class MoeWorkload:
                 "exchange": ("none (one GPU)" if self.world == 1 else
                              "peer memory: rows read in place by the owner's limb split, results stored into the "
                              "home GPU's slots, flag barriers" if self.M.PEER_EXPERTS else
-                             "NCCL all-to-all of packed rows"), "weights": "resident limb planes, all experts",
+                             "NCCL all-to-all of packed rows"),
+                "exchange_check": getattr(self, "paths_compared", None), "weights": "resident limb planes, all experts",
                 "l2": "expert weights (45 GB int32) and token rows far exceed L2"}
 
     def step(self):
@@ -988,7 +989,22 @@ class MoeWorkload:
         shared expert and its eight routed experts.  The GPU's expert choice is passed on so that a score tie
         cannot make the two differ."""
         np, a, moe = self.np, self.args, self.moe
-        got_all = self.step()                   # with N > 1 every rank joins the all-to-all here
+        got_all = self.step()                   # with N > 1 every rank joins the exchange here
+        extra_bad = 0
+        if self.world > 1 and self.M.PEER_EXPERTS:
+            # the two exchanges must agree on every word of every rank's output
+            import torch.distributed as dist
+            self.M.PEER_EXPERTS = False
+            try:
+                other = self.step()
+            finally:
+                self.M.PEER_EXPERTS = True
+            bad = (other != got_all).sum().to(self.torch.int64).reshape(1)
+            dist.all_reduce(bad)
+            extra_bad = int(bad.item())
+            self.paths_compared = ("outputs of the peer-memory and the NCCL all-to-all exchange compared word for "
+                                   "word on every rank: %d differ" % extra_bad)
+            del other
         if orc is None:
             return None
         from oracle import model_oracle as mo
@@ -1012,7 +1028,7 @@ class MoeWorkload:
                       "bias": moe.gate.bias.cpu().numpy()},
              "shared": mlp(moe.shared_experts), "experts": experts}
         want, _, _ = mo.moe_forward(p, xs.cpu().numpy(), 8, 4, 8, indices=idx)
-        return int((got != want).sum())
+        return int((got != want).sum()) + extra_bad
 
     @staticmethod
     def cpu_sample(orc, np, seconds, rank=0):
