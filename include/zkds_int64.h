@@ -248,6 +248,34 @@ int zkds_softmax_pv(const int64_t* scores, const int64_t* KV, int64_t* out, cons
                     int64_t rescale, int64_t B, int64_t S, int64_t H, int64_t T, int64_t C, int causal_skip,
                     int64_t start_pos, int a_limbs, int b_limbs, int flags, void* stream);
 
+/* ---- the latent cache kept as limb planes (decode) ---------------------------------------------------------
+ * The reference's attention reads the whole int64 latent cache every step (model.py:884-926); split into limb
+ * planes per call, that is the whole cache re-read and re-written twice per layer and step.  These entry
+ * points keep the planes resident instead: each step splits only its new positions, and the score and P . KV
+ * contractions read the planes in place.  No reference counterpart.
+ *   score planes [limbs][B][capacity][C1 + round16(C2)] int8   (a position is a row: latent | rope part)
+ *   value planes [limbs][B][C1][capacity] int8                 (a position is a column)
+ * capacity: positions the buffers hold, a multiple of 16; both buffers 16-byte aligned, allocated by the caller
+ * (zero-initialised: the padding columns of the score planes are never written).  `limbs` is a promise like
+ * a_limbs / b_limbs elsewhere: a value that does not fit raises the flag zkds_device_status reports. */
+int zkds_cache_planes_append(const int64_t* kv_new, const int64_t* pe_new, int8_t* score_planes,
+                             int8_t* value_planes, int64_t B, int64_t S, int64_t C1, int64_t C2,
+                             int64_t start_pos, int64_t capacity, int limbs, void* stream);
+
+/* zkds_mla_scores with the cache side (kv, pe) given as resident score planes holding positions [0, T);
+ * b_limbs = the planes' limb count, a_limbs > 0. */
+int zkds_mla_scores_cached(const int64_t* q_abs, const int64_t* q_pe, const int8_t* score_planes,
+                           int64_t capacity, int64_t* out, int64_t B, int64_t S, int64_t H, int64_t T,
+                           int64_t C1, int64_t C2, int64_t rescale1, int64_t rescale2, int64_t ep_mul,
+                           int64_t ep_div, int causal, int64_t start_pos, int64_t mask_value, int a_limbs,
+                           int b_limbs, int flags, void* stream);
+
+/* zkds_softmax_pv with KV given as resident value planes holding positions [0, T). */
+int zkds_softmax_pv_cached(const int64_t* scores, const int8_t* value_planes, int64_t capacity, int64_t* out,
+                           const int64_t* lut, int64_t rescale, int64_t B, int64_t S, int64_t H, int64_t T,
+                           int64_t C, int causal_skip, int64_t start_pos, int a_limbs, int b_limbs, int flags,
+                           void* stream);
+
 /* Grouped linear layer for the routed experts (replaces the per-expert Python loop of
  * MoE.forward, model.py:1355-1379): A is a flat [n_tiles*128, K] int64 matrix whose i-th
  * 128-row tile holds tokens of expert tile_group[i] (device array; negative = unused tile),

@@ -165,6 +165,68 @@ def test_mla_prefill_with_masked_half_skipped(M, mo, kmod, dev):
     kmod.device_status()
 
 
+def test_mla_decode_reads_resident_cache_planes(M, mo, kmod, dev):
+    """Decode steps read the latent cache from resident limb planes (one new position split per step, score
+    rows padded to four columns, the padding never read).  Against the oracle: a prefill, then single-token steps
+    through every residue of the position modulo 4, a two-token step (leaves the planes, marks its positions
+    stale), more single-token steps (the stale positions are split again), a second prefill from position 0 and
+    another decode step; and with batch 3, where every sequence has its own cache row."""
+    a = small_args(M, kv_lora_rank=128, n_heads=8)
+    rng = np.random.default_rng(21)
+    p = mla_weights(rng, a)
+    freqs = freqs_table(M, a)
+    taken = []
+    plain = kmod.CachePlanes.softmax_pv
+
+    def counted(self, *args, **kw):
+        out = plain(self, *args, **kw)
+        taken.append(out is not None)
+        return out
+    kmod.CachePlanes.softmax_pv = counted
+    try:
+        _resident_cache_steps(M, mo, kmod, dev, a, rng, p, freqs)
+    finally:
+        kmod.CachePlanes.softmax_pv = plain
+    assert len(taken) == 16 and all(taken), "the resident planes did not serve every decode step"
+    kmod.device_status()
+
+
+def _resident_cache_steps(M, mo, kmod, dev, a, rng, p, freqs):
+    for batch in (1, 3):
+        attn = M.MLA(0, a, batch).to(dev)
+        load_mla(attn, p, dev)
+        attn.score_limbs = (5, 4)
+        assert attn.resident_cache
+        kv_cache = [np.zeros((1, a.max_seq_len, a.kv_lora_rank), np.int64) for _ in range(batch)]
+        pe_cache = [np.zeros((1, a.max_seq_len, a.qk_rope_head_dim), np.int64) for _ in range(batch)]
+        pos, used_planes = 0, 0
+        for S in (13, 1, 1, 1, 1, 1, 2, 1, 1, -9, 1):
+            if S < 0:                       # a new prompt: prefill from position 0 again
+                pos, S = 0, -S
+            x = np.rint(rng.standard_normal((batch, S, a.dim)) * 2.0**21).astype(np.int64)
+            fr = freqs[pos:pos + S]
+            mask_np = mo.causal_mask(S) if pos == 0 else None
+            mask = t(mask_np, dev) if mask_np is not None else None
+            want = np.concatenate([mo.mla_forward(p, x[b:b + 1], pos, fr.numpy(), mask_np, kv_cache[b], pe_cache[b],
+                                                  a.n_heads) for b in range(batch)])
+            before = attn._planes.filled if attn._planes is not None else -1
+            got = attn(t(x, dev), pos, fr.to(dev), mask)
+            same(got, want, "MLA output at pos %d, batch %d" % (pos, batch))
+            if S == 1 and mask is None:
+                assert attn._planes is not None and attn._planes.filled == pos + 1
+                used_planes += 1
+            elif attn._planes is not None:
+                assert attn._planes.filled <= min(before, pos)
+            pos += S
+        assert used_planes == 8
+        # the same steps with the planes switched off give the same words (and the caches agree)
+        attn.resident_cache = False
+        x = np.rint(rng.standard_normal((batch, 1, a.dim)) * 2.0**21).astype(np.int64)
+        want = np.concatenate([mo.mla_forward(p, x[b:b + 1], pos, freqs[pos:pos + 1].numpy(), None, kv_cache[b],
+                                              pe_cache[b], a.n_heads) for b in range(batch)])
+        same(attn(t(x, dev), pos, freqs[pos:pos + 1].to(dev), None), want, "planes off")
+
+
 def test_mlp_expert_shapes_and_shifts(M, mo, kmod, dev):
     rng = np.random.default_rng(2)
     for (dim, inter, s1, s3) in ((256, 384, 31, 31), (256, 200, 31, 33)):   # equal shifts: stacked GEMM

@@ -544,6 +544,68 @@ int zkds_softmax_pv(const int64_t* scores, const int64_t* KV, int64_t* out, cons
     return finish(rc, "zkds_softmax_pv");
 }
 
+int zkds_cache_planes_append(const int64_t* kv_new, const int64_t* pe_new, int8_t* score_planes,
+                             int8_t* value_planes, int64_t B, int64_t S, int64_t C1, int64_t C2,
+                             int64_t start_pos, int64_t capacity, int limbs, void* stream)
+{
+    if (B < 0 || S < 0 || (B && S && (!kv_new || !pe_new || !score_planes || !value_planes)))
+        return finish(ZKDS_ERR_ARG, "zkds_cache_planes_append");
+    return finish(launch_cache_planes_append(kv_new, pe_new, score_planes, value_planes, B, S, C1, C2, start_pos,
+                                             capacity, limbs, ST(stream)),
+                  "zkds_cache_planes_append");
+}
+
+int zkds_mla_scores_cached(const int64_t* q_abs, const int64_t* q_pe, const int8_t* score_planes,
+                           int64_t capacity, int64_t* out, int64_t B, int64_t S, int64_t H, int64_t T,
+                           int64_t C1, int64_t C2, int64_t rescale1, int64_t rescale2, int64_t ep_mul,
+                           int64_t ep_div, int causal, int64_t start_pos, int64_t mask_value, int a_limbs,
+                           int b_limbs, int flags, void* stream)
+{
+    if (B < 0 || S < 0 || H < 0 || T < 0 || C1 <= 0 || C2 <= 0 || rescale1 < 0 || rescale1 > 127 ||
+        rescale2 < 0 || rescale2 > 127 || a_limbs <= 0 || b_limbs <= 0 || T > capacity)
+        return finish(ZKDS_ERR_ARG, "zkds_mla_scores_cached");
+    if (B == 0 || S == 0 || H == 0 || T == 0) return finish(ZKDS_OK, "zkds_mla_scores_cached");
+    if (!q_abs || !q_pe || !score_planes || !out) return finish(ZKDS_ERR_ARG, "zkds_mla_scores_cached");
+    FusedScores f{};
+    f.A1 = q_abs; f.A2 = q_pe; f.B1 = nullptr; f.B2 = nullptr; f.out = out;
+    f.b_planes = score_planes; f.b_batch_rows = capacity;
+    f.batches = B; f.M = S * H; f.N = T; f.K1 = C1; f.K2 = C2;
+    f.addend1 = rescale1 / 2; f.addend2 = rescale2 / 2;
+    f.shift1 = (int)rescale1; f.shift2 = (int)rescale2;
+    f.ep_mul = ep_mul; f.ep_div = ep_div;
+    f.causal_H = causal ? H : 0; f.causal_start = start_pos; f.mask_value = mask_value;
+    f.dynamic_a = (flags & ZKDS_LIMBS_DYNAMIC) ? 1 : 0;
+    f.skip_tiles = (flags & ZKDS_CAUSAL_SKIP) ? 1 : 0;
+    int rc = launch_scores_fused(f, a_limbs, b_limbs, ST(stream));
+    if (rc == ZKDS_ERR_UNSUPPORTED) { t_status = rc; return rc; }
+    return finish(rc, "zkds_mla_scores_cached");
+}
+
+int zkds_softmax_pv_cached(const int64_t* scores, const int8_t* value_planes, int64_t capacity, int64_t* out,
+                           const int64_t* lut, int64_t rescale, int64_t B, int64_t S, int64_t H, int64_t T,
+                           int64_t C, int causal_skip, int64_t start_pos, int a_limbs, int b_limbs, int flags,
+                           void* stream)
+{
+    if (B < 0 || S < 0 || H < 0 || T < 0 || C < 0 || rescale < 0 || rescale > 127 || start_pos < 0 ||
+        b_limbs <= 0 || T > capacity || (capacity & 15))
+        return finish(ZKDS_ERR_ARG, "zkds_softmax_pv_cached");
+    if (B == 0 || S == 0 || H == 0 || C == 0) return finish(ZKDS_OK, "zkds_softmax_pv_cached");
+    if (T == 0 || !scores || !value_planes || !out || !lut) return finish(ZKDS_ERR_ARG, "zkds_softmax_pv_cached");
+    const int64_t Kp = (T + 15) & ~(int64_t)15;
+    if (!softmax_planes_supported(scores, B * S * H, T, Kp)) { t_status = ZKDS_ERR_UNSUPPORTED; return t_status; }
+    Contraction p = einsum_problem(2, scores, nullptr, out, rescale, B, S, H, T, C);
+    p.softmax_lut = lut; p.softmax_S = S;
+    if (causal_skip) { p.skip_k = 1; p.skip_H = H; p.skip_start = start_pos; }
+    p.dynamic_a = ((flags & ZKDS_LIMBS_DYNAMIC) && a_limbs > 0) ? 1 : 0;
+    if (a_limbs <= 0) a_limbs = 3;
+    Planes pl{};
+    pl.data = const_cast<int8_t*>(value_planes); pl.L = b_limbs; pl.nb = B; pl.rows = C; pl.K = T;
+    pl.pitch = capacity;
+    int rc = launch_contraction_limb(p, a_limbs, b_limbs, &pl, ST(stream));
+    if (rc == ZKDS_ERR_UNSUPPORTED) { t_status = rc; return rc; }
+    return finish(rc, "zkds_softmax_pv_cached");
+}
+
 int zkds_softmax_causal(const int64_t* X, int64_t* C, const int64_t* lut, int64_t B, int64_t S, int64_t H,
                         int64_t T, int64_t start_pos, void* stream)
 {

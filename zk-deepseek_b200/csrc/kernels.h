@@ -151,9 +151,11 @@ int launch_contraction_exact(const Contraction& p, cudaStream_t st);
 // counts fall outside what the kernel handles (caller then uses the exact path).
 // pre_b: limb planes of B prepared ahead of time (static weights), or null to split B now.
 struct Planes {
-    int8_t* data;     // [L][nb][rows][Kp] int8, Kp = K rounded up to 16
+    int8_t* data;     // [L][nb][rows][pitch] int8
     int L;
     int64_t nb, rows, K;
+    int64_t pitch;    // bytes between rows; 0 = K rounded up to 16 (resident cache planes are wider: their
+                      // capacity, of which the first K columns are in use)
 };
 int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* pre_b, cudaStream_t st);
 
@@ -170,7 +172,15 @@ struct FusedScores {
     int64_t ep_mul, ep_div, causal_H, causal_start, mask_value;
     int dynamic_a;
     int skip_tiles;   // with causal_H: tiles whose every column is masked are neither computed nor written
+    // B1 | B2 already split (resident cache planes): [Lb][batches][b_batch_rows][K1 + round16(K2)] int8, of
+    // which rows [0, N) of every batch are in use; B1 and B2 are then ignored
+    const int8_t* b_planes;
+    int64_t b_batch_rows;
 };
+// new cache rows as limb planes in both layouts the attention contractions read (see zkds_cache_planes_append)
+int launch_cache_planes_append(const int64_t* kv_new, const int64_t* pe_new, int8_t* score_planes,
+                               int8_t* value_planes, int64_t B, int64_t S, int64_t C1, int64_t C2,
+                               int64_t start_pos, int64_t cap, int L, cudaStream_t st);
 int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st);
 
 // planes[l][z][r][Kp] <- limb l of X[z*sz + r*sr + k*sk] / div

@@ -528,7 +528,8 @@ struct LimbParams {
     uint32_t tmem_cols;       // power of two >= (La + Lb - 1) * NT
     int64_t M, N, batches;
     int64_t a_rows_per_limb;  // batches * M
-    int64_t b_rows_per_limb;  // nbB * N
+    int64_t b_rows_per_limb;  // nbB * b_batch_rows
+    int64_t b_batch_rows;     // rows between the batches of B: N, or the capacity of resident cache planes
     int b_batched;            // 1: B differs per batch
     int64_t* C;
     int64_t* R;
@@ -1123,7 +1124,7 @@ limb_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                 (int)(i * p.a_rows_per_limb + z * p.M + m0), full);
                 for (int j = 0; j < p.Lb; ++j)
                     tma_load_2d(sb + j * (p.NT * kBlockK), &tmB, kb * kBlockK,
-                                (int)(j * p.b_rows_per_limb + zb * p.N + n0), full);
+                                (int)(j * p.b_rows_per_limb + zb * p.b_batch_rows + n0), full);
                 armed = it + 1;
             }
             if (*abort_flag) {
@@ -1684,7 +1685,7 @@ limb_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                                     (int)(i * p.a_rows_per_limb + tc.z * p.M + tc.m0), full);
                     for (int j = 0; j < p.Lb; ++j)
                         tma_load_2d(sb + j * (p.NT * kBlockK), &tmB, kb * kBlockK,
-                                    (int)(j * p.b_rows_per_limb + zb * p.N + tc.n0), full);
+                                    (int)(j * p.b_rows_per_limb + zb * p.b_batch_rows + tc.n0), full);
                     armed = it + 1;
                 }
             }
@@ -1886,12 +1887,13 @@ EncodeTiledFn encode_fn()
 }
 
 // planes seen as a 2-D uint8 tensor [rows_total][Kp], box = box_rows x 128 bytes, 128B swizzle
-bool make_plane_map(CUtensorMap* map, void* base, int64_t rows_total, int64_t Kp, int box_rows)
+// pitch: bytes between rows when they are wider than the Kp columns in use (0 = Kp)
+bool make_plane_map(CUtensorMap* map, void* base, int64_t rows_total, int64_t Kp, int box_rows, int64_t pitch = 0)
 {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     cuuint64_t gdim[2] = {(cuuint64_t)Kp, (cuuint64_t)rows_total};
-    cuuint64_t gstride[1] = {(cuuint64_t)Kp};
+    cuuint64_t gstride[1] = {(cuuint64_t)(pitch ? pitch : Kp)};
     cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, gdim, gstride, box, estr,
@@ -2125,6 +2127,59 @@ int limbs_needed(uint64_t maxabs)
     return 10;
 }
 
+namespace {
+// New rows of the MLA latent cache (kv [B][S][C1], rope part [B][S][C2]) as balanced 8-bit limb planes, in the
+// two layouts the attention contractions read them in and at their place in buffers that hold `cap` positions:
+//   score planes [L][B][cap][C1 + C2r]: position t is a row, the latent and the rope part side by side
+//                                       (the B operand of the fused score kernel, K = C1 + C2);
+//   value planes [L][B][C1][cap]:       position t is a column (the B operand of P . KV, K = positions).
+// One thread per (b, s, column).
+__global__ void __launch_bounds__(256)
+cache_planes_append_kernel(const int64_t* __restrict__ kv_new, const int64_t* __restrict__ pe_new,
+                           int8_t* __restrict__ sp, int8_t* __restrict__ vp, int64_t B, int64_t S, int C1, int C2,
+                           int64_t start, int64_t cap, int L, int64_t pitch, unsigned* overflow)
+{
+    const int C = C1 + C2;
+    const int64_t total = B * S * C;
+    bool ovf = false;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i % C);
+        const int64_t bs = i / C, s = bs % S, b = bs / S;
+        int64_t u = c < C1 ? kv_new[bs * C1 + c] : pe_new[bs * C2 + (c - C1)];
+        const int64_t t = start + s;
+        for (int l = 0; l < L; ++l) {
+            const int8_t digit = (int8_t)(u & 0xFF);
+            u = (u >> 8) + ((u >> 7) & 1);
+            sp[(((int64_t)l * B + b) * cap + t) * pitch + c] = digit;
+            if (c < C1) vp[(((int64_t)l * B + b) * C1 + c) * cap + t] = digit;
+        }
+        ovf |= (u != 0);
+    }
+    if (ovf) *overflow = 1u;
+}
+}  // namespace
+
+int launch_cache_planes_append(const int64_t* kv_new, const int64_t* pe_new, int8_t* score_planes,
+                               int8_t* value_planes, int64_t B, int64_t S, int64_t C1, int64_t C2,
+                               int64_t start_pos, int64_t cap, int L, cudaStream_t st)
+{
+    if (B <= 0 || S <= 0) return ZKDS_OK;
+    if (C1 <= 0 || C2 <= 0 || C1 > 65536 || C2 > 65536 || (C1 & 15) || L < 1 || L > 9 || start_pos < 0 ||
+        start_pos + S > cap || (cap & 15))
+        return ZKDS_ERR_ARG;
+    DeviceFlags* fl = flags_for_device();
+    if (!fl) return ZKDS_ERR_WORKSPACE;
+    const int64_t pitch = C1 + ((C2 + 15) & ~(int64_t)15);
+    const int64_t total = B * S * (C1 + C2);
+    int64_t blocks = (total + 255) / 256;
+    const int64_t cap_blocks = (int64_t)sm_count() * 16;
+    if (blocks > cap_blocks) blocks = cap_blocks;
+    cache_planes_append_kernel<<<(unsigned)blocks, 256, 0, st>>>(kv_new, pe_new, score_planes, value_planes, B, S,
+                                                                 (int)C1, (int)C2, start_pos, cap, L, pitch,
+                                                                 fl->overflow_dev);
+    return check_launch();
+}
+
 int planes_split(const void* X, int bits, int64_t nb, int64_t rows, int64_t K, int64_t sz, int64_t sr,
                  int64_t sk, int64_t div, int L, int8_t* dst, cudaStream_t st)
 {
@@ -2333,7 +2388,9 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     }
     CUtensorMap tmA, tmB;
     if (!make_plane_map(&tmA, pa, (int64_t)La * a_rows, Kp, a_box)) return ZKDS_ERR_UNSUPPORTED;
-    if (!make_plane_map(&tmB, pb, (int64_t)Lb * b_rows, Kp, NT)) return ZKDS_ERR_UNSUPPORTED;
+    const int64_t b_pitch = (pre_b && pre_b->pitch) ? pre_b->pitch : Kp;
+    if (b_pitch < Kp || (b_pitch & 15)) return ZKDS_ERR_ARG;
+    if (!make_plane_map(&tmB, pb, (int64_t)Lb * b_rows, Kp, NT, b_pitch)) return ZKDS_ERR_UNSUPPORTED;
 
     LimbParams lp{};
     lp.La = La; lp.Lb = Lb; lp.NT = NT; lp.stages = stages;
@@ -2346,7 +2403,7 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
     if (persistent) lp.stages = pstages;
     lp.nbuf = 2;
     lp.M = p.M; lp.N = p.N; lp.batches = p.batches;
-    lp.a_rows_per_limb = a_rows; lp.b_rows_per_limb = b_rows;
+    lp.a_rows_per_limb = a_rows; lp.b_rows_per_limb = b_rows; lp.b_batch_rows = p.N;
     lp.b_batched = p.b_sz ? 1 : 0;
     lp.C = p.C; lp.R = p.R; lp.c_sz = p.c_sz; lp.c_sm = p.c_sm;
     lp.addend = p.addend; lp.shift = p.shift; lp.r_legacy = p.r_legacy;
@@ -2517,7 +2574,8 @@ int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st)
     if (!NT) return ZKDS_ERR_UNSUPPORTED;
     const int64_t Kp2 = (f.K2 + 15) & ~(int64_t)15;
     const int64_t pitch = f.K1 + Kp2;
-    const int64_t a_rows = f.batches * f.M, b_rows = f.batches * f.N;
+    if (f.b_planes && (f.b_batch_rows < f.N || (((uintptr_t)f.b_planes) & 15))) return ZKDS_ERR_ARG;
+    const int64_t a_rows = f.batches * f.M, b_rows = f.batches * (f.b_planes ? f.b_batch_rows : f.N);
     if (a_rows * La > 0x7fffff00ll || b_rows * Lb > 0x7fffff00ll) return ZKDS_ERR_UNSUPPORTED;
     const int64_t mt = (f.M + kTileM - 1) / kTileM, nt = (f.N + NT - 1) / NT;
     if (f.batches * mt * nt > 0x7fffffffll) return ZKDS_ERR_UNSUPPORTED;
@@ -2525,7 +2583,8 @@ int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st)
     DeviceFlags* fl = flags_for_device();
     if (!fl) return ZKDS_ERR_WORKSPACE;
     int8_t* pa = (int8_t*)workspace((size_t)La * a_rows * pitch + 1024, 0);
-    int8_t* pb = (int8_t*)workspace((size_t)Lb * b_rows * pitch + 1024, 1);
+    int8_t* pb = f.b_planes ? const_cast<int8_t*>(f.b_planes)
+                            : (int8_t*)workspace((size_t)Lb * b_rows * pitch + 1024, 1);
     if (!pa || !pb) return ZKDS_ERR_WORKSPACE;
     unsigned long long* d_absmax = nullptr;
     if (f.dynamic_a) {
@@ -2539,10 +2598,10 @@ int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st)
     if (rc == ZKDS_OK)
         rc = launch_split_t<int64_t>(f.A2, pa + f.K1, La, f.batches, f.M, f.K2, Kp2, f.M * f.K2, f.K2, 1, 1,
                                      fl->overflow_dev, st, d_absmax, pitch, 0, 0, E ? delta : 0);
-    if (rc == ZKDS_OK)
+    if (rc == ZKDS_OK && !f.b_planes)
         rc = launch_split_t<int64_t>(f.B1, pb, Lb, f.batches, f.N, f.K1, f.K1, f.N * f.K1, f.K1, 1, 1,
                                      fl->overflow_dev, st, nullptr, pitch);
-    if (rc == ZKDS_OK)
+    if (rc == ZKDS_OK && !f.b_planes)
         rc = launch_split_t<int64_t>(f.B2, pb + f.K1, Lb, f.batches, f.N, f.K2, Kp2, f.N * f.K2, f.K2, 1, 1,
                                      fl->overflow_dev, st, nullptr, pitch);
     if (rc != ZKDS_OK) return rc;
@@ -2564,7 +2623,7 @@ int launch_scores_fused(const FusedScores& f, int La, int Lb, cudaStream_t st)
     lp.merged_E = E;
     lp.fold_epilogue = E ? 1 : 0;
     lp.M = f.M; lp.N = f.N; lp.batches = f.batches;
-    lp.a_rows_per_limb = a_rows; lp.b_rows_per_limb = b_rows;
+    lp.a_rows_per_limb = a_rows; lp.b_rows_per_limb = b_rows; lp.b_batch_rows = f.b_planes ? f.b_batch_rows : f.N;
     lp.b_batched = 1;
     lp.C = f.out; lp.R = nullptr; lp.c_sz = f.M * f.N; lp.c_sm = f.N;
     lp.addend = f.addend1; lp.shift = f.shift1; lp.addend2 = f.addend2; lp.shift2 = f.shift2;

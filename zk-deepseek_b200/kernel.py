@@ -108,6 +108,10 @@ _sig("zkds_glu_q23", [_vp, _vp, _ll, _vp, _vp, _vp, _ll, _ll, _vp])
 _sig("zkds_gather_rows", [_vp, _vp, _vp, _ll, _ll, _vp])
 _sig("zkds_moe_combine", [_vp, _vp, _vp, _vp, _vp, _ll, _i, _ll, _vp])
 _sig("zkds_gate_select", [_vp, _vp, _ll, _i, _i, _i, _i, _vp, _vp, _vp, _vp])
+_sig("zkds_cache_planes_append", [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _i, _vp])
+_sig("zkds_mla_scores_cached", [_vp, _vp, _vp, _ll, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _i, _ll,
+                                _ll, _i, _i, _i, _vp])
+_sig("zkds_softmax_pv_cached", [_vp, _vp, _ll, _vp, _vp, _ll, _ll, _ll, _ll, _ll, _ll, _i, _ll, _i, _i, _i, _vp])
 _sig("zkds_grouped_gather_parts_prepared", [_vp, _i, _ll, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _ll, _i, _i, _vp])
 _sig("zkds_moe_combine_peer", [_vp, _vp, _vp, _ll, _i, _ll, _ll, _vp, _i, _i, _vp])
 _sig("zkds_moe_sum_slots", [_vp, _vp, _vp, _ll, _i, _ll, _i, _i, _vp, _vp])
@@ -518,6 +522,74 @@ def mla_scores_fused(q_abs, kv, q_pe, pe, rescale1=23, rescale2=21, mul=94, div=
         return None
     _check(rc, "mla_scores_fused")
     return out
+
+
+class CachePlanes:
+    """The MLA latent cache of one layer kept as int8 limb planes (decode): `score` [limbs, B, capacity,
+    C1 + round16(C2)] is the cache side of the fused score kernel, `value` [limbs, B, C1, capacity] the KV
+    operand of P . KV.  append() splits only the new positions; scores() / softmax_pv() read the planes in
+    place, so a decode step neither copies nor re-splits the cache.  `limbs` is a promise (values beyond it
+    raise device_status()).  `filled` = positions [0, filled) hold the cache's contents."""
+
+    def __init__(self, batch, capacity, c1, c2, limbs, device):
+        self.batch, self.c1, self.c2, self.limbs = int(batch), int(c1), int(c2), int(limbs)
+        self.capacity = (int(capacity) + 15) // 16 * 16
+        pitch = self.c1 + (self.c2 + 15) // 16 * 16
+        self.score = torch.zeros((self.limbs, self.batch, self.capacity, pitch), dtype=torch.int8, device=device)
+        self.value = torch.zeros((self.limbs, self.batch, self.c1, self.capacity), dtype=torch.int8, device=device)
+        self.filled = 0
+
+    def append(self, kv_new, pe_new, start_pos):
+        """kv_new [B, S, C1], pe_new [B, S, C2] -> positions [start_pos, start_pos + S)"""
+        _dev_i64(kv_new, "kv_new")
+        _dev_i64(pe_new, "pe_new")
+        Bn, S, _ = kv_new.shape
+        assert Bn == self.batch and kv_new.shape[2] == self.c1 and pe_new.shape == (Bn, S, self.c2)
+        assert start_pos + S <= self.capacity
+        with _on(kv_new.device):
+            _check(lib.zkds_cache_planes_append(kv_new.data_ptr(), pe_new.data_ptr(), self.score.data_ptr(),
+                                                self.value.data_ptr(), Bn, S, self.c1, self.c2, int(start_pos),
+                                                self.capacity, self.limbs, _stream()), "cache_planes_append")
+        self.filled = max(self.filled, start_pos + S) if start_pos <= self.filled else self.filled
+
+    def scores(self, q_abs, q_pe, T, rescale1=23, rescale2=21, mul=94, div=695, causal=False, start_pos=0,
+               mask_value=-(64 << 36), a_limbs=3, dynamic=True):
+        """mla_scores_fused against positions [0, T) of the planes; None when the kernel declines the shape"""
+        _dev_i64(q_abs, "q_abs")
+        _dev_i64(q_pe, "q_pe")
+        Bn, S, H, C1 = q_abs.shape
+        assert Bn == self.batch and C1 == self.c1 and q_pe.shape == (Bn, S, H, self.c2) and T <= self.capacity
+        out = torch.empty((Bn, S, H, T), dtype=torch.int64, device=q_abs.device)
+        with _on(q_abs.device):
+            rc = lib.zkds_mla_scores_cached(q_abs.data_ptr(), q_pe.data_ptr(), self.score.data_ptr(), self.capacity,
+                                            out.data_ptr(), Bn, S, H, int(T), C1, self.c2, int(rescale1),
+                                            int(rescale2), int(mul), int(div), 1 if causal else 0, int(start_pos),
+                                            int(mask_value), a_limbs, self.limbs, _a_flags(a_limbs, dynamic),
+                                            _stream())
+        if rc == 6:
+            return None
+        _check(rc, "mla_scores_cached")
+        return out
+
+    def softmax_pv(self, scores, rescale=23, a_limbs=3, valid_start=None):
+        """softmax_pv_fused with KV = positions [0, T) of the planes; None when the kernel declines the shape.
+        valid_start: row (b, s, h) owns columns t <= valid_start + s only, the others are neither read nor
+        weighted (a decode step pads its score rows to a multiple of four columns this way)."""
+        _dev_i64(scores, "scores")
+        Bn, S, H, T = scores.shape
+        assert Bn == self.batch and T <= self.capacity
+        lut = _lut_on(EXP2_FRAC_LUT_Q19, scores.device, "softmax_init_q19")
+        out = torch.empty((Bn, S, H, self.c1), dtype=torch.int64, device=scores.device)
+        with _on(scores.device):
+            rc = lib.zkds_softmax_pv_cached(scores.data_ptr(), self.value.data_ptr(), self.capacity, out.data_ptr(),
+                                            lut.data_ptr(), int(rescale), Bn, S, H, T, self.c1,
+                                            0 if valid_start is None else 1,
+                                            0 if valid_start is None else int(valid_start), a_limbs,
+                                            self.limbs, ALGO_LIMB, _stream())
+        if rc == 6:
+            return None
+        _check(rc, "softmax_pv_cached")
+        return out
 
 
 def gate_select(sigma, bias, n_groups, topk_groups, topk):

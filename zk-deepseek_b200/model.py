@@ -368,6 +368,19 @@ class MLA(nn.Module):
         # weight 0, int64_gemm.cu:706-710); only the masked entries of the two tensors are left
         # undefined, so it is switched off whenever they are dumped (snark).
         self.causal_skip = False
+        # Decode (no mask) reads the latent cache from resident limb planes (K.CachePlanes): a step splits only
+        # its new position instead of copying and re-splitting the whole cache twice.  Needs promised limb
+        # bounds (score_limbs); the int64 caches stay the reference copy (dumps, prefill, measured reruns) and
+        # positions written by any other path are re-split lazily before the next decode step.
+        self.resident_cache = True
+        self._planes = None
+
+    def _cache_planes(self, bsz, limbs):
+        pl = self._planes
+        if pl is None or pl.batch != bsz or pl.limbs != limbs or pl.score.device != self.kv_cache.device:
+            pl = self._planes = K.CachePlanes(bsz, self.kv_cache.shape[1], self.kv_lora_rank, self.qk_rope_head_dim,
+                                              limbs, self.kv_cache.device)
+        return pl
 
     def _per_head_planes(self, lin, k_last):
         """limb planes of wkv_b_1 / wkv_b_2 viewed per head: [H, 128, 512]"""
@@ -463,12 +476,31 @@ class MLA(nn.Module):
             q_abs = K.einsum_bshd_hdc_bshc(q_nope.contiguous(), w1.contiguous(), shift1)
         self.kv_cache[:bsz, start_pos:end_pos] = kv_normed
         self.pe_cache[:bsz, start_pos:end_pos] = k_pe
+        al, bl = self.score_limbs
+        dyn = al > 0
+        if (self.resident_cache and mask is None and seqlen == 1 and not snark and K.ALGO != K.ALGO_EXACT
+                and al > 0 and bl > 0):
+            pl = self._cache_planes(bsz, bl)
+            if pl.filled < start_pos:      # positions another path wrote (prefill, a filled cache): split them once
+                pl.append(self.kv_cache[:bsz, pl.filled:start_pos].contiguous(),
+                          self.pe_cache[:bsz, pl.filled:start_pos].contiguous(), pl.filled)
+            pl.append(kv_normed.contiguous(), k_pe.contiguous(), start_pos)
+            # score rows padded to a multiple of four columns (what the softmax-to-planes kernel reads); the
+            # padding columns come from cache positions that are not in use and are never read: the softmax
+            # and P . KV stop at column start_pos
+            t4 = (end_pos + 3) // 4 * 4
+            scores = pl.scores(q_abs, q_pe.contiguous(), t4, 23, 21, self.softmax_scale1, self.softmax_scale2,
+                               a_limbs=al, dynamic=True)
+            if scores is not None:
+                ctx = pl.softmax_pv(scores, 23, a_limbs=3, valid_start=start_pos)
+                if ctx is not None:
+                    return ctx
+        elif self._planes is not None:
+            self._planes.filled = min(self._planes.filled, start_pos)     # these positions changed under the planes
         kv_all = self.kv_cache[:bsz, :end_pos].contiguous()
         pe_all = self.pe_cache[:bsz, :end_pos].contiguous()
 
         # scores = (score1 + score2) * 94 // 695 (+ mask): the tail runs in the second epilogue
-        al, bl = self.score_limbs
-        dyn = al > 0
         causal = mask is not None and start_pos == 0 and _is_causal_mask(mask, seqlen)
         scores = None
         if K.ALGO != K.ALGO_EXACT:
