@@ -123,10 +123,17 @@ class PipelinedIO:
             ev.record(self.s_in)
         self.ready[b] = ev
 
+    INLINE = False      # True: both copies on the compute stream, before and after the step's kernels
+
     def step(self, fn):
         torch = self.torch
         b = self.k & 1
         main = torch.cuda.current_stream()
+        if self.INLINE:
+            self.x_in[0].copy_(self.x_host, non_blocking=True)
+            out = fn(self.x_in[0])
+            self.out_host[0].copy_(out, non_blocking=True)
+            return out
         if self.ready[b] is None:
             self._load(b)                  # first step: nothing was prefetched
         self._load(b ^ 1)                  # the next step's input, while this step computes
@@ -1596,6 +1603,9 @@ def main():
     ap.add_argument("--moe-exchange", default="peer", choices=["peer", "nccl"],
                     help="expert-parallel MoE on N > 1 GPUs: rows and results over peer memory inside the expert "
                          "kernels (default) or NCCL all-to-all of packed rows")
+    ap.add_argument("--e2e-copies", default="pipelined", choices=["pipelined", "inline"],
+                    help="end-to-end steps of the layer workloads: host copies on copy streams that overlap the "
+                         "neighbouring steps' kernels (default) or on the compute stream around each step")
     ap.add_argument("--op-profile", default=None, metavar="FILE",
                     help="after the timed steps, run three more under torch.profiler and write rank 0's table of "
                          "CUDA time per operator and kernel to FILE (where a multi-rank step's time goes; the "
@@ -1626,6 +1636,7 @@ def main():
     k = importlib.import_module(PKG + ".kernel")
     peaks = measured_peaks()
     importlib.import_module(PKG + ".model").PEER_EXPERTS = args.moe_exchange == "peer"
+    PipelinedIO.INLINE = args.e2e_copies == "inline"
     wl = WORKLOADS[args.workload](torch, k, dev, rank)
 
     def barrier():
