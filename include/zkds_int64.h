@@ -336,7 +336,7 @@ int zkds_moe_combine_peer(const int64_t* out, const int* pos, const int64_t* w, 
 
 /* The home GPU's side: y[t] = base[t] (or 0) + sum over the owners q of token t's experts, each once, of
  * slot_rows[t][q]; q = indices[t][slot] / experts_per_part (indices [tokens, slots] int64 global expert ids).
- * Only slots that an owner wrote in this round are read. */
+ * Only slots that an owner wrote during this exchange are read. */
 int zkds_moe_sum_slots(const int64_t* base, const int64_t* slot_rows, const int64_t* indices, int64_t tokens,
                        int slots, int64_t cols, int n_parts, int experts_per_part, int64_t* y, void* stream);
 

@@ -22,7 +22,7 @@ processes have mapped, the owner's limb split reads the rows it needs in place o
 is part of the first expert GEMM's operand preparation), and the owner's combine kernel writes each
 token's weighted sum straight into a slot of the token's home GPU, which adds the slots it expects.  The
 only collective left is an all-gather of the routing tables (ids and weights, 16 k bytes per token); two
-bounded flag barriers in peer memory order the rounds.  The NCCL all-to-all path above stays for CPU
+bounded flag barriers in peer memory order one layer call after the other.  The NCCL all-to-all path above stays for CPU
 (gloo) runs and for process groups without symmetric memory.
 """
 import torch
@@ -193,7 +193,7 @@ def expert_parallel_forward_peer(moe, K, start_pos, x, weights, indices, group=N
     host.copy_(n_mine, non_blocking=True)
     ev = torch.cuda.Event()
     ev.record()
-    ex.barrier(K)                       # every rank's rows are in place; last round's slots have been read
+    ex.barrier(K)                       # every rank's rows are in place; the previous call's slots have been read
     side = before_sync() if before_sync is not None else None
     ev.synchronize()
     local_pairs = int(host[0])
