@@ -84,10 +84,13 @@ int zkds_device_status(int clear);
                                    128-row tile are tokens and the rest is padding.  The kernel then fetches
                                    only those rows of A (decode: a few rows per expert, the weights stream
                                    from HBM and the A tiles from L2, so a smaller A box is less L2 traffic and
-                                   a deeper pipeline); padding rows come out as zero rows do.  A tile that
-                                   breaks the promise loses its rows beyond the bound silently: callers derive
-                                   the bound from the shape (a token names an expert at most once, so a group
-                                   has at most as many rows as there are tokens). */
+                                   a deeper pipeline); padding rows come out as zero rows do.  A token names
+                                   an expert at most once, so a group never has more rows than there are tokens:
+                                   up to that many tokens the bound is certain.  With the fused gather
+                                   (row_index given) a row beyond the bound raises the flag zkds_device_status
+                                   reports, like a limb bound that did not hold, so a caller may also promise
+                                   optimistically and repeat the call without the flag when it is told so;
+                                   without row_index such a row is lost silently. */
 
 /* =============================================================================
  * Group 1 — the reference's symbols (same names, same argument lists)

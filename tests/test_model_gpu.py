@@ -293,6 +293,44 @@ def test_moe_layer_small(M, mo, kmod, dev):
     kmod.device_status()
 
 
+def test_optimistic_group_rows_are_checked_on_the_device(M, mo, kmod, dev):
+    """72 tokens, 16 experts, top-4: 18 rows per expert on average, so the grouped GEMMs are launched with the
+    optimistic 64-row bound (a bound is only certain up to 64 tokens).  Here every token names expert 0: 72 rows
+    in one group break the promise, the device flag says so
+    (ERR_RANGE) instead of dropping rows silently, and the same call without the promise gives the oracle's
+    words."""
+    a = small_args(M)
+    rng = np.random.default_rng(41)
+    p = moe_weights(rng, a, with_bias=False)
+    moe = build_moe(M, a, p, dev)
+    T = 72
+    x = np.rint(rng.standard_normal((1, T, a.dim)) * 2.0**23).astype(np.int64)
+    idx = np.stack([np.array([0] + list(rng.choice(np.arange(1, 16), 3, replace=False))) for _ in range(T)])
+    original, _ = mo.gate_scores(p["gate"], x[0])
+    w, _ = mo.gate_weights(original, idx)
+    xg, ig, wg = t(x[0], dev), t(idx.astype(np.int64), dev), t(w, dev)
+    assert M.OPTIMISTIC_GROUP_ROWS
+    torch.cuda.synchronize()
+    kmod.device_status()
+    moe.experts_forward(0, xg, wg, ig)
+    torch.cuda.synchronize()
+    with pytest.raises(kmod.ZkdsError) as err:
+        kmod.device_status()
+    assert err.value.status == kmod.ERR_RANGE
+    M.OPTIMISTIC_GROUP_ROWS = False
+    try:
+        got = moe.experts_forward(0, xg, wg, ig)
+    finally:
+        M.OPTIMISTIC_GROUP_ROWS = True
+    want = np.zeros((T, a.dim), np.int64)
+    for e in range(16):
+        rows, slot = np.where(idx == e)
+        if len(rows):
+            want[rows] += (mo.mlp_forward(p["experts"][e], x[:, rows])[0] * w[rows, slot][:, None]) >> 23
+    same(got, want, "routed experts, promise off")
+    kmod.device_status()
+
+
 def test_expert_parallel_over_peer_memory_one_rank(M, mo, kmod, dev):
     """The peer-memory expert-parallel path (rows read in place by the owner's limb split, weighted sums written
     into the home GPU's slots, flag barriers) with a process group of one rank: this GPU is its own peer, so the

@@ -147,7 +147,8 @@ split_rows_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, i
                   int64_t Kp, int64_t sz, int64_t sr, int64_t div, int64_t plane_stride,
                   unsigned* overflow, unsigned long long* absmax_out, int64_t dst_pitch, int64_t valid_H,
                   int64_t valid_start, int tpr_log2, unsigned nb, unsigned gx, int z_fast, int shl,
-                  const int* __restrict__ row_index, unsigned kseg, int64_t seg_quads, const RowParts parts)
+                  const int* __restrict__ row_index, unsigned kseg, int64_t seg_quads, const RowParts parts,
+                  int group_box)
 {
     uint64_t seen = 0;
     bool ovf = false;
@@ -184,6 +185,9 @@ split_rows_kernel(const T* __restrict__ X, int8_t* __restrict__ planes, int L, i
         if (row_index) {
             rs = row_index[r];
             if (rs < 0) Kv = 0;
+            // grouped tiles whose caller promised at most group_box rows per group: a row with data beyond the
+            // box would be dropped by the GEMM, so it is reported like a limb bound that did not hold
+            else if (group_box && (int)(r & 127) >= group_box) ovf = true;
         }
         const T* xr = x + (rs < 0 ? 0 : rs) * sr;
         if (parts.n && rs >= 0) {
@@ -1934,7 +1938,7 @@ int launch_split_t(const T* X, int8_t* planes, int L, int64_t nb, int64_t rows, 
                    int64_t sz, int64_t sr, int64_t sk, int64_t div, unsigned* overflow, cudaStream_t st,
                    unsigned long long* absmax_out = nullptr, int64_t dst_pitch = 0, int64_t valid_H = 0,
                    int64_t valid_start = 0, int shl = 0, const int* row_index = nullptr,
-                   const RowParts* row_parts = nullptr)
+                   const RowParts* row_parts = nullptr, int group_box = 0)
 {
     if (dst_pitch == 0) dst_pitch = Kp;
     RowParts parts{};
@@ -1967,7 +1971,7 @@ int launch_split_t(const T* X, int8_t* planes, int L, int64_t nb, int64_t rows, 
     split_rows_kernel<T, LL><<<g2, 256, 0, st>>>(X, planes, L, rows, K, Kp, sz, sr, div,                  \
                                                  nb * rows * dst_pitch, overflow, absmax_out, dst_pitch, \
                                                  valid_H, valid_start, tl, (unsigned)nb, (unsigned)gx, z_fast, shl, \
-                                                 row_index, (unsigned)kseg, seg_quads, parts)
+                                                 row_index, (unsigned)kseg, seg_quads, parts, group_box)
         switch (L) {
         case 2: ZKDS_SPLIT_ROWS(2); break;
         case 3: ZKDS_SPLIT_ROWS(3); break;
@@ -2361,7 +2365,8 @@ int launch_contraction_limb(const Contraction& p, int La, int Lb, const Planes* 
         }
         rc = launch_split_t<int64_t>(p.A, pa, La, p.batches, p.M, p.K, Kp16, p.a_sz, p.a_sm, 1, p.a_div,
                                      fl->overflow_dev, st, d_absmax, 0, p.skip_k ? p.skip_H : 0, p.skip_start, 0,
-                                     p.a_row_index, parts.n ? &parts : nullptr);
+                                     p.a_row_index, parts.n ? &parts : nullptr,
+                                     (p.tile_group && p.a_row_index) ? p.group_rows : 0);
     }
     if (rc != ZKDS_OK) return rc;
     int8_t* pb;

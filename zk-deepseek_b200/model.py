@@ -66,6 +66,12 @@ CHECK_STATUS = True
 # torch ops.  Same experts and weights; under score ties the kernel takes the lower index, which is the set
 # torch.topk takes, while the ORDER torch gives equal scores is unspecified (False keeps the torch ops).
 FUSED_GATE = True
+# Routed experts with few rows each (decode): up to 64 tokens no expert can have more rows than tokens, and the
+# grouped GEMMs fetch only 32 / 64 rows per tile.  With OPTIMISTIC_GROUP_ROWS the smaller box is also promised
+# where it is merely expected (mean rows per expert <= 8: box 32, <= 20: box 64); a group that breaks the promise
+# raises the device flag (ZkdsError with ERR_RANGE where results leave the model) and generate() repeats the step
+# under measured_limbs, which switches the optimistic promise off.
+OPTIMISTIC_GROUP_ROWS = True
 # token-parallel MoE on GPUs of one node: rows and results move over peer memory inside the expert kernels
 # (parallel.expert_parallel_forward_peer); False = NCCL all-to-all of packed rows
 PEER_EXPERTS = True
@@ -849,6 +855,12 @@ class MoE(nn.Module):
         # a token names an expert at most once: no expert receives more rows than there are token rows
         n_rows = indices.shape[0]
         few = n_rows if n_rows <= 64 else None
+        if OPTIMISTIC_GROUP_ROWS and n_rows > 32:
+            mean_rows = n_rows * indices.shape[1] / float(self.n_routed_experts)
+            if mean_rows <= 8:
+                few = 32
+            elif mean_rows <= 20 and few is None:
+                few = 64
         finish = combine if combine is not None else (
             lambda out, pos: K.moe_combine(out, pos, weights.contiguous(), base))
         # the dispatch gather (model.py:1372-1378) runs inside the limb split of the first GEMM
@@ -999,17 +1011,19 @@ class measured_limbs:
         self.model = model
 
     def __enter__(self):
-        global ACT_LIMBS
+        global ACT_LIMBS, OPTIMISTIC_GROUP_ROWS
         self.saved = (ACT_LIMBS, [(m, m.score_limbs, m.causal_skip) for m in self.model.modules()
-                                  if isinstance(m, MLA)])
+                                  if isinstance(m, MLA)], OPTIMISTIC_GROUP_ROWS)
         ACT_LIMBS = 0
+        OPTIMISTIC_GROUP_ROWS = False
         for m, _, _ in self.saved[1]:
             m.score_limbs, m.causal_skip = (0, 0), False
         return self
 
     def __exit__(self, *exc):
-        global ACT_LIMBS
+        global ACT_LIMBS, OPTIMISTIC_GROUP_ROWS
         ACT_LIMBS = self.saved[0]
+        OPTIMISTIC_GROUP_ROWS = self.saved[2]
         for m, sl, cs in self.saved[1]:
             m.score_limbs, m.causal_skip = sl, cs
         return False
