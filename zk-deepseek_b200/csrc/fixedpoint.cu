@@ -307,7 +307,7 @@ softmax_kernel(const int64_t* X, int64_t* Wout, int64_t* C, const int64_t* __res
 // (w << 19) / sumW uses one 64-bit reciprocal per row (floor((2^64 - 1) / sumW), an estimate that
 // is at most one below the quotient) plus an exact correction.  E = 16-byte pairs per thread.
 template <int E>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, (E <= 4 ? 6 : 1))
 softmax_q19_reg_kernel(const int64_t* X, int64_t* Wout, int64_t* C, const int64_t* __restrict__ lut_g,
                        int T, int valid_H, int valid_S, int valid_start)
 {
@@ -414,8 +414,11 @@ static int launch_softmax_q19_reg(const int64_t* X, int64_t* Wout, int64_t* C, c
 // operand of the tensor-core contraction that consumes them) instead of int64 words: plane l of row
 // r lives at planes + l * plane_stride + r * Kp.  Balanced radix-256 digits as in the limb split;
 // columns from `valid` (or T) up to Kp are written as zero.  E = groups of four columns per thread.
-template <int E, int LL>      // LL: limb count known at compile time, 0 = use L
-__global__ void __launch_bounds__(kThreads)
+// MINB: CTAs per SM the kernel is compiled for.  The 4096-column case (E = 4, three limbs) asks for eight: 32
+// registers and 68 bytes of spills instead of 48 registers and five CTAs, 6.95 against 7.48 ms on the 17 GB
+// score tensor of the 4096-token prefill (six CTAs: 7.13 ms).
+template <int E, int LL, int MINB>      // LL: limb count known at compile time, 0 = use L
+__global__ void __launch_bounds__(kThreads, MINB)
 softmax_q19_planes_kernel(const int64_t* X, const int64_t* __restrict__ lut_g, int8_t* __restrict__ planes,
                           int L, int T, int64_t Kp, int64_t plane_stride, unsigned* overflow,
                           unsigned long long* absmax_out, int valid_H, int valid_S, int valid_start)
@@ -572,11 +575,11 @@ int launch_softmax_planes(const int64_t* X, const int64_t* lut, int8_t* planes, 
 #define ZKDS_SP(E)                                                                                        \
     do {                                                                                                  \
         if (L == 3)                                                                                       \
-            softmax_q19_planes_kernel<E, 3><<<g, kThreads, 0, st>>>(X, lut, planes, L, (int)T, Kp,        \
-                                                                    plane_stride, overflow, absmax_out,   \
-                                                                    (int)valid_H, vS, (int)valid_start);  \
+            softmax_q19_planes_kernel<E, 3, (E == 4 ? 8 : 1)><<<g, kThreads, 0, st>>>(                    \
+                X, lut, planes, L, (int)T, Kp, plane_stride, overflow, absmax_out, (int)valid_H, vS,      \
+                (int)valid_start);                                                                        \
         else                                                                                              \
-            softmax_q19_planes_kernel<E, 0><<<g, kThreads, 0, st>>>(X, lut, planes, L, (int)T, Kp,        \
+            softmax_q19_planes_kernel<E, 0, 1><<<g, kThreads, 0, st>>>(X, lut, planes, L, (int)T, Kp,     \
                                                                     plane_stride, overflow, absmax_out,   \
                                                                     (int)valid_H, vS, (int)valid_start);  \
     } while (0)
