@@ -900,7 +900,7 @@ class MoE(nn.Module):
             from . import parallel
             x2 = x.view(-1, self.dim)
             weights, indices = self.gate(start_pos, x2)
-            if PEER_EXPERTS and x2.is_cuda and not snark:
+            if PEER_EXPERTS and x2.is_cuda and not snark and parallel.peer_available():
                 # rows read and results written over peer memory by the expert kernels themselves; the shared
                 # expert runs while the pair count travels to the host and is added by the slot sum
                 y, _ = parallel.expert_parallel_forward_peer(
