@@ -40,6 +40,9 @@ def _worker(rank, world, port, T, out):
         indices = torch.stack([torch.randperm(FakeMoE.n_routed_experts, generator=g)[:k] for _ in range(T[rank])]) \
             if T[rank] else torch.zeros((0, k), dtype=torch.int64)
         weights = torch.randint(1, 50, (T[rank], k), generator=g, dtype=torch.int64)
+        # no GPUs for the ranks of this group: the peer-memory exchange must declare itself unavailable, so that
+        # MoE.forward takes the collective path below
+        assert not par.peer_available()
         y, side = par.expert_parallel_forward(FakeMoE(), 0, x, weights, indices, before_sync=lambda: 7)
         assert side == 7
         want = (x[:, None, :] * (indices + 1)[:, :, None] * weights[:, :, None]).sum(1)
