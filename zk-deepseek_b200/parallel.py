@@ -157,7 +157,8 @@ _peer_ok = None
 
 def peer_available(group=None):
     """True when the peer-memory exchange can serve this process group: torch's symmetric memory is present,
-    at most 16 ranks, all of them on this node (one GPU each).  Decided once; the same on every rank."""
+    at most 16 ranks, all of them on this node (one GPU each), an NCCL group.  Decided once; the same on every
+    rank."""
     global _peer_ok
     if _peer_ok is None:
         import os
@@ -165,7 +166,8 @@ def peer_available(group=None):
             import torch.distributed._symmetric_memory  # noqa: F401
             world = dist.get_world_size(group)
             local = int(os.environ.get("LOCAL_WORLD_SIZE", world))
-            _peer_ok = world <= 16 and local == world and torch.cuda.device_count() >= world
+            _peer_ok = (world <= 16 and local == world and torch.cuda.device_count() >= world
+                        and "nccl" in str(dist.get_backend(group)))
         except Exception:
             _peer_ok = False
     return _peer_ok
