@@ -908,6 +908,11 @@ class MoeWorkload:
         self.launches_per_step = 0
         self.routing = self._expert_load()
 
+    def _peer(self):
+        """the peer-memory exchange is switched on and available to this process group"""
+        par = importlib.import_module(PKG + ".parallel")
+        return bool(self.world > 1 and self.M.PEER_EXPERTS and par.peer_available())
+
     def _expert_load(self):
         """rows per expert and per GPU that the gate produces for the whole batch (every rank's tokens)"""
         import torch.distributed as dist
@@ -936,7 +941,7 @@ class MoeWorkload:
                 "act_limbs_bound": 3, "routing": self.routing, "useful_ops_per_step": self.ops,
                 "exchange": ("none (one GPU)" if self.world == 1 else
                              "peer memory: rows read in place by the owner's limb split, results stored into the "
-                             "home GPU's slots, flag barriers" if self.M.PEER_EXPERTS else
+                             "home GPU's slots, flag barriers" if self._peer() else
                              "NCCL all-to-all of packed rows"),
                 "exchange_check": getattr(self, "paths_compared", None), "weights": "resident limb planes, all experts",
                 "l2": "expert weights (45 GB int32) and token rows far exceed L2"}
@@ -998,7 +1003,7 @@ class MoeWorkload:
         np, a, moe = self.np, self.args, self.moe
         got_all = self.step()                   # with N > 1 every rank joins the exchange here
         extra_bad = 0
-        if self.world > 1 and self.M.PEER_EXPERTS:
+        if self.world > 1 and self._peer():
             # the two exchanges must agree on every word of every rank's output
             import torch.distributed as dist
             self.M.PEER_EXPERTS = False
