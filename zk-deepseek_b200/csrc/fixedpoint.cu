@@ -306,7 +306,8 @@ softmax_kernel(const int64_t* X, int64_t* Wout, int64_t* C, const int64_t* __res
 // after the clip the difference d fits 26 bits, weights fit 20 bits, and the final division
 // (w << 19) / sumW uses one 64-bit reciprocal per row (floor((2^64 - 1) / sumW), an estimate that
 // is at most one below the quotient) plus an exact correction.  E = 16-byte pairs per thread.
-template <int E>
+// FULL: every row owns all T columns (no causal bound), so no element needs a validity test.
+template <int E, bool FULL>
 __global__ void __launch_bounds__(kThreads, (E <= 4 ? 6 : 1))
 softmax_q19_reg_kernel(const int64_t* X, int64_t* Wout, int64_t* C, const int64_t* __restrict__ lut_g,
                        int T, int valid_H, int valid_S, int valid_start)
@@ -322,7 +323,7 @@ softmax_q19_reg_kernel(const int64_t* X, int64_t* Wout, int64_t* C, const int64_
     // valid_H > 0: row (b, s, h) only counts columns <= valid_start + s; the rest is neither read
     // nor written
     int valid = T;
-    if (valid_H) {
+    if (!FULL && valid_H) {
         const int sidx = (int)((blockIdx.x / (unsigned)valid_H) % (unsigned)valid_S);
         valid = valid_start + sidx + 1 < T ? valid_start + sidx + 1 : T;
     }
@@ -335,7 +336,7 @@ softmax_q19_reg_kernel(const int64_t* X, int64_t* Wout, int64_t* C, const int64_
         const int i = threadIdx.x + j * kThreads;
         if (i < half) {
             v[j] = xv[i];
-            if (2 * i + 1 >= valid) v[j].y = INT64_MIN;   // odd boundary: the second element is masked
+            if (!FULL && 2 * i + 1 >= valid) v[j].y = INT64_MIN;   // odd boundary: the second element is masked
             mx = v[j].x > mx ? v[j].x : mx;
             mx = v[j].y > mx ? v[j].y : mx;
         }
@@ -350,7 +351,7 @@ softmax_q19_reg_kernel(const int64_t* X, int64_t* Wout, int64_t* C, const int64_
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             uint32_t wi = 0;
-            if (i < half && 2 * i + h < valid) {
+            if (i < half && (FULL || 2 * i + h < valid)) {
                 const uint64_t d = (uint64_t)mx - (uint64_t)(h ? v[j].y : v[j].x);
                 if (d <= (uint64_t)(64 << 19)) {
                     const uint32_t y = (uint32_t)(((uint64_t)(uint32_t)d * 756388u) >> 19);
@@ -383,9 +384,10 @@ softmax_q19_reg_kernel(const int64_t* X, int64_t* Wout, int64_t* C, const int64_
             // floor(num * magic / 2^64) = (wi * m_hi + ((wi * m_lo) >> 32)) >> 13
             uint64_t q = ((uint64_t)wi * m_hi + (((uint64_t)wi * m_lo) >> 32)) >> 13;
             if (small) {
-                uint64_t rem = num - q * s32;          // q < 2^20, s32 < 2^32
-                if (rem >= sumW) { ++q; rem -= sumW; }
-                if (rem >= sumW) ++q;
+                // magic = floor((2^64 - 1) / sumW) makes q the quotient or one below it (num < 2^40, so the
+                // estimate's error num * (1 + (2^64 - 1) mod sumW) / (sumW * 2^64) stays below 1): one correction
+                const uint64_t rem = num - q * s32;    // q < 2^20, s32 < 2^32
+                q += rem >= sumW ? 1 : 0;
             } else if (sumW) {
                 q = num / sumW;
             }
@@ -402,11 +404,18 @@ static int launch_softmax_q19_reg(const int64_t* X, int64_t* Wout, int64_t* C, c
 {
     const int pairs = (int)((T / 2 + kThreads - 1) / kThreads);
     const unsigned g = (unsigned)rows;
-    if (pairs <= 1) softmax_q19_reg_kernel<1><<<g, kThreads, 0, st>>>(X, Wout, C, lut, (int)T, vH, vS, vstart);
-    else if (pairs <= 2) softmax_q19_reg_kernel<2><<<g, kThreads, 0, st>>>(X, Wout, C, lut, (int)T, vH, vS, vstart);
-    else if (pairs <= 4) softmax_q19_reg_kernel<4><<<g, kThreads, 0, st>>>(X, Wout, C, lut, (int)T, vH, vS, vstart);
-    else if (pairs <= 8) softmax_q19_reg_kernel<8><<<g, kThreads, 0, st>>>(X, Wout, C, lut, (int)T, vH, vS, vstart);
-    else softmax_q19_reg_kernel<16><<<g, kThreads, 0, st>>>(X, Wout, C, lut, (int)T, vH, vS, vstart);
+    const bool full = vH == 0 && (T & 1) == 0;
+#define ZKDS_SR(E)                                                                                          \
+    do {                                                                                                    \
+        if (full) softmax_q19_reg_kernel<E, true><<<g, kThreads, 0, st>>>(X, Wout, C, lut, (int)T, vH, vS, vstart);  \
+        else softmax_q19_reg_kernel<E, false><<<g, kThreads, 0, st>>>(X, Wout, C, lut, (int)T, vH, vS, vstart);     \
+    } while (0)
+    if (pairs <= 1) ZKDS_SR(1);
+    else if (pairs <= 2) ZKDS_SR(2);
+    else if (pairs <= 4) ZKDS_SR(4);
+    else if (pairs <= 8) ZKDS_SR(8);
+    else ZKDS_SR(16);
+#undef ZKDS_SR
     return check_launch();
 }
 
@@ -417,7 +426,7 @@ static int launch_softmax_q19_reg(const int64_t* X, int64_t* Wout, int64_t* C, c
 // MINB: CTAs per SM the kernel is compiled for.  The 4096-column case (E = 4, three limbs) asks for eight: 32
 // registers and 68 bytes of spills instead of 48 registers and five CTAs, 6.95 against 7.48 ms on the 17 GB
 // score tensor of the 4096-token prefill (six CTAs: 7.13 ms).
-template <int E, int LL, int MINB>      // LL: limb count known at compile time, 0 = use L
+template <int E, int LL, int MINB, bool FULL>      // LL: limb count known at compile time, 0 = use L; FULL as above
 __global__ void __launch_bounds__(kThreads, MINB)
 softmax_q19_planes_kernel(const int64_t* X, const int64_t* __restrict__ lut_g, int8_t* __restrict__ planes,
                           int L, int T, int64_t Kp, int64_t plane_stride, unsigned* overflow,
@@ -430,7 +439,7 @@ softmax_q19_planes_kernel(const int64_t* X, const int64_t* __restrict__ lut_g, i
     const longlong2* xv = reinterpret_cast<const longlong2*>(X + (int64_t)blockIdx.x * T);
     int8_t* drow = planes + (int64_t)blockIdx.x * Kp;
     int valid = T;
-    if (valid_H) {
+    if (!FULL && valid_H) {
         const int sidx = (int)((blockIdx.x / (unsigned)valid_H) % (unsigned)valid_S);
         valid = valid_start + sidx + 1 < T ? valid_start + sidx + 1 : T;
     }
@@ -447,7 +456,7 @@ softmax_q19_planes_kernel(const int64_t* X, const int64_t* __restrict__ lut_g, i
             v[4 * j] = a.x; v[4 * j + 1] = a.y; v[4 * j + 2] = b.x; v[4 * j + 3] = b.y;
 #pragma unroll
             for (int h = 0; h < 4; ++h) {
-                if (4 * q + h >= valid) v[4 * j + h] = INT64_MIN;
+                if (!FULL && 4 * q + h >= valid) v[4 * j + h] = INT64_MIN;
                 mx = v[4 * j + h] > mx ? v[4 * j + h] : mx;
             }
         }
@@ -462,7 +471,7 @@ softmax_q19_planes_kernel(const int64_t* X, const int64_t* __restrict__ lut_g, i
 #pragma unroll
         for (int h = 0; h < 4; ++h) {
             uint32_t wi = 0;
-            if (q < quads_valid && 4 * q + h < valid) {
+            if (q < quads_valid && (FULL || 4 * q + h < valid)) {
                 const uint64_t d = (uint64_t)mx - (uint64_t)v[4 * j + h];
                 if (d <= (uint64_t)(64 << 19)) {
                     const uint32_t y = (uint32_t)(((uint64_t)(uint32_t)d * 756388u) >> 19);
@@ -497,9 +506,8 @@ softmax_q19_planes_kernel(const int64_t* X, const int64_t* __restrict__ lut_g, i
                 const uint64_t num = (uint64_t)wi << 19;
                 uint64_t qt = ((uint64_t)wi * m_hi + (((uint64_t)wi * m_lo) >> 32)) >> 13;
                 if (small) {
-                    uint64_t rem = num - qt * s32;
-                    if (rem >= sumW) { ++qt; rem -= sumW; }
-                    if (rem >= sumW) ++qt;
+                    const uint64_t rem = num - qt * s32;      // qt is the quotient or one below it (see above)
+                    qt += rem >= sumW ? 1 : 0;
                 } else if (sumW) {
                     qt = num / sumW;
                 }
@@ -574,12 +582,16 @@ int launch_softmax_planes(const int64_t* X, const int64_t* lut, int8_t* planes, 
     const int vS = valid_S > 0 ? (int)valid_S : 1;
 #define ZKDS_SP(E)                                                                                        \
     do {                                                                                                  \
-        if (L == 3)                                                                                       \
-            softmax_q19_planes_kernel<E, 3, (E == 4 ? 8 : 1)><<<g, kThreads, 0, st>>>(                    \
+        if (L == 3 && valid_H == 0)                                                                       \
+            softmax_q19_planes_kernel<E, 3, (E == 4 ? 8 : 1), true><<<g, kThreads, 0, st>>>(              \
+                X, lut, planes, L, (int)T, Kp, plane_stride, overflow, absmax_out, (int)valid_H, vS,      \
+                (int)valid_start);                                                                        \
+        else if (L == 3)                                                                                  \
+            softmax_q19_planes_kernel<E, 3, (E == 4 ? 8 : 1), false><<<g, kThreads, 0, st>>>(             \
                 X, lut, planes, L, (int)T, Kp, plane_stride, overflow, absmax_out, (int)valid_H, vS,      \
                 (int)valid_start);                                                                        \
         else                                                                                              \
-            softmax_q19_planes_kernel<E, 0, 1><<<g, kThreads, 0, st>>>(X, lut, planes, L, (int)T, Kp,     \
+            softmax_q19_planes_kernel<E, 0, 1, false><<<g, kThreads, 0, st>>>(X, lut, planes, L, (int)T, Kp, \
                                                                     plane_stride, overflow, absmax_out,   \
                                                                     (int)valid_H, vS, (int)valid_start);  \
     } while (0)
