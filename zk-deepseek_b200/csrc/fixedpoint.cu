@@ -583,7 +583,7 @@ int launch_softmax_planes(const int64_t* X, const int64_t* lut, int8_t* planes, 
 #define ZKDS_SP(E)                                                                                        \
     do {                                                                                                  \
         if (L == 3 && valid_H == 0)                                                                       \
-            softmax_q19_planes_kernel<E, 3, (E == 4 ? 8 : 1), true><<<g, kThreads, 0, st>>>(              \
+            softmax_q19_planes_kernel<E, 3, (E == 4 ? 6 : 1), true><<<g, kThreads, 0, st>>>(              \
                 X, lut, planes, L, (int)T, Kp, plane_stride, overflow, absmax_out, (int)valid_H, vS,      \
                 (int)valid_start);                                                                        \
         else if (L == 3)                                                                                  \
