@@ -1106,6 +1106,7 @@ glu_planes_kernel(const int64_t* __restrict__ r1, const int64_t* __restrict__ r2
     for (int i = threadIdx.x; i < 256; i += blockDim.x) lut[i] = lut_g[i];
     __syncthreads();
     uint64_t seen = 0;
+    uint32_t seen32 = 0;          // largest magnitude met on the 32-bit path
     bool ovf = false;
     const int64_t quads = Kp >> 2;
     const int tpr = 1 << tpr_log2;
@@ -1136,6 +1137,29 @@ glu_planes_kernel(const int64_t* __restrict__ r1, const int64_t* __restrict__ r2
             }
             constexpr int LMAX = LL ? LL : 9;
             uint32_t w[LMAX];
+            if (LL == 3) {
+                // three limbs in 32-bit arithmetic: for -0x808080 <= v <= 0x7F7F7F the balanced digits of v are the
+                // bytes of v + 0x808080 with their top bits flipped; anything outside takes the general path
+                const uint64_t t0 = (uint64_t)v[0] + 0x808080ull, t1 = (uint64_t)v[1] + 0x808080ull,
+                               t2 = (uint64_t)v[2] + 0x808080ull, t3 = (uint64_t)v[3] + 0x808080ull;
+                if (((t0 | t1 | t2 | t3) >> 24) == 0) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int32_t x = (int32_t)v[j];
+                        const uint32_t a32 = (uint32_t)(x ^ (x >> 31));
+                        seen32 = a32 > seen32 ? a32 : seen32;
+                    }
+#pragma unroll
+                    for (int l = 0; l < 3; ++l) {
+                        const uint32_t sel = 0x0040u + 0x0011u * (uint32_t)l;
+                        const uint32_t lo = __byte_perm((uint32_t)t0, (uint32_t)t1, sel),
+                                       hi = __byte_perm((uint32_t)t2, (uint32_t)t3, sel);
+                        *reinterpret_cast<uint32_t*>(drow + k0 + l * plane_stride) =
+                            __byte_perm(lo, hi, 0x5410u) ^ 0x80808080u;
+                    }
+                    continue;
+                }
+            }
 #pragma unroll
             for (int l = 0; l < LMAX; ++l) w[l] = 0;
 #pragma unroll
@@ -1157,6 +1181,7 @@ glu_planes_kernel(const int64_t* __restrict__ r1, const int64_t* __restrict__ r2
                 if (LL || l < L) *reinterpret_cast<uint32_t*>(drow + k0 + l * plane_stride) = w[l];
         }
     }
+    seen = seen32 > seen ? seen32 : seen;
     if (ovf) *overflow = 1u;
     if (absmax_out) {
         seen = warp_max_u64(seen);
