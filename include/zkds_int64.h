@@ -313,7 +313,7 @@ int zkds_glu_prepared(const int64_t* r1, const int64_t* r2, int64_t ld, const in
 /* ---- expert parallelism over peer memory (no reference counterpart: the reference sums every rank's expert
  * outputs with a full-tensor all_reduce, model.py:1381-1382).  One process per GPU; the buffers named "of
  * every GPU" are symmetric allocations that each process has mapped (peer pointers, plain loads and stores
- * over NVLink, no multicast).  A layer then runs: publish the local token rows -> zkds_peer_barrier -> the
+ * over NVLink and nothing else).  A layer then runs: publish the local token rows -> zkds_peer_barrier -> the
  * owner's grouped GEMMs, whose limb split reads the rows of every GPU in place
  * (zkds_grouped_gather_parts_prepared) -> zkds_moe_combine_peer writes each token's weighted sum into its home
  * GPU -> zkds_peer_barrier -> zkds_moe_sum_slots on the home GPU.  No row is packed, sent or unpacked by a
